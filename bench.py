@@ -1,0 +1,335 @@
+#!/usr/bin/env python
+"""MoE-layer throughput benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1: the full-size decode layer (hidden 4096, 256 routed + 1 shared expert,
+ffn 2048, top-8 of 8 groups / 4 kept, MXFP4).  A step is one layer forward over
+one batch of --tokens bf16 tokens (default 64); the other decode batch sizes are
+timed with fewer steps and reported under "series".  Steps rotate over several
+resident copies of the layer's weights so that no step finds its weights in L2.
+Prints one JSON line.  `--impl reference` times the CPU oracle port on the same
+workload (bounded sample per step).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+
+    def summary(self, t0=None, t1=None):
+        sm, mx, reasons = [], [], set()
+        for ts, line in self.rows:
+            if t0 is not None and not (t0 <= ts <= t1 + 0.2):
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_host_layer(cfg, config_id):
+    from deepstrix_b200 import synth
+    return synth.make_layer(cfg, config_id)
+
+
+def oracle_step(oracle, cfg, w, x_f32):
+    """One CPU forward of the oracle port: router logits, top-k, dequantised-f32 layer."""
+    r = cfg.router
+    logits = oracle.router_logits(x_f32, w["router_w"])
+    sel, wt = oracle.router_topk(logits, w["router_bias"], r.n_used, r.n_group, r.topk_group, r.score_fn, r.route_scale, r.weight_eps)
+    shared = tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down")) if cfg.shared_ffn else None
+    return oracle.moe_layer_f32(cfg.fmt, x_f32, sel, wt, w["gate"], w["up"], w["down"], shared=shared, clamp=cfg.clamp,
+                                n_expert=r.n_expert)
+
+
+def run_reference(args):
+    """The reference's CPU path for this layer, as the oracle port (the Rust/HIP
+    sources cannot be compiled here), on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from deepstrix_b200 import CONFIGS, synth
+    from oracle import oracle
+    oracle.build()
+    cfg = CONFIGS[1]
+    w = make_host_layer(cfg, 1)
+    sample = args.ref_tokens
+    xs = [synth.bf16_bits_to_f32(synth.make_tokens(cfg, 1, sample, stream=i)) for i in range(4)]
+    for i in range(args.warmup):
+        oracle_step(oracle, cfg, w, xs[i % 4])
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        oracle_step(oracle, cfg, w, xs[i % 4])
+    dt = time.perf_counter() - t0
+    value = sample * args.steps / dt
+    cores = oracle.num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (dequantised MXFP4 weights, f64 accumulate)", "data": "synthetic",
+        "config": {"workload": f"config1 decode layer, {args.tokens}-token batches; CPU sample of {sample} tokens per step"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{sample} tokens per step x {args.steps} steps of the full-size layer (OpenMP oracle port)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def time_graph_steps(moe, torch, layer, stores, shared, rw, rb, xs, outs, steps, warmup, stream):
+    """K forwards, each replaying a captured graph of one layer forward; returns elapsed ms."""
+    import ctypes as C
+    lib = moe.lib()
+    graphs = []
+    n = len(stores)
+    with torch.cuda.stream(stream):
+        for i in range(n):
+            layer.set_weights(stores[i], shared[i], rw, rb)
+            layer.forward(xs[i % len(xs)], out=outs[i % len(outs)])  # eager once (first-use work outside capture)
+        stream.synchronize()
+        for i in range(n):
+            layer.set_weights(stores[i], shared[i], rw, rb)
+            moe._check(lib.dsx_graph_begin_capture(C.c_void_p(stream.cuda_stream)))
+            layer.forward(xs[i % len(xs)], out=outs[i % len(outs)])
+            g = C.c_void_p()
+            moe._check(lib.dsx_graph_end_capture(C.c_void_p(stream.cuda_stream), C.byref(g)))
+            graphs.append(g)
+        for i in range(warmup):
+            moe._check(lib.dsx_graph_launch(graphs[i % n], C.c_void_p(stream.cuda_stream)))
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            moe._check(lib.dsx_graph_launch(graphs[i % n], C.c_void_p(stream.cuda_stream)))
+        e1.record(stream)
+        stream.synchronize()
+        ms = e0.elapsed_time(e1)
+        for g in graphs:
+            lib.dsx_graph_destroy(g)
+    return ms, 1  # graph launches per step
+
+
+def run_single_gpu(args):
+    import torch
+    from deepstrix_b200 import CONFIGS, moe, synth
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(0)
+    hbm_peak, _, peak_kind = measured_peaks()
+    cfg = CONFIGS[1]
+    E, k, H = cfg.router.n_expert, cfg.router.n_used, cfg.hidden
+    w = make_host_layer(cfg, 1)
+    base = moe.RoutedExpertWeights.from_host(cfg.fmt, H, cfg.ffn, w["gate"], w["up"], w["down"])
+    base_sh = moe.RoutedExpertWeights.from_host(cfg.fmt, H, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
+    stores, shared = [base], [base_sh]
+    for _ in range(args.layers - 1):
+        stores.append(base.clone())
+        shared.append(base_sh.clone())
+    rw = torch.from_numpy(w["router_w"]).cuda()
+    rb = torch.from_numpy(w["router_bias"]).cuda()
+    layer = moe.MoeLayer(cfg, base, base_sh, rw, rb, max_tokens=64)
+    stream = torch.cuda.Stream()
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def batches(T, n=8):
+        xs = [torch.from_numpy(synth.make_tokens(cfg, 1, T, stream=100 * T + i).view(np.int16)).cuda().view(torch.bfloat16) for i in range(n)]
+        outs = [torch.empty_like(x) for x in xs]
+        return xs, outs
+
+    def distinct_experts(T, xs, outs):
+        ds = []
+        for i in range(len(xs)):
+            layer.set_weights(stores[0], shared[0], rw, rb)
+            layer.forward(xs[i], out=outs[i])
+            ds.append(int((layer.routing(T)["hist"] > 0).sum()))
+        return ds
+
+    results = {}
+    for T in sorted(set([1, 8, 32, 64] + [args.tokens])):
+        xs, outs = batches(T)
+        steps = args.steps if T == args.tokens else max(10, args.steps // 2)
+        t_wall0 = time.time()
+        moe.launch_count(reset=True)
+        ms, _ = time_graph_steps(moe, torch, layer, stores, shared, rw, rb, xs, outs, steps, max(args.warmup, 3), stream)
+        t_wall1 = time.time()
+        ds = distinct_experts(T, xs, outs)
+        d_mean = sum(ds[i % len(ds)] for i in range(steps)) / steps
+        layer_bytes = cfg.algorithmic_bytes(T, 0) + d_mean * cfg.expert_bytes()
+        results[T] = {"tokens": T, "steps": steps, "ms_per_step": ms / steps, "value": T * steps / (ms * 1e-3),
+                      "distinct_experts": d_mean, "layer_bytes": layer_bytes,
+                      "layer_gbs": layer_bytes / (ms / steps * 1e-3) / 1e9, "wall": (t_wall0, t_wall1)}
+        results[T]["layer_frac_of_hbm_peak"] = results[T]["layer_gbs"] / hbm_peak
+    T = args.tokens
+    head = results[T]
+
+    # per-stage device time (eager, event pair around each stage), dominant kernel = gate/up GEMV
+    xs, outs = batches(T)
+    layer.profile(True)
+    stage_acc = {}
+    gu_bytes = []
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup + args.steps):
+            j = i % len(stores)
+            layer.set_weights(stores[j], shared[j], rw, rb)
+            layer.forward(xs[i % len(xs)], out=outs[i % len(outs)])
+            st = layer.stage_ms()
+            if i < args.warmup:
+                continue
+            for n_, v in st.items():
+                stage_acc.setdefault(n_, []).append(v)
+            d = int((layer.routing(T)["hist"] > 0).sum())
+            gu_bytes.append((d + 1) * 2 * cfg.matrix_bytes() + T * H * 2 + (T * k + T) * cfg.ffn * 2)
+    layer.profile(False)
+    stage_ms = {n_: sum(v) / len(v) for n_, v in stage_acc.items()}
+    gu_ms = stage_ms["gate_up"]
+    achieved = (sum(gu_bytes) / len(gu_bytes)) / (gu_ms * 1e-3) / 1e9
+    launches_per_step = None
+    moe.launch_count(reset=True)
+    layer.forward(xs[0], out=outs[0])
+    launches_per_step = moe.launch_count()
+
+    # end to end through the host-buffer entry point: H2D of the tokens, forward, D2H of the result
+    xh = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+    oh = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+    for i, t in enumerate(xh):
+        t.copy_(xs[i].cpu())
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            layer.set_weights(stores[i % len(stores)], shared[i % len(stores)], rw, rb)
+            layer.forward_host(xh[i % 4], oh[i % 4])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(args.steps):
+            j = i % len(stores)
+            layer.set_weights(stores[j], shared[j], rw, rb)
+            layer.forward_host(xh[i % 4], oh[i % 4])
+        e1.record(stream)
+        stream.synchronize()
+        e2e_ms = e0.elapsed_time(e1)
+    assert layer.check() == 0
+    sampler.stop()
+    clocks = sampler.summary(*head["wall"])
+
+    # CPU baseline: the oracle port on a bounded sample of the same layer
+    from oracle import oracle
+    oracle.build()
+    xs_cpu = synth.bf16_bits_to_f32(synth.make_tokens(cfg, 1, args.ref_tokens, stream=7))
+    oracle_step(oracle, cfg, w, xs_cpu[:1])
+    t0 = time.perf_counter()
+    n_rep = 0
+    while time.perf_counter() - t0 < 10.0 and n_rep < 8:
+        oracle_step(oracle, cfg, w, xs_cpu)
+        n_rep += 1
+    cpu_dt = time.perf_counter() - t0
+    cpu_value = args.ref_tokens * n_rep / cpu_dt
+
+    series = [{kk: vv for kk, vv in r.items() if kk != "wall"} for _, r in sorted(results.items())]
+    line = {
+        "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 products of exact MXFP4 weights and bf16 activations, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"config1 full-size decode MoE layer, batch {T} tokens (hidden 4096, 256+1 experts, ffn 2048, top-8, "
+                               f"8 groups/4 kept, MXFP4)", "tokens_per_step": T, "resident_layer_copies": len(stores),
+                   "l2": "steps rotate over %d copies of the layer weights (%.1f GB) so no step re-reads L2-resident weights"
+                         % (len(stores), len(stores) * (base.device_bytes + base_sh.device_bytes) / 1e9),
+                   "launch": "one captured CUDA graph per step"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "traffic": None, "kernel": "gemv_kernel<MXFP4, pair> (gate/up + SwiGLU)", "peak_kind": peak_kind,
+                     "avg_launch_ms": gu_ms, "layer_frac": head["layer_frac_of_hbm_peak"]},
+        "stage_ms": stage_ms,
+        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                         "sample": f"{n_rep} forwards of {args.ref_tokens} tokens through the OpenMP oracle port of the same layer"},
+        "e2e": {"value": T * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "series": series,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=64, help="decode batch size of the headline number")
+    ap.add_argument("--layers", type=int, default=6, help="resident copies of the layer weights to rotate over")
+    ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per CPU-oracle sample step")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 or args.gpus > 1:
+        from deepstrix_b200 import ep_bench
+        return ep_bench.run(args)
+    return run_single_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,200 @@
+// Shared declarations of the B200 MoE library: error plumbing, the HBM tile
+// layout of expert weights, and the device math every kernel agrees on.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dsx_moe.h"
+
+namespace dsx {
+
+// ---------------------------------------------------------------- errors
+int set_error(int code, const char* fmt, ...);
+void count_launch();
+
+#define DSX_CUDA(call)                                                                      \
+    do {                                                                                    \
+        cudaError_t _e = (call);                                                            \
+        if (_e != cudaSuccess)                                                              \
+            return ::dsx::set_error((int)_e, "%s failed: %s (%s:%d)", #call,                \
+                                    cudaGetErrorString(_e), __FILE__, __LINE__);            \
+    } while (0)
+
+#define DSX_REQUIRE(cond, ...)                                                              \
+    do {                                                                                    \
+        if (!(cond)) return ::dsx::set_error(DSX_ERR_INVALID, __VA_ARGS__);                 \
+    } while (0)
+
+// Call right after a <<<>>> launch.
+#define DSX_LAUNCHED()                                                                      \
+    do {                                                                                    \
+        ::dsx::count_launch();                                                              \
+        DSX_CUDA(cudaGetLastError());                                                       \
+    } while (0)
+
+// ------------------------------------------------------------ tile layout
+// A weight matrix [rows, K] is stored as sub-tiles of 16 rows.  One sub-tile is
+// what one warp feeds to mma.sync.m16n8k16 with a single 16-byte load per lane:
+//   MXFP4: 16 rows x 64 columns = 512 B of 4-bit codes + 32 B of E8M0 scales
+//   Q8_0 : 16 rows x 32 columns = 512 B of int8 (stored XOR 0x80) + 32 B of f16 scales
+// Codes and scales live in two planes so every sub-tile starts 16-byte aligned
+// (bulk-copy requirement).  Sub-tile order inside a plane: row tile major, then
+// column tile; the gate/up plane interleaves [gate sub-tile][up sub-tile] per
+// (row tile, column tile) so the fused kernel reads one contiguous stream.
+//
+// Lane l = 4*g + t of the warp owns bytes [16*l, 16*l+16) of a sub-tile.
+// MXFP4 word s (s = 0..3, one per k16 step), column base c = 32*(s>>1) + 8*t + 4*(s&1):
+//   byte0 = code(row g  , c+0) | code(row g  , c+2) << 4
+//   byte1 = code(row g  , c+1) | code(row g  , c+3) << 4
+//   byte2 = code(row g+8, c+0) | code(row g+8, c+2) << 4
+//   byte3 = code(row g+8, c+1) | code(row g+8, c+3) << 4
+// so both 32-column scale blocks of the sub-tile map to two consecutive mma
+// steps, and lane t reads 8 consecutive activation values per scale block.
+// MXFP4 scales: bytes [4*g, 4*g+4) = {row g blk0, row g blk1, row g+8 blk0, row g+8 blk1}.
+// Q8_0 word 2*s + h (s = k16 step, h = 0: row g, 1: row g+8): columns 8*t + 4*s + {0,1,2,3}.
+// Q8_0 scales: halves [2*g, 2*g+2) = {row g, row g+8}.
+constexpr int kTileRows = 16;
+constexpr int kSubNibBytes = 512;
+constexpr int kSubScBytes = 32;
+
+__host__ __device__ inline int tile_k(int fmt) { return fmt == DSX_FMT_MXFP4 ? 64 : 32; }
+
+struct MatrixView {       // one matrix (or gate/up pair) of one expert slot, tile layout
+    const uint8_t* nib;   // sub-tile code plane
+    const uint8_t* sc;    // sub-tile scale plane
+};
+
+// --------------------------------------------------- deterministic math
+// exp / log1p from IEEE add, mul and fma only, so that a CPU restatement using
+// fmaf() rounds identically.  Coefficients: Cephes expf / logf.
+__device__ __forceinline__ float det_expf(float x) {
+    x = fminf(fmaxf(x, -87.0f), 88.0f);
+    const float n = floorf(__fmaf_rn(x, 1.44269504088896341f, 0.5f));
+    float r = __fmaf_rn(n, -0.693359375f, x);
+    r = __fmaf_rn(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = __fmaf_rn(p, r, 1.3981999507e-3f);
+    p = __fmaf_rn(p, r, 8.3334519073e-3f);
+    p = __fmaf_rn(p, r, 4.1665795894e-2f);
+    p = __fmaf_rn(p, r, 1.6666665459e-1f);
+    p = __fmaf_rn(p, r, 5.0000001201e-1f);
+    const float r2 = __fmul_rn(r, r);
+    float y = __fmaf_rn(p, r2, r);
+    y = __fadd_rn(y, 1.0f);
+    return __fmul_rn(y, __uint_as_float((uint32_t)((int)n + 127) << 23));
+}
+
+__device__ __forceinline__ float det_logf(float u) {
+    const uint32_t b = __float_as_uint(u);
+    int e = (int)(b >> 23) - 126;
+    float m = __uint_as_float((b & 0x007FFFFFu) | 0x3F000000u);
+    if (m < 0.707106781186547524f) {
+        e -= 1;
+        m = __fadd_rn(__fadd_rn(m, m), -1.0f);
+    } else {
+        m = __fadd_rn(m, -1.0f);
+    }
+    const float z = __fmul_rn(m, m);
+    float y = 7.0376836292e-2f;
+    y = __fmaf_rn(y, m, -1.1514610310e-1f);
+    y = __fmaf_rn(y, m, 1.1676998740e-1f);
+    y = __fmaf_rn(y, m, -1.2420140846e-1f);
+    y = __fmaf_rn(y, m, 1.4249322787e-1f);
+    y = __fmaf_rn(y, m, -1.6668057665e-1f);
+    y = __fmaf_rn(y, m, 2.0000714765e-1f);
+    y = __fmaf_rn(y, m, -2.4999993993e-1f);
+    y = __fmaf_rn(y, m, 3.3333331174e-1f);
+    y = __fmul_rn(y, m);
+    y = __fmul_rn(y, z);
+    const float fe = (float)e;
+    y = __fmaf_rn(fe, -2.12194440e-4f, y);
+    y = __fmaf_rn(z, -0.5f, y);
+    float r = __fadd_rn(m, y);
+    r = __fmaf_rn(fe, 0.693359375f, r);
+    return r;
+}
+
+__device__ __forceinline__ float det_log1pf(float y) {
+    const float u = __fadd_rn(1.0f, y);
+    if (u == 1.0f) return y;
+    const float d = __fadd_rn(u, -1.0f);
+    return __fmul_rn(det_logf(u), __fdiv_rn(y, d));
+}
+
+// Router probability, kernels/router_topk.hip:32-36,71 and laguna_ops.hip:59
+// of the reference, on the deterministic exp/log above.
+__device__ __forceinline__ float router_prob(float logit, int score_fn) {
+    if (score_fn == DSX_SCORE_SIGMOID) return __fdiv_rn(1.0f, __fadd_rn(1.0f, det_expf(-logit)));
+    float sp;
+    if (logit > 20.0f) sp = logit;
+    else if (logit < -20.0f) sp = det_expf(logit);
+    else sp = det_log1pf(det_expf(logit));
+    return __fsqrt_rn(sp);
+}
+
+// ------------------------------------------------------- kernel launchers
+// (defined in the .cu file named in the comment; all asynchronous on `stream`)
+
+// repack.cu
+int launch_repack(int fmt, int src_layout, const uint8_t* q, const uint8_t* s, int64_t rows, int64_t K,
+                  uint8_t* nib, uint8_t* sc, int pair_stride, int pair_index, int n_mats, int64_t src_q_stride,
+                  int64_t src_s_stride, int64_t dst_nib_stride, int64_t dst_sc_stride, cudaStream_t stream);
+int launch_unpack(int fmt, const uint8_t* nib, const uint8_t* sc, int64_t rows, int64_t K, int pair_stride,
+                  int pair_index, uint8_t* q_out, uint8_t* s_out, cudaStream_t stream);
+
+// router.cu
+int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int n_expert, int64_t H, float* logits,
+                         cudaStream_t stream);
+int launch_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg,
+                       int32_t* selected, float* weights, cudaStream_t stream);
+
+// groups.cu
+struct GroupScratch {      // device scratch for the multi-block counting sort
+    int32_t* chunk_hist;   // [n_chunks, n_expert]
+    int64_t capacity_chunks;
+};
+constexpr int kGroupChunk = 2048;  // picks per block of the counting sort
+int launch_group_build(const int32_t* selected, int64_t T, int n_used, int n_expert, int expert_lo, int chunk,
+                       int shared_items_for_T, int32_t* hist, int32_t* offsets, int32_t* perm, int32_t* work_items,
+                       int32_t* n_work_items, int32_t work_cap, GroupScratch scratch, cudaStream_t stream);
+
+// gemv.cu
+struct GemvArgs {
+    int fmt;                 // routed store format
+    int shared_fmt;
+    int n_expert;            // routed slots; item expert id == n_expert means "shared expert"
+    int64_t K;               // reduction length (hidden for gate/up, ffn for down)
+    int64_t rows;            // output rows per matrix (ffn for gate/up, hidden for down)
+    const uint8_t* nib;      // plane base, routed
+    const uint8_t* sc;
+    int64_t nib_slot_stride; // bytes between expert slots
+    int64_t sc_slot_stride;
+    const uint8_t* sh_nib;   // shared expert planes (may be null)
+    const uint8_t* sh_sc;
+    int64_t sh_rows;
+    const int32_t* work_items;   // (e<<16)|member_start, chunk 8
+    const int32_t* n_work_items;
+    const int32_t* offsets;      // [n_expert+1]
+    const int32_t* perm;         // [P]
+    const float* route_w;        // [P] routing weights indexed by t*k+s
+    int n_used;
+    int64_t T;
+    float clamp;
+    const __nv_bfloat16* x;      // gate/up: [T, K] bf16
+    __half* mid;                 // gate/up out / down in: [P + T, ffn] f16, permuted order
+    int64_t mid_stride;          // elements per mid row
+    float* partial;              // down out: [P + T, rows] f32, indexed t*k+s (shared: P+t)
+    uint32_t* error_word;
+};
+int launch_gemv_gate_up(const GemvArgs& a, int sm_count, cudaStream_t stream);
+int launch_gemv_down(const GemvArgs& a, int sm_count, cudaStream_t stream);
+int gemv_configure();  // opt in to large dynamic shared memory (once per device)
+
+// combine.cu
+int launch_combine(const float* partial, int64_t T, int n_used, int64_t H, int with_shared, const int32_t* selected,
+                   int expert_lo, int n_local, __nv_bfloat16* out, cudaStream_t stream);
+
+}  // namespace dsx

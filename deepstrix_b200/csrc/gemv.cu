@@ -1,0 +1,373 @@
+// Decode-size grouped GEMV: gate/up + clamp + SwiGLU + routing weight, and down.
+//
+// Reference counterparts (paths relative to the deepstrix repository):
+//   gate/up  crates/v4flash-kernels/kernels/mxfp4_pair_matvec.hip:165-229 (decode, fused SwiGLU),
+//            :566-640 (grouped by distinct expert: each expert read once)
+//   down     crates/v4flash-kernels/kernels/mxfp4_matvec.hip:120-155, :534-600
+//   Q8_0     crates/v4flash-kernels/kernels/q8_0_matvec.hip:64-91
+//   SwiGLU   crates/v4flash-kernels/kernels/swiglu_clamp_weighted.hip:28-36
+//
+// Design (B200): one persistent block per SM.  A work item is (expert, up to 8
+// tokens); a block takes a contiguous range of (item, 128-row block) units and
+// each of its 8 warps owns one 16-row tile of the unit.  Weights are never
+// touched by ordinary loads: lane 0 of every warp streams its row tile through a
+// private 4-stage ring of shared memory with 1-D bulk copies (cp.async.bulk +
+// mbarrier complete_tx), so each SM keeps ~140 KB of HBM reads in flight
+// without spending registers on it, and every weight byte is read exactly once
+// per item.  Lanes then read their 16 bytes per sub-tile from the ring, expand
+// the 4-bit codes (or int8) to f16 with two shifts, two masks and byte permutes,
+// and feed mma.sync.m16n8k16 with the item's (<= 8) tokens as the n dimension;
+// the E8M0 / f16 block scale multiplies the f32 result of each 32-column block.
+// Token columns are independent in the mma, so a token's result does not
+// depend on which other tokens share its item.
+#include "dsx_common.cuh"
+
+namespace dsx {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 4;
+constexpr int kSubPerStage = 8;  // sub-tiles per ring stage
+constexpr int kStageNib = kSubPerStage * kSubNibBytes;
+constexpr int kStageSc = kSubPerStage * kSubScBytes;
+constexpr int kStageBytes = kStageNib + kStageSc;  // 4352
+constexpr int kActPad = 32;                        // halves of padding per activation row (64 B: bank shift)
+constexpr int kMaxTok = 8;
+constexpr uint32_t kWaitSpins = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: returns false when the phase did not complete in kWaitSpins polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitSpins; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Eight E2M1 codes -> the four f16x2 A-fragment registers of one k16 step.
+// A code `s e1 e0 m` placed at bits 15, 11..9 of an f16 is the E2M1 value times
+// 2^-14 (subnormal codes included), and those four bits sit in the f16's HIGH
+// byte only: build the high bytes of four codes at once with shifts and masks,
+// then spread them to half words with byte permutes.  The 2^14 is folded into
+// the block scale.
+__device__ __forceinline__ void mxfp4_frag(uint32_t q, uint32_t (&a)[4]) {
+    const uint32_t lo = ((q << 4) & 0x80808080u) | ((q << 1) & 0x0E0E0E0Eu);
+    const uint32_t hi = (q & 0x80808080u) | ((q >> 3) & 0x0E0E0E0Eu);
+    a[0] = __byte_perm(lo, 0u, 0x1404);
+    a[1] = __byte_perm(lo, 0u, 0x3424);
+    a[2] = __byte_perm(hi, 0u, 0x1404);
+    a[3] = __byte_perm(hi, 0u, 0x3424);
+}
+// E8M0 byte e -> 2^(e-127) * 2^14 as f32 (exact for e <= 240).
+__device__ __forceinline__ float mxfp4_scale(uint32_t e) { return __uint_as_float(min(e + 14u, 255u) << 23); }
+
+// Four offset-binary int8 (value ^ 0x80) -> two f16x2: 0x6400 | u is 1024 + u.
+__device__ __forceinline__ uint32_t q8_pair(uint32_t w, uint32_t sel) {
+    const uint32_t h = __byte_perm(w, 0x64646464u, sel);
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&h), __half2half2(__ushort_as_half((unsigned short)0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int FMT>
+__device__ __forceinline__ void compute_subtile(const uint8_t* nibp, const uint8_t* scp, int lane, const uint4* bf,
+                                                float (&acc)[4]) {
+    const uint4 wq = *reinterpret_cast<const uint4*>(nibp + lane * 16);
+    const uint32_t sw = *reinterpret_cast<const uint32_t*>(scp + (lane >> 2) * 4);
+    if (FMT == DSX_FMT_MXFP4) {
+        const uint32_t w[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t a[4];
+            mxfp4_frag(w[2 * b], a);
+            mma16816(c, a, bf[b].x, bf[b].y);
+            mxfp4_frag(w[2 * b + 1], a);
+            mma16816(c, a, bf[b].z, bf[b].w);
+            const float s0 = mxfp4_scale((sw >> (8 * b)) & 0xFFu), s1 = mxfp4_scale((sw >> (16 + 8 * b)) & 0xFFu);
+            acc[0] = fmaf(s0, c[0], acc[0]);
+            acc[1] = fmaf(s0, c[1], acc[1]);
+            acc[2] = fmaf(s1, c[2], acc[2]);
+            acc[3] = fmaf(s1, c[3], acc[3]);
+        }
+    } else {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t a[4];
+        a[0] = q8_pair(wq.x, 0x4140);
+        a[2] = q8_pair(wq.x, 0x4342);
+        a[1] = q8_pair(wq.y, 0x4140);
+        a[3] = q8_pair(wq.y, 0x4342);
+        mma16816(c, a, bf[0].x, bf[0].y);
+        a[0] = q8_pair(wq.z, 0x4140);
+        a[2] = q8_pair(wq.z, 0x4342);
+        a[1] = q8_pair(wq.w, 0x4140);
+        a[3] = q8_pair(wq.w, 0x4342);
+        mma16816(c, a, bf[0].z, bf[0].w);
+        const __half2 sh = *reinterpret_cast<const __half2*>(&sw);
+        const float s0 = __low2float(sh), s1 = __high2float(sh);
+        acc[0] = fmaf(s0, c[0], acc[0]);
+        acc[1] = fmaf(s0, c[1], acc[1]);
+        acc[2] = fmaf(s1, c[2], acc[2]);
+        acc[3] = fmaf(s1, c[3], acc[3]);
+    }
+}
+
+struct ItemInfo {
+    int n_tok;
+    int tok[kMaxTok];      // token index (gate/up source row)
+    int mid_row[kMaxTok];  // row of mid (permuted order)
+    int out_row[kMaxTok];  // row of partial (t*k+s, or P+t for the shared expert)
+    float w[kMaxTok];
+    const uint8_t* nib;    // plane base of this item's expert
+    const uint8_t* sc;
+};
+
+// FMT: routed format for routed items; shared items use SFMT.  The kernel is
+// compiled for the (FMT, SFMT) pairs with FMT == SFMT only, which keeps one
+// decode path per item.
+template <int FMT, bool PAIR>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kTileK = (FMT == DSX_FMT_MXFP4) ? 64 : 32;
+    constexpr int kBlocks = kTileK / 32;            // 32-column scale blocks per sub-tile
+    constexpr int kSubPerCt = PAIR ? 2 : 1;          // sub-tiles per column tile
+    constexpr int kCtPerStage = kSubPerStage / kSubPerCt;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int64_t K = a.K;
+    const int act_stride = (int)K + kActPad;  // halves
+    __half* act = reinterpret_cast<__half*>(smem);
+    uint8_t* ring = smem + (((size_t)kMaxTok * act_stride * 2 + 127) & ~(size_t)127);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)kWarps * kStages * kStageBytes);
+    ItemInfo* info = reinterpret_cast<ItemInfo*>(bars + kWarps * kStages);
+
+    uint8_t* my_ring = ring + (size_t)warp * kStages * kStageBytes;
+    const uint32_t my_bars = smem_u32(bars + warp * kStages);
+    if (lane == 0)
+        for (int s = 0; s < kStages; s++) mbar_init(my_bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+
+    const int n_items = a.n_work_items[0];
+    const int n_kt = (int)(K / kTileK);
+    const int n_stage = (n_kt + kCtPerStage - 1) / kCtPerStage;
+    const int blocks_per_item = (int)(a.rows / (kTileRows * kWarps));
+    const int64_t U = (int64_t)n_items * blocks_per_item;
+    const int64_t u0 = U * blockIdx.x / gridDim.x, u1 = U * (blockIdx.x + 1) / gridDim.x;
+    const int64_t total = (u1 - u0) * n_stage;  // ring stages this warp will consume
+    const int64_t P = a.T * a.n_used;
+
+    // source of ring stage `idx` of this warp (lane 0 only)
+    auto issue = [&](int64_t idx) {
+        const int64_t unit = u0 + idx / n_stage;
+        const int ls = (int)(idx % n_stage);
+        const int item = (int)(unit / blocks_per_item), rb = (int)(unit % blocks_per_item);
+        const uint32_t wi = (uint32_t)a.work_items[item];
+        const int e = (int)(wi >> 16);
+        const uint8_t* nib = (e == a.n_expert) ? a.sh_nib : a.nib + (int64_t)e * a.nib_slot_stride;
+        const uint8_t* sc = (e == a.n_expert) ? a.sh_sc : a.sc + (int64_t)e * a.sc_slot_stride;
+        const int64_t rt = (int64_t)rb * kWarps + warp;
+        const int ct0 = ls * kCtPerStage;
+        const int n_ct = min(kCtPerStage, n_kt - ct0);
+        const int64_t sub0 = (rt * n_kt + ct0) * kSubPerCt;
+        const uint32_t nsub = (uint32_t)(n_ct * kSubPerCt);
+        const int slot = (int)(idx % kStages);
+        const uint32_t bar = my_bars + 8 * slot;
+        const uint32_t dst = smem_u32(my_ring + (size_t)slot * kStageBytes);
+        mbar_expect_tx(bar, nsub * (kSubNibBytes + kSubScBytes));
+        bulk_g2s(dst, nib + sub0 * kSubNibBytes, nsub * kSubNibBytes, bar);
+        bulk_g2s(dst + kStageNib, sc + sub0 * kSubScBytes, nsub * kSubScBytes, bar);
+    };
+
+    if (lane == 0)
+        for (int64_t i = 0; i < total && i < kStages; i++) issue(i);
+
+    int cur_item = -1;
+    bool dead = false;
+    float acc0[4], acc1[4];
+    for (int64_t idx = 0; idx < total; idx++) {
+        const int64_t unit = u0 + idx / n_stage;
+        const int ls = (int)(idx % n_stage);
+        const int item = (int)(unit / blocks_per_item), rb = (int)(unit % blocks_per_item);
+        if (ls == 0) {
+            if (item != cur_item) {
+                // all warps of the block change item together (same unit sequence)
+                __syncthreads();
+                if (threadIdx.x < kMaxTok) {
+                    const uint32_t wi = (uint32_t)a.work_items[item];
+                    const int e = (int)(wi >> 16), start = (int)(wi & 0xFFFFu), i = threadIdx.x;
+                    if (e == a.n_expert) {  // shared expert: tokens start..start+7, weight 1
+                        const int n = (int)min((int64_t)kMaxTok, a.T - start);
+                        if (i == 0) info->n_tok = n;
+                        info->tok[i] = start + i;
+                        info->mid_row[i] = (int)P + start + i;
+                        info->out_row[i] = (int)P + start + i;
+                        info->w[i] = 1.0f;
+                    } else {
+                        const int seg0 = a.offsets[e], cnt = a.offsets[e + 1] - seg0;
+                        const int n = min(kMaxTok, cnt - start);
+                        if (i == 0) info->n_tok = n;
+                        const int p = seg0 + start + min(i, n - 1);
+                        const int ts = a.perm[p];
+                        info->tok[i] = ts / a.n_used;
+                        info->mid_row[i] = p;
+                        info->out_row[i] = ts;
+                        info->w[i] = a.route_w[ts];
+                    }
+                }
+                __syncthreads();
+                // stage the item's activation rows as f16
+                const int n = info->n_tok;
+                const int vec_per_row = (int)(K >> 3);
+                for (int v = threadIdx.x; v < n * vec_per_row; v += kThreads) {
+                    const int r = v / vec_per_row, c8 = v - r * vec_per_row;
+                    uint4 out;
+                    if (PAIR) {
+                        const uint4 in = __ldg(reinterpret_cast<const uint4*>(a.x + (int64_t)info->tok[r] * K) + c8);
+                        const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const __half2 h = __floats2half2_rn(__uint_as_float(wds[q] << 16), __uint_as_float(wds[q] & 0xFFFF0000u));
+                            o[q] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        out = make_uint4(o[0], o[1], o[2], o[3]);
+                    } else {
+                        out = *(reinterpret_cast<const uint4*>(a.mid + (int64_t)info->mid_row[r] * a.mid_stride) + c8);
+                    }
+                    *reinterpret_cast<uint4*>(act + (size_t)r * act_stride + c8 * 8) = out;
+                }
+                __syncthreads();
+                cur_item = item;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc0[i] = acc1[i] = 0.f;
+        }
+        const int slot = (int)(idx % kStages);
+        if (!dead && !mbar_wait(my_bars + 8 * slot, (uint32_t)((idx / kStages) & 1))) {
+            dead = true;
+            if (lane == 0) atomicOr(a.error_word, 1u);
+        }
+        if (!dead) {
+            const uint8_t* st_nib = my_ring + (size_t)slot * kStageBytes;
+            const uint8_t* st_sc = st_nib + kStageNib;
+            const int ct0 = ls * kCtPerStage;
+            const int n_ct = min(kCtPerStage, n_kt - ct0);
+            const bool tok_ok = g < info->n_tok;
+            for (int c = 0; c < n_ct; c++) {
+                uint4 bf[kBlocks];
+#pragma unroll
+                for (int b = 0; b < kBlocks; b++) {
+                    bf[b] = make_uint4(0u, 0u, 0u, 0u);
+                    if (tok_ok)
+                        bf[b] = *reinterpret_cast<const uint4*>(act + (size_t)g * act_stride + (size_t)(ct0 + c) * kTileK + 32 * b + 8 * t4);
+                }
+                compute_subtile<FMT>(st_nib + (size_t)(c * kSubPerCt) * kSubNibBytes, st_sc + (size_t)(c * kSubPerCt) * kSubScBytes, lane, bf, acc0);
+                if (PAIR)
+                    compute_subtile<FMT>(st_nib + (size_t)(c * 2 + 1) * kSubNibBytes, st_sc + (size_t)(c * 2 + 1) * kSubScBytes, lane, bf, acc1);
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && !dead && idx + kStages < total) issue(idx + kStages);
+
+        if (ls == n_stage - 1 && !dead) {
+            const int row0 = (rb * kWarps + warp) * kTileRows + g;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int n = 2 * t4 + (i & 1);
+                const int row = row0 + ((i >> 1) ? 8 : 0);
+                if (n < info->n_tok) {
+                    if (PAIR) {
+                        float gv = acc0[i], uv = acc1[i];
+                        if (a.clamp > 1.0e-6f) {
+                            gv = fminf(gv, a.clamp);
+                            uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
+                        }
+                        const float sig = 1.0f / (1.0f + __expf(-gv));
+                        a.mid[(int64_t)info->mid_row[n] * a.mid_stride + row] = __float2half_rn(gv * sig * uv * info->w[n]);
+                    } else {
+                        a.partial[(int64_t)info->out_row[n] * a.rows + row] = acc0[i];
+                    }
+                }
+            }
+        }
+    }
+}
+
+size_t gemv_smem_bytes(int64_t K) {
+    const size_t act = (((size_t)kMaxTok * (size_t)(K + kActPad) * 2) + 127) & ~(size_t)127;
+    return act + (size_t)kWarps * kStages * kStageBytes + sizeof(uint64_t) * kWarps * kStages + sizeof(ItemInfo) + 128;
+}
+
+constexpr size_t kMaxSmem = 227 * 1024;
+
+template <int FMT, bool PAIR>
+int launch_one(const GemvArgs& a, int sm_count, cudaStream_t stream) {
+    const size_t smem = gemv_smem_bytes(a.K);
+    DSX_REQUIRE(smem <= kMaxSmem, "gemv: reduction length %lld needs %zu B of shared memory (max %zu)", (long long)a.K, smem, kMaxSmem);
+    gemv_kernel<FMT, PAIR><<<sm_count, kThreads, smem, stream>>>(a);
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+int check_args(const GemvArgs& a) {
+    DSX_REQUIRE(a.K % 256 == 0, "gemv: reduction length %lld must be a multiple of 256", (long long)a.K);
+    DSX_REQUIRE(a.rows % (kTileRows * kWarps) == 0, "gemv: %lld rows must be a multiple of %d", (long long)a.rows, kTileRows * kWarps);
+    DSX_REQUIRE(a.sh_nib == nullptr || (a.shared_fmt == a.fmt && a.sh_rows == a.rows),
+                "gemv: the shared expert must have the routed experts' format and width");
+    return DSX_OK;
+}
+
+}  // namespace
+
+int launch_gemv_gate_up(const GemvArgs& a, int sm_count, cudaStream_t stream) {
+    if (int rc = check_args(a)) return rc;
+    return a.fmt == DSX_FMT_MXFP4 ? launch_one<DSX_FMT_MXFP4, true>(a, sm_count, stream)
+                                  : launch_one<DSX_FMT_Q8_0, true>(a, sm_count, stream);
+}
+
+int launch_gemv_down(const GemvArgs& a, int sm_count, cudaStream_t stream) {
+    if (int rc = check_args(a)) return rc;
+    return a.fmt == DSX_FMT_MXFP4 ? launch_one<DSX_FMT_MXFP4, false>(a, sm_count, stream)
+                                  : launch_one<DSX_FMT_Q8_0, false>(a, sm_count, stream);
+}
+
+// Opt every instantiation in to the large dynamic shared-memory carve-out.  Done
+// once per device at layer creation so that launches are plain stream work
+// (capturable in a graph).
+int gemv_configure() {
+    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_MXFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_MXFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_Q8_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+    return DSX_OK;
+}
+
+}  // namespace dsx

@@ -1,0 +1,196 @@
+// Router: logits GEMV and top-k selection.
+//
+// Reference counterparts (paths relative to the deepstrix repository):
+//   logits  crates/v4flash-kernels/kernels/f16_matvec.hip:26-45 (warp per row, f32 accumulate)
+//   top-k   crates/v4flash-kernels/kernels/router_topk_par.hip:66-238 (k argmax passes, lower
+//           index wins ties) and :294-434 (the 64-bit-key wave-reduction twin whose key
+//           `(ord(score) << 32) | ~index` is reused here)
+//   sigmoid crates/v4flash-kernels/kernels/laguna_ops.hip:55-62
+#include "dsx_common.cuh"
+
+namespace dsx {
+namespace {
+
+constexpr int kLogitWarps = 8;
+constexpr int kLogitTokens = 8;  // tokens per warp pass
+
+// One warp per (expert, tile of kLogitTokens tokens).  Lane l accumulates
+// columns 4*l + 128*i in increasing i with one fma per element, then the warp
+// folds with an xor butterfly: the f32 operation sequence of a (token, expert)
+// pair is the same for every T, so decode and prefill route identically.
+__global__ void __launch_bounds__(kLogitWarps * 32)
+router_logits_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, const float* __restrict__ W, int n_expert,
+                     int64_t H, float* __restrict__ logits) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * kLogitWarps + warp;
+    if (e >= n_expert) return;
+    const int64_t t0 = (int64_t)blockIdx.y * kLogitTokens;
+    const int nt = (int)min((int64_t)kLogitTokens, T - t0);
+    float acc[kLogitTokens];
+#pragma unroll
+    for (int i = 0; i < kLogitTokens; i++) acc[i] = 0.0f;
+    const float4* wrow = reinterpret_cast<const float4*>(W + (int64_t)e * H);
+    const int n_iter = (int)(H >> 7);
+#pragma unroll 4
+    for (int i = 0; i < n_iter; i++) {
+        const float4 w = __ldg(wrow + i * 32 + lane);
+#pragma unroll
+        for (int tt = 0; tt < kLogitTokens; tt++) {
+            if (tt < nt) {
+                const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (t0 + tt) * H) + i * 32 + lane);
+                const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
+                const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
+                float a = acc[tt];
+                a = __fmaf_rn(w.x, x0, a);
+                a = __fmaf_rn(w.y, x1, a);
+                a = __fmaf_rn(w.z, x2, a);
+                a = __fmaf_rn(w.w, x3, a);
+                acc[tt] = a;
+            }
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < kLogitTokens; tt++) {
+        float a = acc[tt];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, off));
+        if (lane == 0 && tt < nt) logits[(t0 + tt) * n_expert + e] = a;
+    }
+}
+
+__device__ __forceinline__ uint32_t ordered_bits(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+constexpr int kTopkWarps = 8;
+constexpr int kMaxUsed = 16;
+
+// One warp per token, VPL experts per lane (expert e = lane*VPL + j).
+template <int VPL>
+__global__ void __launch_bounds__(kTopkWarps * 32)
+router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, dsx_router_config cfg,
+                   int32_t* __restrict__ selected, float* __restrict__ weights) {
+    __shared__ float s_score[kTopkWarps][VPL * 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * kTopkWarps + warp;
+    if (t >= T) return;
+    const int E = VPL * 32;
+    float p[VPL], s[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; j++) {
+        const int e = lane * VPL + j;
+        p[j] = router_prob(logits[t * E + e], cfg.score_fn);
+        s[j] = bias ? __fadd_rn(p[j], bias[e]) : p[j];
+    }
+    if (cfg.n_group > 1) {
+        // group score = sum of the two largest selection scores of the group;
+        // keep the topk_group best groups (equal -> lower group index)
+#pragma unroll
+        for (int j = 0; j < VPL; j++) s_score[warp][lane * VPL + j] = s[j];
+        __syncwarp();
+        const int per = E / cfg.n_group;
+        float gs = -INFINITY;
+        if (lane < cfg.n_group) {
+            float m1 = -INFINITY, m2 = -INFINITY;
+            for (int i = 0; i < per; i++) {
+                const float v = s_score[warp][lane * per + i];
+                if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
+            }
+            gs = __fadd_rn(m1, m2);
+        }
+        int rank = 0;
+        for (int h = 0; h < cfg.n_group; h++) {
+            const float o = __shfl_sync(0xFFFFFFFFu, gs, h);
+            if (o > gs || (o == gs && h < lane)) rank++;
+        }
+        const uint32_t keep = __ballot_sync(0xFFFFFFFFu, lane < cfg.n_group && rank < cfg.topk_group);
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+            const int grp = (lane * VPL + j) / per;
+            if (!((keep >> grp) & 1u)) s[j] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    unsigned long long key[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; j++)
+        // adding +0 turns -0 into +0, so scores that compare equal get equal key prefixes
+        key[j] = ((unsigned long long)ordered_bits(__fadd_rn(s[j], 0.0f)) << 32) |
+                 (unsigned long long)(0xFFFFFFFFu - (uint32_t)(lane * VPL + j));
+    float psel[kMaxUsed];
+    int esel[kMaxUsed];
+#pragma unroll
+    for (int r = 0; r < kMaxUsed; r++) {
+        if (r < cfg.n_used) {
+            unsigned long long best = key[0];
+#pragma unroll
+            for (int j = 1; j < VPL; j++) best = key[j] > best ? key[j] : best;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const unsigned long long o = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+                best = o > best ? o : best;
+            }
+            const int e = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
+            const int owner = e / VPL, jj = e - owner * VPL;
+            float pv = 0.0f;
+#pragma unroll
+            for (int j = 0; j < VPL; j++)
+                if (lane == owner && j == jj) { pv = p[j]; key[j] = 0ull; }
+            psel[r] = __shfl_sync(0xFFFFFFFFu, pv, owner);
+            esel[r] = e;
+        }
+    }
+    // weights from the unbiased probabilities, summed in slot order
+    float sum = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kMaxUsed; r++)
+        if (r < cfg.n_used) sum = __fadd_rn(sum, psel[r]);
+    if (sum < cfg.weight_eps) sum = cfg.weight_eps;
+#pragma unroll
+    for (int r = 0; r < kMaxUsed; r++)
+        if (r < cfg.n_used && lane == (r & 31)) {
+            selected[t * cfg.n_used + r] = esel[r];
+            weights[t * cfg.n_used + r] = __fmul_rn(__fdiv_rn(psel[r], sum), cfg.route_scale);
+        }
+}
+
+}  // namespace
+
+int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int n_expert, int64_t H, float* logits,
+                         cudaStream_t stream) {
+    DSX_REQUIRE(H % 128 == 0, "router_logits: hidden %lld must be a multiple of 128", (long long)H);
+    if (T == 0) return DSX_OK;
+    dim3 grid((unsigned)((n_expert + kLogitWarps - 1) / kLogitWarps), (unsigned)((T + kLogitTokens - 1) / kLogitTokens));
+    router_logits_kernel<<<grid, kLogitWarps * 32, 0, stream>>>(x, T, W, n_expert, H, logits);
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+int launch_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg,
+                       int32_t* selected, float* weights, cudaStream_t stream) {
+    DSX_REQUIRE(cfg.n_expert > 0 && cfg.n_expert % 32 == 0 && cfg.n_expert <= 512,
+                "router_topk: n_expert %d must be a multiple of 32, at most 512", cfg.n_expert);
+    DSX_REQUIRE(cfg.n_used >= 1 && cfg.n_used <= kMaxUsed && cfg.n_used <= cfg.n_expert, "router_topk: n_used %d out of range", cfg.n_used);
+    if (cfg.n_group > 1) {
+        DSX_REQUIRE(cfg.n_group <= 32 && cfg.n_expert % cfg.n_group == 0 && cfg.topk_group >= 1 && cfg.topk_group <= cfg.n_group,
+                    "router_topk: bad group limit %d/%d", cfg.topk_group, cfg.n_group);
+    }
+    if (T == 0) return DSX_OK;
+    const unsigned grid = (unsigned)((T + kTopkWarps - 1) / kTopkWarps);
+    switch (cfg.n_expert / 32) {
+#define DSX_TOPK_CASE(V)                                                                                   \
+    case V:                                                                                                \
+        router_topk_kernel<V><<<grid, kTopkWarps * 32, 0, stream>>>(logits, bias, T, cfg, selected, weights); \
+        break;
+        DSX_TOPK_CASE(1) DSX_TOPK_CASE(2) DSX_TOPK_CASE(3) DSX_TOPK_CASE(4) DSX_TOPK_CASE(6) DSX_TOPK_CASE(8)
+        DSX_TOPK_CASE(12) DSX_TOPK_CASE(16)
+#undef DSX_TOPK_CASE
+        default:
+            return set_error(DSX_ERR_UNSUPPORTED, "router_topk: n_expert %d not instantiated", cfg.n_expert);
+    }
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+}  // namespace dsx

@@ -1,0 +1,308 @@
+"""Python mirror of the MoE operator interface, over the C ABI (ctypes).
+
+Class and method names follow the reference's Rust wrappers so tests read like
+the reference's: ``RouterTopk.launch_batched`` (src/router_topk.rs:245-364),
+``MoeGroupBuilder.launch`` (src/moe_group_builder.rs:72-259),
+``RoutedExpertWeights`` (src/model_weights.rs:41-52), and a one-call layer in
+the shape of ``MtpState::moe`` (het/mtp.rs:1606-1730).  torch is used only for
+device memory and the current stream; every computation happens inside
+``libdsx_moe.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+from ._build import LIB_PATH
+from .config import FMT_MXFP4, MoeConfig, RouterConfig
+
+SRC_MXFP4_HF, SRC_MXFP4_GGML, SRC_MXFP4_SB2, SRC_Q8_0_BLOCKS, SRC_Q8_0_SPLIT = range(5)
+MAT_GATE, MAT_UP, MAT_DOWN = range(3)
+
+
+class DsxError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"dsx error {code}: {msg}")
+        self.code = code
+
+
+class _RouterCfg(C.Structure):
+    _fields_ = [("n_expert", C.c_int32), ("n_used", C.c_int32), ("n_group", C.c_int32), ("topk_group", C.c_int32),
+                ("score_fn", C.c_int32), ("route_scale", C.c_float), ("weight_eps", C.c_float)]
+
+
+class _MoeCfg(C.Structure):
+    _fields_ = [("hidden", C.c_int32), ("ffn", C.c_int32), ("shared_ffn", C.c_int32), ("max_tokens", C.c_int32),
+                ("clamp", C.c_float), ("router", _RouterCfg)]
+
+
+def _router_struct(r: RouterConfig) -> _RouterCfg:
+    return _RouterCfg(r.n_expert, r.n_used, r.n_group, r.topk_group, r.score_fn, r.route_scale, r.weight_eps)
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load ``libdsx_moe.so``; raises if it has not been built (no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m deepstrix_b200._build` (there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.dsx_last_error.restype = C.c_char_p
+        _lib.dsx_launch_count.restype = C.c_uint64
+        _lib.dsx_wi_upper_bound.restype = C.c_uint32
+        _lib.dsx_wi_upper_bound.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint64]
+    return _lib
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise DsxError(rc, lib().dsx_last_error().decode())
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dptr(t) -> C.c_void_p:
+    return C.c_void_p(0) if t is None else C.c_void_p(t.data_ptr())
+
+
+def launch_count(reset: bool = False) -> int:
+    return int(lib().dsx_launch_count(1 if reset else 0))
+
+
+def wi_upper_bound(members: int, groups: int, chunk: int, cap: int = 1 << 40) -> int:
+    return int(lib().dsx_wi_upper_bound(members, groups, chunk, cap))
+
+
+def bytes_per_expert(fmt: int, k: int, rows: int) -> int:
+    out = C.c_size_t()
+    _check(lib().dsx_bytes_per_expert(fmt, C.c_int64(k), C.c_int64(rows), C.byref(out)))
+    return out.value
+
+
+# --------------------------------------------------------------------------
+class RoutedExpertWeights:
+    """Expert store: n_slots experts (gate, up, down) resident in HBM in the
+    library's tile layout."""
+
+    def __init__(self, fmt: int, n_slots: int, hidden: int, ffn: int, _handle=None):
+        self.fmt, self.n_slots, self.hidden, self.ffn = fmt, n_slots, hidden, ffn
+        if _handle is None:
+            h = C.c_void_p()
+            _check(lib().dsx_expert_store_create(C.byref(h), fmt, n_slots, C.c_int64(hidden), C.c_int64(ffn)))
+            _handle = h
+        self._h = _handle
+
+    def close(self):
+        if self._h:
+            lib().dsx_expert_store_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def device_bytes(self) -> int:
+        out = C.c_size_t()
+        _check(lib().dsx_expert_store_info(self._h, None, None, None, None, C.byref(out)))
+        return out.value
+
+    def load(self, which: int, layout: int, q, s=None, slot: int = -1):
+        """Repack matrix `which` of `slot` (-1: all slots, sources back to back)
+        from host numpy arrays or CUDA tensors."""
+        on_dev = isinstance(q, torch.Tensor)
+        if on_dev:
+            assert q.is_cuda and q.is_contiguous()
+            qp, sp = _dptr(q), _dptr(s)
+        else:
+            q = np.ascontiguousarray(q)
+            s = None if s is None else np.ascontiguousarray(s)
+            qp = C.c_void_p(q.ctypes.data)
+            sp = C.c_void_p(0 if s is None else s.ctypes.data)
+        _check(lib().dsx_expert_store_load(self._h, slot, which, layout, qp, sp, 1 if on_dev else 0, _stream()))
+
+    def unpack(self, slot: int, which: int):
+        """Inverse repack -> (q, s) CUDA uint8 tensors in HF (MXFP4) / split (Q8_0) layout."""
+        rows, k = (self.hidden, self.ffn) if which == MAT_DOWN else (self.ffn, self.hidden)
+        if self.fmt == FMT_MXFP4:
+            q = torch.empty((rows, k // 2), dtype=torch.uint8, device="cuda")
+            s = torch.empty((rows, k // 32), dtype=torch.uint8, device="cuda")
+        else:
+            q = torch.empty((rows, k), dtype=torch.int8, device="cuda")
+            s = torch.empty((rows, k // 32), dtype=torch.float16, device="cuda")
+        _check(lib().dsx_expert_store_unpack(self._h, slot, which, _dptr(q), _dptr(s), _stream()))
+        return q, s
+
+    def clone(self) -> "RoutedExpertWeights":
+        h = C.c_void_p()
+        _check(lib().dsx_expert_store_clone(self._h, C.byref(h), _stream()))
+        return RoutedExpertWeights(self.fmt, self.n_slots, self.hidden, self.ffn, _handle=h)
+
+    @classmethod
+    def from_host(cls, fmt: int, hidden: int, ffn: int, gate, up, down) -> "RoutedExpertWeights":
+        """gate/up/down: (q, s) numpy pairs in the canonical host layout
+        (HF for MXFP4, split for Q8_0), leading dimension = slots."""
+        n = gate[0].shape[0]
+        st = cls(fmt, n, hidden, ffn)
+        layout = SRC_MXFP4_HF if fmt == FMT_MXFP4 else SRC_Q8_0_SPLIT
+        st.load(MAT_GATE, layout, gate[0], gate[1])
+        st.load(MAT_UP, layout, up[0], up[1])
+        st.load(MAT_DOWN, layout, down[0], down[1])
+        return st
+
+
+# --------------------------------------------------------------------------
+class RouterTopk:
+    """Router selection kernel wrapper."""
+
+    def __init__(self, cfg: RouterConfig):
+        self.cfg = cfg
+
+    def logits(self, x_bf16: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
+        T, H = x_bf16.shape
+        E = W.shape[0]
+        assert x_bf16.dtype == torch.bfloat16 and W.dtype == torch.float32 and x_bf16.is_contiguous() and W.is_contiguous()
+        out = torch.empty((T, E), dtype=torch.float32, device=x_bf16.device)
+        _check(lib().dsx_router_logits(_dptr(x_bf16), C.c_int64(T), _dptr(W), E, C.c_int64(H), _dptr(out), _stream()))
+        return out
+
+    def launch_batched(self, logits: torch.Tensor, bias: torch.Tensor | None):
+        T, E = logits.shape
+        assert E == self.cfg.n_expert and logits.dtype == torch.float32 and logits.is_contiguous()
+        sel = torch.empty((T, self.cfg.n_used), dtype=torch.int32, device=logits.device)
+        w = torch.empty((T, self.cfg.n_used), dtype=torch.float32, device=logits.device)
+        rc = _router_struct(self.cfg)
+        _check(lib().dsx_router_topk(_dptr(logits), _dptr(bias), C.c_int64(T), C.byref(rc), _dptr(sel), _dptr(w), _stream()))
+        return sel, w
+
+
+class MoeGroupBuilder:
+    """Histogram / offsets / stable permutation / work items."""
+
+    @staticmethod
+    def launch(selected: torch.Tensor, n_expert: int, chunk: int = 32, with_work_items: bool = True):
+        T, k = selected.shape
+        assert selected.dtype == torch.int32 and selected.is_contiguous()
+        dev = selected.device
+        hist = torch.empty(n_expert, dtype=torch.int32, device=dev)
+        offsets = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
+        perm = torch.full((max(T * k, 1),), -1, dtype=torch.int32, device=dev)
+        items = n_items = None
+        if with_work_items:
+            cap = wi_upper_bound(T * k, n_expert, chunk)
+            items = torch.full((max(cap, 1),), -1, dtype=torch.int32, device=dev)
+            n_items = torch.zeros(1, dtype=torch.int32, device=dev)
+        _check(lib().dsx_moe_group_build(_dptr(selected), C.c_int64(T), k, n_expert, chunk, _dptr(hist), _dptr(offsets),
+                                         _dptr(perm), _dptr(items), _dptr(n_items), _stream()))
+        return hist, offsets, perm, items, n_items
+
+
+# --------------------------------------------------------------------------
+class MoeLayer:
+    """One MoE layer: router weights + routed store + shared store + workspace."""
+
+    def __init__(self, cfg: MoeConfig, routed: RoutedExpertWeights, shared: RoutedExpertWeights | None,
+                 router_w: torch.Tensor, router_bias: torch.Tensor | None, max_tokens: int = 64):
+        assert router_w.is_cuda and router_w.dtype == torch.float32 and router_w.is_contiguous()
+        self.cfg, self.max_tokens = cfg, max_tokens
+        self._keep = (routed, shared, router_w, router_bias)
+        mc = _MoeCfg(cfg.hidden, cfg.ffn, cfg.shared_ffn if shared is not None else 0, max_tokens, cfg.clamp,
+                     _router_struct(cfg.router))
+        h = C.c_void_p()
+        _check(lib().dsx_moe_layer_create(C.byref(h), C.byref(mc), routed._h, shared._h if shared is not None else None,
+                                          _dptr(router_w), _dptr(router_bias)))
+        self._h = h
+
+    def close(self):
+        if self._h:
+            lib().dsx_moe_layer_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_weights(self, routed, shared, router_w, router_bias):
+        _check(lib().dsx_moe_layer_set_weights(self._h, routed._h, shared._h if shared is not None else None,
+                                               _dptr(router_w), _dptr(router_bias)))
+        self._keep = (routed, shared, router_w, router_bias)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        _check(lib().dsx_moe_layer_forward(self._h, _dptr(x), C.c_int64(x.shape[0]), _dptr(out), _dptr(logits), _stream()))
+        return out
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
+        """x_host/out_host: CPU bf16 tensors (pinned for speed).  Synchronous."""
+        assert not x_host.is_cuda and x_host.dtype == torch.bfloat16 and x_host.is_contiguous()
+        _check(lib().dsx_moe_layer_forward_host(self._h, C.c_void_p(x_host.data_ptr()), C.c_int64(x_host.shape[0]),
+                                                C.c_void_p(out_host.data_ptr()), _stream()))
+        return out_host
+
+    def forward_picks(self, x, selected, weights, expert_lo: int = 0, with_shared: bool = True, out=None):
+        assert selected.dtype == torch.int32 and weights.dtype == torch.float32
+        if out is None:
+            out = torch.empty_like(x)
+        _check(lib().dsx_moe_layer_forward_picks(self._h, _dptr(x), C.c_int64(x.shape[0]), _dptr(selected), _dptr(weights),
+                                                 expert_lo, 1 if with_shared else 0, _dptr(out), _stream()))
+        return out
+
+    def routing(self, T: int):
+        """Copies of the last forward's routing: dict of CPU numpy arrays."""
+        ptrs = [C.c_void_p() for _ in range(6)]
+        _check(lib().dsx_moe_layer_routing(self._h, *[C.byref(p) for p in ptrs]))
+        E, k = self.cfg.router.n_expert, self.cfg.router.n_used
+        shapes = {"logits": ((T, E), np.float32), "selected": ((T, k), np.int32), "weights": ((T, k), np.float32),
+                  "hist": ((E,), np.int32), "offsets": ((E + 1,), np.int32), "perm": ((T * k,), np.int32)}
+        torch.cuda.current_stream().synchronize()
+        out = {}
+        for (name, (shape, dt)), p in zip(shapes.items(), ptrs):
+            if not p.value:
+                out[name] = None
+                continue
+            a = np.empty(shape, dt)
+            _check(lib().dsx_memcpy(C.c_void_p(a.ctypes.data), p, C.c_size_t(a.nbytes), 2))
+            out[name] = a
+        return out
+
+    STAGES = ("router_logits", "router_topk", "group_build", "gate_up", "down", "combine")
+
+    def profile(self, enable: bool = True):
+        _check(lib().dsx_moe_layer_profile(self._h, 1 if enable else 0))
+
+    def stage_ms(self) -> dict:
+        """Device time of each stage of the last forward (profiling must be on)."""
+        ms = (C.c_float * len(self.STAGES))()
+        _check(lib().dsx_moe_layer_stage_ms(self._h, ms))
+        return {n: float(v) for n, v in zip(self.STAGES, ms)}
+
+    def check(self) -> int:
+        w = C.c_uint32()
+        _check(lib().dsx_moe_layer_check(self._h, _stream(), C.byref(w)))
+        return w.value
+
+
+def build_layer_from_host(cfg: MoeConfig, weights: dict, max_tokens: int = 64):
+    """weights: the dict of :func:`deepstrix_b200.synth.make_layer`."""
+    routed = RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, weights["gate"], weights["up"], weights["down"])
+    shared = None
+    if cfg.shared_ffn:
+        shared = RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.shared_ffn, weights["shared_gate"],
+                                               weights["shared_up"], weights["shared_down"])
+    rw = torch.from_numpy(weights["router_w"]).cuda()
+    rb = torch.from_numpy(weights["router_bias"]).cuda() if weights.get("router_bias") is not None else None
+    return MoeLayer(cfg, routed, shared, rw, rb, max_tokens=max_tokens)

@@ -1,0 +1,275 @@
+/*
+ * dsx_moe.h -- C ABI of the B200 (sm_100a) routed-MoE path for deepstrix.
+ *
+ * Two groups of entry points, matching the two interfaces the MoE path sits
+ * behind in the reference (paths are relative to the deepstrix repository):
+ *
+ *   1. Device verbs ("v4flash-cuda"): the runtime calls that
+ *      crates/v4flash-hip/src/sys.rs:206-382 declares against libamdhip64 and
+ *      that buffer.rs / stream.rs / event.rs / graph.rs wrap.
+ *   2. MoE operators: what crates/v4flash-kernels/src/{router_topk.rs,
+ *      moe_group_builder.rs, mxfp4_pair.rs, mxfp4.rs, q2_k.rs, mxfp4_repack.rs,
+ *      model_weights.rs} and het/dispatch.rs expose to the engine.
+ *
+ * Conventions: plain pointers and sizes only; every function returns 0 on
+ * success or a negative dsx_status / positive cudaError_t; dsx_last_error()
+ * returns a thread-local message.  No function synchronises the device unless
+ * its comment says so.  All "device" pointers are CUDA device pointers of the
+ * current device; streams are cudaStream_t passed as void*.
+ *
+ * There is no CPU fallback anywhere behind this header.
+ */
+#ifndef DSX_MOE_H
+#define DSX_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSX_API __attribute__((visibility("default")))
+
+typedef void* dsx_stream_t; /* cudaStream_t; NULL = default stream */
+typedef void* dsx_event_t;  /* cudaEvent_t */
+typedef void* dsx_graph_t;  /* cudaGraphExec_t */
+
+enum dsx_status {
+    DSX_OK = 0,
+    DSX_ERR_INVALID = -1,     /* bad argument / size mismatch (launcher-side validation) */
+    DSX_ERR_UNSUPPORTED = -2, /* shape or format outside what the kernels cover */
+    DSX_ERR_DEVICE = -3,      /* a kernel reported a device-side error word (e.g. a bounded wait ran out) */
+    DSX_ERR_NOMEM = -4
+};
+
+/* Thread-local text of the last failure (never NULL).
+ * Replaces HipError{code,name,message,context}, crates/v4flash-hip/src/error.rs:10-78. */
+DSX_API const char* dsx_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * 1. Device verbs
+ * ---------------------------------------------------------------------- */
+
+/* hipGetDeviceCount / hipSetDevice / hipDeviceSynchronize -- sys.rs:206-222, device.rs:41-104 */
+DSX_API int dsx_device_count(int* count);
+DSX_API int dsx_device_set(int device);
+DSX_API int dsx_device_get(int* device);
+DSX_API int dsx_device_sync(void);
+/* hipGetDeviceProperties subset: name (<=255 chars), SM count, total memory, cc major/minor -- device.rs */
+DSX_API int dsx_device_props(int device, char* name256, int* sm_count, size_t* total_mem, int* cc_major, int* cc_minor);
+/* hipDeviceCanAccessPeer / hipDeviceEnablePeerAccess -- sys.rs (peer access) */
+DSX_API int dsx_device_enable_peer(int peer_device);
+
+/* hipMalloc / hipFree / hipMemGetInfo / hipHostMalloc / hipHostFree -- sys.rs, buffer.rs:19-120,450-518 */
+DSX_API int dsx_malloc(void** dptr, size_t bytes);
+DSX_API int dsx_free(void* dptr);
+DSX_API int dsx_mem_get_info(size_t* free_bytes, size_t* total_bytes);
+DSX_API int dsx_host_malloc(void** hptr, size_t bytes); /* pinned */
+DSX_API int dsx_host_free(void* hptr);
+
+/* hipMemcpy / hipMemcpyAsync / hipMemcpyPeerAsync / hipMemset(Async) -- buffer.rs:121-434, het/sync.rs:1-7.
+ * kind: 1 = host->device, 2 = device->host, 3 = device->device.  The blocking forms synchronise. */
+DSX_API int dsx_memcpy(void* dst, const void* src, size_t bytes, int kind);
+DSX_API int dsx_memcpy_async(void* dst, const void* src, size_t bytes, int kind, dsx_stream_t stream);
+DSX_API int dsx_memcpy_peer_async(void* dst, int dst_device, const void* src, int src_device, size_t bytes, dsx_stream_t stream);
+DSX_API int dsx_memset(void* dptr, int value, size_t bytes);
+DSX_API int dsx_memset_async(void* dptr, int value, size_t bytes, dsx_stream_t stream);
+
+/* Stream -- stream.rs:15-173 (create with priority, destroy, synchronize, query, wait_event) */
+DSX_API int dsx_stream_create(dsx_stream_t* stream, int non_blocking, int priority);
+DSX_API int dsx_stream_destroy(dsx_stream_t stream);
+DSX_API int dsx_stream_sync(dsx_stream_t stream);
+DSX_API int dsx_stream_query(dsx_stream_t stream, int* done);
+DSX_API int dsx_stream_wait_event(dsx_stream_t stream, dsx_event_t event);
+
+/* Event -- event.rs (create, record, synchronize, query, elapsed ms) */
+DSX_API int dsx_event_create(dsx_event_t* event, int timing);
+DSX_API int dsx_event_destroy(dsx_event_t event);
+DSX_API int dsx_event_record(dsx_event_t event, dsx_stream_t stream);
+DSX_API int dsx_event_sync(dsx_event_t event);
+DSX_API int dsx_event_query(dsx_event_t event, int* done);
+DSX_API int dsx_event_elapsed_ms(dsx_event_t start, dsx_event_t stop, float* ms);
+
+/* Stream capture -> executable graph -- graph.rs:36-127 (begin/end capture, instantiate, launch) */
+DSX_API int dsx_graph_begin_capture(dsx_stream_t stream);
+DSX_API int dsx_graph_end_capture(dsx_stream_t stream, dsx_graph_t* graph_exec);
+DSX_API int dsx_graph_launch(dsx_graph_t graph_exec, dsx_stream_t stream);
+DSX_API int dsx_graph_destroy(dsx_graph_t graph_exec);
+
+/* ------------------------------------------------------------------------
+ * 2. MoE operators
+ * ---------------------------------------------------------------------- */
+
+enum dsx_weight_fmt {
+    DSX_FMT_MXFP4 = 0, /* E2M1 codes + E8M0 scale per 32 (src/mxfp4_tables.rs) */
+    DSX_FMT_Q8_0 = 1   /* int8 + f16 scale per 32 (kernels/q8_0_matvec.hip:5-16) */
+};
+
+/* Source layouts accepted by dsx_expert_store_load (the loader's job,
+ * v4flash-core/src/weight_src.rs:75-98 and hf_v41.rs:1150-1233). */
+enum dsx_src_layout {
+    DSX_SRC_MXFP4_HF = 0,   /* q: [rows, K/2] bytes, element 2i = low nibble; s: [rows, K/32] E8M0 (2^(e-127)) */
+    DSX_SRC_MXFP4_GGML = 1, /* q: [rows, K/32] blocks of 17 B `e | qs[16]`; s unused */
+    DSX_SRC_MXFP4_SB2 = 2,  /* q: [rows, K/256] super-blocks of 136 B (mxfp4_tables.rs:10-35); s unused */
+    DSX_SRC_Q8_0_BLOCKS = 3,/* q: [rows, K/32] blocks of 34 B `f16 d | i8[32]`; s unused */
+    DSX_SRC_Q8_0_SPLIT = 4  /* q: int8 [rows, K]; s: f16 [rows, K/32] (src/weights.rs:215-240 per-row split) */
+};
+
+enum dsx_matrix_kind { DSX_MAT_GATE = 0, DSX_MAT_UP = 1, DSX_MAT_DOWN = 2 };
+
+enum dsx_score_fn {
+    DSX_SCORE_SQRT_SOFTPLUS = 0, /* kernels/router_topk.hip:32-36,71 */
+    DSX_SCORE_SIGMOID = 1        /* kernels/laguna_ops.hip:59 */
+};
+
+/* bytes_per_expert(dtype, k, rows): rows*(k/32)*17 for MXFP4, rows*(k/32)*34 for Q8_0
+ * -- crates/v4flash-kernels/src/weight_contract.rs:146,363-366. */
+DSX_API int dsx_bytes_per_expert(int fmt, int64_t k, int64_t rows, size_t* bytes);
+
+/* --- Expert store: RoutedExpertWeights (src/model_weights.rs:41-52) ------
+ * n_slots experts, each with gate [ffn, hidden], up [ffn, hidden] and
+ * down [hidden, ffn], kept in HBM in this library's tile layout (16-row x
+ * 64-column tiles for MXFP4, 16 x 32 for Q8_0; gate and up tiles interleaved
+ * so one stream feeds the fused gate/up kernel).  Same byte count as the
+ * reference (17 or 34 bytes per 32 weights). */
+typedef struct dsx_expert_store dsx_expert_store;
+
+DSX_API int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int64_t hidden, int64_t ffn);
+DSX_API int dsx_expert_store_destroy(dsx_expert_store* store);
+/* Repack one matrix of one slot from a source layout into the tile layout
+ * (the role of mxfp4_repack_hf_to_ggml, kernels/mxfp4_repack.hip:35-65 and
+ * load_experts_packed, het/weights.rs:1014-1203).  q/s are DEVICE pointers when
+ * src_on_device != 0, host pointers otherwise (then the call stages them through
+ * an internal device buffer and synchronises the stream). */
+DSX_API int dsx_expert_store_load(dsx_expert_store* store, int slot, int which, int src_layout,
+                                  const void* q, const void* s, int src_on_device, dsx_stream_t stream);
+/* Inverse of the repack, for bit-parity tests: writes HF layout (MXFP4) or the
+ * split layout (Q8_0) to DEVICE buffers q_out/s_out. */
+DSX_API int dsx_expert_store_unpack(const dsx_expert_store* store, int slot, int which,
+                                    void* q_out, void* s_out, dsx_stream_t stream);
+/* Device-to-device clone of every plane (used to keep several layers resident). */
+DSX_API int dsx_expert_store_clone(const dsx_expert_store* src, dsx_expert_store** dst, dsx_stream_t stream);
+DSX_API int dsx_expert_store_info(const dsx_expert_store* store, int* fmt, int* n_slots, int64_t* hidden,
+                                  int64_t* ffn, size_t* device_bytes);
+
+/* --- Router --------------------------------------------------------------
+ * logits[T,E] = x[T,H] (bf16) . W[E,H]^T (f32), f32 accumulate in an order
+ * that does not depend on T (F16Matvec::matvec / matvec_batched_router,
+ * kernels/f16_matvec.hip:26-45; het/forward_prefill.rs:8951-8973). */
+DSX_API int dsx_router_logits(const void* x_bf16, int64_t T, const float* W, int n_expert, int64_t hidden,
+                              float* logits, dsx_stream_t stream);
+
+typedef struct {
+    int32_t n_expert;    /* <= 512, multiple of 32 */
+    int32_t n_used;      /* <= 16 (ROUTER_MAX_USED is 8 in router_topk_par.hip:14-22) */
+    int32_t n_group;     /* <=1: no group limit (the reference); else experts split into contiguous groups */
+    int32_t topk_group;  /* groups kept when n_group > 1 */
+    int32_t score_fn;    /* dsx_score_fn */
+    float route_scale;   /* expert_weight_scale */
+    float weight_eps;    /* 6.103515625e-5 in het/forward_layer.rs:36 */
+} dsx_router_config;
+
+/* RouterTopk::launch_batched (src/router_topk.rs:245-364; kernels
+ * router_topk_par.hip:66-238): p = f(logit); s = p + bias; k argmax passes,
+ * equal scores -> lower index; w_j = p[sel_j] / max(sum, eps) * scale.
+ * bias may be NULL.  selected: int32 [T, n_used] in rank order; weights f32. */
+DSX_API int dsx_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg,
+                            int32_t* selected, float* weights, dsx_stream_t stream);
+
+/* --- Histogram / permute / work items ------------------------------------
+ * MoeGroupBuilder::launch + launch_work_items_split (src/moe_group_builder.rs:72-259;
+ * kernels/moe_group_builder.hip:32-51, moe_work_items_builder.hip:61-145) with the
+ * deterministic member order of b2_moe_group_wi_builder (kernels/b2_fast_chain.hip:94-105):
+ *   hist[e]      picks of expert e (ids < 0 or >= n_expert are dropped)
+ *   offsets[e]   exclusive prefix sum, n_expert+1 entries
+ *   perm[offsets[e]+pos] = t*n_used+s, ascending inside each expert
+ *   work_items[i] = (e << 16) | member_start, ceil(hist[e]/chunk) per expert,
+ *                   sorted by expert; n_work_items[0] = their count
+ * work_items needs room for dsx_wi_upper_bound(...) entries.  Limits as in
+ * moe_group_builder.rs:18-31: T and every member_start must stay below 65536
+ * for the packed work items (larger T: pass work_items = NULL). */
+DSX_API int dsx_moe_group_build(const int32_t* selected, int64_t T, int n_used, int n_expert, int chunk,
+                                int32_t* hist, int32_t* offsets, int32_t* perm,
+                                int32_t* work_items, int32_t* n_work_items, dsx_stream_t stream);
+/* moe_wi_upper_bound, het/dispatch.rs:444-454 */
+DSX_API uint32_t dsx_wi_upper_bound(uint64_t members, uint32_t groups, uint32_t chunk, uint64_t cap);
+
+/* --- Whole layer ---------------------------------------------------------
+ * One call = router GEMV -> top-k -> histogram/permute -> grouped gate/up +
+ * clamp + SwiGLU + routing weight -> grouped down -> slot-order combine (+
+ * shared expert).  The template in the reference is MtpState::moe
+ * (het/mtp.rs:1606-1730) / MoeExecutor::run (het/remote_experts.rs:7428-7442). */
+typedef struct {
+    int32_t hidden;       /* multiple of 256 */
+    int32_t ffn;          /* routed expert width, multiple of 256 */
+    int32_t shared_ffn;   /* 0 = no shared expert */
+    int32_t max_tokens;   /* workspace is sized for this many tokens per call */
+    float clamp;          /* SwiGLU clamp (10.0 in config.rs:104); <= 1e-6 disables */
+    dsx_router_config router;
+} dsx_moe_config;
+
+typedef struct dsx_moe_layer dsx_moe_layer;
+
+/* routed: store with n_expert slots.  shared: store with 1 slot (or NULL).
+ * router_w: DEVICE f32 [n_expert, hidden]; router_bias: DEVICE f32 [n_expert] or NULL.
+ * The layer borrows all four (they must outlive it) and owns its workspace. */
+DSX_API int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg,
+                                 const dsx_expert_store* routed, const dsx_expert_store* shared,
+                                 const float* router_w, const float* router_bias);
+DSX_API int dsx_moe_layer_destroy(dsx_moe_layer* layer);
+/* Re-point an existing layer (and its workspace) at another set of weights. */
+DSX_API int dsx_moe_layer_set_weights(dsx_moe_layer* layer, const dsx_expert_store* routed,
+                                      const dsx_expert_store* shared, const float* router_w, const float* router_bias);
+
+/* x, out: DEVICE bf16 [T, hidden].  logits_in: optional DEVICE f32 [T, n_expert];
+ * when given the router GEMV is skipped and these logits drive the routing
+ * (the "pinned routing" of het/fidelity_tap.rs).  Asynchronous on `stream`. */
+DSX_API int dsx_moe_layer_forward(dsx_moe_layer* layer, const void* x_bf16, int64_t T, void* out_bf16,
+                                  const float* logits_in, dsx_stream_t stream);
+/* Same, with HOST buffers: copies x in, runs, copies out back, synchronises. */
+DSX_API int dsx_moe_layer_forward_host(dsx_moe_layer* layer, const void* x_bf16_host, int64_t T,
+                                       void* out_bf16_host, dsx_stream_t stream);
+
+/* Expert-parallel form (what an owner of a subset of experts computes,
+ * docs/v41/REMOTE_EXPERTS.md:204-229): the caller supplies the picks and
+ * weights (ids outside [expert_lo, expert_lo + store slots) are skipped, as
+ * NO_PICK is), and receives the weighted partial sum per token; with_shared
+ * adds the shared expert. */
+DSX_API int dsx_moe_layer_forward_picks(dsx_moe_layer* layer, const void* x_bf16, int64_t T,
+                                        const int32_t* selected, const float* weights, int expert_lo,
+                                        int with_shared, void* out_bf16, dsx_stream_t stream);
+
+/* Device pointers into the layer's workspace holding the routing of the last
+ * forward (valid until the next call): logits f32 [T,E], selected i32 [T,k],
+ * weights f32 [T,k], hist i32 [E], offsets i32 [E+1], perm i32 [T*k].
+ * Any output pointer may be NULL. */
+DSX_API int dsx_moe_layer_routing(const dsx_moe_layer* layer, const float** logits, const int32_t** selected,
+                                  const float** weights, const int32_t** hist, const int32_t** offsets,
+                                  const int32_t** perm);
+/* Reads (and clears) the device-side error word of the layer; synchronises
+ * the stream.  Non-zero means a bounded wait inside a kernel ran out. */
+DSX_API int dsx_moe_layer_check(dsx_moe_layer* layer, dsx_stream_t stream, uint32_t* error_word);
+/* Per-stage device timing, the counterpart of EventPool::stage(name, stream)
+ * (het/trace.rs:1-22): with profiling on, every forward brackets each stage with
+ * a CUDA event pair on the caller's stream; dsx_moe_layer_stage_ms waits for the
+ * last forward and returns DSX_STAGE_COUNT durations in ms (-1 = stage not run). */
+enum dsx_stage {
+    DSX_STAGE_ROUTER_LOGITS = 0, /* "dgpu.router" */
+    DSX_STAGE_ROUTER_TOPK = 1,   /* "k.router.topk" */
+    DSX_STAGE_GROUP_BUILD = 2,
+    DSX_STAGE_GATE_UP = 3,       /* "igpu.pair_*" */
+    DSX_STAGE_DOWN = 4,          /* "igpu.q2k_down" */
+    DSX_STAGE_COMBINE = 5,
+    DSX_STAGE_COUNT = 6
+};
+DSX_API int dsx_moe_layer_profile(dsx_moe_layer* layer, int enable);
+DSX_API int dsx_moe_layer_stage_ms(dsx_moe_layer* layer, float* ms);
+/* Kernel launches issued by this library on the calling thread since the last
+ * reset (per-thread launch audit, crates/v4flash-hip/src/module.rs:97-131). */
+DSX_API uint64_t dsx_launch_count(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSX_MOE_H */

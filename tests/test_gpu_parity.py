@@ -1,0 +1,245 @@
+"""GPU parity: every kernel through the C ABI against the CPU oracle.
+
+Integer / index results must match bit for bit; layer outputs within
+rel-L2 <= 1e-2 of the dequantised-f32 oracle (the tolerance the workload
+definition states for bf16 activations)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-2
+
+
+def rel_l2(a, b):
+    a = a.astype(np.float64)
+    b = b.astype(np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    return torch
+
+
+@pytest.fixture(scope="module")
+def moe():
+    from deepstrix_b200 import moe as m
+    m.lib()
+    return m
+
+
+# ------------------------------------------------------------------ repack
+@pytest.mark.parametrize("layout", ["hf", "ggml", "sb2"])
+def test_repack_mxfp4_roundtrip_bitexact(torch_cuda, moe, oracle, layout):
+    torch = torch_cuda
+    rng = np.random.default_rng(1)
+    H, F, n = 512, 256, 3
+    st = moe.RoutedExpertWeights(0, n, H, F)
+    src = {}
+    for which, (rows, k) in {moe.MAT_GATE: (F, H), moe.MAT_UP: (F, H), moe.MAT_DOWN: (H, F)}.items():
+        q = rng.integers(0, 256, (n, rows, k // 2), dtype=np.uint8)
+        s = rng.integers(0, 255, (n, rows, k // 32), dtype=np.uint8)
+        src[which] = (q, s)
+        if layout == "hf":
+            st.load(which, moe.SRC_MXFP4_HF, q, s)
+        else:
+            sb2 = np.stack([oracle.mxfp4_repack_hf_to_sb2(q[i], s[i]) for i in range(n)])
+            if layout == "sb2":
+                st.load(which, moe.SRC_MXFP4_SB2, sb2)
+            else:  # ggml 17-byte blocks from the super-block bytes
+                sb = sb2.reshape(n, rows, k // 256, 136)
+                blocks = np.concatenate([sb[..., 128:136, None], sb[..., :128].reshape(n, rows, k // 256, 8, 16)], axis=-1)
+                # same thing from device memory, one slot at a time
+                for i in range(n):
+                    st.load(which, moe.SRC_MXFP4_GGML, torch.from_numpy(np.ascontiguousarray(blocks[i])).cuda(), None, slot=i)
+    for which, (q, s) in src.items():
+        for i in range(n):
+            uq, us = st.unpack(i, which)
+            assert np.array_equal(uq.cpu().numpy(), q[i]) and np.array_equal(us.cpu().numpy(), s[i])
+
+
+def test_repack_q8_0_roundtrip_bitexact(torch_cuda, moe):
+    rng = np.random.default_rng(2)
+    H, F = 512, 256
+    st = moe.RoutedExpertWeights(1, 2, H, F)
+    for which, (rows, k) in {moe.MAT_GATE: (F, H), moe.MAT_UP: (F, H), moe.MAT_DOWN: (H, F)}.items():
+        q = rng.integers(-128, 128, (2, rows, k), dtype=np.int8)
+        s = rng.uniform(1e-3, 1e-2, (2, rows, k // 32)).astype(np.float16)
+        blocks = np.concatenate([s.view(np.uint8).reshape(2, rows, k // 32, 2), q.view(np.uint8).reshape(2, rows, k // 32, 32)], -1)
+        st.load(which, moe.SRC_Q8_0_SPLIT, q[0:1], s[0:1], slot=0)
+        st.load(which, moe.SRC_Q8_0_BLOCKS, np.ascontiguousarray(blocks[1:2]), None, slot=1)
+        for i in range(2):
+            uq, us = st.unpack(i, which)
+            assert np.array_equal(uq.cpu().numpy(), q[i]) and np.array_equal(us.cpu().numpy().view(np.uint16), s[i].view(np.uint16))
+
+
+# ------------------------------------------------------------------ router
+@pytest.mark.parametrize("E,k,n_group,topk_group,score_fn", [
+    (256, 8, 8, 4, 1), (256, 6, 1, 1, 0), (64, 6, 8, 4, 1), (384, 6, 1, 1, 0), (256, 10, 1, 1, 1), (128, 3, 4, 2, 1), (512, 8, 16, 4, 0)])
+def test_router_topk_bitexact(torch_cuda, moe, oracle, E, k, n_group, topk_group, score_fn):
+    torch = torch_cuda
+    from deepstrix_b200.config import RouterConfig
+    rng = np.random.default_rng(E + k)
+    T = 333
+    logits = (rng.standard_normal((T, E)) * 1.5).astype(np.float32)
+    logits[0] = 0.0                       # all equal -> lowest indices
+    logits[1, : E // 2] = 0.25            # two plateaus
+    logits[1, E // 2:] = -0.25
+    logits[2] = np.round(logits[2], 1)    # many exact ties
+    logits[3] = 30.0
+    logits[4] = -30.0
+    logits[5, ::2] = 25.0
+    bias = (rng.standard_normal(E) * 0.01).astype(np.float32)
+    cfg = RouterConfig(n_expert=E, n_used=k, n_group=n_group, topk_group=topk_group, score_fn=score_fn, route_scale=2.5)
+    r = moe.RouterTopk(cfg)
+    for b in (bias, None):
+        sel, w = r.launch_batched(torch.from_numpy(logits).cuda(), None if b is None else torch.from_numpy(b).cuda())
+        osel, ow = oracle.router_topk(logits, b, k, n_group, topk_group, score_fn, 2.5)
+        assert np.array_equal(sel.cpu().numpy(), osel)
+        assert np.array_equal(w.cpu().numpy().view(np.uint32), ow.view(np.uint32))
+
+
+def test_router_logits_close_and_batch_invariant(torch_cuda, moe, oracle):
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS
+    cfg = CONFIGS[1]
+    rng = np.random.default_rng(4)
+    W = rng.normal(0, 0.02, (256, 4096)).astype(np.float32)
+    xb = synth.make_tokens(cfg, 1, 37)
+    r = moe.RouterTopk(cfg.router)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    Wd = torch.from_numpy(W).cuda()
+    lg = r.logits(x, Wd).cpu().numpy()
+    ref = oracle.router_logits(synth.bf16_bits_to_f32(xb), W)
+    assert np.abs(lg - ref).max() < 2e-5
+    # the same token gives the same bits alone and inside a batch
+    one = r.logits(x[17:18].contiguous(), Wd).cpu().numpy()
+    assert np.array_equal(one[0].view(np.uint32), lg[17].view(np.uint32))
+
+
+# ------------------------------------------------------------------ groups
+@pytest.mark.parametrize("T,k,E,chunk", [(1, 8, 256, 8), (16, 6, 64, 8), (64, 8, 256, 8), (300, 8, 256, 32), (2048, 8, 256, 128), (5000, 6, 384, 32)])
+def test_group_build_bitexact(torch_cuda, moe, oracle, T, k, E, chunk):
+    torch = torch_cuda
+    rng = np.random.default_rng(T)
+    sel = np.stack([rng.choice(E, k, replace=False) for _ in range(T)]).astype(np.int32)
+    if T > 4:
+        sel[1, 0] = -1
+        sel[3, k - 1] = E + 5
+        sel[2, :] = sel[2, 0]  # a repeated id (not produced by the router, but the builder must count it)
+    hist, offs, perm, items, n_items = moe.MoeGroupBuilder.launch(torch.from_numpy(sel).cuda(), E, chunk)
+    oh, oo, op = oracle.group_build(sel, E)
+    assert np.array_equal(hist.cpu().numpy(), oh)
+    assert np.array_equal(offs.cpu().numpy(), oo)
+    assert np.array_equal(perm.cpu().numpy()[: op.size], op)
+    oi, on = oracle.work_items(oh, chunk)
+    assert int(n_items.item()) == on
+    assert np.array_equal(items.cpu().numpy()[:on], oi)
+
+
+# ------------------------------------------------------------------- layer
+def _layer_case(torch, moe, oracle, cfg, config_id, T, pin_logits=False, max_tokens=None):
+    from deepstrix_b200 import synth
+    w = synth.make_layer(cfg, config_id)
+    layer = moe.build_layer_from_host(cfg, w, max_tokens=max_tokens or max(T, 1))
+    xb = synth.make_tokens(cfg, config_id, T)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    out = layer.forward(x)
+    assert layer.check() == 0
+    routing = layer.routing(T)
+    out = out.float().cpu().numpy()
+    r = cfg.router
+    # routing must be bit-exact given the same logits
+    osel, ow = oracle.router_topk(routing["logits"], w["router_bias"], r.n_used, r.n_group, r.topk_group, r.score_fn, r.route_scale, r.weight_eps)
+    assert np.array_equal(routing["selected"], osel)
+    assert np.array_equal(routing["weights"].view(np.uint32), ow.view(np.uint32))
+    oh, oo, op = oracle.group_build(osel, r.n_expert)
+    assert np.array_equal(routing["hist"], oh) and np.array_equal(routing["offsets"], oo) and np.array_equal(routing["perm"], op)
+    ref_logits = oracle.router_logits(synth.bf16_bits_to_f32(xb), w["router_w"])
+    assert np.abs(routing["logits"] - ref_logits).max() < 5e-5
+    shared = ((w["shared_gate"][0][0], w["shared_gate"][1][0]), (w["shared_up"][0][0], w["shared_up"][1][0]),
+              (w["shared_down"][0][0], w["shared_down"][1][0])) if cfg.shared_ffn else None
+    ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), osel, ow, w["gate"], w["up"], w["down"], shared=shared,
+                               clamp=cfg.clamp, mid_round=0, n_expert=r.n_expert)
+    return out, ref, layer, w, x, routing
+
+
+def test_layer_config0_small(torch_cuda, moe, oracle):
+    from deepstrix_b200.config import CONFIGS
+    out, ref, *_ = _layer_case(torch_cuda, moe, oracle, CONFIGS[0], 0, 16)
+    err = rel_l2(out, ref)
+    assert err <= REL_L2_TOL, err
+    assert err < 6e-3  # bf16 output rounding alone is ~2e-3
+
+
+@pytest.mark.parametrize("T", [1, 8, 32, 64])
+def test_layer_config1_decode(torch_cuda, moe, oracle, T):
+    from deepstrix_b200.config import CONFIGS
+    out, ref, layer, w, x, routing = _layer_case(torch_cuda, moe, oracle, CONFIGS[1], 1, T, max_tokens=64)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+    # a token's result does not depend on its batch: token 0 alone gives the same bits
+    if T > 1:
+        alone = layer.forward(x[0:1].contiguous()).float().cpu().numpy()
+        assert np.array_equal(alone[0], out[0])
+
+
+def test_layer_q8_0_small(torch_cuda, moe, oracle):
+    from deepstrix_b200.config import CONFIGS, FMT_Q8_0
+    cfg = CONFIGS[0].with_(fmt=FMT_Q8_0)
+    out, ref, *_ = _layer_case(torch_cuda, moe, oracle, cfg, 3, 24)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+
+
+def test_layer_many_tokens_per_expert_and_no_shared(torch_cuda, moe, oracle):
+    from deepstrix_b200.config import MoeConfig, RouterConfig
+    cfg = MoeConfig(hidden=512, ffn=256, shared_ffn=0, router=RouterConfig(n_expert=32, n_used=4, n_group=1, topk_group=1, score_fn=0, route_scale=1.5))
+    out, ref, *_ = _layer_case(torch_cuda, moe, oracle, cfg, 0, 200)   # 25 tokens per expert on average: several items per expert
+    assert rel_l2(out, ref) <= REL_L2_TOL
+
+
+def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
+    """Owner-of-a-subset form: two half stores, each returning its weighted partial
+    sum, add up to the full layer (the reference's het-split property,
+    tests/mxfp4_pair_oracle.rs:198-241)."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS
+    cfg = CONFIGS[0]
+    E = cfg.router.n_expert
+    w = synth.make_layer(cfg, 0)
+    full = moe.build_layer_from_host(cfg, w, max_tokens=16)
+    xb = synth.make_tokens(cfg, 0, 16)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    out_full = full.forward(x).float().cpu().numpy()
+    r = full.routing(16)
+    sel = torch.from_numpy(r["selected"]).cuda()
+    wt = torch.from_numpy(r["weights"]).cuda()
+    rw = torch.from_numpy(w["router_w"]).cuda()
+    acc = np.zeros_like(out_full)
+    for lo in (0, E // 2):
+        sl = slice(lo, lo + E // 2)
+        half = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, tuple(a[sl] for a in w["gate"]),
+                                                 tuple(a[sl] for a in w["up"]), tuple(a[sl] for a in w["down"]))
+        shared = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
+        layer = moe.MoeLayer(cfg, half, shared, rw, None, max_tokens=16)
+        acc += layer.forward_picks(x, sel, wt, expert_lo=lo, with_shared=(lo == 0)).float().cpu().numpy()
+        assert layer.check() == 0
+    assert rel_l2(acc, out_full) < 8e-3   # three bf16 roundings instead of one
+
+
+def test_launcher_validation(torch_cuda, moe):
+    torch = torch_cuda
+    from deepstrix_b200.config import RouterConfig
+    with pytest.raises(moe.DsxError):
+        moe.RoutedExpertWeights(0, 2, 500, 256)          # hidden not a multiple of 256
+    r = moe.RouterTopk(RouterConfig(n_expert=250, n_used=8, n_group=1, topk_group=1))
+    with pytest.raises(moe.DsxError):
+        r.launch_batched(torch.zeros((2, 250), device="cuda"), None)
+    st = moe.RoutedExpertWeights(0, 1, 256, 256)
+    with pytest.raises(moe.DsxError):
+        st.load(moe.MAT_GATE, moe.SRC_Q8_0_SPLIT, np.zeros((256, 256), np.int8), np.zeros((256, 8), np.float16), slot=0)
