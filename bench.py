@@ -208,8 +208,23 @@ def run_single_gpu(args):
             ds.append(int((layer.routing(T)["hist"] > 0).sum()))
         return ds
 
+    def stage_breakdown(T, xs, outs, n):
+        layer.profile(True)
+        acc = {}
+        with torch.cuda.stream(stream):
+            for i in range(n + 2):
+                j = i % len(stores)
+                layer.set_weights(stores[j], shared[j], rw, rb)
+                layer.forward(xs[i % len(xs)], out=outs[i % len(outs)])
+                st = layer.stage_ms()
+                if i >= 2:
+                    for n_, v in st.items():
+                        acc.setdefault(n_, []).append(v)
+        layer.profile(False)
+        return {n_: round(sum(v) / len(v) * 1e3, 2) for n_, v in acc.items()}
+
     results = {}
-    for T in sorted(set([1, 8, 32, 64] + [args.tokens])):
+    for T in sorted(set(([] if args.no_series else [1, 8, 32, 64]) + [args.tokens])):
         xs, outs = batches(T)
         steps = args.steps if T == args.tokens else max(10, args.steps // 2)
         t_wall0 = time.time()
@@ -223,6 +238,7 @@ def run_single_gpu(args):
                       "distinct_experts": d_mean, "layer_bytes": layer_bytes,
                       "layer_gbs": layer_bytes / (ms / steps * 1e-3) / 1e9, "wall": (t_wall0, t_wall1)}
         results[T]["layer_frac_of_hbm_peak"] = results[T]["layer_gbs"] / hbm_peak
+        results[T]["stage_us"] = stage_breakdown(T, xs, outs, 6)
     T = args.tokens
     head = results[T]
 
@@ -278,14 +294,15 @@ def run_single_gpu(args):
     from oracle import oracle
     oracle.build()
     xs_cpu = synth.bf16_bits_to_f32(synth.make_tokens(cfg, 1, args.ref_tokens, stream=7))
-    oracle_step(oracle, cfg, w, xs_cpu[:1])
-    t0 = time.perf_counter()
-    n_rep = 0
-    while time.perf_counter() - t0 < 10.0 and n_rep < 8:
-        oracle_step(oracle, cfg, w, xs_cpu)
-        n_rep += 1
-    cpu_dt = time.perf_counter() - t0
-    cpu_value = args.ref_tokens * n_rep / cpu_dt
+    n_rep, cpu_value = 0, None
+    if not args.skip_cpu:
+        oracle_step(oracle, cfg, w, xs_cpu[:1])
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < 10.0 and n_rep < 8:
+            oracle_step(oracle, cfg, w, xs_cpu)
+            n_rep += 1
+        cpu_dt = time.perf_counter() - t0
+        cpu_value = args.ref_tokens * n_rep / cpu_dt
 
     series = [{kk: vv for kk, vv in r.items() if kk != "wall"} for _, r in sorted(results.items())]
     line = {
@@ -321,6 +338,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=64, help="decode batch size of the headline number")
     ap.add_argument("--layers", type=int, default=6, help="resident copies of the layer weights to rotate over")
     ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per CPU-oracle sample step")
+    ap.add_argument("--no-series", action="store_true", help="time only the headline batch size")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU-baseline leg (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -47,12 +47,14 @@ void count_launch();
 //
 // Lane l = 4*g + t of the warp owns bytes [16*l, 16*l+16) of a sub-tile.
 // MXFP4 word s (s = 0..3, one per k16 step), column base c = 32*(s>>1) + 8*t + 4*(s&1):
-//   byte0 = code(row g  , c+0) | code(row g  , c+2) << 4
-//   byte1 = code(row g  , c+1) | code(row g  , c+3) << 4
-//   byte2 = code(row g+8, c+0) | code(row g+8, c+2) << 4
-//   byte3 = code(row g+8, c+1) | code(row g+8, c+3) << 4
-// so both 32-column scale blocks of the sub-tile map to two consecutive mma
-// steps, and lane t reads 8 consecutive activation values per scale block.
+//   byte0 = code(row g  , c+0) | code(row g  , c+1) << 4
+//   byte1 = code(row g+8, c+0) | code(row g+8, c+1) << 4
+//   byte2 = code(row g  , c+2) | code(row g  , c+3) << 4
+//   byte3 = code(row g+8, c+2) | code(row g+8, c+3) << 4
+// i.e. byte i converts (cvt.rn.f16x2.e2m1x2) straight into A-fragment register
+// a_i of mma.m16n8k16.  Both 32-column scale blocks of the sub-tile map to two
+// consecutive mma steps, and lane t reads 8 consecutive activation values per
+// scale block.
 // MXFP4 scales: bytes [4*g, 4*g+4) = {row g blk0, row g blk1, row g+8 blk0, row g+8 blk1}.
 // Q8_0 word 2*s + h (s = k16 step, h = 0: row g, 1: row g+8): columns 8*t + 4*s + {0,1,2,3}.
 // Q8_0 scales: halves [2*g, 2*g+2) = {row g, row g+8}.

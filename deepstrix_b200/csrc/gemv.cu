@@ -15,8 +15,7 @@
 // mbarrier complete_tx), so each SM keeps ~140 KB of HBM reads in flight
 // without spending registers on it, and every weight byte is read exactly once
 // per item.  Lanes then read their 16 bytes per sub-tile from the ring, expand
-// the 4-bit codes (or int8) to f16 with two shifts, two masks and byte permutes,
-// and feed mma.sync.m16n8k16 with the item's (<= 8) tokens as the n dimension;
+// the 4-bit codes to f16 with the hardware converter (int8: byte permutes), and feed mma.sync.m16n8k16 with the item's (<= 8) tokens as the n dimension;
 // the E8M0 / f16 block scale multiplies the f32 result of each 32-column block.
 // Token columns are independent in the mma, so a token's result does not
 // depend on which other tokens share its item.
@@ -72,22 +71,34 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Eight E2M1 codes -> the four f16x2 A-fragment registers of one k16 step.
-// A code `s e1 e0 m` placed at bits 15, 11..9 of an f16 is the E2M1 value times
-// 2^-14 (subnormal codes included), and those four bits sit in the f16's HIGH
-// byte only: build the high bytes of four codes at once with shifts and masks,
-// then spread them to half words with byte permutes.  The 2^14 is folded into
-// the block scale.
-__device__ __forceinline__ void mxfp4_frag(uint32_t q, uint32_t (&a)[4]) {
-    const uint32_t lo = ((q << 4) & 0x80808080u) | ((q << 1) & 0x0E0E0E0Eu);
-    const uint32_t hi = (q & 0x80808080u) | ((q >> 3) & 0x0E0E0E0Eu);
-    a[0] = __byte_perm(lo, 0u, 0x1404);
-    a[1] = __byte_perm(lo, 0u, 0x3424);
-    a[2] = __byte_perm(hi, 0u, 0x1404);
-    a[3] = __byte_perm(hi, 0u, 0x3424);
+// Same with a zero accumulator input (first step of a scale block).
+__device__ __forceinline__ void mma16816_zero(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
-// E8M0 byte e -> 2^(e-127) * 2^14 as f32 (exact for e <= 240).
-__device__ __forceinline__ float mxfp4_scale(uint32_t e) { return __uint_as_float(min(e + 14u, 255u) << 23); }
+
+// Eight E2M1 codes -> the four f16x2 A-fragment registers of one k16 step: byte i
+// of the word holds the two codes of register a_i, and the hardware converter
+// (cvt.rn.f16x2.e2m1x2) expands a byte to two exact f16 values in one instruction.
+__device__ __forceinline__ void mxfp4_frag(uint32_t q, uint32_t (&a)[4]) {
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+        : "r"(q));
+}
+// E8M0 byte number `b` of the packed scale word -> 2^(e-127) as f32 (mask, then
+// shift into the exponent field; e = 0 gives 0 instead of the denormal 2^-127).
+template <int B>
+__device__ __forceinline__ float mxfp4_scale(uint32_t sw) {
+    if (B == 3) return __uint_as_float((sw >> 1) & 0x7F800000u);
+    return __uint_as_float((sw & (0xFFu << (8 * B))) << (23 - 8 * B));
+}
 
 // Four offset-binary int8 (value ^ 0x80) -> two f16x2: 0x6400 | u is 1024 + u.
 __device__ __forceinline__ uint32_t q8_pair(uint32_t w, uint32_t sel) {
@@ -102,29 +113,37 @@ __device__ __forceinline__ void compute_subtile(const uint8_t* nibp, const uint8
     const uint4 wq = *reinterpret_cast<const uint4*>(nibp + lane * 16);
     const uint32_t sw = *reinterpret_cast<const uint32_t*>(scp + (lane >> 2) * 4);
     if (FMT == DSX_FMT_MXFP4) {
-        const uint32_t w[4] = {wq.x, wq.y, wq.z, wq.w};
-#pragma unroll
-        for (int b = 0; b < 2; b++) {
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t a[4];
-            mxfp4_frag(w[2 * b], a);
-            mma16816(c, a, bf[b].x, bf[b].y);
-            mxfp4_frag(w[2 * b + 1], a);
-            mma16816(c, a, bf[b].z, bf[b].w);
-            const float s0 = mxfp4_scale((sw >> (8 * b)) & 0xFFu), s1 = mxfp4_scale((sw >> (16 + 8 * b)) & 0xFFu);
-            acc[0] = fmaf(s0, c[0], acc[0]);
-            acc[1] = fmaf(s0, c[1], acc[1]);
-            acc[2] = fmaf(s1, c[2], acc[2]);
-            acc[3] = fmaf(s1, c[3], acc[3]);
-        }
+        uint32_t a[4];
+        float c[4];
+        // block 0: k16 steps 0 and 1
+        mxfp4_frag(wq.x, a);
+        mma16816_zero(c, a, bf[0].x, bf[0].y);
+        mxfp4_frag(wq.y, a);
+        mma16816(c, a, bf[0].z, bf[0].w);
+        float s0 = mxfp4_scale<0>(sw), s1 = mxfp4_scale<2>(sw);
+        acc[0] = fmaf(s0, c[0], acc[0]);
+        acc[1] = fmaf(s0, c[1], acc[1]);
+        acc[2] = fmaf(s1, c[2], acc[2]);
+        acc[3] = fmaf(s1, c[3], acc[3]);
+        // block 1: k16 steps 2 and 3
+        mxfp4_frag(wq.z, a);
+        mma16816_zero(c, a, bf[1].x, bf[1].y);
+        mxfp4_frag(wq.w, a);
+        mma16816(c, a, bf[1].z, bf[1].w);
+        s0 = mxfp4_scale<1>(sw);
+        s1 = mxfp4_scale<3>(sw);
+        acc[0] = fmaf(s0, c[0], acc[0]);
+        acc[1] = fmaf(s0, c[1], acc[1]);
+        acc[2] = fmaf(s1, c[2], acc[2]);
+        acc[3] = fmaf(s1, c[3], acc[3]);
     } else {
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        float c[4];
         uint32_t a[4];
         a[0] = q8_pair(wq.x, 0x4140);
         a[2] = q8_pair(wq.x, 0x4342);
         a[1] = q8_pair(wq.y, 0x4140);
         a[3] = q8_pair(wq.y, 0x4342);
-        mma16816(c, a, bf[0].x, bf[0].y);
+        mma16816_zero(c, a, bf[0].x, bf[0].y);
         a[0] = q8_pair(wq.z, 0x4140);
         a[2] = q8_pair(wq.z, 0x4342);
         a[1] = q8_pair(wq.w, 0x4140);
@@ -178,44 +197,49 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
     const int n_items = a.n_work_items[0];
     const int n_kt = (int)(K / kTileK);
     const int n_stage = (n_kt + kCtPerStage - 1) / kCtPerStage;
-    const int blocks_per_item = (int)(a.rows / (kTileRows * kWarps));
-    const int64_t U = (int64_t)n_items * blocks_per_item;
-    const int64_t u0 = U * blockIdx.x / gridDim.x, u1 = U * (blockIdx.x + 1) / gridDim.x;
-    const int64_t total = (u1 - u0) * n_stage;  // ring stages this warp will consume
-    const int64_t P = a.T * a.n_used;
+    const int bpi = (int)(a.rows / (kTileRows * kWarps));  // 128-row blocks per item
+    const int U = n_items * bpi;
+    const int u0 = (int)((int64_t)U * blockIdx.x / gridDim.x), u1 = (int)((int64_t)U * (blockIdx.x + 1) / gridDim.x);
+    const int total = (u1 - u0) * n_stage;  // ring stages this warp will consume
+    const int P = (int)(a.T * a.n_used);
 
-    // source of ring stage `idx` of this warp (lane 0 only)
-    auto issue = [&](int64_t idx) {
-        const int64_t unit = u0 + idx / n_stage;
-        const int ls = (int)(idx % n_stage);
-        const int item = (int)(unit / blocks_per_item), rb = (int)(unit % blocks_per_item);
-        const uint32_t wi = (uint32_t)a.work_items[item];
-        const int e = (int)(wi >> 16);
-        const uint8_t* nib = (e == a.n_expert) ? a.sh_nib : a.nib + (int64_t)e * a.nib_slot_stride;
-        const uint8_t* sc = (e == a.n_expert) ? a.sh_sc : a.sc + (int64_t)e * a.sc_slot_stride;
-        const int64_t rt = (int64_t)rb * kWarps + warp;
-        const int ct0 = ls * kCtPerStage;
+    // ---- producer state (lane 0): next stage to request, tracked incrementally
+    int p_item = u0 / bpi, p_rb = u0 - p_item * bpi, p_ls = 0, p_cnt = 0, p_cached = -1;
+    const uint8_t* p_nib = nullptr;
+    const uint8_t* p_sc = nullptr;
+    auto issue = [&]() {
+        if (p_item != p_cached) {
+            const int e = (int)((uint32_t)a.work_items[p_item] >> 16);
+            p_nib = (e == a.n_expert) ? a.sh_nib : a.nib + (int64_t)e * a.nib_slot_stride;
+            p_sc = (e == a.n_expert) ? a.sh_sc : a.sc + (int64_t)e * a.sc_slot_stride;
+            p_cached = p_item;
+        }
+        const int rt = p_rb * kWarps + warp;
+        const int ct0 = p_ls * kCtPerStage;
         const int n_ct = min(kCtPerStage, n_kt - ct0);
-        const int64_t sub0 = (rt * n_kt + ct0) * kSubPerCt;
+        const int64_t sub0 = ((int64_t)rt * n_kt + ct0) * kSubPerCt;
         const uint32_t nsub = (uint32_t)(n_ct * kSubPerCt);
-        const int slot = (int)(idx % kStages);
+        const int slot = p_cnt & (kStages - 1);
         const uint32_t bar = my_bars + 8 * slot;
         const uint32_t dst = smem_u32(my_ring + (size_t)slot * kStageBytes);
         mbar_expect_tx(bar, nsub * (kSubNibBytes + kSubScBytes));
-        bulk_g2s(dst, nib + sub0 * kSubNibBytes, nsub * kSubNibBytes, bar);
-        bulk_g2s(dst + kStageNib, sc + sub0 * kSubScBytes, nsub * kSubScBytes, bar);
+        bulk_g2s(dst, p_nib + sub0 * kSubNibBytes, nsub * kSubNibBytes, bar);
+        bulk_g2s(dst + kStageNib, p_sc + sub0 * kSubScBytes, nsub * kSubScBytes, bar);
+        p_cnt++;
+        if (++p_ls == n_stage) {
+            p_ls = 0;
+            if (++p_rb == bpi) { p_rb = 0; p_item++; }
+        }
     };
 
     if (lane == 0)
-        for (int64_t i = 0; i < total && i < kStages; i++) issue(i);
+        for (int i = 0; i < total && i < kStages; i++) issue();
 
+    int item = u0 / bpi, rb = u0 - item * bpi, ls = 0;
     int cur_item = -1;
     bool dead = false;
     float acc0[4], acc1[4];
-    for (int64_t idx = 0; idx < total; idx++) {
-        const int64_t unit = u0 + idx / n_stage;
-        const int ls = (int)(idx % n_stage);
-        const int item = (int)(unit / blocks_per_item), rb = (int)(unit % blocks_per_item);
+    for (int cnt = 0; cnt < total; cnt++) {
         if (ls == 0) {
             if (item != cur_item) {
                 // all warps of the block change item together (same unit sequence)
@@ -227,12 +251,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
                         const int n = (int)min((int64_t)kMaxTok, a.T - start);
                         if (i == 0) info->n_tok = n;
                         info->tok[i] = start + i;
-                        info->mid_row[i] = (int)P + start + i;
-                        info->out_row[i] = (int)P + start + i;
+                        info->mid_row[i] = P + start + i;
+                        info->out_row[i] = P + start + i;
                         info->w[i] = 1.0f;
                     } else {
-                        const int seg0 = a.offsets[e], cnt = a.offsets[e + 1] - seg0;
-                        const int n = min(kMaxTok, cnt - start);
+                        const int seg0 = a.offsets[e], cntm = a.offsets[e + 1] - seg0;
+                        const int n = min(kMaxTok, cntm - start);
                         if (i == 0) info->n_tok = n;
                         const int p = seg0 + start + min(i, n - 1);
                         const int ts = a.perm[p];
@@ -270,8 +294,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
 #pragma unroll
             for (int i = 0; i < 4; i++) acc0[i] = acc1[i] = 0.f;
         }
-        const int slot = (int)(idx % kStages);
-        if (!dead && !mbar_wait(my_bars + 8 * slot, (uint32_t)((idx / kStages) & 1))) {
+        const int slot = cnt & (kStages - 1);
+        if (!dead && !mbar_wait(my_bars + 8 * slot, (uint32_t)((cnt / kStages) & 1))) {
             dead = true;
             if (lane == 0) atomicOr(a.error_word, 1u);
         }
@@ -281,21 +305,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
             const int ct0 = ls * kCtPerStage;
             const int n_ct = min(kCtPerStage, n_kt - ct0);
             const bool tok_ok = g < info->n_tok;
-            for (int c = 0; c < n_ct; c++) {
+            const __half* arow = act + (size_t)g * act_stride + (size_t)ct0 * kTileK + 8 * t4;
+            auto col_tile = [&](int c) {
                 uint4 bf[kBlocks];
 #pragma unroll
                 for (int b = 0; b < kBlocks; b++) {
                     bf[b] = make_uint4(0u, 0u, 0u, 0u);
-                    if (tok_ok)
-                        bf[b] = *reinterpret_cast<const uint4*>(act + (size_t)g * act_stride + (size_t)(ct0 + c) * kTileK + 32 * b + 8 * t4);
+                    if (tok_ok) bf[b] = *reinterpret_cast<const uint4*>(arow + c * kTileK + 32 * b);
                 }
                 compute_subtile<FMT>(st_nib + (size_t)(c * kSubPerCt) * kSubNibBytes, st_sc + (size_t)(c * kSubPerCt) * kSubScBytes, lane, bf, acc0);
                 if (PAIR)
                     compute_subtile<FMT>(st_nib + (size_t)(c * 2 + 1) * kSubNibBytes, st_sc + (size_t)(c * 2 + 1) * kSubScBytes, lane, bf, acc1);
+            };
+            if (n_ct == kCtPerStage) {  // full stage: unrolled so independent sub-tiles overlap
+#pragma unroll
+                for (int c = 0; c < kCtPerStage; c++) col_tile(c);
+            } else {
+                for (int c = 0; c < n_ct; c++) col_tile(c);
             }
         }
         __syncwarp();
-        if (lane == 0 && !dead && idx + kStages < total) issue(idx + kStages);
+        if (lane == 0 && !dead && p_cnt < total) issue();
 
         if (ls == n_stage - 1 && !dead) {
             const int row0 = (rb * kWarps + warp) * kTileRows + g;
@@ -317,6 +347,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
                     }
                 }
             }
+        }
+        if (++ls == n_stage) {
+            ls = 0;
+            if (++rb == bpi) { rb = 0; item++; }
         }
     }
 }

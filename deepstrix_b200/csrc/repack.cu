@@ -57,10 +57,10 @@ __global__ void repack_mxfp4_kernel(int layout, const uint8_t* __restrict__ q, c
     for (int st = 0; st < 4; st++) {
         const int64_t c = kt * 64 + 32 * (st >> 1) + 8 * t + 4 * (st & 1);
         uint32_t w = 0;
-        w |= (mxfp4_src_code(layout, q, K, r0, c + 0) | (mxfp4_src_code(layout, q, K, r0, c + 2) << 4)) << 0;
-        w |= (mxfp4_src_code(layout, q, K, r0, c + 1) | (mxfp4_src_code(layout, q, K, r0, c + 3) << 4)) << 8;
-        w |= (mxfp4_src_code(layout, q, K, r1, c + 0) | (mxfp4_src_code(layout, q, K, r1, c + 2) << 4)) << 16;
-        w |= (mxfp4_src_code(layout, q, K, r1, c + 1) | (mxfp4_src_code(layout, q, K, r1, c + 3) << 4)) << 24;
+        w |= (mxfp4_src_code(layout, q, K, r0, c + 0) | (mxfp4_src_code(layout, q, K, r0, c + 1) << 4)) << 0;
+        w |= (mxfp4_src_code(layout, q, K, r1, c + 0) | (mxfp4_src_code(layout, q, K, r1, c + 1) << 4)) << 8;
+        w |= (mxfp4_src_code(layout, q, K, r0, c + 2) | (mxfp4_src_code(layout, q, K, r0, c + 3) << 4)) << 16;
+        w |= (mxfp4_src_code(layout, q, K, r1, c + 2) | (mxfp4_src_code(layout, q, K, r1, c + 3) << 4)) << 24;
         words[st] = w;
     }
     const int64_t dsub = sub * pair_stride + pair_index;
@@ -142,8 +142,8 @@ __global__ void unpack_kernel(int fmt, const uint8_t* __restrict__ nib, const ui
         uint8_t codes[32];
         for (int within = 0; within < 32; within++) {
             const int t = within >> 3, rem = within & 7, st = 2 * b + (rem >> 2), j = rem & 3;
-            const uint8_t byte = tile[(g * 4 + t) * 16 + st * 4 + hi_row * 2 + (j & 1)];
-            codes[within] = (j >> 1) ? (byte >> 4) : (byte & 0xF);
+            const uint8_t byte = tile[(g * 4 + t) * 16 + st * 4 + (j >> 1) * 2 + hi_row];
+            codes[within] = (j & 1) ? (byte >> 4) : (byte & 0xF);
         }
         for (int i = 0; i < 16; i++) q_out[row * (K >> 1) + blk * 16 + i] = (uint8_t)(codes[2 * i] | (codes[2 * i + 1] << 4));
         s_out[row * nb + blk] = sc[dsub * kSubScBytes + g * 4 + hi_row * 2 + b];

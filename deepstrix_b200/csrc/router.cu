@@ -27,26 +27,32 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, const float
     const int64_t t0 = (int64_t)blockIdx.y * kLogitTokens;
     const int nt = (int)min((int64_t)kLogitTokens, T - t0);
     float acc[kLogitTokens];
+    const uint2* xrow[kLogitTokens];
 #pragma unroll
-    for (int i = 0; i < kLogitTokens; i++) acc[i] = 0.0f;
-    const float4* wrow = reinterpret_cast<const float4*>(W + (int64_t)e * H);
+    for (int i = 0; i < kLogitTokens; i++) {
+        acc[i] = 0.0f;
+        // rows past the batch alias the last valid row: every load is legal, so the
+        // compiler can issue all loads of an iteration before the first fma
+        xrow[i] = reinterpret_cast<const uint2*>(x + min(t0 + i, T - 1) * H) + lane;
+    }
+    const float4* wrow = reinterpret_cast<const float4*>(W + (int64_t)e * H) + lane;
     const int n_iter = (int)(H >> 7);
-#pragma unroll 4
+#pragma unroll 2
     for (int i = 0; i < n_iter; i++) {
-        const float4 w = __ldg(wrow + i * 32 + lane);
+        const float4 w = __ldg(wrow + i * 32);
+        uint2 xv[kLogitTokens];
+#pragma unroll
+        for (int tt = 0; tt < kLogitTokens; tt++) xv[tt] = __ldg(xrow[tt] + i * 32);
 #pragma unroll
         for (int tt = 0; tt < kLogitTokens; tt++) {
-            if (tt < nt) {
-                const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (t0 + tt) * H) + i * 32 + lane);
-                const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
-                const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
-                float a = acc[tt];
-                a = __fmaf_rn(w.x, x0, a);
-                a = __fmaf_rn(w.y, x1, a);
-                a = __fmaf_rn(w.z, x2, a);
-                a = __fmaf_rn(w.w, x3, a);
-                acc[tt] = a;
-            }
+            const float x0 = __uint_as_float(xv[tt].x << 16), x1 = __uint_as_float(xv[tt].x & 0xFFFF0000u);
+            const float x2 = __uint_as_float(xv[tt].y << 16), x3 = __uint_as_float(xv[tt].y & 0xFFFF0000u);
+            float a = acc[tt];
+            a = __fmaf_rn(w.x, x0, a);
+            a = __fmaf_rn(w.y, x1, a);
+            a = __fmaf_rn(w.z, x2, a);
+            a = __fmaf_rn(w.w, x3, a);
+            acc[tt] = a;
         }
     }
 #pragma unroll
