@@ -360,6 +360,15 @@ int dsx_moe_group_build(const int32_t* selected, int64_t T, int n_used, int n_ex
     return rc;
 }
 
+int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n_used, int n_expert, int chunk, int32_t* hist,
+                               int32_t* offsets, int32_t* perm, int32_t* work_items, int32_t* n_work_items, dsx_stream_t stream) {
+    DSX_REQUIRE(selected && hist && offsets && perm && T >= 0 && n_used >= 1, "group_build_static: null argument");
+    DSX_REQUIRE((work_items == nullptr) == (n_work_items == nullptr), "group_build_static: work_items and n_work_items go together");
+    const int32_t cap = work_items ? (int32_t)dsx_wi_upper_bound((uint64_t)(T * n_used), (uint32_t)n_expert, (uint32_t)chunk, 1u << 30) : 0;
+    return launch_group_build_static(selected, T, n_used, n_expert, chunk, hist, offsets, perm, work_items, n_work_items, cap,
+                                     (cudaStream_t)stream);
+}
+
 // ------------------------------------------------------------------- layer
 struct StageTimer {  // brackets one stage with an event pair when profiling is on
     dsx_moe_layer* L; int stage; cudaStream_t stream;

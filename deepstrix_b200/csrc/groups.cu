@@ -10,6 +10,8 @@
 // stable counting sort, so hist, offsets AND perm are reproducible bit for bit:
 // warp ballots (match_any) rank equal experts inside a 32-pick step, per-warp
 // and per-block prefix sums order the steps.
+#include <mutex>
+
 #include "dsx_common.cuh"
 
 namespace dsx {
@@ -183,7 +185,50 @@ group_place_kernel(const int32_t* __restrict__ sel, int64_t P, int E, int lo, co
     chunk_place(sel, P, base, E, lo, wh, perm);
 }
 
+// Scratch of the allocation-free entry point: the per-chunk histograms of the
+// multi-block counting sort, for at most kStaticMaxChunks chunks of kGroupChunk
+// picks (131072 picks, e.g. 16384 tokens x top-8).  128 KiB of device memory on
+// every GPU that loads the library, held until the process exits.
+constexpr int kStaticMaxChunks = 64;
+static __device__ __align__(256) int32_t g_static_chunk_hist[kStaticMaxChunks * kMaxExperts];
+
 }  // namespace
+
+// Device address of g_static_chunk_hist on the CURRENT device.  In host code the
+// array's name is only a handle for cudaGetSymbolAddress, never a pointer a
+// kernel may receive; the lookup is done once per device and cached.
+static int static_scratch(int32_t** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int32_t* cache[kMaxDevices] = {};
+    int dev = 0;
+    DSX_CUDA(cudaGetDevice(&dev));
+    DSX_REQUIRE(dev >= 0 && dev < kMaxDevices, "group_build_static: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == nullptr) {
+        void* p = nullptr;
+        DSX_CUDA(cudaGetSymbolAddress(&p, g_static_chunk_hist));
+        cache[dev] = static_cast<int32_t*>(p);
+    }
+    *out = cache[dev];
+    return DSX_OK;
+}
+
+int launch_group_build_static(const int32_t* selected, int64_t T, int n_used, int n_expert, int chunk, int32_t* hist,
+                              int32_t* offsets, int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap,
+                              cudaStream_t stream) {
+    const int64_t P = T * n_used;
+    const int64_t n_chunks = (P + kGroupChunk - 1) / kGroupChunk;
+    if (n_chunks > kStaticMaxChunks)
+        return set_error(DSX_ERR_UNSUPPORTED,
+                         "group_build_static: %lld picks exceed the built-in scratch (at most %d picks); use dsx_moe_group_build",
+                         (long long)P, kStaticMaxChunks * kGroupChunk);
+    GroupScratch gs{};
+    if (int rc = static_scratch(&gs.chunk_hist)) return rc;
+    gs.capacity_chunks = kStaticMaxChunks;
+    return launch_group_build(selected, T, n_used, n_expert, 0, chunk, 0, hist, offsets, perm, work_items, n_work_items, work_cap,
+                              gs, stream);
+}
 
 int launch_group_build(const int32_t* selected, int64_t T, int n_used, int n_expert, int expert_lo, int chunk,
                        int shared_items_for_T, int32_t* hist, int32_t* offsets, int32_t* perm, int32_t* work_items,

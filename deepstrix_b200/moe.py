@@ -190,7 +190,15 @@ class MoeGroupBuilder:
     """Histogram / offsets / stable permutation / work items."""
 
     @staticmethod
-    def launch(selected: torch.Tensor, n_expert: int, chunk: int = 32, with_work_items: bool = True):
+    def launch_static(selected: torch.Tensor, n_expert: int, chunk: int = 32, with_work_items: bool = True):
+        """Same result as :meth:`launch` through the entry point that never allocates
+        device memory (the library's built-in 128 KiB scratch; at most 131072 picks).
+        The output tensors are still the caller's; only the kernel's temporary moved."""
+        return MoeGroupBuilder.launch(selected, n_expert, chunk, with_work_items, _entry="dsx_moe_group_build_static")
+
+    @staticmethod
+    def launch(selected: torch.Tensor, n_expert: int, chunk: int = 32, with_work_items: bool = True,
+               _entry: str = "dsx_moe_group_build"):
         T, k = selected.shape
         assert selected.dtype == torch.int32 and selected.is_contiguous()
         dev = selected.device
@@ -202,8 +210,8 @@ class MoeGroupBuilder:
             cap = wi_upper_bound(T * k, n_expert, chunk)
             items = torch.full((max(cap, 1),), -1, dtype=torch.int32, device=dev)
             n_items = torch.zeros(1, dtype=torch.int32, device=dev)
-        _check(lib().dsx_moe_group_build(_dptr(selected), C.c_int64(T), k, n_expert, chunk, _dptr(hist), _dptr(offsets),
-                                         _dptr(perm), _dptr(items), _dptr(n_items), _stream()))
+        _check(getattr(lib(), _entry)(_dptr(selected), C.c_int64(T), k, n_expert, chunk, _dptr(hist), _dptr(offsets),
+                                      _dptr(perm), _dptr(items), _dptr(n_items), _stream()))
         return hist, offsets, perm, items, n_items
 
 

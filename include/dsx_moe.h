@@ -192,6 +192,31 @@ DSX_API int dsx_router_topk(const float* logits, const float* bias, int64_t T, c
 DSX_API int dsx_moe_group_build(const int32_t* selected, int64_t T, int n_used, int n_expert, int chunk,
                                 int32_t* hist, int32_t* offsets, int32_t* perm,
                                 int32_t* work_items, int32_t* n_work_items, dsx_stream_t stream);
+/* Same operation and outputs as dsx_moe_group_build, for callers that must not
+ * allocate device memory.  This entry point has no counterpart in the
+ * reference.  Who needs it: an engine that hands the whole GPU to its own arena
+ * at start-up (the way deepstrix sizes its per-layer scratch once), so that a
+ * cudaMalloc made behind its back fails or eats into memory it has planned for;
+ * and a serving loop that cannot afford the device-wide synchronisation an
+ * allocation or a free may imply.  dsx_moe_group_build borrows a temporary
+ * buffer from the driver when T * n_used exceeds 2048; this variant keeps that
+ * buffer inside the library instead, as a fixed 128 KiB array in device memory
+ * that every GPU which loads the library holds until the process exits.
+ *   - Limit: T * n_used <= 131072 picks (for example 16384 tokens x top-8) and
+ *     n_expert <= 512.  Larger inputs are refused with DSX_ERR_UNSUPPORTED and a
+ *     message; nothing is launched.
+ *   - It calls no cudaMalloc / cudaFree / cudaMallocAsync and no library routine
+ *     that allocates.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it; make that
+ *     first call before starting any stream capture on that device.
+ *   - All calls on one device share the one array.  Its previous contents never
+ *     matter (every entry a call reads is first written by that call), but two
+ *     calls that overlap on the GPU -- different streams, or different threads --
+ *     race on it: issue them on one stream, or order them with events. */
+DSX_API int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n_used, int n_expert, int chunk,
+                                       int32_t* hist, int32_t* offsets, int32_t* perm,
+                                       int32_t* work_items, int32_t* n_work_items, dsx_stream_t stream);
 /* moe_wi_upper_bound, het/dispatch.rs:444-454 */
 DSX_API uint32_t dsx_wi_upper_bound(uint64_t members, uint32_t groups, uint32_t chunk, uint64_t cap);
 
