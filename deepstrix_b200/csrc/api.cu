@@ -446,7 +446,7 @@ int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const
         delete L;
         return rc;
     }
-    if (int rc = prefill_workspace_create(&L->pf, c)) {
+    if (int rc = prefill_workspace_create(&L->pf, c, c.router.n_used, L->mid)) {
         layer_free(L);
         delete L;
         return rc;
@@ -482,13 +482,14 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
         pc.x = x; pc.T = T; pc.selected = selected; pc.route_w = weights; pc.expert_lo = expert_lo; pc.n_local = n_local;
         pc.filter_picks = filter_picks; pc.with_shared = shared; pc.out = out;
         pc.hist = L->hist; pc.offsets = L->offsets; pc.perm = L->perm; pc.gs = L->gs;
-        pc.work_items = L->work_items; pc.n_work_items = L->n_work_items; pc.work_cap = L->work_cap;
-        pc.partial = L->partial; pc.error_word = L->error_word; pc.sm_count = L->sm_count;
+        pc.mid = L->mid; pc.partial = L->partial; pc.error_word = L->error_word; pc.sm_count = L->sm_count;
+        pc.n_used = k; pc.clamp = c.clamp;
         pc.gu_nib = L->routed->gu_nib; pc.gu_sc = L->routed->gu_sc; pc.dn_nib = L->routed->dn_nib; pc.dn_sc = L->routed->dn_sc;
         pc.gu_nib_stride = L->routed->gu_nib_stride; pc.gu_sc_stride = L->routed->gu_sc_stride;
         pc.dn_nib_stride = L->routed->dn_nib_stride; pc.dn_sc_stride = L->routed->dn_sc_stride;
         if (shared) { pc.sh_gu_nib = L->shared->gu_nib; pc.sh_gu_sc = L->shared->gu_sc; pc.sh_dn_nib = L->shared->dn_nib; pc.sh_dn_sc = L->shared->dn_sc; }
         pc.fmt = L->routed->fmt;
+        StageTimer tm(L, DSX_STAGE_GATE_UP, stream);
         return prefill_forward(&L->pf, c, pc, stream);
     }
     {

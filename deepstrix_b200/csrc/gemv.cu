@@ -96,8 +96,8 @@ __device__ __forceinline__ void mxfp4_frag(uint32_t q, uint32_t (&a)[4]) {
 // shift into the exponent field; e = 0 gives 0 instead of the denormal 2^-127).
 template <int B>
 __device__ __forceinline__ float mxfp4_scale(uint32_t sw) {
-    if (B == 3) return __uint_as_float((sw >> 1) & 0x7F800000u);
-    return __uint_as_float((sw & (0xFFu << (8 * B))) << (23 - 8 * B));
+    if constexpr (B == 3) return __uint_as_float((sw >> 1) & 0x7F800000u);
+    else return __uint_as_float((sw & (0xFFu << (8 * B))) << (23 - 8 * B));
 }
 
 // Four offset-binary int8 (value ^ 0x80) -> two f16x2: 0x6400 | u is 1024 + u.

@@ -1,17 +1,565 @@
-// Prefill-size grouped GEMM on tcgen05.  Not built yet: every batch size runs
-// the grouped-GEMV kernels.
+// Prefill-size grouped GEMM on the 5th-generation tensor cores (tcgen05).
+//
+// Reference counterparts (paths relative to the deepstrix repository): the
+// by-expert prefill kernels and their matrix-core arms,
+//   gate/up  crates/v4flash-kernels/kernels/mxfp4_pair_matvec.hip:293-564, mxfp4_moe_wmma.hip:137-368
+//   down     crates/v4flash-kernels/kernels/mxfp4_matvec.hip:219-369,      mxfp4_moe_wmma.hip:370-388
+//   grouping crates/v4flash-kernels/kernels/moe_work_items_builder.hip:61-145 (work items sorted by expert)
+//
+// Design.  Expert-sorted token rows (the permutation of groups.cu) are cut into
+// segments of <= 256 rows of one expert.  A tile = (segment, 256 weight rows).
+// The weight rows are the M side of the MMA (two 128-row halves that share the
+// token operand), the segment's tokens the N side (any multiple of 16 up to
+// 256), so ragged expert sizes cost MMA time in proportion to their tokens.
+// For gate/up the two halves are gate rows f0..f0+127 and up rows f0..f0+127: a
+// TMEM lane then holds gate and up of the same output row and SwiGLU needs no
+// exchange.  Per 64-column chunk of the reduction:
+//   producer thread   bulk-copies the packed 4-bit sub-tiles (8.5 KB) into a deep
+//                     ring, and TMA-loads the token tile (256 x 64 f16, 128-byte swizzle)
+//   8 converter warps expand codes with cvt.rn.f16x2.e2m1x2, multiply by the E8M0
+//                     block scale (exact in f16) and write the swizzled K-major A tile
+//   MMA thread        8 x tcgen05.mma.kind::f16 (M128 x N x K16) into two TMEM accumulators
+// and after the last chunk 4 epilogue warps read TMEM (tcgen05.ld), apply
+// clamp + SwiGLU + routing weight (gate/up) and store mid (f16) or the per-pick
+// partial rows (f32).  Every wait is bounded; on a timeout the block raises an
+// abort flag, all roles drain, TMEM is freed and the layer's error word is set.
 #include "prefill.cuh"
 
 namespace dsx {
+namespace {
 
-int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config&) {
-    ws->ready = false;
+constexpr int kThreads = 14 * 32;      // producer, MMA, 8 converters, 4 epilogue warps
+constexpr int kConvWarps = 8;
+constexpr int kEpiWarp0 = 10;
+constexpr int kSegRows = 256;          // max token rows per segment (MMA N)
+constexpr int kTileM = 256;            // weight rows per tile (2 x M128)
+constexpr int kChunkK = 64;            // reduction columns per pipeline step
+constexpr int kRawStages = 6, kAStages = 2, kBStages = 3;
+constexpr int kRawNib = 16 * kSubNibBytes;           // 16 sub-tiles of 16 rows x 64 columns
+constexpr int kRawSc = 16 * kSubScBytes;
+constexpr int kRawBytes = kRawNib + kRawSc;          // 8704
+constexpr int kABytes = kTileM * kChunkK * 2;        // 32768
+constexpr int kBBytes = kSegRows * kChunkK * 2;      // 32768
+constexpr int kSmemA = 0;
+constexpr int kSmemB = kSmemA + kAStages * kABytes;
+constexpr int kSmemRaw = kSmemB + kBStages * kBBytes;
+constexpr int kSmemBar = kSmemRaw + kRawStages * kRawBytes;
+constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2 * kBStages + 2;
+constexpr int kSmemMisc = kSmemBar + kNumBars * 8;   // tmem base, abort flag, per-tile arrays
+constexpr int kSmemTotal = kSmemMisc + 16 + kSegRows * 8 + 1024;  // + alignment slack
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait that also gives up when another role of the block has aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; i++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled shared-memory operand: 8-row groups of 1024 B.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);       // start address
+    d |= (uint64_t)(1024u >> 4) << 32;              // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                         // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                         // 128-byte swizzle
+    return d;
+}
+// kind::f16, f16 x f16 -> f32, both operands K-major, M = 128.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// E8M0 byte -> f16x2 splat of 2^(e-127); subnormal below 2^-14, zero below 2^-24.
+__device__ __forceinline__ uint32_t scale_h2(uint32_t e) {
+    uint32_t b = e >= 113u ? (e - 112u) << 10 : (e >= 103u ? 1u << (e - 103u) : 0u);
+    return b | (b << 16);
+}
+__device__ __forceinline__ void cvt4(uint32_t q, uint32_t (&h)[4]) {
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(q));
+}
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+struct GemmArgs {
+    const PrefillSeg* segs;
+    const int32_t* n_segs;
+    const uint8_t* nib;        // routed plane base
+    const uint8_t* sc;
+    int64_t nib_slot_stride, sc_slot_stride;
+    const uint8_t* sh_nib;     // shared expert plane (may be null)
+    const uint8_t* sh_sc;
+    int n_local;               // seg.expert == n_local -> shared expert
+    int K;                     // reduction length (hidden for gate/up, ffn for down)
+    int rows;                  // output rows of the matrix (ffn for gate/up, hidden for down)
+    int n_used;
+    int64_t P;                 // T * n_used: first row of the shared expert's rows
+    const int32_t* perm;
+    const float* route_w;
+    float clamp;
+    __half* mid;               // gate/up output [rows_total, ffn]
+    int64_t mid_stride;
+    float* partial;            // down output [rows_total, hidden]
+    uint32_t* error_word;
+};
+
+template <bool GATE_UP>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
+    const uint32_t bar0 = sbase + kSmemBar;
+    // barrier indices
+    constexpr int RAW_FULL = 0, RAW_EMPTY = RAW_FULL + kRawStages, A_FULL = RAW_EMPTY + kRawStages, A_EMPTY = A_FULL + kAStages,
+                  B_FULL = A_EMPTY + kAStages, B_EMPTY = B_FULL + kBStages, ACC_FULL = B_EMPTY + kBStages, ACC_EMPTY = ACC_FULL + 1;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* s_w = reinterpret_cast<float*>(smem + kSmemMisc + 16);          // routing weight per tile column
+    int32_t* s_row = reinterpret_cast<int32_t*>(s_w + kSegRows);           // output row per tile column
+    (void)bars;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kRawStages; i++) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), kConvWarps); }
+        for (int i = 0; i < kAStages; i++) { mbar_init(bar(A_FULL + i), kConvWarps); mbar_init(bar(A_EMPTY + i), 1); }
+        for (int i = 0; i < kBStages; i++) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
+        mbar_init(bar(ACC_FULL), 1);
+        mbar_init(bar(ACC_EMPTY), 4);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM: all 512 columns (two 256-column accumulators)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32((const void*)tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_segs = a.n_segs[0];
+    const int n_mb = a.rows / (GATE_UP ? 128 : 256);   // 256-row tiles (gate/up: 128 gate + 128 up)
+    const int n_tiles = n_segs * n_mb;
+    const int n_kc = a.K / kChunkK;
+    const int n_kt = a.K / 64;                          // MXFP4 column tiles per row tile
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t rcnt = 0, bcnt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const PrefillSeg seg = a.segs[tile / n_mb];
+                const int mb = tile % n_mb;
+                const bool sh = seg.expert == a.n_local;
+                const uint8_t* nib = sh ? a.sh_nib : a.nib + (int64_t)seg.expert * a.nib_slot_stride;
+                const uint8_t* sc = sh ? a.sh_sc : a.sc + (int64_t)seg.expert * a.sc_slot_stride;
+                for (int kc = 0; kc < n_kc && ok; kc++) {
+                    {   // packed weights of this chunk
+                        const int s = rcnt % kRawStages;
+                        ok = mbar_wait(bar(RAW_EMPTY + s), ((rcnt / kRawStages) & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        const uint32_t dst = sbase + kSmemRaw + s * kRawBytes;
+                        mbar_expect_tx(bar(RAW_FULL + s), kRawBytes);
+                        if (GATE_UP) {  // 8 row tiles, each [gate | up] sub-tile pair contiguous
+#pragma unroll 1
+                            for (int r = 0; r < 8; r++) {
+                                const int64_t sub = ((int64_t)(mb * 8 + r) * n_kt + kc) * 2;
+                                bulk_g2s(dst + r * 1024, nib + sub * kSubNibBytes, 1024, bar(RAW_FULL + s));
+                                bulk_g2s(dst + kRawNib + r * 64, sc + sub * kSubScBytes, 64, bar(RAW_FULL + s));
+                            }
+                        } else {
+#pragma unroll 1
+                            for (int r = 0; r < 16; r++) {
+                                const int64_t sub = (int64_t)(mb * 16 + r) * n_kt + kc;
+                                bulk_g2s(dst + r * 512, nib + sub * kSubNibBytes, 512, bar(RAW_FULL + s));
+                                bulk_g2s(dst + kRawNib + r * 32, sc + sub * kSubScBytes, 32, bar(RAW_FULL + s));
+                            }
+                        }
+                        rcnt++;
+                    }
+                    {   // token tile of this chunk
+                        const int s = bcnt % kBStages;
+                        ok = mbar_wait(bar(B_EMPTY + s), ((bcnt / kBStages) & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(bar(B_FULL + s), kBBytes);
+                        tma_load_2d(sbase + kSmemB + s * kBBytes, &tmap_b, kc * kChunkK, seg.row0, bar(B_FULL + s));
+                        bcnt++;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ----------------------------------------------------------- MMA issue
+        if (lane == 0) {
+            uint32_t acnt = 0, bcnt = 0, tcnt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const PrefillSeg seg = a.segs[tile / n_mb];
+                const int n16 = max(16, (seg.n + 15) & ~15);
+                const uint32_t idesc = umma_idesc(n16);
+                ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // epilogue has drained TMEM
+                if (!ok) break;
+                tc_fence_after();
+                for (int kc = 0; kc < n_kc && ok; kc++) {
+                    const int sa = acnt % kAStages, sb = bcnt % kBStages;
+                    ok = mbar_wait(bar(A_FULL + sa), (acnt / kAStages) & 1u, abort_flag) &&
+                         mbar_wait(bar(B_FULL + sb), (bcnt / kBStages) & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = umma_desc(sbase + kSmemA + sa * kABytes);
+                    const uint64_t db = umma_desc(sbase + kSmemB + sb * kBBytes);
+#pragma unroll
+                    for (int ks = 0; ks < kChunkK / 16; ks++) {
+                        const uint32_t acc = (kc | ks) != 0 ? 1u : 0u;
+                        tc_mma_f16(tmem_base, da + 2u * ks, db + 2u * ks, idesc, acc);
+                        tc_mma_f16(tmem_base + 256u, da + (128u * 128u >> 4) + 2u * ks, db + 2u * ks, idesc, acc);
+                    }
+                    tc_commit(bar(A_EMPTY + sa));   // arrives when the MMAs above have read their operands
+                    tc_commit(bar(B_EMPTY + sb));
+                    acnt++;
+                    bcnt++;
+                }
+                if (ok) tc_commit(bar(ACC_FULL));
+                tcnt++;
+            }
+        }
+    } else if (warp < 2 + kConvWarps) {
+        // ---------------------------------------------------------- converters
+        const int cw = warp - 2, g = lane >> 2, t = lane & 3;
+        uint32_t rcnt = 0, acnt = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            for (int kc = 0; kc < n_kc && ok; kc++) {
+                const int sr = rcnt % kRawStages, sa = acnt % kAStages;
+                ok = mbar_wait(bar(RAW_FULL + sr), (rcnt / kRawStages) & 1u, abort_flag) &&
+                     mbar_wait(bar(A_EMPTY + sa), ((acnt / kAStages) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                const uint8_t* raw = smem + kSmemRaw + sr * kRawBytes;
+                uint8_t* A = smem + kSmemA + sa * kABytes;
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    const int st = cw + 8 * half;   // sub-tile of the raw stage
+                    // gate/up stage order is [rt][gate, up]; A rows 0..127 = gate, 128..255 = up
+                    const int row_base = GATE_UP ? ((st & 1) * 128 + (st >> 1) * 16) : st * 16;
+                    const uint4 wq = *reinterpret_cast<const uint4*>(raw + st * kSubNibBytes + lane * 16);
+                    const uint32_t sw = *reinterpret_cast<const uint32_t*>(raw + kRawNib + st * kSubScBytes + g * 4);
+                    const uint32_t w[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                    for (int b = 0; b < 2; b++) {
+                        const uint32_t m0 = scale_h2((sw >> (8 * b)) & 0xFFu), m1 = scale_h2((sw >> (16 + 8 * b)) & 0xFFu);
+                        uint32_t p[4], q[4];
+                        cvt4(w[2 * b], p);       // (g; c0,c1) (g+8; c0,c1) (g; c2,c3) (g+8; c2,c3)
+                        cvt4(w[2 * b + 1], q);   // same for columns c4..c7
+                        const uint4 r0 = make_uint4(hmul2(p[0], m0), hmul2(p[2], m0), hmul2(q[0], m0), hmul2(q[2], m0));
+                        const uint4 r1 = make_uint4(hmul2(p[1], m1), hmul2(p[3], m1), hmul2(q[1], m1), hmul2(q[3], m1));
+                        const int j = 4 * b + t;   // 16-byte chunk of the 128-byte row
+                        const int R = row_base + g;
+                        const uint32_t off = (uint32_t)(R >> 3) * 1024u + (uint32_t)g * 128u + (uint32_t)((j ^ g) << 4);
+                        *reinterpret_cast<uint4*>(A + off) = r0;
+                        *reinterpret_cast<uint4*>(A + off + 1024u) = r1;   // row R + 8: next 8-row group, same swizzle phase
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar(A_FULL + sa));
+                    mbar_arrive(bar(RAW_EMPTY + sr));
+                }
+                rcnt++;
+                acnt++;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        const int et = threadIdx.x - kEpiWarp0 * 32;  // 0..127
+        uint32_t tcnt = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const PrefillSeg seg = a.segs[tile / n_mb];
+            const int mb = tile % n_mb;
+            const bool sh = seg.expert == a.n_local;
+            // per-column routing weight and output row
+            for (int c = et; c < kSegRows; c += 128) {
+                float wv = 0.f;
+                int orow = 0;
+                if (c < seg.n) {
+                    if (sh) { wv = 1.0f; orow = seg.row0 + c; }
+                    else { const int ts = a.perm[seg.row0 + c]; wv = a.route_w[ts]; orow = ts; }
+                }
+                s_w[c] = wv;
+                s_row[c] = orow;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const int r_in = q * 32 + lane;           // row inside a 128-row half
+            for (int c0 = 0; c0 < seg.n; c0 += 32) {
+                uint32_t v0[32], v1[32];
+                tc_ld32(lane_addr + (uint32_t)c0, v0);
+                tc_ld32(lane_addr + 256u + (uint32_t)c0, v1);
+                tc_wait_ld();
+                if (GATE_UP) {
+                    const int f = mb * 128 + r_in;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (c0 + j < seg.n) {
+                            float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
+                            if (a.clamp > 1.0e-6f) {
+                                gv = fminf(gv, a.clamp);
+                                uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
+                            }
+                            const float sig = 1.0f / (1.0f + __expf(-gv));
+                            a.mid[(int64_t)(seg.row0 + c0 + j) * a.mid_stride + f] = __float2half_rn(gv * sig * uv * s_w[c0 + j]);
+                        }
+                    }
+                } else {
+                    const int h = mb * 256 + r_in;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (c0 + j < seg.n) {
+                            float* dst = a.partial + (int64_t)s_row[c0 + j] * a.rows + h;
+                            dst[0] = __uint_as_float(v0[j]);
+                            dst[128] = __uint_as_float(v1[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // all four warps are done with TMEM and the per-tile arrays
+            if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
+            tcnt++;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error_word, 2u);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- helpers
+__device__ __forceinline__ int seg_size(int cnt) {  // even split into <= 256-row segments, multiples of 16
+    const int n = (cnt + kSegRows - 1) / kSegRows;
+    return n == 0 ? 0 : min(kSegRows, (((cnt + n - 1) / n) + 15) & ~15);
+}
+
+// One block.  Segments sorted by expert; the shared expert's segments (expert id
+// n_local) follow and cover rows P .. P+T-1.
+__global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t P, int T_shared,
+                                      PrefillSeg* __restrict__ segs, int32_t* __restrict__ n_segs, int cap) {
+    __shared__ int s_base[513];
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_local; e++) {
+            s_base[e] = run;
+            const int cnt = offsets[e + 1] - offsets[e];
+            const int sz = seg_size(cnt);
+            run += sz ? (cnt + sz - 1) / sz : 0;
+        }
+        s_base[n_local] = run;
+        const int sz = seg_size(T_shared);
+        n_segs[0] = min(cap, run + (sz ? (T_shared + sz - 1) / sz : 0));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= n_local; e += blockDim.x) {
+        const int cnt = e < n_local ? offsets[e + 1] - offsets[e] : T_shared;
+        const int row0 = e < n_local ? offsets[e] : (int)P;
+        const int sz = seg_size(cnt);
+        for (int i = 0, st = 0; st < cnt; i++, st += sz) {
+            const int idx = s_base[e] + i;
+            if (idx < cap) segs[idx] = PrefillSeg{e, row0 + st, min(sz, cnt - st), 0};
+        }
+    }
+}
+
+// Token rows in expert-sorted order as f16 (row p < placed: token perm[p] / k),
+// then every token once more for the shared expert (row P + t).
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ perm, const int32_t* __restrict__ offsets,
+                   int n_local, int n_used, int64_t P, int64_t T, int shared_rows, int64_t H, __half* __restrict__ xperm) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int64_t placed = offsets[n_local];
+    int64_t src, dst;
+    if (row < placed) { src = perm[row] / n_used; dst = row; }
+    else if (row >= P && row < P + (shared_rows ? T : 0)) { src = row - P; dst = row; }
+    else return;
+    const uint4* in = reinterpret_cast<const uint4*>(x + src * H);
+    uint4* out = reinterpret_cast<uint4*>(xperm + dst * H);
+    for (int64_t c = lane; c < H / 8; c += 32) {
+        const uint4 v = __ldg(in + c);
+        const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(wds[i] << 16), __uint_as_float(wds[i] & 0xFFFF0000u));
+            o[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        out[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encode_rows_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        DSX_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !p) return set_error(DSX_ERR_UNSUPPORTED, "driver has no cuTensorMapEncodeTiled");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)kSegRows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(DSX_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed with %d", (int)r);
     return DSX_OK;
 }
-void prefill_workspace_free(PrefillWorkspace*) {}
-bool prefill_wanted(const PrefillWorkspace& ws, const dsx_moe_config&, int, int64_t T) { return ws.ready && T >= ws.min_tokens; }
-int prefill_forward(PrefillWorkspace*, const dsx_moe_config&, const PrefillCall&, cudaStream_t) {
-    return set_error(DSX_ERR_UNSUPPORTED, "prefill path not built");
+
+}  // namespace
+
+int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid) {
+    ws->ready = false;
+    // shapes the tiles cover: 128 gate + 128 up rows per tile, 256 down rows per tile, 64-column chunks
+    if (cfg.ffn % 128 != 0 || cfg.hidden % 256 != 0 || (cfg.shared_ffn != 0 && cfg.shared_ffn != cfg.ffn)) return DSX_OK;
+    ws->H = cfg.hidden;
+    ws->F = cfg.ffn;
+    ws->cap_rows = (int64_t)cfg.max_tokens * n_used + cfg.max_tokens;
+    ws->seg_cap = cfg.router.n_expert + (int)((ws->cap_rows + kSegRows - 1) / kSegRows) + 8;
+    DSX_CUDA(cudaMalloc((void**)&ws->xperm, (size_t)ws->cap_rows * (size_t)cfg.hidden * 2));
+    DSX_CUDA(cudaMalloc((void**)&ws->segs, sizeof(PrefillSeg) * (size_t)ws->seg_cap));
+    DSX_CUDA(cudaMalloc((void**)&ws->n_segs, 256));
+    if (int rc = encode_rows_map(&ws->tmap_x, ws->xperm, ws->cap_rows, cfg.hidden)) return rc;
+    if (int rc = encode_rows_map(&ws->tmap_mid, mid, ws->cap_rows, cfg.ffn)) return rc;
+    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    ws->min_tokens = 65;
+    ws->ready = true;
+    return DSX_OK;
+}
+
+void prefill_workspace_free(PrefillWorkspace* ws) {
+    cudaFree(ws->xperm);
+    cudaFree(ws->segs);
+    cudaFree(ws->n_segs);
+    ws->xperm = nullptr; ws->segs = nullptr; ws->n_segs = nullptr; ws->ready = false;
+}
+
+bool prefill_wanted(const PrefillWorkspace& ws, const dsx_moe_config&, int fmt, int64_t T) {
+    return ws.ready && fmt == DSX_FMT_MXFP4 && T >= ws.min_tokens;
+}
+
+int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& c, cudaStream_t stream) {
+    const int64_t P = c.T * c.n_used;
+    DSX_REQUIRE(P + c.T <= ws->cap_rows, "prefill: %lld rows exceed the workspace (%lld)", (long long)(P + c.T), (long long)ws->cap_rows);
+    if (int rc = launch_group_build(c.selected, c.T, c.n_used, c.n_local, c.expert_lo, kSegRows, 0, c.hist, c.offsets, c.perm,
+                                    nullptr, nullptr, 0, c.gs, stream))
+        return rc;
+    build_segments_kernel<<<1, 512, 0, stream>>>(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, ws->segs, ws->n_segs, ws->seg_cap);
+    DSX_LAUNCHED();
+    const int64_t rows = P + c.T;
+    gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(c.x, c.perm, c.offsets, c.n_local, c.n_used, P, c.T,
+                                                                      c.with_shared ? 1 : 0, cfg.hidden, ws->xperm);
+    DSX_LAUNCHED();
+    GemmArgs g{};
+    g.segs = ws->segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
+    g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.error_word = c.error_word;
+    // gate/up: K = hidden, rows = ffn
+    g.nib = c.gu_nib; g.sc = c.gu_sc; g.nib_slot_stride = c.gu_nib_stride; g.sc_slot_stride = c.gu_sc_stride;
+    g.sh_nib = c.sh_gu_nib; g.sh_sc = c.sh_gu_sc; g.K = cfg.hidden; g.rows = cfg.ffn;
+    prefill_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_x, g);
+    DSX_LAUNCHED();
+    // down: K = ffn, rows = hidden
+    g.nib = c.dn_nib; g.sc = c.dn_sc; g.nib_slot_stride = c.dn_nib_stride; g.sc_slot_stride = c.dn_sc_stride;
+    g.sh_nib = c.sh_dn_nib; g.sh_sc = c.sh_dn_sc; g.K = cfg.ffn; g.rows = cfg.hidden;
+    prefill_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mid, g);
+    DSX_LAUNCHED();
+    return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr,
+                          c.expert_lo, c.n_local, c.out, stream);
 }
 
 }  // namespace dsx

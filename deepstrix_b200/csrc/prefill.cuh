@@ -1,12 +1,29 @@
 // Prefill-size grouped GEMM on tcgen05 (interface used by api.cu).
 #pragma once
+#include <cuda.h>
+
 #include "dsx_common.cuh"
 
 namespace dsx {
 
+struct PrefillSeg {   // a run of <= 256 expert-sorted token rows of one expert
+    int32_t expert;   // local slot, or n_local for the shared expert
+    int32_t row0;     // first row in the sorted activation / mid buffers
+    int32_t n;        // rows
+    int32_t pad;
+};
+
 struct PrefillWorkspace {
     bool ready = false;
     int min_tokens = 1 << 30;  // batches of at least this many tokens take the tensor-core path
+    int64_t cap_rows = 0;      // rows of xperm / mid the tensor maps cover
+    int64_t H = 0, F = 0;
+    __half* xperm = nullptr;   // [cap_rows, H] f16: token rows in expert-sorted order, then all tokens (shared expert)
+    PrefillSeg* segs = nullptr;
+    int32_t* n_segs = nullptr;
+    int32_t seg_cap = 0;
+    CUtensorMap tmap_x;        // xperm as [cap_rows, H], box 64 x 256, 128-byte swizzle
+    CUtensorMap tmap_mid;      // mid   as [cap_rows, F]
 };
 
 struct PrefillCall {
@@ -17,19 +34,21 @@ struct PrefillCall {
     int expert_lo, n_local;
     bool filter_picks, with_shared;
     __nv_bfloat16* out;
-    int32_t *hist, *offsets, *perm, *work_items, *n_work_items;
-    int32_t work_cap;
+    int32_t *hist, *offsets, *perm;
     GroupScratch gs;
+    __half* mid;
     float* partial;
     uint32_t* error_word;
     int sm_count;
+    int n_used;
     int fmt;
+    float clamp;
     const uint8_t *gu_nib, *gu_sc, *dn_nib, *dn_sc;
     int64_t gu_nib_stride, gu_sc_stride, dn_nib_stride, dn_sc_stride;
     const uint8_t *sh_gu_nib, *sh_gu_sc, *sh_dn_nib, *sh_dn_sc;
 };
 
-int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg);
+int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid);
 void prefill_workspace_free(PrefillWorkspace* ws);
 bool prefill_wanted(const PrefillWorkspace& ws, const dsx_moe_config& cfg, int fmt, int64_t T);
 int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& call, cudaStream_t stream);

@@ -202,6 +202,24 @@ def test_layer_many_tokens_per_expert_and_no_shared(torch_cuda, moe, oracle):
     assert rel_l2(out, ref) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("T,E,k", [(65, 32, 4), (300, 32, 4), (2500, 32, 4)])
+def test_layer_prefill_tensor_core_path_small(torch_cuda, moe, oracle, T, E, k):
+    """Batches above 64 tokens run the tcgen05 grouped GEMM: ragged segments (some experts
+    above 256 tokens, so they split), shared expert, several reduction chunks."""
+    from deepstrix_b200.config import MoeConfig, RouterConfig
+    cfg = MoeConfig(hidden=512, ffn=256, shared_ffn=256,
+                    router=RouterConfig(n_expert=E, n_used=k, n_group=1, topk_group=1, score_fn=1, route_scale=2.5))
+    moe.launch_count(reset=True)
+    out, ref, layer, *_ = _layer_case(torch_cuda, moe, oracle, cfg, 2, T)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+
+
+def test_layer_prefill_config0_shapes(torch_cuda, moe, oracle):
+    from deepstrix_b200.config import CONFIGS
+    out, ref, *_ = _layer_case(torch_cuda, moe, oracle, CONFIGS[0], 0, 192)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+
+
 def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
     """Owner-of-a-subset form: two half stores, each returning its weighted partial
     sum, add up to the full layer (the reference's het-split property,
