@@ -14,27 +14,32 @@
 // For gate/up the two halves are gate rows f0..f0+127 and up rows f0..f0+127: a
 // TMEM lane then holds gate and up of the same output row and SwiGLU needs no
 // exchange.  Per 64-column chunk of the reduction:
-//   producer thread   bulk-copies the packed 4-bit sub-tiles (8.5 KB) into a deep
-//                     ring, and TMA-loads the token tile (256 x 64 f16, 128-byte swizzle)
+//   two producer threads  TMA-load the packed 4-bit sub-tiles (8.5 KB, a 4-D box) into a deep ring, and
+//                     the token tile (256 x 64 f16, 128-byte swizzle) into its own ring
 //   8 converter warps expand codes with cvt.rn.f16x2.e2m1x2, multiply by the E8M0
 //                     block scale (exact in f16) and write the swizzled K-major A tile
 //   MMA thread        8 x tcgen05.mma.kind::f16 (M128 x N x K16) into two TMEM accumulators
-// and after the last chunk 4 epilogue warps read TMEM (tcgen05.ld), apply
+// and after the last chunk the 4 epilogue warps and the 8 converter warps read TMEM (tcgen05.ld), apply
 // clamp + SwiGLU + routing weight (gate/up) and store mid (f16) or the per-pick
 // partial rows (f32).  Every wait is bounded; on a timeout the block raises an
 // abort flag, all roles drain, TMEM is freed and the layer's error word is set.
+#include <stdio.h>
+
 #include "prefill.cuh"
 
 namespace dsx {
 namespace {
 
-constexpr int kThreads = 14 * 32;      // producer, MMA, 8 converters, 4 epilogue warps
+constexpr int kThreads = 15 * 32;      // weight producer, MMA, 8 converters, 4 epilogue warps, token-tile producer
+constexpr int kBProducerWarp = 14;
 constexpr int kConvWarps = 8;
 constexpr int kEpiWarp0 = 10;
 constexpr int kSegRows = 256;          // max token rows per segment (MMA N)
 constexpr int kTileM = 256;            // weight rows per tile (2 x M128)
 constexpr int kChunkK = 64;            // reduction columns per pipeline step
-constexpr int kRawStages = 6, kAStages = 2, kBStages = 3;
+constexpr int kRawStages = 3, kAStages = 3, kBStages = 3;
+static_assert(kAStages == kBStages, "the converted-weight and token-tile rings advance in lockstep");
+constexpr int kPrefetchAhead = 8;     // chunks of packed weights requested into L2 ahead of the ring
 constexpr int kRawNib = 16 * kSubNibBytes;           // 16 sub-tiles of 16 rows x 64 columns
 constexpr int kRawSc = 16 * kSubScBytes;
 constexpr int kRawBytes = kRawNib + kRawSc;          // 8704
@@ -44,9 +49,9 @@ constexpr int kSmemA = 0;
 constexpr int kSmemB = kSmemA + kAStages * kABytes;
 constexpr int kSmemRaw = kSmemB + kBStages * kBBytes;
 constexpr int kSmemBar = kSmemRaw + kRawStages * kRawBytes;
-constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2 * kBStages + 2;
+constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2;
 constexpr int kSmemMisc = kSmemBar + kNumBars * 8;   // tmem base, abort flag, per-tile arrays
-constexpr int kSmemTotal = kSmemMisc + 16 + kSegRows * 8 + 1024;  // + alignment slack
+constexpr int kSmemTotal = kSmemMisc + 16 + 1024;  // + alignment slack
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -89,6 +94,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  "l"(map), "r"(x), "r"(y), "r"(bar)
                  : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -129,10 +143,12 @@ __device__ __forceinline__ uint32_t umma_idesc(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-// E8M0 byte -> f16x2 splat of 2^(e-127); subnormal below 2^-14, zero below 2^-24.
+// E8M0 byte -> f16x2 splat of 2^(e-127).  Normal f16 for e >= 113 (two integer
+// ops); below that the multiplier is an f16 subnormal (2^-24 .. 2^-15) or zero.
 __device__ __forceinline__ uint32_t scale_h2(uint32_t e) {
-    uint32_t b = e >= 113u ? (e - 112u) << 10 : (e >= 103u ? 1u << (e - 103u) : 0u);
-    return b | (b << 16);
+    uint32_t b = (e << 10) - (112u << 10);
+    if (__builtin_expect(e < 113u, 0)) b = e >= 103u ? 1u << (e - 103u) : 0u;
+    return b * 0x00010001u;
 }
 __device__ __forceinline__ void cvt4(uint32_t q, uint32_t (&h)[4]) {
     asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
@@ -149,14 +165,16 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+#ifdef DSX_TRACE
+#define DSX_TR(ev, idx) do { if (blockIdx.x == 0 && (idx) < 512 && a.trace) a.trace[(ev) * 512 + (idx)] = clock64(); } while (0)
+#else
+#define DSX_TR(ev, idx) do {} while (0)
+#endif
+
 struct GemmArgs {
+    long long* trace;          // debug timeline (only with -DDSX_TRACE)
     const PrefillSeg* segs;
     const int32_t* n_segs;
-    const uint8_t* nib;        // routed plane base
-    const uint8_t* sc;
-    int64_t nib_slot_stride, sc_slot_stride;
-    const uint8_t* sh_nib;     // shared expert plane (may be null)
-    const uint8_t* sh_sc;
     int n_local;               // seg.expert == n_local -> shared expert
     int K;                     // reduction length (hidden for gate/up, ffn for down)
     int rows;                  // output rows of the matrix (ffn for gate/up, hidden for down)
@@ -173,7 +191,9 @@ struct GemmArgs {
 
 template <bool GATE_UP>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a) {
+prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_nib,
+                    const __grid_constant__ CUtensorMap tmap_sc, const __grid_constant__ CUtensorMap tmap_sh_nib,
+                    const __grid_constant__ CUtensorMap tmap_sh_sc, const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -181,21 +201,20 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
     const uint32_t bar0 = sbase + kSmemBar;
     // barrier indices
-    constexpr int RAW_FULL = 0, RAW_EMPTY = RAW_FULL + kRawStages, A_FULL = RAW_EMPTY + kRawStages, A_EMPTY = A_FULL + kAStages,
-                  B_FULL = A_EMPTY + kAStages, B_EMPTY = B_FULL + kBStages, ACC_FULL = B_EMPTY + kBStages, ACC_EMPTY = ACC_FULL + 1;
+    // AB_FULL[s]: converted weights (8 converter warps) and token tile (TMA bytes) of stage s are in
+    // shared memory; AB_EMPTY[s]: the MMAs reading stage s have completed (one tcgen05.commit).
+    constexpr int RAW_FULL = 0, RAW_EMPTY = RAW_FULL + kRawStages, AB_FULL = RAW_EMPTY + kRawStages, AB_EMPTY = AB_FULL + kAStages,
+                  ACC_FULL = AB_EMPTY + kAStages, ACC_EMPTY = ACC_FULL + 1;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_w = reinterpret_cast<float*>(smem + kSmemMisc + 16);          // routing weight per tile column
-    int32_t* s_row = reinterpret_cast<int32_t*>(s_w + kSegRows);           // output row per tile column
     (void)bars;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kRawStages; i++) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), kConvWarps); }
-        for (int i = 0; i < kAStages; i++) { mbar_init(bar(A_FULL + i), kConvWarps); mbar_init(bar(A_EMPTY + i), 1); }
-        for (int i = 0; i < kBStages; i++) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
+        for (int i = 0; i < kAStages; i++) { mbar_init(bar(AB_FULL + i), kConvWarps + 1); mbar_init(bar(AB_EMPTY + i), 1); }
         mbar_init(bar(ACC_FULL), 1);
-        mbar_init(bar(ACC_EMPTY), 4);
+        mbar_init(bar(ACC_EMPTY), 4 + kConvWarps);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -214,82 +233,147 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a
     const int n_kc = a.K / kChunkK;
     const int n_kt = a.K / 64;                          // MXFP4 column tiles per row tile
 
+    // Accumulator read-out of one tile, shared by the 4 epilogue warps (rank 0) and the 8 converter
+    // warps (ranks 1, 2), which are idle once a tile's last chunk is converted: warp w may read
+    // TMEM lanes 32*(w%4)..+31, so each lane quarter has three warps that split the 32-column
+    // chunks of the tile between them.
+    auto epilogue = [&](int tile, int rank) {
+        const PrefillSeg seg = a.segs[tile / n_mb];
+        const int mb = tile % n_mb;
+        const bool sh = seg.expert == a.n_local;
+        const int q = warp & 3;
+        tc_fence_after();
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const int r_in = q * 32 + lane;           // row inside a 128-row half
+        for (int c0 = 32 * rank; c0 < seg.n; c0 += 96) {
+            // lane j of the warp fetches the routing weight / output row of column c0 + j
+            float wv = 0.f;
+            int orow = 0;
+            if (c0 + lane < seg.n) {
+                if (sh) { wv = 1.0f; orow = seg.row0 + c0 + lane; }
+                else { const int ts = a.perm[seg.row0 + c0 + lane]; wv = a.route_w[ts]; orow = ts; }
+            }
+            uint32_t v0[32], v1[32];
+            tc_ld32(lane_addr + (uint32_t)c0, v0);
+            tc_ld32(lane_addr + 256u + (uint32_t)c0, v1);
+            tc_wait_ld();
+            if (GATE_UP) {
+                __half* dst = a.mid + (int64_t)(seg.row0 + c0) * a.mid_stride + mb * 128 + r_in;
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const float wj = __shfl_sync(0xFFFFFFFFu, wv, j);
+                    if (c0 + j < seg.n) {
+                        float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
+                        if (a.clamp > 1.0e-6f) {
+                            gv = fminf(gv, a.clamp);
+                            uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
+                        }
+                        const float sig = __fdividef(1.0f, 1.0f + __expf(-gv));
+                        dst[(int64_t)j * a.mid_stride] = __float2half_rn(gv * sig * uv * wj);
+                    }
+                }
+            } else {
+                const int h = mb * 256 + r_in;
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int rj = __shfl_sync(0xFFFFFFFFu, orow, j);
+                    if (c0 + j < seg.n) {
+                        float* dst = a.partial + (int64_t)rj * a.rows + h;
+                        dst[0] = __uint_as_float(v0[j]);
+                        dst[128] = __uint_as_float(v1[j]);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncwarp();
+    };
+
     if (warp == 0) {
-        // ------------------------------------------------------------ producer
+        // ------------------------------------------------- packed-weight producer
         if (lane == 0) {
-            uint32_t rcnt = 0, bcnt = 0;
+            uint32_t rcnt = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 const int mb = tile % n_mb;
                 const bool sh = seg.expert == a.n_local;
-                const uint8_t* nib = sh ? a.sh_nib : a.nib + (int64_t)seg.expert * a.nib_slot_stride;
-                const uint8_t* sc = sh ? a.sh_sc : a.sc + (int64_t)seg.expert * a.sc_slot_stride;
+                const CUtensorMap* m_nib = sh ? &tmap_sh_nib : &tmap_nib;
+                const CUtensorMap* m_sc = sh ? &tmap_sh_sc : &tmap_sc;
+                const int slot = sh ? 0 : seg.expert;
+                constexpr int kRtPerTile = GATE_UP ? 8 : 16;   // 16-row tiles per stage (gate/up: each carries a gate and an up sub-tile)
+                if (tile == (int)blockIdx.x)   // first tile: warm L2 with the first chunks
+                    for (int kc = 0; kc < kPrefetchAhead && kc < n_kc; kc++) tma_prefetch_4d(m_nib, 0, kc, mb * kRtPerTile, slot);
+                // the tile this block runs next (its first chunks are prefetched while this one finishes)
+                const int ntile = tile + gridDim.x;
+                PrefillSeg nseg = seg;
+                int nmb = mb;
+                if (ntile < n_tiles) { nseg = a.segs[ntile / n_mb]; nmb = ntile % n_mb; }
+                const bool nsh = nseg.expert == a.n_local;
                 for (int kc = 0; kc < n_kc && ok; kc++) {
-                    {   // packed weights of this chunk
-                        const int s = rcnt % kRawStages;
-                        ok = mbar_wait(bar(RAW_EMPTY + s), ((rcnt / kRawStages) & 1u) ^ 1u, abort_flag);
-                        if (!ok) break;
-                        const uint32_t dst = sbase + kSmemRaw + s * kRawBytes;
-                        mbar_expect_tx(bar(RAW_FULL + s), kRawBytes);
-                        if (GATE_UP) {  // 8 row tiles, each [gate | up] sub-tile pair contiguous
-#pragma unroll 1
-                            for (int r = 0; r < 8; r++) {
-                                const int64_t sub = ((int64_t)(mb * 8 + r) * n_kt + kc) * 2;
-                                bulk_g2s(dst + r * 1024, nib + sub * kSubNibBytes, 1024, bar(RAW_FULL + s));
-                                bulk_g2s(dst + kRawNib + r * 64, sc + sub * kSubScBytes, 64, bar(RAW_FULL + s));
-                            }
-                        } else {
-#pragma unroll 1
-                            for (int r = 0; r < 16; r++) {
-                                const int64_t sub = (int64_t)(mb * 16 + r) * n_kt + kc;
-                                bulk_g2s(dst + r * 512, nib + sub * kSubNibBytes, 512, bar(RAW_FULL + s));
-                                bulk_g2s(dst + kRawNib + r * 32, sc + sub * kSubScBytes, 32, bar(RAW_FULL + s));
-                            }
-                        }
-                        rcnt++;
-                    }
-                    {   // token tile of this chunk
-                        const int s = bcnt % kBStages;
-                        ok = mbar_wait(bar(B_EMPTY + s), ((bcnt / kBStages) & 1u) ^ 1u, abort_flag);
-                        if (!ok) break;
-                        mbar_expect_tx(bar(B_FULL + s), kBBytes);
-                        tma_load_2d(sbase + kSmemB + s * kBBytes, &tmap_b, kc * kChunkK, seg.row0, bar(B_FULL + s));
-                        bcnt++;
-                    }
+                    const int pk = kc + kPrefetchAhead;
+                    if (pk < n_kc) tma_prefetch_4d(m_nib, 0, pk, mb * kRtPerTile, slot);
+                    else if (ntile < n_tiles) tma_prefetch_4d(nsh ? &tmap_sh_nib : &tmap_nib, 0, pk - n_kc, nmb * kRtPerTile, nsh ? 0 : nseg.expert);
+                    // one box of codes, one of scales
+                    const int s = rcnt % kRawStages;
+                    ok = mbar_wait(bar(RAW_EMPTY + s), ((rcnt / kRawStages) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    DSX_TR(0, rcnt);
+                    const uint32_t dst = sbase + kSmemRaw + s * kRawBytes;
+                    mbar_expect_tx(bar(RAW_FULL + s), kRawBytes);
+                    tma_load_4d(dst, m_nib, 0, kc, mb * kRtPerTile, slot, bar(RAW_FULL + s));
+                    tma_load_4d(dst + kRawNib, m_sc, 0, kc, mb * kRtPerTile, slot, bar(RAW_FULL + s));
+                    rcnt++;
+                }
+            }
+        }
+    } else if (warp == kBProducerWarp) {
+        // ---------------------------------------------------- token-tile producer
+        if (lane == 0) {
+            uint32_t bcnt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const PrefillSeg seg = a.segs[tile / n_mb];
+                for (int kc = 0; kc < n_kc && ok; kc++) {
+                    const int s = bcnt % kBStages;
+                    ok = mbar_wait(bar(AB_EMPTY + s), ((bcnt / kBStages) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    DSX_TR(1, bcnt);
+                    mbar_expect_tx(bar(AB_FULL + s), kBBytes);
+                    tma_load_2d(sbase + kSmemB + s * kBBytes, &tmap_b, kc * kChunkK, seg.row0, bar(AB_FULL + s));
+                    bcnt++;
                 }
             }
         }
     } else if (warp == 1) {
         // ----------------------------------------------------------- MMA issue
         if (lane == 0) {
-            uint32_t acnt = 0, bcnt = 0, tcnt = 0;
+            uint32_t acnt = 0, tcnt = 0;
             bool ok = true;
+            const uint64_t da0 = umma_desc(sbase + kSmemA), db0 = umma_desc(sbase + kSmemB);   // stage 0; stages are 2048 units apart
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 const int n16 = max(16, (seg.n + 15) & ~15);
                 const uint32_t idesc = umma_idesc(n16);
-                ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // epilogue has drained TMEM
+                ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // the previous tile's accumulators are drained
                 if (!ok) break;
                 tc_fence_after();
                 for (int kc = 0; kc < n_kc && ok; kc++) {
-                    const int sa = acnt % kAStages, sb = bcnt % kBStages;
-                    ok = mbar_wait(bar(A_FULL + sa), (acnt / kAStages) & 1u, abort_flag) &&
-                         mbar_wait(bar(B_FULL + sb), (bcnt / kBStages) & 1u, abort_flag);
+                    const int sa = acnt % kAStages;
+                    ok = mbar_wait(bar(AB_FULL + sa), (acnt / kAStages) & 1u, abort_flag);
                     if (!ok) break;
+                    DSX_TR(6, acnt);
                     tc_fence_after();
-                    const uint64_t da = umma_desc(sbase + kSmemA + sa * kABytes);
-                    const uint64_t db = umma_desc(sbase + kSmemB + sb * kBBytes);
+                    const uint64_t da = da0 + (uint64_t)(sa * (kABytes >> 4)), db = db0 + (uint64_t)(sa * (kBBytes >> 4));
 #pragma unroll
                     for (int ks = 0; ks < kChunkK / 16; ks++) {
                         const uint32_t acc = (kc | ks) != 0 ? 1u : 0u;
                         tc_mma_f16(tmem_base, da + 2u * ks, db + 2u * ks, idesc, acc);
                         tc_mma_f16(tmem_base + 256u, da + (128u * 128u >> 4) + 2u * ks, db + 2u * ks, idesc, acc);
                     }
-                    tc_commit(bar(A_EMPTY + sa));   // arrives when the MMAs above have read their operands
-                    tc_commit(bar(B_EMPTY + sb));
+                    tc_commit(bar(AB_EMPTY + sa));   // arrives when the MMAs above have read their operands
+                    DSX_TR(7, acnt);
                     acnt++;
-                    bcnt++;
                 }
                 if (ok) tc_commit(bar(ACC_FULL));
                 tcnt++;
@@ -298,110 +382,78 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs a
     } else if (warp < 2 + kConvWarps) {
         // ---------------------------------------------------------- converters
         const int cw = warp - 2, g = lane >> 2, t = lane & 3;
-        uint32_t rcnt = 0, acnt = 0;
+        uint32_t rcnt = 0, acnt = 0, tcnt = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             for (int kc = 0; kc < n_kc && ok; kc++) {
                 const int sr = rcnt % kRawStages, sa = acnt % kAStages;
-                ok = mbar_wait(bar(RAW_FULL + sr), (rcnt / kRawStages) & 1u, abort_flag) &&
-                     mbar_wait(bar(A_EMPTY + sa), ((acnt / kAStages) & 1u) ^ 1u, abort_flag);
+                ok = mbar_wait(bar(RAW_FULL + sr), (rcnt / kRawStages) & 1u, abort_flag);
+                if (cw == 0 && lane == 0) DSX_TR(2, rcnt);
+                ok = ok && mbar_wait(bar(AB_EMPTY + sa), ((acnt / kAStages) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
+                if (cw == 0 && lane == 0) DSX_TR(3, rcnt);
                 const uint8_t* raw = smem + kSmemRaw + sr * kRawBytes;
                 uint8_t* A = smem + kSmemA + sa * kABytes;
+                // both sub-tiles of this warp: loads first, then the conversions
+                uint4 wq[2];
+                uint32_t sw[2];
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
                     const int st = cw + 8 * half;   // sub-tile of the raw stage
+                    wq[half] = *reinterpret_cast<const uint4*>(raw + st * kSubNibBytes + lane * 16);
+                    sw[half] = *reinterpret_cast<const uint32_t*>(raw + kRawNib + st * kSubScBytes + g * 4);
+                }
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    const int st = cw + 8 * half;
                     // gate/up stage order is [rt][gate, up]; A rows 0..127 = gate, 128..255 = up
                     const int row_base = GATE_UP ? ((st & 1) * 128 + (st >> 1) * 16) : st * 16;
-                    const uint4 wq = *reinterpret_cast<const uint4*>(raw + st * kSubNibBytes + lane * 16);
-                    const uint32_t sw = *reinterpret_cast<const uint32_t*>(raw + kRawNib + st * kSubScBytes + g * 4);
-                    const uint32_t w[4] = {wq.x, wq.y, wq.z, wq.w};
+                    const uint32_t w[4] = {wq[half].x, wq[half].y, wq[half].z, wq[half].w};
+                    uint8_t* arow = A + (uint32_t)((row_base + g) >> 3) * 1024u + (uint32_t)g * 128u;
 #pragma unroll
-                    for (int b = 0; b < 2; b++) {
-                        const uint32_t m0 = scale_h2((sw >> (8 * b)) & 0xFFu), m1 = scale_h2((sw >> (16 + 8 * b)) & 0xFFu);
+                    for (int bi = 0; bi < 2; bi++) {
+                        // odd row groups take the two scale blocks in the opposite order, so the eight
+                        // lanes of a quarter warp store to eight different 16-byte bank groups
+                        const int b = bi ^ (g & 1);
+                        const uint32_t m0 = scale_h2((sw[half] >> (8 * b)) & 0xFFu), m1 = scale_h2((sw[half] >> (16 + 8 * b)) & 0xFFu);
                         uint32_t p[4], q[4];
-                        cvt4(w[2 * b], p);       // (g; c0,c1) (g+8; c0,c1) (g; c2,c3) (g+8; c2,c3)
-                        cvt4(w[2 * b + 1], q);   // same for columns c4..c7
+                        cvt4(b ? w[2] : w[0], p);   // (g; c0,c1) (g+8; c0,c1) (g; c2,c3) (g+8; c2,c3)
+                        cvt4(b ? w[3] : w[1], q);   // same for columns c4..c7
                         const uint4 r0 = make_uint4(hmul2(p[0], m0), hmul2(p[2], m0), hmul2(q[0], m0), hmul2(q[2], m0));
                         const uint4 r1 = make_uint4(hmul2(p[1], m1), hmul2(p[3], m1), hmul2(q[1], m1), hmul2(q[3], m1));
-                        const int j = 4 * b + t;   // 16-byte chunk of the 128-byte row
-                        const int R = row_base + g;
-                        const uint32_t off = (uint32_t)(R >> 3) * 1024u + (uint32_t)g * 128u + (uint32_t)((j ^ g) << 4);
-                        *reinterpret_cast<uint4*>(A + off) = r0;
-                        *reinterpret_cast<uint4*>(A + off + 1024u) = r1;   // row R + 8: next 8-row group, same swizzle phase
+                        const uint32_t off = (uint32_t)(((4 * b + t) ^ g) << 4);   // 16-byte chunk 4b+t, swizzled by the row
+                        *reinterpret_cast<uint4*>(arow + off) = r0;
+                        *reinterpret_cast<uint4*>(arow + off + 1024u) = r1;   // row + 8: next 8-row group, same swizzle phase
                     }
                 }
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(bar(A_FULL + sa));
+                    mbar_arrive(bar(AB_FULL + sa));
                     mbar_arrive(bar(RAW_EMPTY + sr));
                 }
+                if (cw == 0 && lane == 0) DSX_TR(4, rcnt);
                 rcnt++;
                 acnt++;
             }
+            // the tile's operands are all converted: help drain its accumulators
+            if (ok) ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
+            if (!ok) break;
+            epilogue(tile, 1 + (cw >> 2));
+            if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
+            tcnt++;
         }
-    } else {
+    } else if (warp < kEpiWarp0 + 4) {
         // ------------------------------------------------------------ epilogue
-        const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        const int et = threadIdx.x - kEpiWarp0 * 32;  // 0..127
         uint32_t tcnt = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const PrefillSeg seg = a.segs[tile / n_mb];
-            const int mb = tile % n_mb;
-            const bool sh = seg.expert == a.n_local;
-            // per-column routing weight and output row
-            for (int c = et; c < kSegRows; c += 128) {
-                float wv = 0.f;
-                int orow = 0;
-                if (c < seg.n) {
-                    if (sh) { wv = 1.0f; orow = seg.row0 + c; }
-                    else { const int ts = a.perm[seg.row0 + c]; wv = a.route_w[ts]; orow = ts; }
-                }
-                s_w[c] = wv;
-                s_row[c] = orow;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
             ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
             if (!ok) break;
-            tc_fence_after();
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-            const int r_in = q * 32 + lane;           // row inside a 128-row half
-            for (int c0 = 0; c0 < seg.n; c0 += 32) {
-                uint32_t v0[32], v1[32];
-                tc_ld32(lane_addr + (uint32_t)c0, v0);
-                tc_ld32(lane_addr + 256u + (uint32_t)c0, v1);
-                tc_wait_ld();
-                if (GATE_UP) {
-                    const int f = mb * 128 + r_in;
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (c0 + j < seg.n) {
-                            float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
-                            if (a.clamp > 1.0e-6f) {
-                                gv = fminf(gv, a.clamp);
-                                uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
-                            }
-                            const float sig = 1.0f / (1.0f + __expf(-gv));
-                            a.mid[(int64_t)(seg.row0 + c0 + j) * a.mid_stride + f] = __float2half_rn(gv * sig * uv * s_w[c0 + j]);
-                        }
-                    }
-                } else {
-                    const int h = mb * 256 + r_in;
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (c0 + j < seg.n) {
-                            float* dst = a.partial + (int64_t)s_row[c0 + j] * a.rows + h;
-                            dst[0] = __uint_as_float(v0[j]);
-                            dst[128] = __uint_as_float(v1[j]);
-                        }
-                    }
-                }
-            }
-            tc_fence_before();
-            asm volatile("bar.sync 1, 128;" ::: "memory");   // all four warps are done with TMEM and the per-tile arrays
+            if (threadIdx.x == kEpiWarp0 * 32) DSX_TR(8, tcnt);
+            epilogue(tile, 0);
             if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
+            if (threadIdx.x == kEpiWarp0 * 32) DSX_TR(9, tcnt);
             tcnt++;
         }
     }
@@ -500,6 +552,44 @@ int encode_rows_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
     return DSX_OK;
 }
 
+// One plane of packed weights as [slot][row tile][column tile][inner bytes as u32]; the box is all
+// `box_rt` row tiles of one column tile, landing in shared memory as [row tile][inner bytes].
+int encode_plane_map(CUtensorMap* map, const void* base, int inner_bytes, int64_t n_kt, int64_t n_rt, int64_t n_slots,
+                     int64_t slot_stride, int box_rt) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        DSX_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !p) return set_error(DSX_ERR_UNSUPPORTED, "driver has no cuTensorMapEncodeTiled");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint64_t dims[4] = {(cuuint64_t)(inner_bytes / 4), (cuuint64_t)n_kt, (cuuint64_t)n_rt, (cuuint64_t)n_slots};
+    const cuuint64_t strides[3] = {(cuuint64_t)inner_bytes, (cuuint64_t)(n_kt * inner_bytes), (cuuint64_t)slot_stride};
+    const cuuint32_t box[4] = {(cuuint32_t)(inner_bytes / 4), 1, (cuuint32_t)box_rt, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(DSX_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled (weights) failed with %d", (int)r);
+    return DSX_OK;
+}
+
+// (Re-)encode the weight maps when the layer points at other planes.
+int map_weights(PrefillWorkspace* ws, int which, const uint8_t* gu_nib, const uint8_t* gu_sc, const uint8_t* dn_nib,
+                const uint8_t* dn_sc, int64_t gu_nib_stride, int64_t gu_sc_stride, int64_t dn_nib_stride, int64_t dn_sc_stride,
+                int n_slots) {
+    if (ws->mapped_gu_nib[which] == gu_nib && ws->mapped_dn_nib[which] == dn_nib) return DSX_OK;
+    const int64_t H = ws->H, F = ws->F;
+    if (int rc = encode_plane_map(&ws->tmap_gu_nib[which], gu_nib, 2 * kSubNibBytes, H / 64, F / 16, n_slots, gu_nib_stride, 8)) return rc;
+    if (int rc = encode_plane_map(&ws->tmap_gu_sc[which], gu_sc, 2 * kSubScBytes, H / 64, F / 16, n_slots, gu_sc_stride, 8)) return rc;
+    if (int rc = encode_plane_map(&ws->tmap_dn_nib[which], dn_nib, kSubNibBytes, F / 64, H / 16, n_slots, dn_nib_stride, 16)) return rc;
+    if (int rc = encode_plane_map(&ws->tmap_dn_sc[which], dn_sc, kSubScBytes, F / 64, H / 16, n_slots, dn_sc_stride, 16)) return rc;
+    ws->mapped_gu_nib[which] = gu_nib;
+    ws->mapped_dn_nib[which] = dn_nib;
+    return DSX_OK;
+}
+
 }  // namespace
 
 int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid) {
@@ -545,19 +635,53 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(c.x, c.perm, c.offsets, c.n_local, c.n_used, P, c.T,
                                                                       c.with_shared ? 1 : 0, cfg.hidden, ws->xperm);
     DSX_LAUNCHED();
+    if (int rc = map_weights(ws, 0, c.gu_nib, c.gu_sc, c.dn_nib, c.dn_sc, c.gu_nib_stride, c.gu_sc_stride, c.dn_nib_stride,
+                             c.dn_sc_stride, c.n_local))
+        return rc;
+    const int shi = c.with_shared ? 1 : 0;   // without a shared expert the shared maps alias the routed ones (never used)
+    if (c.with_shared)
+        if (int rc = map_weights(ws, 1, c.sh_gu_nib, c.sh_gu_sc, c.sh_dn_nib, c.sh_dn_sc, c.gu_nib_stride, c.gu_sc_stride,
+                                 c.dn_nib_stride, c.dn_sc_stride, 1))
+            return rc;
     GemmArgs g{};
+#ifdef DSX_TRACE
+    static long long* trace_buf = nullptr;
+    if (!trace_buf) { cudaMalloc((void**)&trace_buf, 2 * 10 * 512 * 8); }
+    cudaMemsetAsync(trace_buf, 0, 2 * 10 * 512 * 8, stream);
+    g.trace = trace_buf;
+#endif
     g.segs = ws->segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
     g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.error_word = c.error_word;
     // gate/up: K = hidden, rows = ffn
-    g.nib = c.gu_nib; g.sc = c.gu_sc; g.nib_slot_stride = c.gu_nib_stride; g.sc_slot_stride = c.gu_sc_stride;
-    g.sh_nib = c.sh_gu_nib; g.sh_sc = c.sh_gu_sc; g.K = cfg.hidden; g.rows = cfg.ffn;
-    prefill_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_x, g);
+    g.K = cfg.hidden; g.rows = cfg.ffn;
+    prefill_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_x, ws->tmap_gu_nib[0], ws->tmap_gu_sc[0],
+                                                                           ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
     DSX_LAUNCHED();
     // down: K = ffn, rows = hidden
-    g.nib = c.dn_nib; g.sc = c.dn_sc; g.nib_slot_stride = c.dn_nib_stride; g.sc_slot_stride = c.dn_sc_stride;
-    g.sh_nib = c.sh_dn_nib; g.sh_sc = c.sh_dn_sc; g.K = cfg.ffn; g.rows = cfg.hidden;
-    prefill_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mid, g);
+    g.K = cfg.ffn; g.rows = cfg.hidden;
+#ifdef DSX_TRACE
+    g.trace = trace_buf + 10 * 512;
+#endif
+    prefill_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0],
+                                                                            ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
     DSX_LAUNCHED();
+#ifdef DSX_TRACE
+    {
+        static long long host[2 * 10 * 512];
+        cudaStreamSynchronize(stream);
+        cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
+        FILE* f = fopen("gpurun_out/prefill_trace.txt", "w");
+        if (f) {
+            for (int k = 0; k < 2; k++)
+                for (int ev = 0; ev < 10; ev++) {
+                    fprintf(f, "k%d ev%d", k, ev);
+                    for (int i = 0; i < 512; i++) fprintf(f, " %lld", host[(k * 10 + ev) * 512 + i]);
+                    fprintf(f, "\n");
+                }
+            fclose(f);
+        }
+    }
+#endif
     return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr,
                           c.expert_lo, c.n_local, c.out, stream);
 }

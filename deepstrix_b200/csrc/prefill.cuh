@@ -24,6 +24,10 @@ struct PrefillWorkspace {
     int32_t seg_cap = 0;
     CUtensorMap tmap_x;        // xperm as [cap_rows, H], box 64 x 256, 128-byte swizzle
     CUtensorMap tmap_mid;      // mid   as [cap_rows, F]
+    // packed-weight planes as 4-D tensors [slot][row tile][column tile][bytes as u32]; index 0 routed, 1 shared
+    CUtensorMap tmap_gu_nib[2], tmap_gu_sc[2], tmap_dn_nib[2], tmap_dn_sc[2];
+    const void* mapped_gu_nib[2] = {nullptr, nullptr};   // planes the maps above were encoded for
+    const void* mapped_dn_nib[2] = {nullptr, nullptr};
 };
 
 struct PrefillCall {
