@@ -36,6 +36,11 @@ struct dsx_expert_store {
     uint8_t* stage = nullptr;  // device staging for host sources
     size_t stage_bytes = 0;
     size_t device_bytes = 0;
+    // largest E8M0 scale byte seen by a load (device word, folded by every load); the host copy is
+    // refreshed lazily.  The tensor-core path holds weights as f16 and needs every scale <= 2^13.
+    uint32_t* d_scale_max = nullptr;
+    mutable uint32_t h_scale_max = 0;
+    mutable bool scale_dirty = false;
 };
 
 struct dsx_moe_layer {
@@ -216,6 +221,8 @@ int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int6
     if (e == cudaSuccess) e = cudaMalloc(&s->gu_sc, n * s->gu_sc_stride);
     if (e == cudaSuccess) e = cudaMalloc(&s->dn_nib, n * s->dn_nib_stride);
     if (e == cudaSuccess) e = cudaMalloc(&s->dn_sc, n * s->dn_sc_stride);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&s->d_scale_max, 256);
+    if (e == cudaSuccess) e = cudaMemset(s->d_scale_max, 0, 256);
     if (e != cudaSuccess) {
         dsx_expert_store_destroy(s);
         return set_error((int)e, "expert_store: cudaMalloc failed: %s", cudaGetErrorString(e));
@@ -227,7 +234,7 @@ int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int6
 
 int dsx_expert_store_destroy(dsx_expert_store* s) {
     if (!s) return DSX_OK;
-    cudaFree(s->gu_nib); cudaFree(s->gu_sc); cudaFree(s->dn_nib); cudaFree(s->dn_sc); cudaFree(s->stage);
+    cudaFree(s->gu_nib); cudaFree(s->gu_sc); cudaFree(s->dn_nib); cudaFree(s->dn_sc); cudaFree(s->stage); cudaFree(s->d_scale_max);
     delete s;
     return DSX_OK;
 }
@@ -259,9 +266,16 @@ int dsx_expert_store_load(dsx_expert_store* st, int slot, int which, int src_lay
     const int64_t nstr = down ? st->dn_nib_stride : st->gu_nib_stride, sstr = down ? st->dn_sc_stride : st->gu_sc_stride;
     const int pair_stride = down ? 1 : 2, pair_index = which == DSX_MAT_UP ? 1 : 0;
     const int first = slot < 0 ? 0 : slot, count = slot < 0 ? st->n_slots : 1;
+    auto fold_scales = [&]() -> int {  // MXFP4 scale planes hold nothing but E8M0 bytes
+        st->scale_dirty = true;
+        if (st->fmt != DSX_FMT_MXFP4) return DSX_OK;
+        return launch_max_byte(sc + first * sstr, (int64_t)count * sstr, st->d_scale_max, stream);
+    };
     if (src_on_device) {
-        return launch_repack(st->fmt, src_layout, (const uint8_t*)q, (const uint8_t*)s, rows, K, nib + first * nstr,
-                             sc + first * sstr, pair_stride, pair_index, count, (int64_t)qb, (int64_t)sb, nstr, sstr, stream);
+        if (int rc = launch_repack(st->fmt, src_layout, (const uint8_t*)q, (const uint8_t*)s, rows, K, nib + first * nstr,
+                                   sc + first * sstr, pair_stride, pair_index, count, (int64_t)qb, (int64_t)sb, nstr, sstr, stream))
+            return rc;
+        return fold_scales();
     }
     // host source: stage through device memory in batches
     const size_t qpad = (qb + 255) & ~(size_t)255, spad = (sb + 255) & ~(size_t)255;
@@ -286,7 +300,7 @@ int dsx_expert_store_load(dsx_expert_store* st, int slot, int which, int src_lay
             return rc;
         DSX_CUDA(cudaStreamSynchronize(stream));  // the staging buffer is reused
     }
-    return DSX_OK;
+    return fold_scales();
 }
 
 int dsx_expert_store_unpack(const dsx_expert_store* st, int slot, int which, void* q_out, void* s_out, dsx_stream_t stream) {
@@ -309,6 +323,8 @@ int dsx_expert_store_clone(const dsx_expert_store* src, dsx_expert_store** dst, 
     if (e == cudaSuccess) e = cudaMemcpyAsync(d->gu_sc, src->gu_sc, n * src->gu_sc_stride, cudaMemcpyDeviceToDevice, stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(d->dn_nib, src->dn_nib, n * src->dn_nib_stride, cudaMemcpyDeviceToDevice, stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(d->dn_sc, src->dn_sc, n * src->dn_sc_stride, cudaMemcpyDeviceToDevice, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d->d_scale_max, src->d_scale_max, 4, cudaMemcpyDeviceToDevice, stream);
+    d->scale_dirty = true;
     if (e != cudaSuccess) {
         dsx_expert_store_destroy(d);
         return set_error((int)e, "expert_store_clone: copy failed: %s", cudaGetErrorString(e));
@@ -471,13 +487,26 @@ int dsx_moe_layer_set_weights(dsx_moe_layer* L, const dsx_expert_store* routed, 
     return DSX_OK;
 }
 
+// The tensor-core path multiplies f16 weights: E2M1 (<= 6) x 2^(e-127) must stay finite in f16, i.e.
+// e <= 140.  Reads the store's folded maximum once after its last load (synchronises then).
+static bool scales_fit_f16(const dsx_expert_store* st) {
+    if (st->fmt != DSX_FMT_MXFP4) return true;
+    if (st->scale_dirty) {
+        uint32_t v = 255;
+        if (cudaMemcpy(&v, st->d_scale_max, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+        st->h_scale_max = v;
+        st->scale_dirty = false;
+    }
+    return st->h_scale_max <= 140u;
+}
+
 // picks -> out.  expert_lo / n_local select the owned id range (0 / n_expert for a full layer).
 static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, const int32_t* selected, const float* weights,
                         int expert_lo, bool filter_picks, int with_shared, __nv_bfloat16* out, cudaStream_t stream) {
     const dsx_moe_config& c = L->cfg;
     const int k = c.router.n_used, n_local = L->routed->n_slots;
     const bool shared = with_shared && L->shared != nullptr;
-    if (prefill_wanted(L->pf, c, L->routed->fmt, T)) {
+    if (prefill_wanted(L->pf, c, L->routed->fmt, T) && scales_fit_f16(L->routed) && (!shared || scales_fit_f16(L->shared))) {
         PrefillCall pc{};
         pc.x = x; pc.T = T; pc.selected = selected; pc.route_w = weights; pc.expert_lo = expert_lo; pc.n_local = n_local;
         pc.filter_picks = filter_picks; pc.with_shared = shared; pc.out = out;

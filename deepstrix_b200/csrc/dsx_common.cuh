@@ -147,6 +147,8 @@ int launch_repack(int fmt, int src_layout, const uint8_t* q, const uint8_t* s, i
 int launch_unpack(int fmt, const uint8_t* nib, const uint8_t* sc, int64_t rows, int64_t K, int pair_stride,
                   int pair_index, uint8_t* q_out, uint8_t* s_out, cudaStream_t stream);
 
+int launch_max_byte(const uint8_t* p, int64_t bytes, uint32_t* out, cudaStream_t stream);
+
 // router.cu
 int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int n_expert, int64_t H, float* logits,
                          cudaStream_t stream);

@@ -23,8 +23,6 @@
 // clamp + SwiGLU + routing weight (gate/up) and store mid (f16) or the per-pick
 // partial rows (f32).  Every wait is bounded; on a timeout the block raises an
 // abort flag, all roles drain, TMEM is freed and the layer's error word is set.
-#include <stdio.h>
-
 #include "prefill.cuh"
 
 namespace dsx {
@@ -84,11 +82,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1u;
     return false;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
                  "l"(map), "r"(x), "r"(y), "r"(bar)
@@ -109,12 +102,51 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// The eight MMAs of one 64-column chunk (4 k16 steps x 2 row halves) in one block of PTX: the
+// issuing thread is latency-bound on its own scalar instructions, so the descriptors are formed
+// with one 32-bit add each (all operands of a stage share the high descriptor word).
+// a_lo / b_lo: low descriptor words of the stage's A and B tiles; second row half = +1024 (16 KB).
+__device__ __forceinline__ void tc_mma_chunk(uint32_t t0, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b32 t1, x, y;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "add.u32 t1, %0, 256;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "add.u32 x, %1, 1024;\n\t"
+        "mov.b64 da, {x, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [t1], da, db, %4, p;\n\t"
+        "setp.eq.b32 p, %4, %4;\n\t"
+        "add.u32 x, %1, 2;\n\t"
+        "add.u32 y, %2, 2;\n\t"
+        "mov.b64 da, {x, %3};\n\t"
+        "mov.b64 db, {y, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "add.u32 x, %1, 1026;\n\t"
+        "mov.b64 da, {x, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [t1], da, db, %4, p;\n\t"
+        "add.u32 x, %1, 4;\n\t"
+        "add.u32 y, %2, 4;\n\t"
+        "mov.b64 da, {x, %3};\n\t"
+        "mov.b64 db, {y, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "add.u32 x, %1, 1028;\n\t"
+        "mov.b64 da, {x, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [t1], da, db, %4, p;\n\t"
+        "add.u32 x, %1, 6;\n\t"
+        "add.u32 y, %2, 6;\n\t"
+        "mov.b64 da, {x, %3};\n\t"
+        "mov.b64 db, {y, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "add.u32 x, %1, 1030;\n\t"
+        "mov.b64 da, {x, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [t1], da, db, %4, p;\n\t"
+        "}"
+        ::"r"(t0), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -165,14 +197,7 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-#ifdef DSX_TRACE
-#define DSX_TR(ev, idx) do { if (blockIdx.x == 0 && (idx) < 512 && a.trace) a.trace[(ev) * 512 + (idx)] = clock64(); } while (0)
-#else
-#define DSX_TR(ev, idx) do {} while (0)
-#endif
-
 struct GemmArgs {
-    long long* trace;          // debug timeline (only with -DDSX_TRACE)
     const PrefillSeg* segs;
     const int32_t* n_segs;
     int n_local;               // seg.expert == n_local -> shared expert
@@ -231,7 +256,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
     const int n_mb = a.rows / (GATE_UP ? 128 : 256);   // 256-row tiles (gate/up: 128 gate + 128 up)
     const int n_tiles = n_segs * n_mb;
     const int n_kc = a.K / kChunkK;
-    const int n_kt = a.K / 64;                          // MXFP4 column tiles per row tile
 
     // Accumulator read-out of one tile, shared by the 4 epilogue warps (rank 0) and the 8 converter
     // warps (ranks 1, 2), which are idle once a tile's last chunk is converted: warp w may read
@@ -318,7 +342,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                     const int s = rcnt % kRawStages;
                     ok = mbar_wait(bar(RAW_EMPTY + s), ((rcnt / kRawStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
-                    DSX_TR(0, rcnt);
                     const uint32_t dst = sbase + kSmemRaw + s * kRawBytes;
                     mbar_expect_tx(bar(RAW_FULL + s), kRawBytes);
                     tma_load_4d(dst, m_nib, 0, kc, mb * kRtPerTile, slot, bar(RAW_FULL + s));
@@ -338,7 +361,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                     const int s = bcnt % kBStages;
                     ok = mbar_wait(bar(AB_EMPTY + s), ((bcnt / kBStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
-                    DSX_TR(1, bcnt);
                     mbar_expect_tx(bar(AB_FULL + s), kBBytes);
                     tma_load_2d(sbase + kSmemB + s * kBBytes, &tmap_b, kc * kChunkK, seg.row0, bar(AB_FULL + s));
                     bcnt++;
@@ -348,9 +370,11 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
     } else if (warp == 1) {
         // ----------------------------------------------------------- MMA issue
         if (lane == 0) {
-            uint32_t acnt = 0, tcnt = 0;
+            uint32_t tcnt = 0, sa = 0, ph = 0;   // ring stage and its phase parity
             bool ok = true;
-            const uint64_t da0 = umma_desc(sbase + kSmemA), db0 = umma_desc(sbase + kSmemB);   // stage 0; stages are 2048 units apart
+            const uint64_t d0 = umma_desc(sbase + kSmemA);
+            const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
+            const uint32_t a_lo0 = (uint32_t)d0, b_lo0 = (uint32_t)umma_desc(sbase + kSmemB);
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 const int n16 = max(16, (seg.n + 15) & ~15);
@@ -358,22 +382,13 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // the previous tile's accumulators are drained
                 if (!ok) break;
                 tc_fence_after();
-                for (int kc = 0; kc < n_kc && ok; kc++) {
-                    const int sa = acnt % kAStages;
-                    ok = mbar_wait(bar(AB_FULL + sa), (acnt / kAStages) & 1u, abort_flag);
-                    if (!ok) break;
-                    DSX_TR(6, acnt);
+                for (int kc = 0; kc < n_kc; kc++) {
+                    const uint32_t full = bar(AB_FULL) + 8u * sa;
+                    if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t da = da0 + (uint64_t)(sa * (kABytes >> 4)), db = db0 + (uint64_t)(sa * (kBBytes >> 4));
-#pragma unroll
-                    for (int ks = 0; ks < kChunkK / 16; ks++) {
-                        const uint32_t acc = (kc | ks) != 0 ? 1u : 0u;
-                        tc_mma_f16(tmem_base, da + 2u * ks, db + 2u * ks, idesc, acc);
-                        tc_mma_f16(tmem_base + 256u, da + (128u * 128u >> 4) + 2u * ks, db + 2u * ks, idesc, acc);
-                    }
-                    tc_commit(bar(AB_EMPTY + sa));   // arrives when the MMAs above have read their operands
-                    DSX_TR(7, acnt);
-                    acnt++;
+                    tc_mma_chunk(tmem_base, a_lo0 + sa * (kABytes >> 4), b_lo0 + sa * (kBBytes >> 4), hi, idesc, kc != 0 ? 1u : 0u);
+                    tc_commit(bar(AB_EMPTY) + 8u * sa);   // arrives when the MMAs above have read their operands
+                    if (++sa == kAStages) { sa = 0; ph ^= 1u; }
                 }
                 if (ok) tc_commit(bar(ACC_FULL));
                 tcnt++;
@@ -388,10 +403,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             for (int kc = 0; kc < n_kc && ok; kc++) {
                 const int sr = rcnt % kRawStages, sa = acnt % kAStages;
                 ok = mbar_wait(bar(RAW_FULL + sr), (rcnt / kRawStages) & 1u, abort_flag);
-                if (cw == 0 && lane == 0) DSX_TR(2, rcnt);
                 ok = ok && mbar_wait(bar(AB_EMPTY + sa), ((acnt / kAStages) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
-                if (cw == 0 && lane == 0) DSX_TR(3, rcnt);
                 const uint8_t* raw = smem + kSmemRaw + sr * kRawBytes;
                 uint8_t* A = smem + kSmemA + sa * kABytes;
                 // both sub-tiles of this warp: loads first, then the conversions
@@ -432,7 +445,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                     mbar_arrive(bar(AB_FULL + sa));
                     mbar_arrive(bar(RAW_EMPTY + sr));
                 }
-                if (cw == 0 && lane == 0) DSX_TR(4, rcnt);
                 rcnt++;
                 acnt++;
             }
@@ -450,10 +462,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
             if (!ok) break;
-            if (threadIdx.x == kEpiWarp0 * 32) DSX_TR(8, tcnt);
             epilogue(tile, 0);
             if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
-            if (threadIdx.x == kEpiWarp0 * 32) DSX_TR(9, tcnt);
             tcnt++;
         }
     }
@@ -644,12 +654,6 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
                                  c.dn_nib_stride, c.dn_sc_stride, 1))
             return rc;
     GemmArgs g{};
-#ifdef DSX_TRACE
-    static long long* trace_buf = nullptr;
-    if (!trace_buf) { cudaMalloc((void**)&trace_buf, 2 * 10 * 512 * 8); }
-    cudaMemsetAsync(trace_buf, 0, 2 * 10 * 512 * 8, stream);
-    g.trace = trace_buf;
-#endif
     g.segs = ws->segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
     g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.error_word = c.error_word;
     // gate/up: K = hidden, rows = ffn
@@ -659,29 +663,9 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     DSX_LAUNCHED();
     // down: K = ffn, rows = hidden
     g.K = cfg.ffn; g.rows = cfg.hidden;
-#ifdef DSX_TRACE
-    g.trace = trace_buf + 10 * 512;
-#endif
     prefill_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0],
                                                                             ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
     DSX_LAUNCHED();
-#ifdef DSX_TRACE
-    {
-        static long long host[2 * 10 * 512];
-        cudaStreamSynchronize(stream);
-        cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
-        FILE* f = fopen("gpurun_out/prefill_trace.txt", "w");
-        if (f) {
-            for (int k = 0; k < 2; k++)
-                for (int ev = 0; ev < 10; ev++) {
-                    fprintf(f, "k%d ev%d", k, ev);
-                    for (int i = 0; i < 512; i++) fprintf(f, " %lld", host[(k * 10 + ev) * 512 + i]);
-                    fprintf(f, "\n");
-                }
-            fclose(f);
-        }
-    }
-#endif
     return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr,
                           c.expert_lo, c.n_local, c.out, stream);
 }

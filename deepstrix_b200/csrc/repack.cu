@@ -6,6 +6,8 @@
 // super-block v2).  Here the destination is this library's own layout, so the
 // kernels accept all three MXFP4 layouts the reference moves between (HF,
 // ggml 17-byte blocks, super-block v2) and both Q8_0 forms.
+#include <algorithm>
+
 #include "dsx_common.cuh"
 
 namespace dsx {
@@ -160,7 +162,27 @@ __global__ void unpack_kernel(int fmt, const uint8_t* __restrict__ nib, const ui
     }
 }
 
+// Largest byte of a scale plane (E8M0 exponents), folded into *out with atomicMax.
+__global__ void max_byte_kernel(const uint8_t* __restrict__ p, int64_t n_words, uint32_t* out) {
+    uint32_t m = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t w = reinterpret_cast<const uint32_t*>(p)[i];
+        m = max(m, max(max(w & 0xFFu, (w >> 8) & 0xFFu), max((w >> 16) & 0xFFu, w >> 24)));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
 }  // namespace
+
+int launch_max_byte(const uint8_t* p, int64_t bytes, uint32_t* out, cudaStream_t stream) {
+    const int64_t n_words = bytes / 4;
+    if (n_words == 0) return DSX_OK;
+    max_byte_kernel<<<(unsigned)std::min<int64_t>(1024, (n_words + 255) / 256), 256, 0, stream>>>(p, n_words, out);
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
 
 int launch_repack(int fmt, int src_layout, const uint8_t* q, const uint8_t* s, int64_t rows, int64_t K, uint8_t* nib,
                   uint8_t* sc, int pair_stride, int pair_index, int n_mats, int64_t src_q_stride, int64_t src_s_stride,

@@ -220,6 +220,67 @@ def test_layer_prefill_config0_shapes(torch_cuda, moe, oracle):
     assert rel_l2(out, ref) <= REL_L2_TOL
 
 
+def test_prefill_path_declines_scales_beyond_f16(torch_cuda, moe, oracle):
+    """Block scales above 2^13 do not fit the tensor-core path's f16 weights: the layer must take
+    the grouped-GEMV kernels instead and still match the oracle."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import MoeConfig, RouterConfig
+    cfg = MoeConfig(hidden=512, ffn=256, shared_ffn=0,
+                    router=RouterConfig(n_expert=32, n_used=2, n_group=1, topk_group=1, score_fn=1, route_scale=1.0))
+    w = synth.make_layer(cfg, 5)
+    for name in ("gate", "up", "down"):
+        w[name][1][...] = 127          # unit scales
+    w["gate"][1][:, :, 0] = 143        # one block per row at 2^16 (the SwiGLU clamp bounds what follows)
+    layer = moe.build_layer_from_host(cfg, w, max_tokens=96)
+    xb = synth.make_tokens(cfg, 5, 96)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    moe.launch_count(reset=True)
+    out = layer.forward(x).float().cpu().numpy()
+    assert moe.launch_count() == 6     # logits, top-k, group build, gate/up GEMV, down GEMV, combine
+    r = layer.routing(96)
+    ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), r["selected"], r["weights"], w["gate"], w["up"], w["down"],
+                               clamp=cfg.clamp, n_expert=32)
+    assert np.isfinite(out).all() and rel_l2(out, ref) <= REL_L2_TOL
+
+
+def test_prefill_full_size_agrees_with_decode_kernels(torch_cuda, moe, oracle):
+    """Configuration 2 at full size (8192 tokens, uniform-random routing): routing bit-exact against
+    the oracle, and -- the oracle being too slow for 65536 picks -- the tensor-core path checked
+    against the independent grouped-GEMV kernels on a slice of the same tokens with the same routing."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS
+    cfg = CONFIGS[2]
+    T = 8192
+    w = synth.make_layer(cfg, 2)
+    layer = moe.build_layer_from_host(cfg, w, max_tokens=T)
+    xb = synth.make_tokens(cfg, 2, T)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    logits = torch.from_numpy(synth.uniform_logits(cfg, 2, T)).cuda()
+    out = layer.forward(x, logits=logits)
+    assert layer.check() == 0
+    r = layer.routing(T)
+    rc = cfg.router
+    osel, ow = oracle.router_topk(logits.cpu().numpy(), w["router_bias"], rc.n_used, rc.n_group, rc.topk_group, rc.score_fn,
+                                  rc.route_scale, rc.weight_eps)
+    assert np.array_equal(r["selected"], osel) and np.array_equal(r["weights"].view(np.uint32), ow.view(np.uint32))
+    oh, oo, op = oracle.group_build(osel, rc.n_expert)
+    assert np.array_equal(r["hist"], oh) and np.array_equal(r["offsets"], oo) and np.array_equal(r["perm"], op)
+    assert oh.min() > 128 and oh.max() > 256      # every expert busy, some above one segment
+    out = out.float().cpu().numpy()
+    assert np.isfinite(out).all()
+    for lo in (0, 4096 + 17, T - 64):
+        sl = slice(lo, lo + 64)
+        dec = layer.forward(x[sl].contiguous(), logits=logits[sl].contiguous()).float().cpu().numpy()   # 64 tokens: GEMV kernels
+        assert rel_l2(out[sl], dec) < 5e-3
+    # and the first 4 tokens against the oracle itself
+    shared = tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down"))
+    ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb[:4]), osel[:4], ow[:4], w["gate"], w["up"], w["down"],
+                               shared=shared, clamp=cfg.clamp, n_expert=rc.n_expert)
+    assert rel_l2(out[:4], ref) <= REL_L2_TOL
+
+
 def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
     """Owner-of-a-subset form: two half stores, each returning its weighted partial
     sum, add up to the full layer (the reference's het-split property,
