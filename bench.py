@@ -287,6 +287,37 @@ def run_single_gpu(args):
         stream.synchronize()
         e2e_ms = e0.elapsed_time(e1)
     assert layer.check() == 0
+
+    # configuration 2: 8192-token prefill, uniform-random routing, tensor-core path
+    prefill = None
+    if not args.no_prefill:
+        Tp = 8192
+        _, bf16_peak, _ = measured_peaks()
+        layer_p = moe.MoeLayer(cfg, base, base_sh, rw, rb, max_tokens=Tp)
+        xp = [torch.from_numpy(synth.make_tokens(cfg, 2, Tp, stream=i).view(np.int16)).cuda().view(torch.bfloat16) for i in range(2)]
+        lg = torch.from_numpy(synth.uniform_logits(cfg, 2, Tp)).cuda()
+        op = torch.empty_like(xp[0])
+        n_p = max(6, args.steps // 4)
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                layer_p.set_weights(stores[i % len(stores)], shared[i % len(stores)], rw, rb)
+                layer_p.forward(xp[i % 2], logits=lg, out=op)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(n_p):
+                layer_p.set_weights(stores[i % len(stores)], shared[i % len(stores)], rw, rb)
+                layer_p.forward(xp[i % 2], logits=lg, out=op)
+            e1.record(stream)
+            stream.synchronize()
+        assert layer_p.check() == 0
+        ms_p = e0.elapsed_time(e1) / n_p
+        fl = cfg.flops(Tp) - 2.0 * Tp * E * H   # router GEMV not run: logits are the workload's input
+        prefill = {"workload": "config2: 8192 bf16 tokens, uniform-random routing, MXFP4", "tokens": Tp, "steps": n_p,
+                   "ms_per_step": ms_p, "value": Tp / (ms_p * 1e-3), "unit": UNIT, "tflops": fl / (ms_p * 1e-3) / 1e12,
+                   "operands": "f16 x f16 -> f32 on tcgen05 (MXFP4 weights expanded exactly to f16 in shared memory)",
+                   "frac_of_measured_bf16_peak": fl / (ms_p * 1e-3) / 1e12 / bf16_peak,
+                   "frac_of_nominal_fp4_peak_9pf": fl / (ms_p * 1e-3) / 9e15}
+        layer_p.close()
     sampler.stop()
     clocks = sampler.summary(*head["wall"])
 
@@ -325,6 +356,7 @@ def run_single_gpu(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "series": series,
+        "prefill": prefill,
     }
     print(json.dumps(line))
 
@@ -339,6 +371,7 @@ def main():
     ap.add_argument("--layers", type=int, default=6, help="resident copies of the layer weights to rotate over")
     ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per CPU-oracle sample step")
     ap.add_argument("--no-series", action="store_true", help="time only the headline batch size")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 8192-token prefill leg")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU-baseline leg (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
