@@ -116,23 +116,33 @@ def run_reference(args):
     from deepstrix_b200 import CONFIGS, synth
     from oracle import oracle
     oracle.build()
-    cfg = CONFIGS[1]
-    w = make_host_layer(cfg, 1)
+    multi = args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1
+    cfg = CONFIGS[4 if multi else 1]
+    w = make_host_layer(cfg, 4 if multi else 1)
     sample = args.ref_tokens
+    n_layers = 8 if multi else 1        # the multi-GPU arm is the 8-layer stack; value counts tokens x layers
     xs = [synth.bf16_bits_to_f32(synth.make_tokens(cfg, 1, sample, stream=i)) for i in range(4)]
+
+    def ref_step(x):
+        for _ in range(n_layers):
+            y = oracle_step(oracle, cfg, w, x)
+            x = y / np.sqrt((y * y).mean(axis=1, keepdims=True) + 1e-6)
+        return x
+
     for i in range(args.warmup):
-        oracle_step(oracle, cfg, w, xs[i % 4])
+        ref_step(xs[i % 4])
     t0 = time.perf_counter()
     for i in range(args.steps):
-        oracle_step(oracle, cfg, w, xs[i % 4])
+        ref_step(xs[i % 4])
     dt = time.perf_counter() - t0
-    value = sample * args.steps / dt
+    value = sample * n_layers * args.steps / dt
     cores = oracle.num_threads()
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 (dequantised MXFP4 weights, f64 accumulate)", "data": "synthetic",
-        "config": {"workload": f"config1 decode layer, {args.tokens}-token batches; CPU sample of {sample} tokens per step"},
+        "config": {"workload": (f"config4: stack of 8 full-size MoE layers; CPU sample of {sample} tokens per step, value counts tokens x layers"
+                                if multi else f"config1 decode layer, {args.tokens}-token batches; CPU sample of {sample} tokens per step")},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{sample} tokens per step x {args.steps} steps of the full-size layer (OpenMP oracle port)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

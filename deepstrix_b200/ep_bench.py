@@ -1,0 +1,191 @@
+"""Expert-parallel benchmark leg (configuration 4): a stack of 8 full-size MoE
+layers, 256 experts sharded evenly over the GPUs of one node, the shared expert
+replicated, 4096 bf16 tokens per GPU, dispatch and combine over NCCL.
+
+Launched by ``bench.py`` under ``torch.distributed.run`` (one rank per GPU).
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+N_LAYERS = 8
+TOKENS_PER_GPU = 4096
+
+
+def _rms_normalise(x: torch.Tensor) -> torch.Tensor:
+    """Stand-in for the model's norm between layers: keeps the stack's activations at unit scale."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(dim=1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+
+
+def selfcheck(rank: int, world: int):
+    """Small layer, experts sharded over the ranks: the expert-parallel result must equal the
+    unsharded layer computed on the same GPU (configuration 4's check, at a size that takes a
+    second).  Covers both kernel families: 16 tokens (GEMV kernels) and 160 (tensor-core path)."""
+    from deepstrix_b200 import CONFIGS, moe, synth
+    from deepstrix_b200.ep import ExpertParallelMoe
+    cfg = CONFIGS[0]
+    E, k, H = cfg.router.n_expert, cfg.router.n_used, cfg.hidden
+    per, lo = E // world, rank * (E // world)
+    w = synth.make_layer(cfg, 0)
+    full = moe.build_layer_from_host(cfg, w, max_tokens=160 * world)
+    shard = moe.RoutedExpertWeights.from_host(cfg.fmt, H, cfg.ffn, *[tuple(a[lo:lo + per] for a in w[n]) for n in ("gate", "up", "down")])
+    shared = moe.RoutedExpertWeights.from_host(cfg.fmt, H, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
+    rw, rb = torch.from_numpy(w["router_w"]).cuda(), torch.from_numpy(w["router_bias"]).cuda()
+    part = moe.MoeLayer(cfg, shard, shared, rw, rb, max_tokens=160 * world)
+    router = moe.RouterTopk(cfg.router)
+    worst = 0.0
+    for T in (16, 160):
+        x = torch.from_numpy(synth.make_tokens(cfg, 0, T, stream=50 + rank).view(np.int16)).cuda().view(torch.bfloat16)
+        sel, wt = router.launch_batched(router.logits(x, rw), rb)
+        none_sel = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
+        ep = ExpertParallelMoe(E, None, lambda xr, s, ww: part.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False),
+                               lambda xr: part.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
+        got = ep.forward(x, sel, wt).float()
+        ref = full.forward(x).float()
+        worst = max(worst, float((got - ref).norm() / ref.norm()))
+    assert part.check() == 0 and full.check() == 0
+    t = torch.tensor([worst], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    worst = float(t.item())
+    assert worst < 1e-2, f"expert-parallel result differs from the unsharded layer: rel-L2 {worst}"
+    return worst
+
+
+def run(args):
+    from deepstrix_b200 import CONFIGS, moe, synth
+    from deepstrix_b200.ep import ExpertParallelMoe
+    import bench as B
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "the expert-parallel bench needs CUDA devices"
+    torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    check_err = selfcheck(rank, world)
+    cfg = CONFIGS[4]
+    E, k, H, F = cfg.router.n_expert, cfg.router.n_used, cfg.hidden, cfg.ffn
+    per = E // world
+    lo = rank * per
+    T = TOKENS_PER_GPU
+    hbm_peak, bf16_peak, peak_kind = B.measured_peaks()
+
+    # every rank draws the same layer and keeps its shard; the routed weights are reused by the 8
+    # layers (a shard is 427 MB at 8 GPUs, well above L2), router weights differ per layer
+    w = synth.make_layer(cfg, 4)
+    shard = {n: (w[n][0][lo:lo + per], w[n][1][lo:lo + per]) for n in ("gate", "up", "down")}
+    routed = moe.RoutedExpertWeights.from_host(cfg.fmt, H, F, shard["gate"], shard["up"], shard["down"])
+    shared = moe.RoutedExpertWeights.from_host(cfg.fmt, H, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
+    del w, shard
+    routers = []
+    for layer_i in range(N_LAYERS):
+        rng = synth.rng_for(4, 500 + layer_i)
+        rw = torch.from_numpy(rng.normal(0.0, 0.02, size=(E, H)).astype(np.float32)).cuda()
+        rb = torch.from_numpy(rng.normal(0.0, 0.01, size=(E,)).astype(np.float32)).cuda()
+        routers.append((rw, rb))
+    max_rows = T * world                       # every token of every rank at worst
+    layer = moe.MoeLayer(cfg, routed, shared, routers[0][0], routers[0][1], max_tokens=max_rows)
+    router = moe.RouterTopk(cfg.router)
+    none_sel = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
+    none_w = torch.zeros((T, k), dtype=torch.float32, device="cuda")
+
+    def local_compute(xr, s, ww):
+        return layer.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False)
+
+    def shared_compute(xr):
+        return layer.forward_picks(xr, none_sel, none_w, expert_lo=lo, with_shared=True)
+
+    ep = ExpertParallelMoe(E, None, local_compute, shared_compute)
+    stats = {"received_rows": [], "fanout": []}
+
+    def step(x):
+        for rw, rb in routers:
+            logits = router.logits(x, rw)
+            sel, wt = router.launch_batched(logits, rb)
+            out = ep.forward(x, sel, wt)
+            stats["received_rows"].append(ep.last_stats["received_rows"])
+            stats["fanout"].append(ep.last_stats["fanout"])
+            x = _rms_normalise(out)
+        return x
+
+    xs = [torch.from_numpy(synth.make_tokens(cfg, 4, T, stream=1000 * rank + i).view(np.int16)).cuda().view(torch.bfloat16) for i in range(4)]
+    sampler = B.ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    warm = max(args.warmup, 3)
+    for i in range(warm):
+        step(xs[i % 4])
+    stats = {"received_rows": [], "fanout": []}
+    torch.cuda.synchronize()
+    dist.barrier()
+    moe.launch_count(reset=True)
+    t_w0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(xs[i % 4])
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t_w1 = time.time()
+    launches = moe.launch_count()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    assert layer.check() == 0
+
+    # end to end: tokens start in pinned host memory, the stack's output returns to the host
+    xh = [t.cpu().pin_memory() for t in xs]
+    oh = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    for i in range(2):
+        oh.copy_(step(xh[i % 4].cuda(non_blocking=True)), non_blocking=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    for i in range(args.steps):
+        oh.copy_(step(xh[i % 4].cuda(non_blocking=True)), non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e2e = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+    e2e = float(e2e.item())
+    rows = torch.tensor([float(np.mean(stats["received_rows"])), float(np.mean(stats["fanout"]))], device="cuda")
+    dist.all_reduce(rows, op=dist.ReduceOp.SUM)
+    if sampler:
+        sampler.stop()
+    if rank == 0:
+        layer_tokens = world * T * N_LAYERS * args.steps
+        picks_per_rank = T * k                                 # on average every rank computes T*k picks + T shared rows
+        flops_rank_step = N_LAYERS * 2.0 * 3 * F * H * (picks_per_rank + T)
+        tf = flops_rank_step * args.steps / (ms * 1e-3) / 1e12
+        line = {
+            "metric": B.METRIC, "value": layer_tokens / (ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 products of exact MXFP4 weights and bf16 activations, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"config4: stack of {N_LAYERS} full-size MoE layers, 256 experts sharded over {world} GPUs "
+                                   f"({per} per GPU), shared expert replicated, {T} bf16 tokens per GPU; value counts tokens x layers",
+                       "tokens_per_gpu": T, "layers": N_LAYERS, "parallelism": f"ep{world}",
+                       "exchange": "per-peer NCCL send/recv batches (dispatch: token rows + picks + weights once per owner rank; "
+                                   "combine: one weighted partial row per token and owner)",
+                       "l2": "each layer streams the rank's expert shard (%.0f MB) and %d token rows: far above L2" % (routed.device_bytes / 1e6, T)},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16_peak, "unit": "TFLOP/s", "frac": tf / bf16_peak, "traffic": None,
+                         "kernel": "prefill_gemm_kernel (tcgen05, f16 operands)", "peak_kind": peak_kind,
+                         "note": "per-GPU expert FLOPs of the whole step over the step time (exchange and routing included)"},
+            "e2e": {"value": layer_tokens / (e2e * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
+                    "ms_per_step": e2e / args.steps},
+            "gpu_launches": launches,
+            "clocks": sampler.summary(t_w0, t_w1) if sampler else None,
+            "ep": {"selfcheck_rel_l2_vs_unsharded_layer": check_err, "mean_received_rows_per_rank_per_layer": float(rows[0].item()) / world, "mean_fanout": float(rows[1].item()) / world},
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
