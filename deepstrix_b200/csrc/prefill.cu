@@ -35,21 +35,29 @@ constexpr int kEpiWarp0 = 10;
 constexpr int kSegRows = 256;          // max token rows per segment (MMA N)
 constexpr int kTileM = 256;            // weight rows per tile (2 x M128)
 constexpr int kChunkK = 64;            // reduction columns per pipeline step
-constexpr int kRawStages = 3, kAStages = 3, kBStages = 3;
-static_assert(kAStages == kBStages, "the converted-weight and token-tile rings advance in lockstep");
 constexpr int kPrefetchAhead = 8;     // chunks of packed weights requested into L2 ahead of the ring
-constexpr int kRawNib = 16 * kSubNibBytes;           // 16 sub-tiles of 16 rows x 64 columns
-constexpr int kRawSc = 16 * kSubScBytes;
-constexpr int kRawBytes = kRawNib + kRawSc;          // 8704
-constexpr int kABytes = kTileM * kChunkK * 2;        // 32768
-constexpr int kBBytes = kSegRows * kChunkK * 2;      // 32768
-constexpr int kSmemA = 0;
-constexpr int kSmemB = kSmemA + kAStages * kABytes;
-constexpr int kSmemRaw = kSmemB + kBStages * kBBytes;
-constexpr int kSmemBar = kSmemRaw + kRawStages * kRawBytes;
-constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2;
-constexpr int kSmemMisc = kSmemBar + kNumBars * 8;   // tmem base, abort flag, per-tile arrays
-constexpr int kSmemTotal = kSmemMisc + 16 + 1024;  // + alignment slack
+constexpr int kABytes = kTileM * kChunkK * 2;        // 32768: converted weights of one chunk
+constexpr int kBBytes = kSegRows * kChunkK * 2;      // 32768: token tile of one chunk
+
+// Per-format pipeline shape.  A 64-column chunk of 256 weight rows is 16 MXFP4 sub-tiles
+// (8.5 KB) or 32 Q8_0 sub-tiles (17 KB); Q8_0 pays for the larger raw stages with shallower rings.
+template <int FMT>
+struct Shape {
+    static constexpr int kSubPerChunk = FMT == DSX_FMT_MXFP4 ? 16 : 32;
+    static constexpr int kKtPerChunk = FMT == DSX_FMT_MXFP4 ? 1 : 2;       // column tiles per 64 columns
+    static constexpr int kRawStages = FMT == DSX_FMT_MXFP4 ? 3 : 2;
+    static constexpr int kAStages = FMT == DSX_FMT_MXFP4 ? 3 : 2;          // also the token-tile ring (lockstep)
+    static constexpr int kRawNib = kSubPerChunk * kSubNibBytes;
+    static constexpr int kRawSc = kSubPerChunk * kSubScBytes;
+    static constexpr int kRawBytes = kRawNib + kRawSc;
+    static constexpr int kSmemA = 0;
+    static constexpr int kSmemB = kSmemA + kAStages * kABytes;
+    static constexpr int kSmemRaw = kSmemB + kAStages * kBBytes;
+    static constexpr int kSmemBar = kSmemRaw + kRawStages * kRawBytes;
+    static constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2;
+    static constexpr int kSmemMisc = kSmemBar + kNumBars * 8;              // tmem base, abort flag
+    static constexpr int kSmemTotal = kSmemMisc + 16 + 1024;               // + alignment slack
+};
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -192,6 +200,12 @@ __device__ __forceinline__ void cvt4(uint32_t q, uint32_t (&h)[4]) {
         : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
         : "r"(q));
 }
+// Four offset-binary int8 (value ^ 0x80) -> two exact f16: 0x6400 | u is 1024 + u, minus 1152.
+__device__ __forceinline__ uint32_t q8_pair(uint32_t w, uint32_t sel) {
+    const uint32_t h = __byte_perm(w, 0x64646464u, sel);
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&h), __half2half2(__ushort_as_half((unsigned short)0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
     return *reinterpret_cast<const uint32_t*>(&r);
@@ -214,30 +228,31 @@ struct GemmArgs {
     uint32_t* error_word;
 };
 
-template <bool GATE_UP>
+template <int FMT, bool GATE_UP>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_nib,
                     const __grid_constant__ CUtensorMap tmap_sc, const __grid_constant__ CUtensorMap tmap_sh_nib,
                     const __grid_constant__ CUtensorMap tmap_sh_sc, const GemmArgs a) {
+    using C = Shape<FMT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
-    const uint32_t bar0 = sbase + kSmemBar;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
+    const uint32_t bar0 = sbase + C::kSmemBar;
     // barrier indices
     // AB_FULL[s]: converted weights (8 converter warps) and token tile (TMA bytes) of stage s are in
     // shared memory; AB_EMPTY[s]: the MMAs reading stage s have completed (one tcgen05.commit).
-    constexpr int RAW_FULL = 0, RAW_EMPTY = RAW_FULL + kRawStages, AB_FULL = RAW_EMPTY + kRawStages, AB_EMPTY = AB_FULL + kAStages,
-                  ACC_FULL = AB_EMPTY + kAStages, ACC_EMPTY = ACC_FULL + 1;
+    constexpr int RAW_FULL = 0, RAW_EMPTY = RAW_FULL + C::kRawStages, AB_FULL = RAW_EMPTY + C::kRawStages, AB_EMPTY = AB_FULL + C::kAStages,
+                  ACC_FULL = AB_EMPTY + C::kAStages, ACC_EMPTY = ACC_FULL + 1;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kSmemMisc);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     (void)bars;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kRawStages; i++) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), kConvWarps); }
-        for (int i = 0; i < kAStages; i++) { mbar_init(bar(AB_FULL + i), kConvWarps + 1); mbar_init(bar(AB_EMPTY + i), 1); }
+        for (int i = 0; i < C::kRawStages; i++) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), kConvWarps); }
+        for (int i = 0; i < C::kAStages; i++) { mbar_init(bar(AB_FULL + i), kConvWarps + 1); mbar_init(bar(AB_EMPTY + i), 1); }
         mbar_init(bar(ACC_FULL), 1);
         mbar_init(bar(ACC_EMPTY), 4 + kConvWarps);
         *abort_flag = 0u;
@@ -327,7 +342,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 const int slot = sh ? 0 : seg.expert;
                 constexpr int kRtPerTile = GATE_UP ? 8 : 16;   // 16-row tiles per stage (gate/up: each carries a gate and an up sub-tile)
                 if (tile == (int)blockIdx.x)   // first tile: warm L2 with the first chunks
-                    for (int kc = 0; kc < kPrefetchAhead && kc < n_kc; kc++) tma_prefetch_4d(m_nib, 0, kc, mb * kRtPerTile, slot);
+                    for (int kc = 0; kc < kPrefetchAhead && kc < n_kc; kc++) tma_prefetch_4d(m_nib, 0, kc * C::kKtPerChunk, mb * kRtPerTile, slot);
                 // the tile this block runs next (its first chunks are prefetched while this one finishes)
                 const int ntile = tile + gridDim.x;
                 PrefillSeg nseg = seg;
@@ -336,16 +351,17 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 const bool nsh = nseg.expert == a.n_local;
                 for (int kc = 0; kc < n_kc && ok; kc++) {
                     const int pk = kc + kPrefetchAhead;
-                    if (pk < n_kc) tma_prefetch_4d(m_nib, 0, pk, mb * kRtPerTile, slot);
-                    else if (ntile < n_tiles) tma_prefetch_4d(nsh ? &tmap_sh_nib : &tmap_nib, 0, pk - n_kc, nmb * kRtPerTile, nsh ? 0 : nseg.expert);
+                    if (pk < n_kc) tma_prefetch_4d(m_nib, 0, pk * C::kKtPerChunk, mb * kRtPerTile, slot);
+                    else if (ntile < n_tiles)
+                        tma_prefetch_4d(nsh ? &tmap_sh_nib : &tmap_nib, 0, (pk - n_kc) * C::kKtPerChunk, nmb * kRtPerTile, nsh ? 0 : nseg.expert);
                     // one box of codes, one of scales
-                    const int s = rcnt % kRawStages;
-                    ok = mbar_wait(bar(RAW_EMPTY + s), ((rcnt / kRawStages) & 1u) ^ 1u, abort_flag);
+                    const int s = rcnt % C::kRawStages;
+                    ok = mbar_wait(bar(RAW_EMPTY + s), ((rcnt / C::kRawStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
-                    const uint32_t dst = sbase + kSmemRaw + s * kRawBytes;
-                    mbar_expect_tx(bar(RAW_FULL + s), kRawBytes);
-                    tma_load_4d(dst, m_nib, 0, kc, mb * kRtPerTile, slot, bar(RAW_FULL + s));
-                    tma_load_4d(dst + kRawNib, m_sc, 0, kc, mb * kRtPerTile, slot, bar(RAW_FULL + s));
+                    const uint32_t dst = sbase + C::kSmemRaw + s * C::kRawBytes;
+                    mbar_expect_tx(bar(RAW_FULL + s), C::kRawBytes);
+                    tma_load_4d(dst, m_nib, 0, kc * C::kKtPerChunk, mb * kRtPerTile, slot, bar(RAW_FULL + s));
+                    tma_load_4d(dst + C::kRawNib, m_sc, 0, kc * C::kKtPerChunk, mb * kRtPerTile, slot, bar(RAW_FULL + s));
                     rcnt++;
                 }
             }
@@ -358,11 +374,11 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 for (int kc = 0; kc < n_kc && ok; kc++) {
-                    const int s = bcnt % kBStages;
-                    ok = mbar_wait(bar(AB_EMPTY + s), ((bcnt / kBStages) & 1u) ^ 1u, abort_flag);
+                    const int s = bcnt % C::kAStages;
+                    ok = mbar_wait(bar(AB_EMPTY + s), ((bcnt / C::kAStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(bar(AB_FULL + s), kBBytes);
-                    tma_load_2d(sbase + kSmemB + s * kBBytes, &tmap_b, kc * kChunkK, seg.row0, bar(AB_FULL + s));
+                    tma_load_2d(sbase + C::kSmemB + s * kBBytes, &tmap_b, kc * kChunkK, seg.row0, bar(AB_FULL + s));
                     bcnt++;
                 }
             }
@@ -372,9 +388,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         if (lane == 0) {
             uint32_t tcnt = 0, sa = 0, ph = 0;   // ring stage and its phase parity
             bool ok = true;
-            const uint64_t d0 = umma_desc(sbase + kSmemA);
+            const uint64_t d0 = umma_desc(sbase + C::kSmemA);
             const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
-            const uint32_t a_lo0 = (uint32_t)d0, b_lo0 = (uint32_t)umma_desc(sbase + kSmemB);
+            const uint32_t a_lo0 = (uint32_t)d0, b_lo0 = (uint32_t)umma_desc(sbase + C::kSmemB);
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 const int n16 = max(16, (seg.n + 15) & ~15);
@@ -388,7 +404,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                     tc_fence_after();
                     tc_mma_chunk(tmem_base, a_lo0 + sa * (kABytes >> 4), b_lo0 + sa * (kBBytes >> 4), hi, idesc, kc != 0 ? 1u : 0u);
                     tc_commit(bar(AB_EMPTY) + 8u * sa);   // arrives when the MMAs above have read their operands
-                    if (++sa == kAStages) { sa = 0; ph ^= 1u; }
+                    if (++sa == C::kAStages) { sa = 0; ph ^= 1u; }
                 }
                 if (ok) tc_commit(bar(ACC_FULL));
                 tcnt++;
@@ -401,42 +417,73 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             for (int kc = 0; kc < n_kc && ok; kc++) {
-                const int sr = rcnt % kRawStages, sa = acnt % kAStages;
-                ok = mbar_wait(bar(RAW_FULL + sr), (rcnt / kRawStages) & 1u, abort_flag);
-                ok = ok && mbar_wait(bar(AB_EMPTY + sa), ((acnt / kAStages) & 1u) ^ 1u, abort_flag);
+                const int sr = rcnt % C::kRawStages, sa = acnt % C::kAStages;
+                ok = mbar_wait(bar(RAW_FULL + sr), (rcnt / C::kRawStages) & 1u, abort_flag);
+                ok = ok && mbar_wait(bar(AB_EMPTY + sa), ((acnt / C::kAStages) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
-                const uint8_t* raw = smem + kSmemRaw + sr * kRawBytes;
-                uint8_t* A = smem + kSmemA + sa * kABytes;
-                // both sub-tiles of this warp: loads first, then the conversions
-                uint4 wq[2];
-                uint32_t sw[2];
+                const uint8_t* raw = smem + C::kSmemRaw + sr * C::kRawBytes;
+                uint8_t* A = smem + C::kSmemA + sa * kABytes;
+                if constexpr (FMT == DSX_FMT_MXFP4) {
+                    // both sub-tiles of this warp: loads first, then the conversions
+                    uint4 wq[2];
+                    uint32_t sw[2];
+    #pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const int st = cw + 8 * half;   // sub-tile of the raw stage
+                        wq[half] = *reinterpret_cast<const uint4*>(raw + st * kSubNibBytes + lane * 16);
+                        sw[half] = *reinterpret_cast<const uint32_t*>(raw + C::kRawNib + st * kSubScBytes + g * 4);
+                    }
+    #pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const int st = cw + 8 * half;
+                        // gate/up stage order is [rt][gate, up]; A rows 0..127 = gate, 128..255 = up
+                        const int row_base = GATE_UP ? ((st & 1) * 128 + (st >> 1) * 16) : st * 16;
+                        const uint32_t w[4] = {wq[half].x, wq[half].y, wq[half].z, wq[half].w};
+                        uint8_t* arow = A + (uint32_t)((row_base + g) >> 3) * 1024u + (uint32_t)g * 128u;
+    #pragma unroll
+                        for (int bi = 0; bi < 2; bi++) {
+                            // odd row groups take the two scale blocks in the opposite order, so the eight
+                            // lanes of a quarter warp store to eight different 16-byte bank groups
+                            const int b = bi ^ (g & 1);
+                            const uint32_t m0 = scale_h2((sw[half] >> (8 * b)) & 0xFFu), m1 = scale_h2((sw[half] >> (16 + 8 * b)) & 0xFFu);
+                            uint32_t p[4], q[4];
+                            cvt4(b ? w[2] : w[0], p);   // (g; c0,c1) (g+8; c0,c1) (g; c2,c3) (g+8; c2,c3)
+                            cvt4(b ? w[3] : w[1], q);   // same for columns c4..c7
+                            const uint4 r0 = make_uint4(hmul2(p[0], m0), hmul2(p[2], m0), hmul2(q[0], m0), hmul2(q[2], m0));
+                            const uint4 r1 = make_uint4(hmul2(p[1], m1), hmul2(p[3], m1), hmul2(q[1], m1), hmul2(q[3], m1));
+                            const uint32_t off = (uint32_t)(((4 * b + t) ^ g) << 4);   // 16-byte chunk 4b+t, swizzled by the row
+                            *reinterpret_cast<uint4*>(arow + off) = r0;
+                            *reinterpret_cast<uint4*>(arow + off + 1024u) = r1;   // row + 8: next 8-row group, same swizzle phase
+                        }
+                    }
+                } else {
+                    // Q8_0: 32 sub-tiles of 16 rows x 32 columns, stage order [row tile][column tile 0/1][gate, up]
+                    // (down: [row tile][column tile]); four sub-tiles per warp.  A lane's 16 bytes are rows
+                    // g / g+8 x 8 consecutive columns: words {row g cols 0-3, row g+8 cols 0-3, row g cols 4-7, row g+8 cols 4-7}.
+                    uint4 wq[4];
+                    uint32_t sw[4];
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    const int st = cw + 8 * half;   // sub-tile of the raw stage
-                    wq[half] = *reinterpret_cast<const uint4*>(raw + st * kSubNibBytes + lane * 16);
-                    sw[half] = *reinterpret_cast<const uint32_t*>(raw + kRawNib + st * kSubScBytes + g * 4);
-                }
+                    for (int i = 0; i < 4; i++) {
+                        const int st = cw + 8 * i;
+                        wq[i] = *reinterpret_cast<const uint4*>(raw + st * kSubNibBytes + lane * 16);
+                        sw[i] = *reinterpret_cast<const uint32_t*>(raw + C::kRawNib + st * kSubScBytes + g * 4);
+                    }
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    const int st = cw + 8 * half;
-                    // gate/up stage order is [rt][gate, up]; A rows 0..127 = gate, 128..255 = up
-                    const int row_base = GATE_UP ? ((st & 1) * 128 + (st >> 1) * 16) : st * 16;
-                    const uint32_t w[4] = {wq[half].x, wq[half].y, wq[half].z, wq[half].w};
-                    uint8_t* arow = A + (uint32_t)((row_base + g) >> 3) * 1024u + (uint32_t)g * 128u;
-#pragma unroll
-                    for (int bi = 0; bi < 2; bi++) {
-                        // odd row groups take the two scale blocks in the opposite order, so the eight
-                        // lanes of a quarter warp store to eight different 16-byte bank groups
-                        const int b = bi ^ (g & 1);
-                        const uint32_t m0 = scale_h2((sw[half] >> (8 * b)) & 0xFFu), m1 = scale_h2((sw[half] >> (16 + 8 * b)) & 0xFFu);
-                        uint32_t p[4], q[4];
-                        cvt4(b ? w[2] : w[0], p);   // (g; c0,c1) (g+8; c0,c1) (g; c2,c3) (g+8; c2,c3)
-                        cvt4(b ? w[3] : w[1], q);   // same for columns c4..c7
-                        const uint4 r0 = make_uint4(hmul2(p[0], m0), hmul2(p[2], m0), hmul2(q[0], m0), hmul2(q[2], m0));
-                        const uint4 r1 = make_uint4(hmul2(p[1], m1), hmul2(p[3], m1), hmul2(q[1], m1), hmul2(q[3], m1));
-                        const uint32_t off = (uint32_t)(((4 * b + t) ^ g) << 4);   // 16-byte chunk 4b+t, swizzled by the row
+                    for (int i = 0; i < 4; i++) {
+                        const int st = cw + 8 * i;
+                        int rt, kt2, gu;
+                        if (GATE_UP) { gu = st & 1; kt2 = (st >> 1) & 1; rt = st >> 2; }
+                        else { gu = 0; kt2 = st & 1; rt = st >> 1; }
+                        const int row_base = gu * 128 + rt * 16;
+                        uint8_t* arow = A + (uint32_t)((row_base + g) >> 3) * 1024u + (uint32_t)g * 128u;
+                        const uint32_t m0 = (sw[i] & 0xFFFFu) * 0x00010001u, m1 = (sw[i] >> 16) * 0x00010001u;   // f16 scale of row g / g+8
+                        const uint4 r0 = make_uint4(hmul2(q8_pair(wq[i].x, 0x4140), m0), hmul2(q8_pair(wq[i].x, 0x4342), m0),
+                                                    hmul2(q8_pair(wq[i].z, 0x4140), m0), hmul2(q8_pair(wq[i].z, 0x4342), m0));
+                        const uint4 r1 = make_uint4(hmul2(q8_pair(wq[i].y, 0x4140), m1), hmul2(q8_pair(wq[i].y, 0x4342), m1),
+                                                    hmul2(q8_pair(wq[i].w, 0x4140), m1), hmul2(q8_pair(wq[i].w, 0x4342), m1));
+                        const uint32_t off = (uint32_t)(((4 * kt2 + t) ^ g) << 4);
                         *reinterpret_cast<uint4*>(arow + off) = r0;
-                        *reinterpret_cast<uint4*>(arow + off + 1024u) = r1;   // row + 8: next 8-row group, same swizzle phase
+                        *reinterpret_cast<uint4*>(arow + off + 1024u) = r1;
                     }
                 }
                 fence_proxy_async();
@@ -563,9 +610,10 @@ int encode_rows_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
 }
 
 // One plane of packed weights as [slot][row tile][column tile][inner bytes as u32]; the box is all
-// `box_rt` row tiles of one column tile, landing in shared memory as [row tile][inner bytes].
+// `box_rt` row tiles x `box_kt` column tiles (one 64-column chunk), landing in shared memory as
+// [row tile][column tile][inner bytes].
 int encode_plane_map(CUtensorMap* map, const void* base, int inner_bytes, int64_t n_kt, int64_t n_rt, int64_t n_slots,
-                     int64_t slot_stride, int box_rt) {
+                     int64_t slot_stride, int box_kt, int box_rt) {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
         void* p = nullptr;
@@ -576,7 +624,7 @@ int encode_plane_map(CUtensorMap* map, const void* base, int inner_bytes, int64_
     }
     const cuuint64_t dims[4] = {(cuuint64_t)(inner_bytes / 4), (cuuint64_t)n_kt, (cuuint64_t)n_rt, (cuuint64_t)n_slots};
     const cuuint64_t strides[3] = {(cuuint64_t)inner_bytes, (cuuint64_t)(n_kt * inner_bytes), (cuuint64_t)slot_stride};
-    const cuuint32_t box[4] = {(cuuint32_t)(inner_bytes / 4), 1, (cuuint32_t)box_rt, 1};
+    const cuuint32_t box[4] = {(cuuint32_t)(inner_bytes / 4), (cuuint32_t)box_kt, (cuuint32_t)box_rt, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -591,10 +639,11 @@ int map_weights(PrefillWorkspace* ws, int which, const uint8_t* gu_nib, const ui
                 int n_slots) {
     if (ws->mapped_gu_nib[which] == gu_nib && ws->mapped_dn_nib[which] == dn_nib) return DSX_OK;
     const int64_t H = ws->H, F = ws->F;
-    if (int rc = encode_plane_map(&ws->tmap_gu_nib[which], gu_nib, 2 * kSubNibBytes, H / 64, F / 16, n_slots, gu_nib_stride, 8)) return rc;
-    if (int rc = encode_plane_map(&ws->tmap_gu_sc[which], gu_sc, 2 * kSubScBytes, H / 64, F / 16, n_slots, gu_sc_stride, 8)) return rc;
-    if (int rc = encode_plane_map(&ws->tmap_dn_nib[which], dn_nib, kSubNibBytes, F / 64, H / 16, n_slots, dn_nib_stride, 16)) return rc;
-    if (int rc = encode_plane_map(&ws->tmap_dn_sc[which], dn_sc, kSubScBytes, F / 64, H / 16, n_slots, dn_sc_stride, 16)) return rc;
+    const int tk = tile_k(ws->fmt), box_kt = 64 / tk;   // column tiles per 64-column chunk
+    if (int rc = encode_plane_map(&ws->tmap_gu_nib[which], gu_nib, 2 * kSubNibBytes, H / tk, F / 16, n_slots, gu_nib_stride, box_kt, 8)) return rc;
+    if (int rc = encode_plane_map(&ws->tmap_gu_sc[which], gu_sc, 2 * kSubScBytes, H / tk, F / 16, n_slots, gu_sc_stride, box_kt, 8)) return rc;
+    if (int rc = encode_plane_map(&ws->tmap_dn_nib[which], dn_nib, kSubNibBytes, F / tk, H / 16, n_slots, dn_nib_stride, box_kt, 16)) return rc;
+    if (int rc = encode_plane_map(&ws->tmap_dn_sc[which], dn_sc, kSubScBytes, F / tk, H / 16, n_slots, dn_sc_stride, box_kt, 16)) return rc;
     ws->mapped_gu_nib[which] = gu_nib;
     ws->mapped_dn_nib[which] = dn_nib;
     return DSX_OK;
@@ -615,8 +664,10 @@ int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, in
     DSX_CUDA(cudaMalloc((void**)&ws->n_segs, 256));
     if (int rc = encode_rows_map(&ws->tmap_x, ws->xperm, ws->cap_rows, cfg.hidden)) return rc;
     if (int rc = encode_rows_map(&ws->tmap_mid, mid, ws->cap_rows, cfg.ffn)) return rc;
-    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
-    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_Q8_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_Q8_0>::kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_Q8_0>::kSmemTotal));
     ws->min_tokens = 65;
     ws->ready = true;
     return DSX_OK;
@@ -630,7 +681,8 @@ void prefill_workspace_free(PrefillWorkspace* ws) {
 }
 
 bool prefill_wanted(const PrefillWorkspace& ws, const dsx_moe_config&, int fmt, int64_t T) {
-    return ws.ready && fmt == DSX_FMT_MXFP4 && T >= ws.min_tokens;
+    (void)fmt;
+    return ws.ready && T >= ws.min_tokens;
 }
 
 int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& c, cudaStream_t stream) {
@@ -645,6 +697,7 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(c.x, c.perm, c.offsets, c.n_local, c.n_used, P, c.T,
                                                                       c.with_shared ? 1 : 0, cfg.hidden, ws->xperm);
     DSX_LAUNCHED();
+    if (ws->fmt != c.fmt) { ws->fmt = c.fmt; ws->mapped_gu_nib[0] = ws->mapped_gu_nib[1] = nullptr; }
     if (int rc = map_weights(ws, 0, c.gu_nib, c.gu_sc, c.dn_nib, c.dn_sc, c.gu_nib_stride, c.gu_sc_stride, c.dn_nib_stride,
                              c.dn_sc_stride, c.n_local))
         return rc;
@@ -658,13 +711,21 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.error_word = c.error_word;
     // gate/up: K = hidden, rows = ffn
     g.K = cfg.hidden; g.rows = cfg.ffn;
-    prefill_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_x, ws->tmap_gu_nib[0], ws->tmap_gu_sc[0],
-                                                                           ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
+    if (c.fmt == DSX_FMT_MXFP4)
+        prefill_gemm_kernel<DSX_FMT_MXFP4, true><<<c.sm_count, kThreads, Shape<DSX_FMT_MXFP4>::kSmemTotal, stream>>>(
+            ws->tmap_x, ws->tmap_gu_nib[0], ws->tmap_gu_sc[0], ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
+    else
+        prefill_gemm_kernel<DSX_FMT_Q8_0, true><<<c.sm_count, kThreads, Shape<DSX_FMT_Q8_0>::kSmemTotal, stream>>>(
+            ws->tmap_x, ws->tmap_gu_nib[0], ws->tmap_gu_sc[0], ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
     DSX_LAUNCHED();
     // down: K = ffn, rows = hidden
     g.K = cfg.ffn; g.rows = cfg.hidden;
-    prefill_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0],
-                                                                            ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
+    if (c.fmt == DSX_FMT_MXFP4)
+        prefill_gemm_kernel<DSX_FMT_MXFP4, false><<<c.sm_count, kThreads, Shape<DSX_FMT_MXFP4>::kSmemTotal, stream>>>(
+            ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0], ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
+    else
+        prefill_gemm_kernel<DSX_FMT_Q8_0, false><<<c.sm_count, kThreads, Shape<DSX_FMT_Q8_0>::kSmemTotal, stream>>>(
+            ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0], ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
     DSX_LAUNCHED();
     return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr,
                           c.expert_lo, c.n_local, c.out, stream);

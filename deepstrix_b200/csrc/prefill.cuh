@@ -18,6 +18,7 @@ struct PrefillWorkspace {
     int min_tokens = 1 << 30;  // batches of at least this many tokens take the tensor-core path
     int64_t cap_rows = 0;      // rows of xperm / mid the tensor maps cover
     int64_t H = 0, F = 0;
+    int fmt = DSX_FMT_MXFP4;   // format of the stores the weight maps describe
     __half* xperm = nullptr;   // [cap_rows, H] f16: token rows in expert-sorted order, then all tokens (shared expert)
     PrefillSeg* segs = nullptr;
     int32_t* n_segs = nullptr;

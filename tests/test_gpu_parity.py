@@ -220,6 +220,34 @@ def test_layer_prefill_config0_shapes(torch_cuda, moe, oracle):
     assert rel_l2(out, ref) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("T", [96, 1500])
+def test_layer_prefill_q8_0_zipf(torch_cuda, moe, oracle, T):
+    """Configuration 3 in miniature: Q8_0 experts on the tensor-core path with a Zipf(1.1)-skewed
+    router bias, so a few experts get several segments and many get a handful of tokens."""
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import FMT_Q8_0, MoeConfig, RouterConfig
+    torch = torch_cuda
+    cfg = MoeConfig(hidden=512, ffn=256, shared_ffn=256, fmt=FMT_Q8_0,
+                    router=RouterConfig(n_expert=32, n_used=4, n_group=1, topk_group=1, score_fn=1, route_scale=2.5))
+    w = synth.make_layer(cfg, 3)
+    w["router_bias"] = synth.zipf_bias(cfg)
+    layer = moe.build_layer_from_host(cfg, w, max_tokens=T)
+    xb = synth.make_tokens(cfg, 3, T)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    out = layer.forward(x).float().cpu().numpy()
+    assert layer.check() == 0
+    r = layer.routing(T)
+    rc = cfg.router
+    osel, ow = oracle.router_topk(r["logits"], w["router_bias"], rc.n_used, 1, 1, 1, 2.5)
+    assert np.array_equal(r["selected"], osel)
+    if T > 1000:
+        assert r["hist"].max() > 256 and r["hist"].max() > 6 * max(r["hist"].min(), 1)   # skewed: busiest expert needs several segments
+    shared = tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down"))
+    ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), osel, ow, w["gate"], w["up"], w["down"], shared=shared,
+                               clamp=cfg.clamp, n_expert=rc.n_expert)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+
+
 def test_prefill_path_declines_scales_beyond_f16(torch_cuda, moe, oracle):
     """Block scales above 2^13 do not fit the tensor-core path's f16 weights: the layer must take
     the grouped-GEMV kernels instead and still match the oracle."""
