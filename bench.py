@@ -257,6 +257,7 @@ def run_single_gpu(args):
     layer.profile(True)
     stage_acc = {}
     gu_bytes = []
+    gu_items = []
     with torch.cuda.stream(stream):
         for i in range(args.warmup + args.steps):
             j = i % len(stores)
@@ -269,6 +270,7 @@ def run_single_gpu(args):
                 stage_acc.setdefault(n_, []).append(v)
             d = int((layer.routing(T)["hist"] > 0).sum())
             gu_bytes.append((d + 1) * 2 * cfg.matrix_bytes() + T * H * 2 + (T * k + T) * cfg.ffn * 2)
+            gu_items.append(d + 1)
     layer.profile(False)
     stage_ms = {n_: sum(v) / len(v) for n_, v in stage_acc.items()}
     gu_ms = stage_ms["gate_up"]
@@ -328,6 +330,44 @@ def run_single_gpu(args):
                    "frac_of_measured_bf16_peak": fl / (ms_p * 1e-3) / 1e12 / bf16_peak,
                    "frac_of_nominal_fp4_peak_9pf": fl / (ms_p * 1e-3) / 9e15}
         layer_p.close()
+    # configuration 3: Q8_0 experts, 2048 tokens, Zipf(1.1)-skewed expert popularity
+    q8 = None
+    if not args.no_q8:
+        from deepstrix_b200.config import CONFIGS as _C
+        cfg3 = _C[3]
+        Tq = 2048
+        for st_ in stores[1:] + shared[1:]:
+            st_.close()                      # make room: free the rotating MXFP4 copies
+        w3 = synth.make_layer(cfg3, 3)
+        r3 = moe.RoutedExpertWeights.from_host(cfg3.fmt, H, cfg3.ffn, w3["gate"], w3["up"], w3["down"])
+        s3 = moe.RoutedExpertWeights.from_host(cfg3.fmt, H, cfg3.shared_ffn, w3["shared_gate"], w3["shared_up"], w3["shared_down"])
+        rw3 = torch.from_numpy(w3["router_w"]).cuda()
+        rb3 = torch.from_numpy(synth.zipf_bias(cfg3)).cuda()
+        del w3
+        layer3 = moe.MoeLayer(cfg3, r3, s3, rw3, rb3, max_tokens=Tq)
+        x3 = [torch.from_numpy(synth.make_tokens(cfg3, 3, Tq, stream=i).view(np.int16)).cuda().view(torch.bfloat16) for i in range(2)]
+        o3 = torch.empty_like(x3[0])
+        n3 = max(6, args.steps // 4)
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                layer3.forward(x3[i % 2], out=o3)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(n3):
+                layer3.forward(x3[i % 2], out=o3)
+            e1.record(stream)
+            stream.synchronize()
+        assert layer3.check() == 0
+        hist3 = layer3.routing(Tq)["hist"]
+        ms3 = e0.elapsed_time(e1) / n3
+        d3 = int((hist3 > 0).sum())
+        bytes3 = cfg3.algorithmic_bytes(Tq, d3)
+        q8 = {"workload": "config3: 2048 bf16 tokens, Q8_0 experts, router bias skewed to a Zipf(1.1) popularity profile", "tokens": Tq,
+              "steps": n3, "ms_per_step": ms3, "value": Tq / (ms3 * 1e-3), "unit": UNIT, "distinct_experts": d3,
+              "tokens_per_expert": {"max": int(hist3.max()), "mean": float(hist3.mean()), "min": int(hist3.min())},
+              "layer_bytes": bytes3, "layer_gbs": bytes3 / (ms3 * 1e-3) / 1e9, "layer_frac_of_hbm_peak": bytes3 / (ms3 * 1e-3) / 1e9 / hbm_peak,
+              "l2": "%.1f GB of expert weights per step, far above L2" % (bytes3 / 1e9)}
+        layer3.close()
     sampler.stop()
     clocks = sampler.summary(*head["wall"])
 
@@ -356,7 +396,10 @@ def run_single_gpu(args):
                          % (len(stores), len(stores) * (base.device_bytes + base_sh.device_bytes) / 1e9),
                    "launch": "one captured CUDA graph per step"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "kernel": "gemv_kernel<MXFP4, pair> (gate/up + SwiGLU)", "peak_kind": peak_kind,
+                     # dram__bytes_read + write of this kernel from the ncu capture of a 41-item launch
+                     # (370.21 MB, profiles/gemv_decode_t8_64experts.md), scaled by the items of this launch
+                     "traffic": int(370.21e6 / 41 * (sum(gu_items) / len(gu_items))),
+                     "kernel": "gemv_kernel<MXFP4, pair> (gate/up + SwiGLU)", "peak_kind": peak_kind,
                      "avg_launch_ms": gu_ms, "layer_frac": head["layer_frac_of_hbm_peak"]},
         "stage_ms": stage_ms,
         "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
@@ -367,6 +410,7 @@ def run_single_gpu(args):
         "clocks": clocks,
         "series": series,
         "prefill": prefill,
+        "q8_0_zipf": q8,
     }
     print(json.dumps(line))
 
@@ -382,6 +426,7 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per CPU-oracle sample step")
     ap.add_argument("--no-series", action="store_true", help="time only the headline batch size")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 8192-token prefill leg")
+    ap.add_argument("--no-q8", action="store_true", help="skip the Q8_0 / Zipf leg (configuration 3)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU-baseline leg (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
