@@ -74,9 +74,29 @@ class ExpertParallelMoe:
         self.local_compute = local_compute
         self.shared_compute = shared_compute
         self.last_stats = {}
+        self._side = None   # side stream: the shared expert runs beside the dispatch exchange
+        self.profile = False  # when set, forward() brackets its phases with CUDA events (see phase_ms)
+        self._events = []
+
+    def _mark(self, name):
+        if self.profile:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._events.append((name, e))
+
+    def phase_ms(self) -> dict:
+        """Device time per phase accumulated since the last call (profile mode)."""
+        torch.cuda.synchronize()
+        out = {}
+        for (n0, e0), (n1, e1) in zip(self._events[:-1], self._events[1:]):
+            if n1 != "start":
+                out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
+        self._events = []
+        return out
 
     def forward(self, x: torch.Tensor, selected: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         W, r = self.world, self.rank
+        self._mark("start")
         T, H = x.shape
         k = selected.shape[1]
         tok, counts = build_dispatch(selected, W, self.experts_per_rank)
@@ -86,6 +106,7 @@ class ExpertParallelMoe:
         cm = torch.stack(all_counts).cpu()                             # [src, dst]
         send_n = cm[r].tolist()
         recv_n = cm[:, r].tolist()
+        self._mark("dispatch_lists_and_counts")
         # pack rows and (picks | weights bit-cast) per destination
         xs = x.index_select(0, tok)
         meta = torch.cat([selected.index_select(0, tok), weights.index_select(0, tok).view(torch.int32)], dim=1)
@@ -96,15 +117,32 @@ class ExpertParallelMoe:
         rm = torch.empty((R, 2 * k), dtype=torch.int32, device=x.device)
         recv_x = list(torch.split(rx, recv_n))
         recv_m = list(torch.split(rm, recv_n))
+        # shared expert of the rank's own tokens: independent of the exchange, so on a GPU it runs
+        # on a side stream while the rows travel (het/forward_layer.rs:50-80 overlaps the same way)
+        sh = None
+        if self.shared_compute is not None and x.is_cuda:
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            main = torch.cuda.current_stream()
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                sh = self.shared_compute(x)
+                sh.record_stream(main)
         _exchange(send_x, recv_x, self.group, r)
         _exchange(send_m, recv_m, self.group, r)
-        # shared expert of the rank's own tokens: independent of the exchange
-        out = self.shared_compute(x).float() if self.shared_compute is not None else torch.zeros((T, H), dtype=torch.float32, device=x.device)
+        if self.shared_compute is not None and not x.is_cuda:
+            sh = self.shared_compute(x)
+        self._mark("pack_and_dispatch_exchange")
+        if sh is not None and x.is_cuda:
+            torch.cuda.current_stream().wait_stream(self._side)
+        self._mark("wait_shared_expert")
+        out = sh.float() if sh is not None else torch.zeros((T, H), dtype=torch.float32, device=x.device)
         # owned experts on everything received
         if R:
             part = self.local_compute(rx, rm[:, :k].contiguous(), rm[:, k:].contiguous().view(torch.float32))
         else:
             part = torch.empty((0, H), dtype=x.dtype, device=x.device)
+        self._mark("owned_experts")
         # combine: partial rows travel back the way the tokens came
         back = torch.empty((tok.numel(), H), dtype=x.dtype, device=x.device)
         _exchange(list(torch.split(part, recv_n)), list(torch.split(back, send_n)), self.group, r)
@@ -115,5 +153,6 @@ class ExpertParallelMoe:
             if n:
                 out.index_add_(0, tok[off:off + n], back[off:off + n].float())
                 off += n
+        self._mark("combine_exchange_and_sum")
         self.last_stats = {"sent_rows": int(tok.numel()), "received_rows": R, "fanout": float(tok.numel()) / max(T, 1)}
         return out.to(x.dtype)

@@ -93,6 +93,8 @@ def run(args):
         routers.append((rw, rb))
     max_rows = T * world                       # every token of every rank at worst
     layer = moe.MoeLayer(cfg, routed, shared, routers[0][0], routers[0][1], max_tokens=max_rows)
+    # the shared expert runs on a side stream beside the dispatch: it needs its own workspace
+    layer_sh = moe.MoeLayer(cfg, routed, shared, routers[0][0], routers[0][1], max_tokens=T)
     router = moe.RouterTopk(cfg.router)
     none_sel = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
     none_w = torch.zeros((T, k), dtype=torch.float32, device="cuda")
@@ -101,7 +103,7 @@ def run(args):
         return layer.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False)
 
     def shared_compute(xr):
-        return layer.forward_picks(xr, none_sel, none_w, expert_lo=lo, with_shared=True)
+        return layer_sh.forward_picks(xr, none_sel, none_w, expert_lo=lo, with_shared=True)
 
     ep = ExpertParallelMoe(E, None, local_compute, shared_compute)
     stats = {"received_rows": [], "fanout": []}
@@ -140,7 +142,7 @@ def run(args):
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
-    assert layer.check() == 0
+    assert layer.check() == 0 and layer_sh.check() == 0
 
     # end to end: tokens start in pinned host memory, the stack's output returns to the host
     xh = [t.cpu().pin_memory() for t in xs]
@@ -158,6 +160,15 @@ def run(args):
     e2e = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
     e2e = float(e2e.item())
+    # one more pass with per-phase events (rank 0's view)
+    ep.profile = True
+    t_r0 = torch.cuda.Event(enable_timing=True); t_r1 = torch.cuda.Event(enable_timing=True)
+    t_r0.record()
+    step(xs[0])
+    t_r1.record()
+    phases = ep.phase_ms()
+    phases["step_total"] = t_r0.elapsed_time(t_r1)
+    ep.profile = False
     rows = torch.tensor([float(np.mean(stats["received_rows"])), float(np.mean(stats["fanout"]))], device="cuda")
     dist.all_reduce(rows, op=dist.ReduceOp.SUM)
     if sampler:
@@ -184,7 +195,7 @@ def run(args):
                     "ms_per_step": e2e / args.steps},
             "gpu_launches": launches,
             "clocks": sampler.summary(t_w0, t_w1) if sampler else None,
-            "ep": {"selfcheck_rel_l2_vs_unsharded_layer": check_err, "mean_received_rows_per_rank_per_layer": float(rows[0].item()) / world, "mean_fanout": float(rows[1].item()) / world},
+            "ep": {"phase_ms_per_step_rank0": {n: round(v, 3) for n, v in phases.items()}, "selfcheck_rel_l2_vs_unsharded_layer": check_err, "mean_received_rows_per_rank_per_layer": float(rows[0].item()) / world, "mean_fanout": float(rows[1].item()) / world},
         }
         print(json.dumps(line))
     dist.barrier()
