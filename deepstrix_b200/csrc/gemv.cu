@@ -24,9 +24,7 @@
 namespace dsx {
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 4;
+constexpr int kRingStagesPerBlock = 32;  // ring stages per block: 8 warps x 4 deep, or 16 warps x 2 deep
 constexpr int kSubPerStage = 8;  // sub-tiles per ring stage
 constexpr int kStageNib = kSubPerStage * kSubNibBytes;
 constexpr int kStageSc = kSubPerStage * kSubScBytes;
@@ -171,8 +169,12 @@ struct ItemInfo {
 // FMT: routed format for routed items; shared items use SFMT.  The kernel is
 // compiled for the (FMT, SFMT) pairs with FMT == SFMT only, which keeps one
 // decode path per item.
-template <int FMT, bool PAIR>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
+// WARPS: 8 (4 ring stages per warp) for very small batches, where the units would not cover all SMs
+// with 256-row blocks; 16 (2 stages per warp) otherwise: four warps per scheduler hide the
+// cvt -> mma -> fma latencies that two cannot.
+template <int FMT, bool PAIR, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
+    constexpr int kWarps = WARPS, kThreads = WARPS * 32, kStages = kRingStagesPerBlock / WARPS;
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kTileK = (FMT == DSX_FMT_MXFP4) ? 64 : 32;
     constexpr int kBlocks = kTileK / 32;            // 32-column scale blocks per sub-tile
@@ -357,7 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a) {
 
 size_t gemv_smem_bytes(int64_t K) {
     const size_t act = (((size_t)kMaxTok * (size_t)(K + kActPad) * 2) + 127) & ~(size_t)127;
-    return act + (size_t)kWarps * kStages * kStageBytes + sizeof(uint64_t) * kWarps * kStages + sizeof(ItemInfo) + 128;
+    return act + (size_t)kRingStagesPerBlock * kStageBytes + sizeof(uint64_t) * kRingStagesPerBlock + sizeof(ItemInfo) + 128;
 }
 
 constexpr size_t kMaxSmem = 227 * 1024;
@@ -366,14 +368,18 @@ template <int FMT, bool PAIR>
 int launch_one(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     const size_t smem = gemv_smem_bytes(a.K);
     DSX_REQUIRE(smem <= kMaxSmem, "gemv: reduction length %lld needs %zu B of shared memory (max %zu)", (long long)a.K, smem, kMaxSmem);
-    gemv_kernel<FMT, PAIR><<<sm_count, kThreads, smem, stream>>>(a);
+    // 256-row blocks need enough (item, block) units to occupy every SM twice over; the item count
+    // lives on the device, so decide on the batch size (>= 8 tokens x top-k picks is plenty)
+    const bool wide = a.rows % (kTileRows * 16) == 0 && a.T >= 8;
+    if (wide) gemv_kernel<FMT, PAIR, 16><<<sm_count, 16 * 32, smem, stream>>>(a);
+    else gemv_kernel<FMT, PAIR, 8><<<sm_count, 8 * 32, smem, stream>>>(a);
     DSX_LAUNCHED();
     return DSX_OK;
 }
 
 int check_args(const GemvArgs& a) {
     DSX_REQUIRE(a.K % 256 == 0, "gemv: reduction length %lld must be a multiple of 256", (long long)a.K);
-    DSX_REQUIRE(a.rows % (kTileRows * kWarps) == 0, "gemv: %lld rows must be a multiple of %d", (long long)a.rows, kTileRows * kWarps);
+    DSX_REQUIRE(a.rows % (kTileRows * 8) == 0, "gemv: %lld rows must be a multiple of %d", (long long)a.rows, kTileRows * 8);
     DSX_REQUIRE(a.sh_nib == nullptr || (a.shared_fmt == a.fmt && a.sh_rows == a.rows),
                 "gemv: the shared expert must have the routed experts' format and width");
     return DSX_OK;
@@ -397,10 +403,12 @@ int launch_gemv_down(const GemvArgs& a, int sm_count, cudaStream_t stream) {
 // once per device at layer creation so that launches are plain stream work
 // (capturable in a graph).
 int gemv_configure() {
-    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_MXFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_MXFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_Q8_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-    DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<DSX_FMT_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+#define DSX_GEMV_ATTR(F, P, W) DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<F, P, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem))
+    DSX_GEMV_ATTR(DSX_FMT_MXFP4, true, 8); DSX_GEMV_ATTR(DSX_FMT_MXFP4, false, 8);
+    DSX_GEMV_ATTR(DSX_FMT_MXFP4, true, 16); DSX_GEMV_ATTR(DSX_FMT_MXFP4, false, 16);
+    DSX_GEMV_ATTR(DSX_FMT_Q8_0, true, 8); DSX_GEMV_ATTR(DSX_FMT_Q8_0, false, 8);
+    DSX_GEMV_ATTR(DSX_FMT_Q8_0, true, 16); DSX_GEMV_ATTR(DSX_FMT_Q8_0, false, 16);
+#undef DSX_GEMV_ATTR
     return DSX_OK;
 }
 
