@@ -59,6 +59,7 @@ struct dsx_moe_layer {
     __half* mid = nullptr;
     float* partial = nullptr;
     uint32_t* error_word = nullptr;
+    unsigned int* router_counters = nullptr;   // ticket counters of the one-launch decode router
     __nv_bfloat16 *x_stage = nullptr, *out_stage = nullptr;
     PrefillWorkspace pf{};
     // optional per-stage event pairs (dsx_moe_layer_profile)
@@ -398,7 +399,7 @@ static void layer_free(dsx_moe_layer* L) {
     for (cudaEvent_t e : L->ev) if (e) cudaEventDestroy(e);
     cudaFree(L->logits); cudaFree(L->selected); cudaFree(L->weights); cudaFree(L->hist); cudaFree(L->offsets);
     cudaFree(L->perm); cudaFree(L->work_items); cudaFree(L->n_work_items); cudaFree(L->gs.chunk_hist); cudaFree(L->mid);
-    cudaFree(L->partial); cudaFree(L->error_word); cudaFree(L->x_stage); cudaFree(L->out_stage);
+    cudaFree(L->partial); cudaFree(L->error_word); cudaFree(L->router_counters); cudaFree(L->x_stage); cudaFree(L->out_stage);
     prefill_workspace_free(&L->pf);
 }
 
@@ -449,13 +450,20 @@ int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const
     alloc((void**)&L->mid, (P + Tm) * (size_t)std::max(c.ffn, c.shared_ffn) * 2);
     alloc((void**)&L->partial, (P + Tm) * (size_t)c.hidden * 4);
     alloc((void**)&L->error_word, 256);
+    alloc((void**)&L->router_counters, 256);
     alloc((void**)&L->x_stage, Tm * (size_t)c.hidden * 2);
     alloc((void**)&L->out_stage, Tm * (size_t)c.hidden * 2);
     if (e == cudaSuccess) e = cudaMemset(L->error_word, 0, 256);
+    if (e == cudaSuccess) e = cudaMemset(L->router_counters, 0, 256);
     if (e != cudaSuccess) {
         layer_free(L);
         delete L;
         return set_error((int)e, "moe_layer: workspace allocation failed: %s", cudaGetErrorString(e));
+    }
+    if (int rc = router_configure()) {
+        layer_free(L);
+        delete L;
+        return rc;
     }
     if (int rc = gemv_configure()) {
         layer_free(L);
@@ -502,7 +510,8 @@ static bool scales_fit_f16(const dsx_expert_store* st) {
 
 // picks -> out.  expert_lo / n_local select the owned id range (0 / n_expert for a full layer).
 static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, const int32_t* selected, const float* weights,
-                        int expert_lo, bool filter_picks, int with_shared, __nv_bfloat16* out, cudaStream_t stream) {
+                        int expert_lo, bool filter_picks, int with_shared, __nv_bfloat16* out, cudaStream_t stream,
+                        bool groups_ready = false) {
     const dsx_moe_config& c = L->cfg;
     const int k = c.router.n_used, n_local = L->routed->n_slots;
     const bool shared = with_shared && L->shared != nullptr;
@@ -521,7 +530,7 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
         StageTimer tm(L, DSX_STAGE_GATE_UP, stream);
         return prefill_forward(&L->pf, c, pc, stream);
     }
-    {
+    if (!groups_ready) {   // the one-launch decode router has already built them
         StageTimer tm(L, DSX_STAGE_GROUP_BUILD, stream);
         if (int rc = launch_group_build(selected, T, k, n_local, expert_lo, 8, shared ? (int)T : 0, L->hist, L->offsets, L->perm,
                                         L->work_items, L->n_work_items, L->work_cap, L->gs, stream))
@@ -562,6 +571,18 @@ int dsx_moe_layer_forward(dsx_moe_layer* L, const void* x_bf16, int64_t T, void*
     const __nv_bfloat16* x = (const __nv_bfloat16*)x_bf16;
     const float* logits = logits_in;
     if (L->profile) for (bool& u : L->ev_used) u = false;
+    if (!logits && router_fused_ok(T, L->cfg.router, L->cfg.hidden)) {
+        // decode: logits, top-k and the group build in one launch
+        {
+            StageTimer tm(L, DSX_STAGE_ROUTER_LOGITS, stream);
+            if (int rc = launch_router_fused(x, T, L->router_w, L->router_bias, L->cfg.hidden, L->cfg.router, L->logits, L->selected,
+                                             L->weights, 8, L->shared ? (int)T : 0, L->hist, L->offsets, L->perm, L->work_items,
+                                             L->n_work_items, L->work_cap, L->router_counters, stream))
+                return rc;
+        }
+        L->last_logits = L->logits; L->last_selected = L->selected; L->last_weights = L->weights;
+        return forward_core(L, x, T, L->selected, L->weights, 0, false, 1, (__nv_bfloat16*)out_bf16, stream, true);
+    }
     if (!logits) {
         StageTimer tm(L, DSX_STAGE_ROUTER_LOGITS, stream);
         if (int rc = launch_router_logits(x, T, L->router_w, L->cfg.router.n_expert, L->cfg.hidden, L->logits, stream)) return rc;

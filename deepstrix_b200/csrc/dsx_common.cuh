@@ -154,6 +154,12 @@ int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int 
                          cudaStream_t stream);
 int launch_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg,
                        int32_t* selected, float* weights, cudaStream_t stream);
+int router_configure();
+bool router_fused_ok(int64_t T, const dsx_router_config& cfg, int64_t H);
+int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const float* bias, int64_t H, const dsx_router_config& cfg,
+                        float* logits, int32_t* selected, float* weights, int chunk, int shared_T, int32_t* hist, int32_t* offsets,
+                        int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap, unsigned int* counters,
+                        cudaStream_t stream);
 
 // groups.cu
 struct GroupScratch {      // device scratch for the multi-block counting sort

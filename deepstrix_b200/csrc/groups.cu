@@ -12,109 +12,15 @@
 // and per-block prefix sums order the steps.
 #include <mutex>
 
-#include "dsx_common.cuh"
+#include "groups.cuh"
 
 namespace dsx {
 namespace {
 
+using namespace groupdev;
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kPerWarp = kGroupChunk / kWarps;  // 128 picks per warp
 constexpr int kMaxExperts = 512;
-
-// wh[w*E + e] = picks of local expert e inside warp w's slice of the chunk.
-__device__ void chunk_count(const int32_t* __restrict__ sel, int64_t P, int64_t chunk_base, int E, int lo, int* wh) {
-    for (int i = threadIdx.x; i < kWarps * E; i += kThreads) wh[i] = 0;
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int it = 0; it < kPerWarp / 32; it++) {
-        const int64_t idx = chunk_base + warp * kPerWarp + it * 32 + lane;
-        if (idx < P) {
-            const int e = sel[idx] - lo;
-            if (e >= 0 && e < E) atomicAdd(&wh[warp * E + e], 1);
-        }
-    }
-    __syncthreads();
-}
-
-// Exclusive scan of one value per thread over the block (kThreads threads).
-__device__ int block_exclusive_scan(int v, int* total, int* s_warp /*[kWarps+1]*/) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int inc = v;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const int o = __shfl_up_sync(0xFFFFFFFFu, inc, off);
-        if (lane >= off) inc += o;
-    }
-    if (lane == 31) s_warp[warp] = inc;
-    __syncthreads();
-    if (warp == 0) {
-        int w = lane < kWarps ? s_warp[lane] : 0;
-        int winc = w;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const int o = __shfl_up_sync(0xFFFFFFFFu, winc, off);
-            if (lane >= off) winc += o;
-        }
-        if (lane < kWarps) s_warp[lane] = winc - w;
-        if (lane == kWarps - 1) s_warp[kWarps] = winc;
-    }
-    __syncthreads();
-    const int res = s_warp[warp] + inc - v;
-    *total = s_warp[kWarps];
-    __syncthreads();
-    return res;
-}
-
-// From hist (one expert per thread): offsets, work items (+ shared-expert items).
-__device__ void write_offsets_and_items(int e, int E, int h, int chunk, int shared_T, int32_t* hist, int32_t* offsets,
-                                        int32_t* work_items, int32_t* n_work_items, int32_t work_cap, int* s_warp) {
-    int total;
-    const int off = block_exclusive_scan(e < E ? h : 0, &total, s_warp);
-    if (e < E) {
-        hist[e] = h;
-        offsets[e] = off;
-    }
-    if (threadIdx.x == 0) offsets[E] = total;
-    if (work_items != nullptr) {
-        const int ni = (e < E) ? (h + chunk - 1) / chunk : 0;
-        int n_items;
-        const int ibase = block_exclusive_scan(ni, &n_items, s_warp);
-        for (int c = 0; c < ni; c++) {
-            const int p = ibase + c;
-            if (p < work_cap) work_items[p] = (int32_t)(((uint32_t)e << 16) | (((uint32_t)(c * chunk)) & 0xFFFFu));
-        }
-        // the shared expert is appended as pseudo expert id E over all tokens
-        const int n_sh = (shared_T + chunk - 1) / chunk;
-        for (int c = threadIdx.x; c < n_sh; c += kThreads) {
-            const int p = n_items + c;
-            if (p < work_cap) work_items[p] = (int32_t)(((uint32_t)E << 16) | (((uint32_t)(c * chunk)) & 0xFFFFu));
-        }
-        if (threadIdx.x == 0) n_work_items[0] = n_items + n_sh;
-    }
-}
-
-// Stable placement of this block's chunk.  wh[w*E+e] holds the first free
-// position of expert e for warp w; each warp walks its slice in order.
-__device__ void chunk_place(const int32_t* __restrict__ sel, int64_t P, int64_t chunk_base, int E, int lo, int* wh,
-                            int32_t* __restrict__ perm) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int it = 0; it < kPerWarp / 32; it++) {
-        const int64_t idx = chunk_base + warp * kPerWarp + it * 32 + lane;
-        int e = -1;
-        if (idx < P) {
-            e = sel[idx] - lo;
-            if (e < 0 || e >= E) e = -1;
-        }
-        const int key = e >= 0 ? e : (0x40000000 | lane);
-        const uint32_t mask = __match_any_sync(0xFFFFFFFFu, key);
-        const int rank = __popc(mask & ((1u << lane) - 1u));
-        if (e >= 0) perm[wh[warp * E + e] + rank] = (int32_t)idx;
-        __syncwarp();
-        if (e >= 0 && rank == 0) wh[warp * E + e] += __popc(mask);
-        __syncwarp();
-    }
-}
 
 // Single block: T*k <= kGroupChunk.
 __global__ void __launch_bounds__(kThreads)
@@ -123,28 +29,13 @@ group_build_small_kernel(const int32_t* __restrict__ sel, int64_t P, int E, int 
                          int32_t work_cap) {
     extern __shared__ int wh[];
     __shared__ int s_warp[kWarps + 1];
-    chunk_count(sel, P, 0, E, lo, wh);
-    const int e = threadIdx.x;
-    int h = 0;
-    if (e < E)
-        for (int w = 0; w < kWarps; w++) h += wh[w * E + e];
-    write_offsets_and_items(e, E, h, chunk, shared_T, hist, offsets, work_items, n_work_items, work_cap, s_warp);
-    if (e < E) {
-        int run = offsets[e];
-        for (int w = 0; w < kWarps; w++) {
-            const int v = wh[w * E + e];
-            wh[w * E + e] = run;
-            run += v;
-        }
-    }
-    __syncthreads();
-    chunk_place(sel, P, 0, E, lo, wh, perm);
+    build_small<kThreads>(sel, P, E, lo, chunk, shared_T, hist, offsets, perm, work_items, n_work_items, work_cap, wh, s_warp);
 }
 
 __global__ void __launch_bounds__(kThreads)
 group_count_kernel(const int32_t* __restrict__ sel, int64_t P, int E, int lo, int32_t* __restrict__ chunk_hist) {
     extern __shared__ int wh[];
-    chunk_count(sel, P, (int64_t)blockIdx.x * kGroupChunk, E, lo, wh);
+    chunk_count<kThreads>(sel, P, (int64_t)blockIdx.x * kGroupChunk, E, lo, wh);
     for (int e = threadIdx.x; e < E; e += kThreads) {
         int h = 0;
         for (int w = 0; w < kWarps; w++) h += wh[w * E + e];
@@ -164,7 +55,7 @@ group_scan_kernel(int n_chunks, int E, int chunk, int shared_T, int32_t* chunk_h
             chunk_hist[(int64_t)c * E + e] = run;  // picks of e in earlier chunks
             run += v;
         }
-    write_offsets_and_items(e, E, run, chunk, shared_T, hist, offsets, work_items, n_work_items, work_cap, s_warp);
+    write_offsets_and_items<kThreads>(e, E, run, chunk, shared_T, hist, offsets, work_items, n_work_items, work_cap, s_warp);
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -172,7 +63,7 @@ group_place_kernel(const int32_t* __restrict__ sel, int64_t P, int E, int lo, co
                    const int32_t* __restrict__ offsets, int32_t* __restrict__ perm) {
     extern __shared__ int wh[];
     const int64_t base = (int64_t)blockIdx.x * kGroupChunk;
-    chunk_count(sel, P, base, E, lo, wh);
+    chunk_count<kThreads>(sel, P, base, E, lo, wh);
     for (int e = threadIdx.x; e < E; e += kThreads) {
         int run = offsets[e] + chunk_hist[(int64_t)blockIdx.x * E + e];
         for (int w = 0; w < kWarps; w++) {
@@ -182,7 +73,7 @@ group_place_kernel(const int32_t* __restrict__ sel, int64_t P, int E, int lo, co
         }
     }
     __syncthreads();
-    chunk_place(sel, P, base, E, lo, wh, perm);
+    chunk_place<kThreads>(sel, P, base, E, lo, wh, perm);
 }
 
 // Scratch of the allocation-free entry point: the per-chunk histograms of the

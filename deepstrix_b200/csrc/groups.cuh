@@ -1,0 +1,134 @@
+// Device building blocks of the stable counting sort (histogram, offsets, permutation, work
+// items), templated on the block size so that both the stand-alone group-build kernels (512
+// threads) and the fused decode router (256 threads) use the same code.  See groups.cu.
+#pragma once
+#include "dsx_common.cuh"
+
+namespace dsx {
+namespace groupdev {
+
+// wh[w*E + e] = picks of local expert e inside warp w's slice of the chunk.
+template <int NT>
+__device__ void chunk_count(const int32_t* __restrict__ sel, int64_t P, int64_t chunk_base, int E, int lo, int* wh) {
+    for (int i = threadIdx.x; i < (NT / 32) * E; i += NT) wh[i] = 0;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int it = 0; it < (kGroupChunk / (NT / 32)) / 32; it++) {
+        const int64_t idx = chunk_base + warp * (kGroupChunk / (NT / 32)) + it * 32 + lane;
+        if (idx < P) {
+            const int e = sel[idx] - lo;
+            if (e >= 0 && e < E) atomicAdd(&wh[warp * E + e], 1);
+        }
+    }
+    __syncthreads();
+}
+
+// Exclusive scan of one value per thread over the block (NT threads).
+template <int NT>
+__device__ int block_exclusive_scan(int v, int* total, int* s_warp /*[(NT / 32)+1]*/) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int inc = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(0xFFFFFFFFu, inc, off);
+        if (lane >= off) inc += o;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < (NT / 32) ? s_warp[lane] : 0;
+        int winc = w;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xFFFFFFFFu, winc, off);
+            if (lane >= off) winc += o;
+        }
+        if (lane < (NT / 32)) s_warp[lane] = winc - w;
+        if (lane == (NT / 32) - 1) s_warp[(NT / 32)] = winc;
+    }
+    __syncthreads();
+    const int res = s_warp[warp] + inc - v;
+    *total = s_warp[(NT / 32)];
+    __syncthreads();
+    return res;
+}
+
+// From hist (one expert per thread): offsets, work items (+ shared-expert items).
+template <int NT>
+__device__ void write_offsets_and_items(int e, int E, int h, int chunk, int shared_T, int32_t* hist, int32_t* offsets,
+                                        int32_t* work_items, int32_t* n_work_items, int32_t work_cap, int* s_warp) {
+    int total;
+    const int off = block_exclusive_scan<NT>(e < E ? h : 0, &total, s_warp);
+    if (e < E) {
+        hist[e] = h;
+        offsets[e] = off;
+    }
+    if (threadIdx.x == 0) offsets[E] = total;
+    if (work_items != nullptr) {
+        const int ni = (e < E) ? (h + chunk - 1) / chunk : 0;
+        int n_items;
+        const int ibase = block_exclusive_scan<NT>(ni, &n_items, s_warp);
+        for (int c = 0; c < ni; c++) {
+            const int p = ibase + c;
+            if (p < work_cap) work_items[p] = (int32_t)(((uint32_t)e << 16) | (((uint32_t)(c * chunk)) & 0xFFFFu));
+        }
+        // the shared expert is appended as pseudo expert id E over all tokens
+        const int n_sh = (shared_T + chunk - 1) / chunk;
+        for (int c = threadIdx.x; c < n_sh; c += NT) {
+            const int p = n_items + c;
+            if (p < work_cap) work_items[p] = (int32_t)(((uint32_t)E << 16) | (((uint32_t)(c * chunk)) & 0xFFFFu));
+        }
+        if (threadIdx.x == 0) n_work_items[0] = n_items + n_sh;
+    }
+}
+
+// Stable placement of this block's chunk.  wh[w*E+e] holds the first free
+// position of expert e for warp w; each warp walks its slice in order.
+template <int NT>
+__device__ void chunk_place(const int32_t* __restrict__ sel, int64_t P, int64_t chunk_base, int E, int lo, int* wh,
+                            int32_t* __restrict__ perm) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int it = 0; it < (kGroupChunk / (NT / 32)) / 32; it++) {
+        const int64_t idx = chunk_base + warp * (kGroupChunk / (NT / 32)) + it * 32 + lane;
+        int e = -1;
+        if (idx < P) {
+            e = sel[idx] - lo;
+            if (e < 0 || e >= E) e = -1;
+        }
+        const int key = e >= 0 ? e : (0x40000000 | lane);
+        const uint32_t mask = __match_any_sync(0xFFFFFFFFu, key);
+        const int rank = __popc(mask & ((1u << lane) - 1u));
+        if (e >= 0) perm[wh[warp * E + e] + rank] = (int32_t)idx;
+        __syncwarp();
+        if (e >= 0 && rank == 0) wh[warp * E + e] += __popc(mask);
+        __syncwarp();
+    }
+}
+
+
+// One expert per thread (needs E <= NT): the whole build for T*k <= kGroupChunk picks inside one block.  wh: NT/32 * E ints of shared memory,
+// s_warp: NT/32 + 1 ints.
+template <int NT>
+__device__ void build_small(const int32_t* __restrict__ sel, int64_t P, int E, int lo, int chunk, int shared_T, int32_t* hist,
+                            int32_t* offsets, int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap,
+                            int* wh, int* s_warp) {
+    chunk_count<NT>(sel, P, 0, E, lo, wh);
+    const int e = threadIdx.x;
+    int h = 0;
+    if (e < E)
+        for (int w = 0; w < NT / 32; w++) h += wh[w * E + e];
+    write_offsets_and_items<NT>(e, E, h, chunk, shared_T, hist, offsets, work_items, n_work_items, work_cap, s_warp);
+    if (e < E) {
+        int run = offsets[e];
+        for (int w = 0; w < NT / 32; w++) {
+            const int v = wh[w * E + e];
+            wh[w * E + e] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    chunk_place<NT>(sel, P, 0, E, lo, wh, perm);
+}
+
+}  // namespace groupdev
+}  // namespace dsx

@@ -6,7 +6,9 @@
 //           index wins ties) and :294-434 (the 64-bit-key wave-reduction twin whose key
 //           `(ord(score) << 32) | ~index` is reused here)
 //   sigmoid crates/v4flash-kernels/kernels/laguna_ops.hip:55-62
-#include "dsx_common.cuh"
+#include <algorithm>
+
+#include "groups.cuh"
 
 namespace dsx {
 namespace {
@@ -72,35 +74,32 @@ __device__ __forceinline__ uint32_t ordered_bits(float f) {
 constexpr int kTopkWarps = 8;
 constexpr int kMaxUsed = 16;
 
-// One warp per token, VPL experts per lane (expert e = lane*VPL + j).
-template <int VPL>
-__global__ void __launch_bounds__(kTopkWarps * 32)
-router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, dsx_router_config cfg,
-                   int32_t* __restrict__ selected, float* __restrict__ weights) {
-    __shared__ float s_score[kTopkWarps][VPL * 32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t t = (int64_t)blockIdx.x * kTopkWarps + warp;
-    if (t >= T) return;
+// Top-k of one token by one warp, VPL experts per lane (expert e = lane*VPL + j).
+// s_score: E floats of shared memory private to the warp.
+template <int VPL, typename LoadLogit>
+__device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float* __restrict__ bias, const dsx_router_config& cfg,
+                                               int32_t* __restrict__ sel_out, float* __restrict__ w_out, float* s_score) {
+    const int lane = threadIdx.x & 31;
     const int E = VPL * 32;
     float p[VPL], s[VPL];
 #pragma unroll
     for (int j = 0; j < VPL; j++) {
         const int e = lane * VPL + j;
-        p[j] = router_prob(logits[t * E + e], cfg.score_fn);
+        p[j] = router_prob(load_logit(e), cfg.score_fn);
         s[j] = bias ? __fadd_rn(p[j], bias[e]) : p[j];
     }
     if (cfg.n_group > 1) {
         // group score = sum of the two largest selection scores of the group;
         // keep the topk_group best groups (equal -> lower group index)
 #pragma unroll
-        for (int j = 0; j < VPL; j++) s_score[warp][lane * VPL + j] = s[j];
+        for (int j = 0; j < VPL; j++) s_score[lane * VPL + j] = s[j];
         __syncwarp();
         const int per = E / cfg.n_group;
         float gs = -INFINITY;
         if (lane < cfg.n_group) {
             float m1 = -INFINITY, m2 = -INFINITY;
             for (int i = 0; i < per; i++) {
-                const float v = s_score[warp][lane * per + i];
+                const float v = s_score[lane * per + i];
                 if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
             }
             gs = __fadd_rn(m1, m2);
@@ -156,12 +155,117 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
 #pragma unroll
     for (int r = 0; r < kMaxUsed; r++)
         if (r < cfg.n_used && lane == (r & 31)) {
-            selected[t * cfg.n_used + r] = esel[r];
-            weights[t * cfg.n_used + r] = __fmul_rn(__fdiv_rn(psel[r], sum), cfg.route_scale);
+            sel_out[r] = esel[r];
+            w_out[r] = __fmul_rn(__fdiv_rn(psel[r], sum), cfg.route_scale);
         }
 }
 
+template <int VPL>
+__global__ void __launch_bounds__(kTopkWarps * 32)
+router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, dsx_router_config cfg,
+                   int32_t* __restrict__ selected, float* __restrict__ weights) {
+    __shared__ float s_score[kTopkWarps][VPL * 32];
+    const int warp = threadIdx.x >> 5;
+    const int64_t t = (int64_t)blockIdx.x * kTopkWarps + warp;
+    if (t >= T) return;
+    const float* row = logits + t * (VPL * 32);
+    topk_one_token<VPL>([&](int e) { return row[e]; }, bias, cfg, selected + t * cfg.n_used, weights + t * cfg.n_used, s_score[warp]);
+}
+
+// ---- Decode router in ONE launch (T <= 64, E <= 256): logits, top-k and the group build.
+// Grid (E/8, ceil(T/8)), 8 warps.  Each block stages its 8 token rows in shared memory and its warps
+// stream one router row each (same f32 operation order as router_logits_kernel, so the logits
+// are the same bits).  The last block of a token tile to finish (ticket counter) selects the
+// experts of that tile's tokens, one warp per token; the last tile to finish builds histogram,
+// offsets, permutation and work items.  The counters return to zero for the next launch.
+template <int VPL>
+__global__ void __launch_bounds__(kLogitWarps * 32)
+router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __restrict__ W, const float* __restrict__ bias, int H,
+                    dsx_router_config cfg, float* __restrict__ logits, int32_t* __restrict__ selected, float* __restrict__ weights,
+                    int chunk, int shared_T, int32_t* hist, int32_t* offsets, int32_t* perm, int32_t* work_items,
+                    int32_t* n_work_items, int32_t work_cap, unsigned int* counters /* [0]: tiles done, [1 + tile]: blocks done */) {
+    extern __shared__ __align__(16) uint8_t fsm[];
+    __shared__ int s_flag;
+    __shared__ int s_warp[kLogitWarps + 1];
+    constexpr int E = VPL * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.y, t0 = tile * kLogitTokens;
+    const int nt = min(kLogitTokens, T - t0);
+    // token rows of the tile -> shared memory (rows past the batch alias the last valid row)
+    uint2* xs = reinterpret_cast<uint2*>(fsm);   // [8][H/4] of 4 x bf16
+    const int vec = H >> 2;
+    for (int i = threadIdx.x; i < kLogitTokens * vec; i += kLogitWarps * 32) {
+        const int r = i / vec, c = i - r * vec;
+        xs[i] = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)min(t0 + r, T - 1) * H) + c);
+    }
+    __syncthreads();
+    const int e = blockIdx.x * kLogitWarps + warp;
+    {
+        float acc[kLogitTokens];
+#pragma unroll
+        for (int i = 0; i < kLogitTokens; i++) acc[i] = 0.0f;
+        const float4* wrow = reinterpret_cast<const float4*>(W + (int64_t)e * H) + lane;
+        const int n_iter = H >> 7;
+#pragma unroll 8
+        for (int i = 0; i < n_iter; i++) {
+            const float4 w = __ldg(wrow + i * 32);
+#pragma unroll
+            for (int tt = 0; tt < kLogitTokens; tt++) {
+                const uint2 xv = xs[tt * vec + i * 32 + lane];
+                const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
+                const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
+                float a = acc[tt];
+                a = __fmaf_rn(w.x, x0, a);
+                a = __fmaf_rn(w.y, x1, a);
+                a = __fmaf_rn(w.z, x2, a);
+                a = __fmaf_rn(w.w, x3, a);
+                acc[tt] = a;
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < kLogitTokens; tt++) {
+            float a = acc[tt];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, off));
+            if (lane == 0 && tt < nt) logits[(int64_t)(t0 + tt) * E + e] = a;
+        }
+    }
+    // ---- last block of this token tile?
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_flag = (atomicAdd(&counters[1 + tile], 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_flag) return;
+    if (threadIdx.x == 0) counters[1 + tile] = 0u;
+    __threadfence();
+    float* s_score = reinterpret_cast<float*>(fsm);   // the token rows are no longer needed
+    if (warp < nt) {
+        const float* row = logits + (int64_t)(t0 + warp) * E;
+        topk_one_token<VPL>([&](int ee) { return __ldcg(row + ee); }, bias, cfg, selected + (int64_t)(t0 + warp) * cfg.n_used,
+                            weights + (int64_t)(t0 + warp) * cfg.n_used, s_score + warp * E);
+    }
+    // ---- last tile of the launch?
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_flag = (atomicAdd(&counters[0], 1u) == gridDim.y - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_flag) return;
+    if (threadIdx.x == 0) counters[0] = 0u;
+    __threadfence();
+    int* wh = reinterpret_cast<int*>(fsm);
+    groupdev::build_small<kLogitWarps * 32>(selected, (int64_t)T * cfg.n_used, E, 0, chunk, shared_T, hist, offsets, perm, work_items,
+                                            n_work_items, work_cap, wh, s_warp);
+}
+
 }  // namespace
+
+// Shapes the one-launch decode router covers (everything else takes the three separate kernels).
+bool router_fused_ok(int64_t T, const dsx_router_config& cfg, int64_t H) {
+    const int v = cfg.n_expert / 32;
+    return T >= 1 && T <= 64 && cfg.n_expert % 32 == 0 && (v == 1 || v == 2 || v == 4 || v == 8) && H % 128 == 0 &&
+           (size_t)kLogitTokens * H * 2 <= 96 * 1024 && T * cfg.n_used <= kGroupChunk && cfg.n_used <= kMaxUsed &&
+           (cfg.n_group <= 1 || (cfg.n_group <= 32 && cfg.n_expert % cfg.n_group == 0));
+}
 
 int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int n_expert, int64_t H, float* logits,
                          cudaStream_t stream) {
@@ -170,6 +274,38 @@ int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int 
     dim3 grid((unsigned)((n_expert + kLogitWarps - 1) / kLogitWarps), (unsigned)((T + kLogitTokens - 1) / kLogitTokens));
     router_logits_kernel<<<grid, kLogitWarps * 32, 0, stream>>>(x, T, W, n_expert, H, logits);
     DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const float* bias, int64_t H, const dsx_router_config& cfg,
+                        float* logits, int32_t* selected, float* weights, int chunk, int shared_T, int32_t* hist, int32_t* offsets,
+                        int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap, unsigned int* counters,
+                        cudaStream_t stream) {
+    DSX_REQUIRE(router_fused_ok(T, cfg, H), "router_fused: shape not covered");
+    const size_t smem = std::max<size_t>((size_t)kLogitTokens * H * 2, (size_t)kLogitWarps * cfg.n_expert * 4);
+    dim3 grid((unsigned)(cfg.n_expert / kLogitWarps), (unsigned)((T + kLogitTokens - 1) / kLogitTokens));
+    switch (cfg.n_expert / 32) {
+#define DSX_FUSED_CASE(V)                                                                                                     \
+    case V:                                                                                                                   \
+        router_fused_kernel<V><<<grid, kLogitWarps * 32, smem, stream>>>(x, (int)T, W, bias, (int)H, cfg, logits, selected, weights, \
+                                                                        chunk, shared_T, hist, offsets, perm, work_items,     \
+                                                                        n_work_items, work_cap, counters);                    \
+        break;
+        DSX_FUSED_CASE(1) DSX_FUSED_CASE(2) DSX_FUSED_CASE(4) DSX_FUSED_CASE(8)
+#undef DSX_FUSED_CASE
+        default:
+            return set_error(DSX_ERR_UNSUPPORTED, "router_fused: n_expert %d not instantiated", cfg.n_expert);
+    }
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+// Opt the fused router in to 96 KB of dynamic shared memory (once per device, at layer creation).
+int router_configure() {
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     return DSX_OK;
 }
 
