@@ -15,6 +15,8 @@ namespace {
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int64_t H, int with_shared,
                const int32_t* __restrict__ selected, int expert_lo, int n_local, __nv_bfloat16* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();   // partial rows come from the down kernel
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t per_row = H >> 2;
     if (gid >= T * per_row) return;
@@ -52,8 +54,8 @@ int launch_combine(const float* partial, int64_t T, int n_used, int64_t H, int w
     DSX_REQUIRE(H % 4 == 0, "combine: hidden must be a multiple of 4");
     if (T == 0) return DSX_OK;
     const int64_t n = T * (H / 4);
-    combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(partial, T, n_used, H, with_shared, selected, expert_lo,
-                                                                    n_local, out);
+    DSX_CUDA(launch_pdl(combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, partial, T, n_used, H, with_shared,
+                        selected, expert_lo, n_local, out));
     DSX_LAUNCHED();
     return DSX_OK;
 }

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/dsx_moe.h"
 
 namespace dsx {
@@ -34,6 +36,29 @@ void count_launch();
         ::dsx::count_launch();                                                              \
         DSX_CUDA(cudaGetLastError());                                                       \
     } while (0)
+
+// Programmatic dependent launch: the decode chain (router -> gate/up -> down -> combine) is four
+// short kernels, so each is launched with the stream-serialization attribute: its blocks may be
+// scheduled while the previous kernel drains, do their set-up, and block in pdl_wait() until the
+// previous grid has completed and its writes are visible.  Every kernel of the chain calls
+// pdl_wait() before its first global access to data another kernel of the chain touches.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
 
 // ------------------------------------------------------------ tile layout
 // A weight matrix [rows, K] is stored as sub-tiles of 16 rows.  One sub-tile is

@@ -169,12 +169,16 @@ struct ItemInfo {
 // FMT: routed format for routed items; shared items use SFMT.  The kernel is
 // compiled for the (FMT, SFMT) pairs with FMT == SFMT only, which keeps one
 // decode path per item.
-// WARPS: 8 (4 ring stages per warp) for very small batches, where the units would not cover all SMs
-// with 256-row blocks; 16 (2 stages per warp) otherwise: four warps per scheduler hide the
-// cvt -> mma -> fma latencies that two cannot.
-template <int FMT, bool PAIR, int WARPS>
+// WARPS / KSPLIT: four warps per scheduler hide the cvt -> mma -> fma latencies that two cannot, so
+// blocks have 16 warps (2 ring stages each) whenever the shape allows.  With >= 8 tokens there are
+// enough (item, 256-row block) units for every SM (KSPLIT 1: one row tile per warp).  Below that,
+// units stay 128 rows and two warps share a row tile, each taking one half of the reduction
+// (KSPLIT 2); the halves are added through shared memory.  Every variant adds
+// (first half of the columns) + (second half), so the bits do not depend on the variant.
+template <int FMT, bool PAIR, int WARPS, int KSPLIT>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     constexpr int kWarps = WARPS, kThreads = WARPS * 32, kStages = kRingStagesPerBlock / WARPS;
+    constexpr int kRowWarps = WARPS / KSPLIT;   // row tiles per unit
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int kTileK = (FMT == DSX_FMT_MXFP4) ? 64 : 32;
     constexpr int kBlocks = kTileK / 32;            // 32-column scale blocks per sub-tile
@@ -188,6 +192,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     uint8_t* ring = smem + (((size_t)kMaxTok * act_stride * 2 + 127) & ~(size_t)127);
     uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)kWarps * kStages * kStageBytes);
     ItemInfo* info = reinterpret_cast<ItemInfo*>(bars + kWarps * kStages);
+    float* halves = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(info) + ((sizeof(ItemInfo) + 127) & ~(size_t)127));  // KSPLIT 2: [2][kRowWarps][32][8]
+    const int rw = warp % kRowWarps, kh = warp / kRowWarps;   // row tile inside the unit, reduction half
 
     uint8_t* my_ring = ring + (size_t)warp * kStages * kStageBytes;
     const uint32_t my_bars = smem_u32(bars + warp * kStages);
@@ -195,14 +201,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
         for (int s = 0; s < kStages; s++) mbar_init(my_bars + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();   // work items, routing and activations come from the previous kernels of the chain
 
     const int n_items = a.n_work_items[0];
     const int n_kt = (int)(K / kTileK);
     const int n_stage = (n_kt + kCtPerStage - 1) / kCtPerStage;
-    const int bpi = (int)(a.rows / (kTileRows * kWarps));  // 128-row blocks per item
+    const int bpi = (int)(a.rows / (kTileRows * kRowWarps));  // row blocks per item
     const int U = n_items * bpi;
     const int u0 = (int)((int64_t)U * blockIdx.x / gridDim.x), u1 = (int)((int64_t)U * (blockIdx.x + 1) / gridDim.x);
-    const int total = (u1 - u0) * n_stage;  // ring stages this warp will consume
+    const int n_half = n_stage / KSPLIT;    // stages of a unit this warp consumes (the launcher picks KSPLIT 2 only for even n_stage)
+    const int hs = n_stage / 2;             // stages below hs form the "first half" sum in every variant
+    const int total = (u1 - u0) * n_half;   // ring stages this warp will consume
     const int P = (int)(a.T * a.n_used);
 
     // ---- producer state (lane 0): next stage to request, tracked incrementally
@@ -216,8 +226,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
             p_sc = (e == a.n_expert) ? a.sh_sc : a.sc + (int64_t)e * a.sc_slot_stride;
             p_cached = p_item;
         }
-        const int rt = p_rb * kWarps + warp;
-        const int ct0 = p_ls * kCtPerStage;
+        const int rt = p_rb * kRowWarps + rw;
+        const int ct0 = (kh * n_half + p_ls) * kCtPerStage;
         const int n_ct = min(kCtPerStage, n_kt - ct0);
         const int64_t sub0 = ((int64_t)rt * n_kt + ct0) * kSubPerCt;
         const uint32_t nsub = (uint32_t)(n_ct * kSubPerCt);
@@ -228,7 +238,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
         bulk_g2s(dst, p_nib + sub0 * kSubNibBytes, nsub * kSubNibBytes, bar);
         bulk_g2s(dst + kStageNib, p_sc + sub0 * kSubScBytes, nsub * kSubScBytes, bar);
         p_cnt++;
-        if (++p_ls == n_stage) {
+        if (++p_ls == n_half) {
             p_ls = 0;
             if (++p_rb == bpi) { p_rb = 0; p_item++; }
         }
@@ -240,7 +250,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     int item = u0 / bpi, rb = u0 - item * bpi, ls = 0;
     int cur_item = -1;
     bool dead = false;
-    float acc0[4], acc1[4];
+    int unit_parity = 0;
+    float acc0[4], acc1[4];     // running sums of the current half of the columns (gate / up, or single)
+    float acc0a[4], acc1a[4];   // finished first half
     for (int cnt = 0; cnt < total; cnt++) {
         if (ls == 0) {
             if (item != cur_item) {
@@ -294,7 +306,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
                 cur_item = item;
             }
 #pragma unroll
-            for (int i = 0; i < 4; i++) acc0[i] = acc1[i] = 0.f;
+            for (int i = 0; i < 4; i++) acc0[i] = acc1[i] = acc0a[i] = acc1a[i] = 0.f;
         }
         const int slot = cnt & (kStages - 1);
         if (!dead && !mbar_wait(my_bars + 8 * slot, (uint32_t)((cnt / kStages) & 1))) {
@@ -304,8 +316,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
         if (!dead) {
             const uint8_t* st_nib = my_ring + (size_t)slot * kStageBytes;
             const uint8_t* st_sc = st_nib + kStageNib;
-            const int ct0 = ls * kCtPerStage;
+            const int ls_all = kh * n_half + ls;   // stage index inside the whole reduction
+            const int ct0 = ls_all * kCtPerStage;
             const int n_ct = min(kCtPerStage, n_kt - ct0);
+            if (ls_all == hs) {   // the second half starts: park the first half's sums
+#pragma unroll
+                for (int i = 0; i < 4; i++) { acc0a[i] = acc0[i]; acc1a[i] = acc1[i]; acc0[i] = acc1[i] = 0.f; }
+            }
             const bool tok_ok = g < info->n_tok;
             const __half* arow = act + (size_t)g * act_stride + (size_t)ct0 * kTileK + 8 * t4;
             auto col_tile = [&](int c) {
@@ -329,8 +346,27 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
         __syncwarp();
         if (lane == 0 && !dead && p_cnt < total) issue();
 
-        if (ls == n_stage - 1 && !dead) {
-            const int row0 = (rb * kWarps + warp) * kTileRows + g;
+        if (KSPLIT == 2 && ls == n_half - 1) {
+            // hand the second half's sums to the warp that owns the row tile
+            float* slot = halves + ((size_t)(unit_parity * kRowWarps + rw) * 32 + lane) * 8;
+            if (kh == 1) {   // this warp's running sums ARE the second half
+#pragma unroll
+                for (int i = 0; i < 4; i++) { slot[i] = acc0[i]; slot[4 + i] = acc1[i]; }
+            }
+            __syncthreads();
+            if (kh == 0) {   // this warp's running sums are the first half
+#pragma unroll
+                for (int i = 0; i < 4; i++) { acc0a[i] = acc0[i]; acc1a[i] = acc1[i]; acc0[i] = slot[i]; acc1[i] = slot[4 + i]; }
+            }
+            unit_parity ^= 1;
+        }
+        if (ls == n_half - 1 && !dead && kh == 0) {
+            const int row0 = (rb * kRowWarps + rw) * kTileRows + g;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {   // (first half) + (second half), the same in every variant
+                acc0[i] = acc0a[i] + acc0[i];
+                acc1[i] = acc1a[i] + acc1[i];
+            }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int n = 2 * t4 + (i & 1);
@@ -350,7 +386,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
                 }
             }
         }
-        if (++ls == n_stage) {
+        if (++ls == n_half) {
             ls = 0;
             if (++rb == bpi) { rb = 0; item++; }
         }
@@ -359,7 +395,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
 
 size_t gemv_smem_bytes(int64_t K) {
     const size_t act = (((size_t)kMaxTok * (size_t)(K + kActPad) * 2) + 127) & ~(size_t)127;
-    return act + (size_t)kRingStagesPerBlock * kStageBytes + sizeof(uint64_t) * kRingStagesPerBlock + sizeof(ItemInfo) + 128;
+    return act + (size_t)kRingStagesPerBlock * kStageBytes + sizeof(uint64_t) * kRingStagesPerBlock + ((sizeof(ItemInfo) + 127) & ~(size_t)127) +
+           (size_t)2 * 8 * 32 * 8 * sizeof(float) + 128;
 }
 
 constexpr size_t kMaxSmem = 227 * 1024;
@@ -371,8 +408,11 @@ int launch_one(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     // 256-row blocks need enough (item, block) units to occupy every SM twice over; the item count
     // lives on the device, so decide on the batch size (>= 8 tokens x top-k picks is plenty)
     const bool wide = a.rows % (kTileRows * 16) == 0 && a.T >= 8;
-    if (wide) gemv_kernel<FMT, PAIR, 16><<<sm_count, 16 * 32, smem, stream>>>(a);
-    else gemv_kernel<FMT, PAIR, 8><<<sm_count, 8 * 32, smem, stream>>>(a);
+    const int tile_k = FMT == DSX_FMT_MXFP4 ? 64 : 32, ct_per_stage = PAIR ? kSubPerStage / 2 : kSubPerStage;
+    const int n_stage = (int)((a.K / tile_k + ct_per_stage - 1) / ct_per_stage);
+    if (wide) DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, 16, 1>, dim3(sm_count), dim3(16 * 32), smem, stream, a));
+    else if (n_stage % 2 == 0) DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, 16, 2>, dim3(sm_count), dim3(16 * 32), smem, stream, a));
+    else DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, 8, 1>, dim3(sm_count), dim3(8 * 32), smem, stream, a));
     DSX_LAUNCHED();
     return DSX_OK;
 }
@@ -403,11 +443,11 @@ int launch_gemv_down(const GemvArgs& a, int sm_count, cudaStream_t stream) {
 // once per device at layer creation so that launches are plain stream work
 // (capturable in a graph).
 int gemv_configure() {
-#define DSX_GEMV_ATTR(F, P, W) DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<F, P, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem))
-    DSX_GEMV_ATTR(DSX_FMT_MXFP4, true, 8); DSX_GEMV_ATTR(DSX_FMT_MXFP4, false, 8);
-    DSX_GEMV_ATTR(DSX_FMT_MXFP4, true, 16); DSX_GEMV_ATTR(DSX_FMT_MXFP4, false, 16);
-    DSX_GEMV_ATTR(DSX_FMT_Q8_0, true, 8); DSX_GEMV_ATTR(DSX_FMT_Q8_0, false, 8);
-    DSX_GEMV_ATTR(DSX_FMT_Q8_0, true, 16); DSX_GEMV_ATTR(DSX_FMT_Q8_0, false, 16);
+#define DSX_GEMV_ATTR(F, P, W, S) DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<F, P, W, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem))
+#define DSX_GEMV_ATTR3(F, P) DSX_GEMV_ATTR(F, P, 8, 1); DSX_GEMV_ATTR(F, P, 16, 1); DSX_GEMV_ATTR(F, P, 16, 2)
+    DSX_GEMV_ATTR3(DSX_FMT_MXFP4, true); DSX_GEMV_ATTR3(DSX_FMT_MXFP4, false);
+    DSX_GEMV_ATTR3(DSX_FMT_Q8_0, true); DSX_GEMV_ATTR3(DSX_FMT_Q8_0, false);
+#undef DSX_GEMV_ATTR3
 #undef DSX_GEMV_ATTR
     return DSX_OK;
 }

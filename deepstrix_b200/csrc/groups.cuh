@@ -10,16 +10,19 @@ namespace groupdev {
 // wh[w*E + e] = picks of local expert e inside warp w's slice of the chunk.
 template <int NT>
 __device__ void chunk_count(const int32_t* __restrict__ sel, int64_t P, int64_t chunk_base, int E, int lo, int* wh) {
+    constexpr int kIt = (kGroupChunk / (NT / 32)) / 32;
     for (int i = threadIdx.x; i < (NT / 32) * E; i += NT) wh[i] = 0;
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int it = 0; it < (kGroupChunk / (NT / 32)) / 32; it++) {
+    int ev[kIt];   // all picks of the thread first: the loads overlap instead of queueing behind the atomics
+#pragma unroll
+    for (int it = 0; it < kIt; it++) {
         const int64_t idx = chunk_base + warp * (kGroupChunk / (NT / 32)) + it * 32 + lane;
-        if (idx < P) {
-            const int e = sel[idx] - lo;
-            if (e >= 0 && e < E) atomicAdd(&wh[warp * E + e], 1);
-        }
+        ev[it] = idx < P ? sel[idx] - lo : -1;
     }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < kIt; it++)
+        if (ev[it] >= 0 && ev[it] < E) atomicAdd(&wh[warp * E + ev[it]], 1);
     __syncthreads();
 }
 
@@ -87,14 +90,19 @@ __device__ void write_offsets_and_items(int e, int E, int h, int chunk, int shar
 template <int NT>
 __device__ void chunk_place(const int32_t* __restrict__ sel, int64_t P, int64_t chunk_base, int E, int lo, int* wh,
                             int32_t* __restrict__ perm) {
+    constexpr int kIt = (kGroupChunk / (NT / 32)) / 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int it = 0; it < (kGroupChunk / (NT / 32)) / 32; it++) {
+    int ev[kIt];
+#pragma unroll
+    for (int it = 0; it < kIt; it++) {
         const int64_t idx = chunk_base + warp * (kGroupChunk / (NT / 32)) + it * 32 + lane;
-        int e = -1;
-        if (idx < P) {
-            e = sel[idx] - lo;
-            if (e < 0 || e >= E) e = -1;
-        }
+        int e = idx < P ? sel[idx] - lo : -1;
+        ev[it] = (e < 0 || e >= E) ? -1 : e;
+    }
+#pragma unroll
+    for (int it = 0; it < kIt; it++) {
+        const int64_t idx = chunk_base + warp * (kGroupChunk / (NT / 32)) + it * 32 + lane;
+        const int e = ev[it];
         const int key = e >= 0 ? e : (0x40000000 | lane);
         const uint32_t mask = __match_any_sync(0xFFFFFFFFu, key);
         const int rank = __popc(mask & ((1u << lane) - 1u));
@@ -104,7 +112,6 @@ __device__ void chunk_place(const int32_t* __restrict__ sel, int64_t P, int64_t 
         __syncwarp();
     }
 }
-
 
 // One expert per thread (needs E <= NT): the whole build for T*k <= kGroupChunk picks inside one block.  wh: NT/32 * E ints of shared memory,
 // s_warp: NT/32 + 1 ints.

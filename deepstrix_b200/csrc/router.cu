@@ -39,22 +39,33 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, const float
     }
     const float4* wrow = reinterpret_cast<const float4*>(W + (int64_t)e * H) + lane;
     const int n_iter = (int)(H >> 7);
-#pragma unroll 2
-    for (int i = 0; i < n_iter; i++) {
-        const float4 w = __ldg(wrow + i * 32);
-        uint2 xv[kLogitTokens];
+    for (int i0 = 0; i0 < n_iter; i0 += 4) {
+        // four iterations' loads (router row and token rows) go out together, then the fmas
+        float4 w4[4];
+        uint2 xv[4][kLogitTokens];
 #pragma unroll
-        for (int tt = 0; tt < kLogitTokens; tt++) xv[tt] = __ldg(xrow[tt] + i * 32);
+        for (int j = 0; j < 4; j++) {
+            const int i = min(i0 + j, n_iter - 1);
+            w4[j] = __ldg(wrow + i * 32);
 #pragma unroll
-        for (int tt = 0; tt < kLogitTokens; tt++) {
-            const float x0 = __uint_as_float(xv[tt].x << 16), x1 = __uint_as_float(xv[tt].x & 0xFFFF0000u);
-            const float x2 = __uint_as_float(xv[tt].y << 16), x3 = __uint_as_float(xv[tt].y & 0xFFFF0000u);
-            float a = acc[tt];
-            a = __fmaf_rn(w.x, x0, a);
-            a = __fmaf_rn(w.y, x1, a);
-            a = __fmaf_rn(w.z, x2, a);
-            a = __fmaf_rn(w.w, x3, a);
-            acc[tt] = a;
+            for (int tt = 0; tt < kLogitTokens; tt++) xv[j][tt] = __ldg(xrow[tt] + i * 32);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (i0 + j < n_iter) {
+                const float4 w = w4[j];
+#pragma unroll
+                for (int tt = 0; tt < kLogitTokens; tt++) {
+                    const float x0 = __uint_as_float(xv[j][tt].x << 16), x1 = __uint_as_float(xv[j][tt].x & 0xFFFF0000u);
+                    const float x2 = __uint_as_float(xv[j][tt].y << 16), x3 = __uint_as_float(xv[j][tt].y & 0xFFFF0000u);
+                    float a = acc[tt];
+                    a = __fmaf_rn(w.x, x0, a);
+                    a = __fmaf_rn(w.y, x1, a);
+                    a = __fmaf_rn(w.z, x2, a);
+                    a = __fmaf_rn(w.w, x3, a);
+                    acc[tt] = a;
+                }
+            }
         }
     }
 #pragma unroll
@@ -91,18 +102,39 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
     if (cfg.n_group > 1) {
         // group score = sum of the two largest selection scores of the group;
         // keep the topk_group best groups (equal -> lower group index)
-#pragma unroll
-        for (int j = 0; j < VPL; j++) s_score[lane * VPL + j] = s[j];
-        __syncwarp();
         const int per = E / cfg.n_group;
-        float gs = -INFINITY;
-        if (lane < cfg.n_group) {
+        const int lpg = per / VPL;   // lanes per group when a group is a whole number of lanes
+        float gs = -INFINITY;        // score of group `lane` (lanes < n_group)
+        if (per % VPL == 0 && (lpg & (lpg - 1)) == 0 && lpg >= 1 && lpg <= 32) {
+            // top-2 of the lane's own values, then merged across the lanes of the group
             float m1 = -INFINITY, m2 = -INFINITY;
-            for (int i = 0; i < per; i++) {
-                const float v = s_score[lane * per + i];
+#pragma unroll
+            for (int j = 0; j < VPL; j++) {
+                const float v = s[j];
                 if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
             }
-            gs = __fadd_rn(m1, m2);
+            for (int off = 1; off < lpg; off <<= 1) {
+                const float o1 = __shfl_xor_sync(0xFFFFFFFFu, m1, off), o2 = __shfl_xor_sync(0xFFFFFFFFu, m2, off);
+                const float lo = fminf(m1, o1);
+                m1 = fmaxf(m1, o1);
+                m2 = fmaxf(lo, fmaxf(m2, o2));
+            }
+            const float mine = __fadd_rn(m1, m2);                      // same in every lane of the group
+            gs = __shfl_sync(0xFFFFFFFFu, mine, (lane * lpg) & 31);    // lane g reads group g's score
+            if (lane >= cfg.n_group) gs = -INFINITY;
+        } else {
+#pragma unroll
+            for (int j = 0; j < VPL; j++) s_score[lane * VPL + j] = s[j];
+            __syncwarp();
+            if (lane < cfg.n_group) {
+                float m1 = -INFINITY, m2 = -INFINITY;
+                for (int i = 0; i < per; i++) {
+                    const float v = s_score[lane * per + i];
+                    if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
+                }
+                gs = __fadd_rn(m1, m2);
+            }
+            __syncwarp();
         }
         int rank = 0;
         for (int h = 0; h < cfg.n_group; h++) {
@@ -115,33 +147,31 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
             const int grp = (lane * VPL + j) / per;
             if (!((keep >> grp) & 1u)) s[j] = -INFINITY;
         }
-        __syncwarp();
     }
-    unsigned long long key[VPL];
+    // k selection rounds: warp-wide max of the ordered score bits (redux), then the lowest expert
+    // index among the lanes that hold that score (redux min) -- equal scores go to the lower index.
+    uint32_t ob[VPL];
 #pragma unroll
-    for (int j = 0; j < VPL; j++)
-        // adding +0 turns -0 into +0, so scores that compare equal get equal key prefixes
-        key[j] = ((unsigned long long)ordered_bits(__fadd_rn(s[j], 0.0f)) << 32) |
-                 (unsigned long long)(0xFFFFFFFFu - (uint32_t)(lane * VPL + j));
+    for (int j = 0; j < VPL; j++) ob[j] = ordered_bits(__fadd_rn(s[j], 0.0f));   // adding +0 turns -0 into +0
+    // 0 marks "already taken": every non-NaN score maps to at least 0x007FFFFF (-inf)
     float psel[kMaxUsed];
     int esel[kMaxUsed];
 #pragma unroll
     for (int r = 0; r < kMaxUsed; r++) {
         if (r < cfg.n_used) {
-            unsigned long long best = key[0];
+            uint32_t lb = 0u;
+            int lj = 0;
 #pragma unroll
-            for (int j = 1; j < VPL; j++) best = key[j] > best ? key[j] : best;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                const unsigned long long o = __shfl_xor_sync(0xFFFFFFFFu, best, off);
-                best = o > best ? o : best;
-            }
-            const int e = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
+            for (int j = VPL - 1; j >= 0; j--)
+                if (ob[j] >= lb) { lb = ob[j]; lj = j; }   // ties inside the lane: lowest j
+            const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, lb);
+            const uint32_t cand = (lb == mx) ? (uint32_t)(lane * VPL + lj) : 0xFFFFFFFFu;
+            const int e = (int)__reduce_min_sync(0xFFFFFFFFu, cand);
             const int owner = e / VPL, jj = e - owner * VPL;
             float pv = 0.0f;
 #pragma unroll
             for (int j = 0; j < VPL; j++)
-                if (lane == owner && j == jj) { pv = p[j]; key[j] = 0ull; }
+                if (lane == owner && j == jj) { pv = p[j]; ob[j] = 0u; }
             psel[r] = __shfl_sync(0xFFFFFFFFu, pv, owner);
             esel[r] = e;
         }
@@ -191,12 +221,22 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.y, t0 = tile * kLogitTokens;
     const int nt = min(kLogitTokens, T - t0);
+    pdl_launch_dependents();
+    pdl_wait();   // the routing buffers written below may still be read by the previous step's kernels
     // token rows of the tile -> shared memory (rows past the batch alias the last valid row)
     uint2* xs = reinterpret_cast<uint2*>(fsm);   // [8][H/4] of 4 x bf16
     const int vec = H >> 2;
-    for (int i = threadIdx.x; i < kLogitTokens * vec; i += kLogitWarps * 32) {
-        const int r = i / vec, c = i - r * vec;
-        xs[i] = __ldg(reinterpret_cast<const uint2*>(x + (int64_t)min(t0 + r, T - 1) * H) + c);
+    {   // warp r copies token row r: eight loads in flight per lane
+        const uint2* src = reinterpret_cast<const uint2*>(x + (int64_t)min(t0 + warp, T - 1) * H);
+        uint2* dst = xs + warp * vec;
+        for (int c0 = lane; c0 < vec; c0 += 32 * 8) {
+            uint2 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = (c0 + 32 * j < vec) ? __ldg(src + c0 + 32 * j) : make_uint2(0u, 0u);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (c0 + 32 * j < vec) dst[c0 + 32 * j] = v[j];
+        }
     }
     __syncthreads();
     const int e = blockIdx.x * kLogitWarps + warp;
@@ -206,20 +246,28 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
         for (int i = 0; i < kLogitTokens; i++) acc[i] = 0.0f;
         const float4* wrow = reinterpret_cast<const float4*>(W + (int64_t)e * H) + lane;
         const int n_iter = H >> 7;
-#pragma unroll 8
-        for (int i = 0; i < n_iter; i++) {
-            const float4 w = __ldg(wrow + i * 32);
+        // router rows stream from HBM: fetch sixteen 512-byte pieces per round trip, then do the math
+        for (int i0 = 0; i0 < n_iter; i0 += 16) {
+            float4 w8[16];
 #pragma unroll
-            for (int tt = 0; tt < kLogitTokens; tt++) {
-                const uint2 xv = xs[tt * vec + i * 32 + lane];
-                const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
-                const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
-                float a = acc[tt];
-                a = __fmaf_rn(w.x, x0, a);
-                a = __fmaf_rn(w.y, x1, a);
-                a = __fmaf_rn(w.z, x2, a);
-                a = __fmaf_rn(w.w, x3, a);
-                acc[tt] = a;
+            for (int j = 0; j < 16; j++) w8[j] = (i0 + j < n_iter) ? __ldg(wrow + (i0 + j) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                if (i0 + j < n_iter) {
+                    const float4 w = w8[j];
+#pragma unroll
+                    for (int tt = 0; tt < kLogitTokens; tt++) {
+                        const uint2 xv = xs[tt * vec + (i0 + j) * 32 + lane];
+                        const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
+                        const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
+                        float a = acc[tt];
+                        a = __fmaf_rn(w.x, x0, a);
+                        a = __fmaf_rn(w.y, x1, a);
+                        a = __fmaf_rn(w.z, x2, a);
+                        a = __fmaf_rn(w.w, x3, a);
+                        acc[tt] = a;
+                    }
+                }
             }
         }
 #pragma unroll
@@ -287,9 +335,9 @@ int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const
     switch (cfg.n_expert / 32) {
 #define DSX_FUSED_CASE(V)                                                                                                     \
     case V:                                                                                                                   \
-        router_fused_kernel<V><<<grid, kLogitWarps * 32, smem, stream>>>(x, (int)T, W, bias, (int)H, cfg, logits, selected, weights, \
-                                                                        chunk, shared_T, hist, offsets, perm, work_items,     \
-                                                                        n_work_items, work_cap, counters);                    \
+        DSX_CUDA(launch_pdl(router_fused_kernel<V>, grid, dim3(kLogitWarps * 32), smem, stream, x, (int)T, W, bias, (int)H, cfg,     \
+                            logits, selected, weights, chunk, shared_T, hist, offsets, perm, work_items, n_work_items, work_cap,  \
+                            counters));                                                                                       \
         break;
         DSX_FUSED_CASE(1) DSX_FUSED_CASE(2) DSX_FUSED_CASE(4) DSX_FUSED_CASE(8)
 #undef DSX_FUSED_CASE
