@@ -69,11 +69,49 @@ def uniform_logits(cfg: MoeConfig, config_id: int, T: int) -> np.ndarray:
     return rng.standard_normal((T, cfg.router.n_expert), dtype=np.float32)
 
 
-def zipf_bias(cfg: MoeConfig, s: float = 1.1, strength: float = 0.25) -> np.ndarray:
-    """Router bias that skews expert popularity towards a Zipf(s) profile:
-    bias_e grows with log of the target probability of rank e."""
-    E = cfg.router.n_expert
-    p = 1.0 / np.arange(1, E + 1, dtype=np.float64) ** s
-    p /= p.sum()
-    b = strength * (np.log(p) - np.log(p).mean())
-    return b.astype(np.float32)
+def _route_numpy(logits: np.ndarray, bias: np.ndarray, cfg: MoeConfig) -> np.ndarray:
+    """Plain numpy restatement of the router's selection (sigmoid or sqrt-softplus scores + bias,
+    optional group limit, top-k), used only to calibrate synthetic biases: returns picks [T, k]."""
+    r = cfg.router
+    lg = logits.astype(np.float64)
+    p = 1.0 / (1.0 + np.exp(-lg)) if r.score_fn == 1 else np.sqrt(np.log1p(np.exp(lg)))
+    s = p + bias.astype(np.float64)
+    T, E = s.shape
+    if r.n_group > 1:
+        per = E // r.n_group
+        gs = np.sort(s.reshape(T, r.n_group, per), axis=2)[:, :, -2:].sum(2)
+        keep = np.zeros((T, r.n_group), bool)
+        np.put_along_axis(keep, np.argsort(-gs, axis=1, kind="stable")[:, : r.topk_group], True, axis=1)
+        s = np.where(np.repeat(keep, per, axis=1), s, -np.inf)
+    return np.argsort(-s, axis=1, kind="stable")[:, : r.n_used]
+
+
+def zipf_bias(cfg: MoeConfig, logits: np.ndarray | None = None, s: float = 1.1, seed: int = 3) -> np.ndarray:
+    """Router bias that skews expert popularity towards a Zipf(s) profile (expert e has rank e+1).
+    bias = c * (log p_e - mean), with the single strength c found by bisection so that the 32
+    most popular experts receive the share of picks the (capped) Zipf profile gives them; one
+    pick per token caps an expert's share at 1/k.  A per-expert fit is not attempted: with a
+    group limit the experts' popularities are coupled and such a fit does not converge.
+    Calibrated on a sample of router logits (default: N(0, 1.28), the logit distribution of
+    N(0, 0.02) router weights on N(0, 1) activations of width 4096)."""
+    E, k = cfg.router.n_expert, cfg.router.n_used
+    if logits is None:
+        logits = np.random.Generator(np.random.PCG64([SEED_BASE + seed, 77])).normal(0.0, 1.28, size=(2048, E)).astype(np.float32)
+    target = 1.0 / np.arange(1, E + 1, dtype=np.float64) ** s
+    target /= target.sum()
+    shape = np.log(target) - np.log(target).mean()
+    for _ in range(8):                       # cap at one pick per token, renormalise the rest
+        over = target > 1.0 / k
+        if not over.any():
+            break
+        target[over] = 1.0 / k
+        target[~over] *= (1.0 - over.sum() / k) / target[~over].sum()
+    head = min(32, E // 2)
+    want = target[:head].sum()
+    lo, hi = 0.0, 1.0
+    for _ in range(14):
+        c = 0.5 * (lo + hi)
+        sel = _route_numpy(logits, c * shape, cfg)
+        got = (sel < head).mean()
+        lo, hi = (c, hi) if got < want else (lo, c)
+    return (0.5 * (lo + hi) * shape).astype(np.float32)
