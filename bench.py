@@ -234,7 +234,7 @@ def run_single_gpu(args):
         return {n_: round(sum(v) / len(v) * 1e3, 2) for n_, v in acc.items()}
 
     results = {}
-    for T in sorted(set(([] if args.no_series else [1, 8, 32, 64]) + [args.tokens])):
+    for T in sorted(set(([] if args.no_series else args.series_tokens) + [args.tokens])):
         xs, outs = batches(T)
         steps = args.steps if T == args.tokens else max(10, args.steps // 2)
         t_wall0 = time.time()
@@ -425,6 +425,8 @@ def main():
     ap.add_argument("--layers", type=int, default=6, help="resident copies of the layer weights to rotate over")
     ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per CPU-oracle sample step")
     ap.add_argument("--no-series", action="store_true", help="time only the headline batch size")
+    ap.add_argument("--series-tokens", type=lambda v: [int(t) for t in v.split(",")], default=[1, 8, 32, 64],
+                    help="decode batch sizes of the series (comma separated, each at most 64)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 8192-token prefill leg")
     ap.add_argument("--no-q8", action="store_true", help="skip the Q8_0 / Zipf leg (configuration 3)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU-baseline leg (for profiler runs)")

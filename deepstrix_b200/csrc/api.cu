@@ -55,6 +55,7 @@ struct dsx_moe_layer {
     int32_t *selected = nullptr, *hist = nullptr, *offsets = nullptr, *perm = nullptr, *work_items = nullptr, *n_work_items = nullptr;
     float* weights = nullptr;
     int32_t work_cap = 0;
+    ItemRec* item_recs = nullptr;   // one record per work item, written by the one-launch decode router for batches below 8 tokens
     GroupScratch gs{};
     __half* mid = nullptr;
     float* partial = nullptr;
@@ -399,7 +400,7 @@ static void layer_free(dsx_moe_layer* L) {
     for (cudaEvent_t e : L->ev) if (e) cudaEventDestroy(e);
     cudaFree(L->logits); cudaFree(L->selected); cudaFree(L->weights); cudaFree(L->hist); cudaFree(L->offsets);
     cudaFree(L->perm); cudaFree(L->work_items); cudaFree(L->n_work_items); cudaFree(L->gs.chunk_hist); cudaFree(L->mid);
-    cudaFree(L->partial); cudaFree(L->error_word); cudaFree(L->router_counters); cudaFree(L->x_stage); cudaFree(L->out_stage);
+    cudaFree(L->partial); cudaFree(L->error_word); cudaFree(L->router_counters); cudaFree(L->item_recs); cudaFree(L->x_stage); cudaFree(L->out_stage);
     prefill_workspace_free(&L->pf);
 }
 
@@ -445,6 +446,7 @@ int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const
     alloc((void**)&L->offsets, (E + 1) * 4);
     alloc((void**)&L->perm, P * 4);
     alloc((void**)&L->work_items, (size_t)L->work_cap * 4);
+    alloc((void**)&L->item_recs, (size_t)128 * sizeof(ItemRec));   // at most 7 * n_used + 1 items, n_used <= 16
     alloc((void**)&L->n_work_items, 256);
     alloc((void**)&L->gs.chunk_hist, (size_t)L->gs.capacity_chunks * E * 4);
     alloc((void**)&L->mid, (P + Tm) * (size_t)std::max(c.ffn, c.shared_ffn) * 2);
@@ -539,6 +541,7 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
     GemvArgs a{};
     a.fmt = L->routed->fmt; a.shared_fmt = shared ? L->shared->fmt : a.fmt; a.n_expert = n_local;
     a.work_items = L->work_items; a.n_work_items = L->n_work_items; a.offsets = L->offsets; a.perm = L->perm;
+    a.item_recs = (groups_ready && T < 8) ? L->item_recs : nullptr;   // the decode router writes them for small batches only
     a.route_w = weights; a.n_used = k; a.T = T; a.clamp = c.clamp; a.x = x; a.mid = L->mid; a.mid_stride = c.ffn;
     a.partial = L->partial; a.error_word = L->error_word;
     // gate/up: rows = ffn, K = hidden
@@ -577,7 +580,7 @@ int dsx_moe_layer_forward(dsx_moe_layer* L, const void* x_bf16, int64_t T, void*
             StageTimer tm(L, DSX_STAGE_ROUTER_LOGITS, stream);
             if (int rc = launch_router_fused(x, T, L->router_w, L->router_bias, L->cfg.hidden, L->cfg.router, L->logits, L->selected,
                                              L->weights, 8, L->shared ? (int)T : 0, L->hist, L->offsets, L->perm, L->work_items,
-                                             L->n_work_items, L->work_cap, L->router_counters, stream))
+                                             L->n_work_items, L->work_cap, T < 8 ? L->item_recs : nullptr, L->router_counters, L->error_word, stream))
                 return rc;
         }
         L->last_logits = L->logits; L->last_selected = L->selected; L->last_weights = L->weights;

@@ -162,6 +162,20 @@ __device__ __forceinline__ float router_prob(float logit, int score_fn) {
     return __fsqrt_rn(sp);
 }
 
+// One decode work item (an expert and up to 8 of its tokens) spelled out for the grouped GEMV:
+// written by the decode router's group build, read with one coalesced load per item.
+struct ItemRec {
+    int32_t expert;       // local slot; n_expert means the shared expert
+    int32_t n_tok;
+    int32_t tok[8];       // token index (gate/up source row)
+    int32_t mid_row[8];   // row of mid (expert-sorted order)
+    int32_t out_row[8];   // row of partial (t*k+s, or P+t for the shared expert)
+    float w[8];           // routing weight
+    int32_t pad[2];
+};
+static_assert(sizeof(ItemRec) == 144, "ItemRec is 36 words");
+constexpr int kItemRecWords = 34;   // words of an ItemRec that carry data
+
 // ------------------------------------------------------- kernel launchers
 // (defined in the .cu file named in the comment; all asynchronous on `stream`)
 
@@ -183,8 +197,8 @@ int router_configure();
 bool router_fused_ok(int64_t T, const dsx_router_config& cfg, int64_t H);
 int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const float* bias, int64_t H, const dsx_router_config& cfg,
                         float* logits, int32_t* selected, float* weights, int chunk, int shared_T, int32_t* hist, int32_t* offsets,
-                        int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap, unsigned int* counters,
-                        cudaStream_t stream);
+                        int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap, ItemRec* item_recs,
+                        unsigned int* counters, uint32_t* error_word, cudaStream_t stream);
 
 // groups.cu
 struct GroupScratch {      // device scratch for the multi-block counting sort
@@ -216,6 +230,7 @@ struct GemvArgs {
     int64_t sh_rows;
     const int32_t* work_items;   // (e<<16)|member_start, chunk 8
     const int32_t* n_work_items;
+    const ItemRec* item_recs;    // one record per work item, or null (the kernel then derives them from offsets / perm / route_w)
     const int32_t* offsets;      // [n_expert+1]
     const int32_t* perm;         // [P]
     const float* route_w;        // [P] routing weights indexed by t*k+s

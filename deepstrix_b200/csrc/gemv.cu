@@ -19,6 +19,8 @@
 // the E8M0 / f16 block scale multiplies the f32 result of each 32-column block.
 // Token columns are independent in the mma, so a token's result does not
 // depend on which other tokens share its item.
+#include <type_traits>
+
 #include "dsx_common.cuh"
 
 namespace dsx {
@@ -156,14 +158,14 @@ __device__ __forceinline__ void compute_subtile(const uint8_t* nibp, const uint8
     }
 }
 
+// The current item of the block, in shared memory: derived in the kernel (ItemInfo), or an
+// ItemRec copied from the decode router's records (small batches).
 struct ItemInfo {
     int n_tok;
     int tok[kMaxTok];      // token index (gate/up source row)
     int mid_row[kMaxTok];  // row of mid (permuted order)
     int out_row[kMaxTok];  // row of partial (t*k+s, or P+t for the shared expert)
     float w[kMaxTok];
-    const uint8_t* nib;    // plane base of this item's expert
-    const uint8_t* sc;
 };
 
 // FMT: routed format for routed items; shared items use SFMT.  The kernel is
@@ -175,7 +177,16 @@ struct ItemInfo {
 // units stay 128 rows and two warps share a row tile, each taking one half of the reduction
 // (KSPLIT 2); the halves are added through shared memory.  Every variant adds
 // (first half of the columns) + (second half), so the bits do not depend on the variant.
-template <int FMT, bool PAIR, int WARPS, int KSPLIT>
+//
+// SMALL (batches below 8 tokens routed by the one-launch decode router, where the kernels' fixed
+// costs are a large share): an item is one ready-made ItemRec, and what does not depend on the
+// previous kernel of the chain runs before the wait for it.  Gate/up stages every token row once,
+// as f16 (its predecessor releases it only after the token rows are complete); an item then only
+// selects rows.  The down kernel reads the routing and requests its first weights (gate/up
+// releases it after its own wait, when the routing is complete).  Otherwise the kernel derives an
+// item from offsets / perm / weights and stages its rows when the block reaches it; that code is
+// kept apart at compile time because the streaming loop's schedule is sensitive to it.
+template <int FMT, bool PAIR, int WARPS, int KSPLIT, bool SMALL>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     constexpr int kWarps = WARPS, kThreads = WARPS * 32, kStages = kRingStagesPerBlock / WARPS;
     constexpr int kRowWarps = WARPS / KSPLIT;   // row tiles per unit
@@ -191,8 +202,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     __half* act = reinterpret_cast<__half*>(smem);
     uint8_t* ring = smem + (((size_t)kMaxTok * act_stride * 2 + 127) & ~(size_t)127);
     uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)kWarps * kStages * kStageBytes);
-    ItemInfo* info = reinterpret_cast<ItemInfo*>(bars + kWarps * kStages);
-    float* halves = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(info) + ((sizeof(ItemInfo) + 127) & ~(size_t)127));  // KSPLIT 2: [2][kRowWarps][32][8]
+    using Info = typename std::conditional<SMALL, ItemRec, ItemInfo>::type;
+    Info* info = reinterpret_cast<Info*>(bars + kWarps * kStages);
+    float* halves = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(info) + ((sizeof(ItemRec) + 127) & ~(size_t)127));  // KSPLIT 2: [2][kRowWarps][32][8]
     const int rw = warp % kRowWarps, kh = warp / kRowWarps;   // row tile inside the unit, reduction half
 
     uint8_t* my_ring = ring + (size_t)warp * kStages * kStageBytes;
@@ -200,9 +212,36 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     if (lane == 0)
         for (int s = 0; s < kStages; s++) mbar_init(my_bars + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    constexpr bool all_rows_staged = SMALL && PAIR;
+    if (all_rows_staged) {
+        // loads that bypass L1: this runs while the previous kernel may still be executing
+        const int vec_per_row = (int)(K >> 3);
+        for (int v = threadIdx.x; v < (int)a.T * vec_per_row; v += kThreads) {
+            const int r = v / vec_per_row, c8 = v - r * vec_per_row;
+            const uint4 in = __ldcg(reinterpret_cast<const uint4*>(a.x + (int64_t)r * K) + c8);
+            const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const __half2 h = __floats2half2_rn(__uint_as_float(wds[q] << 16), __uint_as_float(wds[q] & 0xFFFF0000u));
+                o[q] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(act + (size_t)r * act_stride + c8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
     __syncthreads();
-    pdl_launch_dependents();
-    pdl_wait();   // work items, routing and activations come from the previous kernels of the chain
+    if (!SMALL) {
+        pdl_launch_dependents();
+        pdl_wait();   // work items, routing and activations come from the previous kernels of the chain
+    } else if (PAIR) {
+        pdl_wait();   // work items and routing come from the previous kernel of the chain
+        // the next kernel (down) reads the routing before its own wait: release it only now
+        pdl_launch_dependents();
+    } else {
+        // routing and weights are complete (the gate/up kernel released this one after its own wait):
+        // everything up to the first weight requests runs beside the gate/up kernel's tail
+        pdl_launch_dependents();
+    }
 
     const int n_items = a.n_work_items[0];
     const int n_kt = (int)(K / kTileK);
@@ -221,7 +260,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     const uint8_t* p_sc = nullptr;
     auto issue = [&]() {
         if (p_item != p_cached) {
-            const int e = (int)((uint32_t)a.work_items[p_item] >> 16);
+            const int e = SMALL ? __ldcg(&a.item_recs[p_item].expert) : (int)((uint32_t)a.work_items[p_item] >> 16);
             p_nib = (e == a.n_expert) ? a.sh_nib : a.nib + (int64_t)e * a.nib_slot_stride;
             p_sc = (e == a.n_expert) ? a.sh_sc : a.sc + (int64_t)e * a.sc_slot_stride;
             p_cached = p_item;
@@ -246,6 +285,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
 
     if (lane == 0)
         for (int i = 0; i < total && i < kStages; i++) issue();
+    if (SMALL && !PAIR) pdl_wait();   // the rows of mid come from the gate/up kernel
 
     int item = u0 / bpi, rb = u0 - item * bpi, ls = 0;
     int cur_item = -1;
@@ -258,7 +298,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
             if (item != cur_item) {
                 // all warps of the block change item together (same unit sequence)
                 __syncthreads();
-                if (threadIdx.x < kMaxTok) {
+                if constexpr (SMALL) {
+                    if (threadIdx.x < kItemRecWords)
+                        reinterpret_cast<int32_t*>(info)[threadIdx.x] = __ldcg(reinterpret_cast<const int32_t*>(a.item_recs + item) + threadIdx.x);
+                } else if (threadIdx.x < kMaxTok) {
                     const uint32_t wi = (uint32_t)a.work_items[item];
                     const int e = (int)(wi >> 16), start = (int)(wi & 0xFFFFu), i = threadIdx.x;
                     if (e == a.n_expert) {  // shared expert: tokens start..start+7, weight 1
@@ -281,28 +324,30 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
                     }
                 }
                 __syncthreads();
-                // stage the item's activation rows as f16
-                const int n = info->n_tok;
-                const int vec_per_row = (int)(K >> 3);
-                for (int v = threadIdx.x; v < n * vec_per_row; v += kThreads) {
-                    const int r = v / vec_per_row, c8 = v - r * vec_per_row;
-                    uint4 out;
-                    if (PAIR) {
-                        const uint4 in = __ldg(reinterpret_cast<const uint4*>(a.x + (int64_t)info->tok[r] * K) + c8);
-                        const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
-                        uint32_t o[4];
-#pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            const __half2 h = __floats2half2_rn(__uint_as_float(wds[q] << 16), __uint_as_float(wds[q] & 0xFFFF0000u));
-                            o[q] = *reinterpret_cast<const uint32_t*>(&h);
+                if (!all_rows_staged) {
+                    // stage the item's activation rows as f16
+                    const int n = info->n_tok;
+                    const int vec_per_row = (int)(K >> 3);
+                    for (int v = threadIdx.x; v < n * vec_per_row; v += kThreads) {
+                        const int r = v / vec_per_row, c8 = v - r * vec_per_row;
+                        uint4 out;
+                        if (PAIR) {
+                            const uint4 in = __ldg(reinterpret_cast<const uint4*>(a.x + (int64_t)info->tok[r] * K) + c8);
+                            const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
+                            uint32_t o[4];
+    #pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                const __half2 h = __floats2half2_rn(__uint_as_float(wds[q] << 16), __uint_as_float(wds[q] & 0xFFFF0000u));
+                                o[q] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            out = make_uint4(o[0], o[1], o[2], o[3]);
+                        } else {
+                            out = *(reinterpret_cast<const uint4*>(a.mid + (int64_t)info->mid_row[r] * a.mid_stride) + c8);
                         }
-                        out = make_uint4(o[0], o[1], o[2], o[3]);
-                    } else {
-                        out = *(reinterpret_cast<const uint4*>(a.mid + (int64_t)info->mid_row[r] * a.mid_stride) + c8);
+                        *reinterpret_cast<uint4*>(act + (size_t)r * act_stride + c8 * 8) = out;
                     }
-                    *reinterpret_cast<uint4*>(act + (size_t)r * act_stride + c8 * 8) = out;
+                    __syncthreads();
                 }
-                __syncthreads();
                 cur_item = item;
             }
 #pragma unroll
@@ -324,7 +369,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
                 for (int i = 0; i < 4; i++) { acc0a[i] = acc0[i]; acc1a[i] = acc1[i]; acc0[i] = acc1[i] = 0.f; }
             }
             const bool tok_ok = g < info->n_tok;
-            const __half* arow = act + (size_t)g * act_stride + (size_t)ct0 * kTileK + 8 * t4;
+            const __half* arow = act + (size_t)(all_rows_staged ? (tok_ok ? info->tok[g] : 0) : g) * act_stride + (size_t)ct0 * kTileK + 8 * t4;
             auto col_tile = [&](int c) {
                 uint4 bf[kBlocks];
 #pragma unroll
@@ -395,7 +440,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
 
 size_t gemv_smem_bytes(int64_t K) {
     const size_t act = (((size_t)kMaxTok * (size_t)(K + kActPad) * 2) + 127) & ~(size_t)127;
-    return act + (size_t)kRingStagesPerBlock * kStageBytes + sizeof(uint64_t) * kRingStagesPerBlock + ((sizeof(ItemInfo) + 127) & ~(size_t)127) +
+    return act + (size_t)kRingStagesPerBlock * kStageBytes + sizeof(uint64_t) * kRingStagesPerBlock + ((sizeof(ItemRec) + 127) & ~(size_t)127) +
            (size_t)2 * 8 * 32 * 8 * sizeof(float) + 128;
 }
 
@@ -410,9 +455,12 @@ int launch_one(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     const bool wide = a.rows % (kTileRows * 16) == 0 && a.T >= 8;
     const int tile_k = FMT == DSX_FMT_MXFP4 ? 64 : 32, ct_per_stage = PAIR ? kSubPerStage / 2 : kSubPerStage;
     const int n_stage = (int)((a.K / tile_k + ct_per_stage - 1) / ct_per_stage);
-    if (wide) DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, 16, 1>, dim3(sm_count), dim3(16 * 32), smem, stream, a));
-    else if (n_stage % 2 == 0) DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, 16, 2>, dim3(sm_count), dim3(16 * 32), smem, stream, a));
-    else DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, 8, 1>, dim3(sm_count), dim3(8 * 32), smem, stream, a));
+    const bool small = a.item_recs != nullptr && a.T < kMaxTok;
+#define DSX_GEMV_LAUNCH(W, S, SM) DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, W, S, SM>, dim3(sm_count), dim3(W * 32), smem, stream, a))
+    if (wide) DSX_GEMV_LAUNCH(16, 1, false);
+    else if (n_stage % 2 == 0) { if (small) DSX_GEMV_LAUNCH(16, 2, true); else DSX_GEMV_LAUNCH(16, 2, false); }
+    else { if (small) DSX_GEMV_LAUNCH(8, 1, true); else DSX_GEMV_LAUNCH(8, 1, false); }
+#undef DSX_GEMV_LAUNCH
     DSX_LAUNCHED();
     return DSX_OK;
 }
@@ -443,8 +491,9 @@ int launch_gemv_down(const GemvArgs& a, int sm_count, cudaStream_t stream) {
 // once per device at layer creation so that launches are plain stream work
 // (capturable in a graph).
 int gemv_configure() {
-#define DSX_GEMV_ATTR(F, P, W, S) DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<F, P, W, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem))
-#define DSX_GEMV_ATTR3(F, P) DSX_GEMV_ATTR(F, P, 8, 1); DSX_GEMV_ATTR(F, P, 16, 1); DSX_GEMV_ATTR(F, P, 16, 2)
+#define DSX_GEMV_ATTR(F, P, W, S, SM) DSX_CUDA(cudaFuncSetAttribute(gemv_kernel<F, P, W, S, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem))
+#define DSX_GEMV_ATTR3(F, P) DSX_GEMV_ATTR(F, P, 16, 1, false); DSX_GEMV_ATTR(F, P, 16, 2, false); DSX_GEMV_ATTR(F, P, 16, 2, true); \
+                             DSX_GEMV_ATTR(F, P, 8, 1, false); DSX_GEMV_ATTR(F, P, 8, 1, true)
     DSX_GEMV_ATTR3(DSX_FMT_MXFP4, true); DSX_GEMV_ATTR3(DSX_FMT_MXFP4, false);
     DSX_GEMV_ATTR3(DSX_FMT_Q8_0, true); DSX_GEMV_ATTR3(DSX_FMT_Q8_0, false);
 #undef DSX_GEMV_ATTR3

@@ -89,7 +89,8 @@ constexpr int kMaxUsed = 16;
 // s_score: E floats of shared memory private to the warp.
 template <int VPL, typename LoadLogit>
 __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float* __restrict__ bias, const dsx_router_config& cfg,
-                                               int32_t* __restrict__ sel_out, float* __restrict__ w_out, float* s_score) {
+                                               int32_t* __restrict__ sel_out, float* __restrict__ w_out, float* s_score,
+                                               int32_t* s_sel = nullptr, float* s_wsel = nullptr /* optional copies in shared memory */) {
     const int lane = threadIdx.x & 31;
     const int E = VPL * 32;
     float p[VPL], s[VPL];
@@ -159,35 +160,52 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
 #pragma unroll
     for (int r = 0; r < kMaxUsed; r++) {
         if (r < cfg.n_used) {
-            uint32_t lb = 0u;
-            int lj = 0;
+            // the lane's best by a tournament (depth log2 VPL); `>` keeps the lower j on ties
+            uint32_t v[VPL];
+            int ix[VPL];
+            float pp[VPL];
 #pragma unroll
-            for (int j = VPL - 1; j >= 0; j--)
-                if (ob[j] >= lb) { lb = ob[j]; lj = j; }   // ties inside the lane: lowest j
-            const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, lb);
-            const uint32_t cand = (lb == mx) ? (uint32_t)(lane * VPL + lj) : 0xFFFFFFFFu;
+            for (int j = 0; j < VPL; j++) { v[j] = ob[j]; ix[j] = j; pp[j] = p[j]; }
+#pragma unroll
+            for (int lvl = 0; lvl < 5; lvl++) {
+                const int w = 1 << lvl;
+#pragma unroll
+                for (int j = 0; j < VPL; j++) {
+                    if (w < VPL && (j & (2 * w - 1)) == 0 && j + w < VPL) {
+                        const bool take = v[j + w] > v[j];
+                        v[j] = take ? v[j + w] : v[j];
+                        ix[j] = take ? ix[j + w] : ix[j];
+                        pp[j] = take ? pp[j + w] : pp[j];
+                    }
+                }
+            }
+            const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, v[0]);
+            const uint32_t cand = (v[0] == mx) ? (uint32_t)(lane * VPL + ix[0]) : 0xFFFFFFFFu;
             const int e = (int)__reduce_min_sync(0xFFFFFFFFu, cand);
-            const int owner = e / VPL, jj = e - owner * VPL;
-            float pv = 0.0f;
+            const bool mine = cand == (uint32_t)e;
 #pragma unroll
             for (int j = 0; j < VPL; j++)
-                if (lane == owner && j == jj) { pv = p[j]; ob[j] = 0u; }
-            psel[r] = __shfl_sync(0xFFFFFFFFu, pv, owner);
+                ob[j] = (mine && ix[0] == j) ? 0u : ob[j];
+            psel[r] = __shfl_sync(0xFFFFFFFFu, pp[0], e / VPL);
             esel[r] = e;
         }
     }
-    // weights from the unbiased probabilities, summed in slot order
-    float sum = 0.0f;
+    // weights from the unbiased probabilities, summed in slot order; lane r writes slot r
+    float sum = 0.0f, my_p = 0.0f;
+    int my_e = 0;
 #pragma unroll
     for (int r = 0; r < kMaxUsed; r++)
-        if (r < cfg.n_used) sum = __fadd_rn(sum, psel[r]);
-    if (sum < cfg.weight_eps) sum = cfg.weight_eps;
-#pragma unroll
-    for (int r = 0; r < kMaxUsed; r++)
-        if (r < cfg.n_used && lane == (r & 31)) {
-            sel_out[r] = esel[r];
-            w_out[r] = __fmul_rn(__fdiv_rn(psel[r], sum), cfg.route_scale);
+        if (r < cfg.n_used) {
+            sum = __fadd_rn(sum, psel[r]);
+            if (lane == r) { my_p = psel[r]; my_e = esel[r]; }
         }
+    if (sum < cfg.weight_eps) sum = cfg.weight_eps;
+    if (lane < cfg.n_used) {
+        const float wv = __fmul_rn(__fdiv_rn(my_p, sum), cfg.route_scale);
+        sel_out[lane] = my_e;
+        w_out[lane] = wv;
+        if (s_sel != nullptr) { s_sel[lane] = my_e; s_wsel[lane] = wv; }
+    }
 }
 
 template <int VPL>
@@ -203,81 +221,140 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
 }
 
 // ---- Decode router in ONE launch (T <= 64, E <= 256): logits, top-k and the group build.
-// Grid (E/8, ceil(T/8)), 8 warps.  Each block stages its 8 token rows in shared memory and its warps
-// stream one router row each (same f32 operation order as router_logits_kernel, so the logits
-// are the same bits).  The last block of a token tile to finish (ticket counter) selects the
+//
+// Grid (E/4, token tiles), 8 warps.  A tile is 2*NT tokens (NT = 1, 2 or 4, chosen from T).  The
+// block's four router rows (f32) and the tile's token rows (bf16) come into shared memory as bulk
+// async copies, all in flight at once, completing on mbarriers (a router row in two halves, so
+// the arithmetic starts when the first half has landed).  Warp w works on row w/2 and on tokens
+// (w%2)*NT .. +NT of the tile, in the f32 operation order of router_logits_kernel, so the logits
+// are the same bits.  The last block of a token tile to finish (ticket counter) selects the
 // experts of that tile's tokens, one warp per token; the last tile to finish builds histogram,
 // offsets, permutation and work items.  The counters return to zero for the next launch.
-template <int VPL>
-__global__ void __launch_bounds__(kLogitWarps * 32)
+constexpr int kFusedRows = 4;                 // router rows per block
+constexpr int kFusedWarps = 2 * kFusedRows;   // two token halves per row
+constexpr int kFusedMaxPicks = 512;           // T * n_used the in-kernel group build covers
+constexpr int kFusedMaxItems = kFusedMaxPicks + 8;   // work items: at most one per pick, plus the shared expert's
+constexpr size_t kFusedScratch = (size_t)(kFusedWarps * 256 + kFusedMaxPicks + kFusedMaxItems + 256 + 2) * 4;   // group-build scratch
+constexpr uint32_t kRouterWaitSpins = 1u << 22;
+
+__device__ __forceinline__ uint32_t r_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void r_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void r_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false when the phase did not complete in kRouterWaitSpins polls.
+__device__ __forceinline__ bool r_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kRouterWaitSpins; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void r_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int VPL, int NT>
+__global__ void __launch_bounds__(kFusedWarps * 32)
 router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __restrict__ W, const float* __restrict__ bias, int H,
                     dsx_router_config cfg, float* __restrict__ logits, int32_t* __restrict__ selected, float* __restrict__ weights,
                     int chunk, int shared_T, int32_t* hist, int32_t* offsets, int32_t* perm, int32_t* work_items,
-                    int32_t* n_work_items, int32_t work_cap, unsigned int* counters /* [0]: tiles done, [1 + tile]: blocks done */) {
-    extern __shared__ __align__(16) uint8_t fsm[];
+                    int32_t* n_work_items, int32_t work_cap, ItemRec* item_recs,
+                    unsigned int* counters /* [0]: tiles done, [1 + tile]: blocks done */, uint32_t* error_word) {
+    extern __shared__ __align__(128) uint8_t fsm[];
+    __shared__ __align__(8) uint64_t s_bar[1 + 2 * kFusedRows];
     __shared__ int s_flag;
-    __shared__ int s_warp[kLogitWarps + 1];
+    __shared__ int s_warp[kFusedWarps + 1];
+    __shared__ int32_t s_sel[kFusedMaxPicks];
+    __shared__ float s_wsel[kFusedMaxPicks];
     constexpr int E = VPL * 32;
+    constexpr int kTile = 2 * NT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.y, t0 = tile * kLogitTokens;
-    const int nt = min(kLogitTokens, T - t0);
-    pdl_launch_dependents();
-    pdl_wait();   // the routing buffers written below may still be read by the previous step's kernels
-    // token rows of the tile -> shared memory (rows past the batch alias the last valid row)
-    uint2* xs = reinterpret_cast<uint2*>(fsm);   // [8][H/4] of 4 x bf16
+    const int tile = blockIdx.y, t0 = tile * kTile;
+    const int nt = min(kTile, T - t0);
+    const int row = warp >> 1, th = warp & 1;
+    float* ws = reinterpret_cast<float*>(fsm);                              // [4][H] f32
+    uint2* xs = reinterpret_cast<uint2*>(fsm + (size_t)kFusedRows * H * 4); // [kTile][H/4] of 4 x bf16
     const int vec = H >> 2;
-    {   // warp r copies token row r: eight loads in flight per lane
-        const uint2* src = reinterpret_cast<const uint2*>(x + (int64_t)min(t0 + warp, T - 1) * H);
-        uint2* dst = xs + warp * vec;
-        for (int c0 = lane; c0 < vec; c0 += 32 * 8) {
-            uint2 v[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[j] = (c0 + 32 * j < vec) ? __ldg(src + c0 + 32 * j) : make_uint2(0u, 0u);
-#pragma unroll
-            for (int j = 0; j < 8; j++)
-                if (c0 + 32 * j < vec) dst[c0 + 32 * j] = v[j];
-        }
+    const uint32_t bar_x = r_smem_u32(&s_bar[0]);
+    const uint32_t bar_w0 = r_smem_u32(&s_bar[1 + 2 * row]), bar_w1 = bar_w0 + 8;
+    if (threadIdx.x == 0) {
+        r_mbar_init(bar_x, (uint32_t)nt);
+        for (int i = 0; i < 2 * kFusedRows; i++) r_mbar_init(r_smem_u32(&s_bar[1 + i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    const int e = blockIdx.x * kLogitWarps + warp;
-    {
-        float acc[kLogitTokens];
+    const int e = blockIdx.x * kFusedRows + row;
+    if (lane == 0) {
+        // router weights are constants of the layer: their copies may start before the previous kernel ends
+        const uint32_t half_bytes = (uint32_t)H * 2u;
+        const uint32_t bw = th ? bar_w1 : bar_w0;
+        r_mbar_expect_tx(bw, half_bytes);
+        r_bulk_g2s(r_smem_u32(ws + (size_t)row * H) + th * half_bytes, reinterpret_cast<const uint8_t*>(W + (int64_t)e * H) + th * half_bytes,
+                   half_bytes, bw);
+    }
+    pdl_wait();   // the token rows come from the previous kernel; the routing buffers written below may still be read by it
+    // only now may the next kernel start: whatever it does before its own wait sees complete token rows
+    pdl_launch_dependents();
+    if (lane == 0 && warp < nt) {
+        r_mbar_expect_tx(bar_x, (uint32_t)H * 2u);
+        r_bulk_g2s(r_smem_u32(xs + (size_t)warp * vec), x + (int64_t)(t0 + warp) * H, (uint32_t)H * 2u, bar_x);
+    }
+    bool ok = true;
+    if (th * NT < nt) {   // this warp has tokens (warp-uniform)
+        float acc[NT];
+        const uint2* xrow[NT];
 #pragma unroll
-        for (int i = 0; i < kLogitTokens; i++) acc[i] = 0.0f;
-        const float4* wrow = reinterpret_cast<const float4*>(W + (int64_t)e * H) + lane;
-        const int n_iter = H >> 7;
-        // router rows stream from HBM: fetch sixteen 512-byte pieces per round trip, then do the math
-        for (int i0 = 0; i0 < n_iter; i0 += 16) {
-            float4 w8[16];
+        for (int i = 0; i < NT; i++) {
+            acc[i] = 0.0f;
+            xrow[i] = xs + (size_t)min(th * NT + i, nt - 1) * vec + lane;   // slots past the batch alias the last valid row
+        }
+        const float4* wrow = reinterpret_cast<const float4*>(ws + (size_t)row * H) + lane;
+        const int n_iter = H >> 7, half_iter = n_iter >> 1;
+        ok = r_mbar_wait(bar_x, 0) && r_mbar_wait(bar_w0, 0);
+        for (int hlf = 0; hlf < 2 && ok; hlf++) {
+            if (hlf == 1) ok = r_mbar_wait(bar_w1, 0);
+            if (!ok) break;
+#pragma unroll 4
+            for (int i = hlf * half_iter; i < (hlf + 1) * half_iter; i++) {
+                const float4 w = wrow[i * 32];
 #pragma unroll
-            for (int j = 0; j < 16; j++) w8[j] = (i0 + j < n_iter) ? __ldg(wrow + (i0 + j) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                if (i0 + j < n_iter) {
-                    const float4 w = w8[j];
-#pragma unroll
-                    for (int tt = 0; tt < kLogitTokens; tt++) {
-                        const uint2 xv = xs[tt * vec + (i0 + j) * 32 + lane];
-                        const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
-                        const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
-                        float a = acc[tt];
-                        a = __fmaf_rn(w.x, x0, a);
-                        a = __fmaf_rn(w.y, x1, a);
-                        a = __fmaf_rn(w.z, x2, a);
-                        a = __fmaf_rn(w.w, x3, a);
-                        acc[tt] = a;
-                    }
+                for (int tt = 0; tt < NT; tt++) {
+                    const uint2 xv = xrow[tt][i * 32];
+                    const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
+                    const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
+                    float a = acc[tt];
+                    a = __fmaf_rn(w.x, x0, a);
+                    a = __fmaf_rn(w.y, x1, a);
+                    a = __fmaf_rn(w.z, x2, a);
+                    a = __fmaf_rn(w.w, x3, a);
+                    acc[tt] = a;
                 }
             }
         }
 #pragma unroll
-        for (int tt = 0; tt < kLogitTokens; tt++) {
+        for (int tt = 0; tt < NT; tt++) {
             float a = acc[tt];
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, off));
-            if (lane == 0 && tt < nt) logits[(int64_t)(t0 + tt) * E + e] = a;
+            if (lane == 0 && th * NT + tt < nt) logits[(int64_t)(t0 + th * NT + tt) * E + e] = a;
         }
+    } else {
+        // no tokens here, but no thread may leave while copies into this block's shared memory are in flight
+        ok = r_mbar_wait(bar_x, 0) && r_mbar_wait(bar_w0, 0) && r_mbar_wait(bar_w1, 0);
     }
+    if (!ok && lane == 0) atomicOr(error_word, 4u);
     // ---- last block of this token tile?
     __threadfence();
     __syncthreads();
@@ -286,23 +363,36 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
     if (!s_flag) return;
     if (threadIdx.x == 0) counters[1 + tile] = 0u;
     __threadfence();
-    float* s_score = reinterpret_cast<float*>(fsm);   // the token rows are no longer needed
+    float* s_score = reinterpret_cast<float*>(fsm);   // rows and tokens are no longer needed
     if (warp < nt) {
-        const float* row = logits + (int64_t)(t0 + warp) * E;
-        topk_one_token<VPL>([&](int ee) { return __ldcg(row + ee); }, bias, cfg, selected + (int64_t)(t0 + warp) * cfg.n_used,
-                            weights + (int64_t)(t0 + warp) * cfg.n_used, s_score + warp * E);
+        const float* lrow = logits + (int64_t)(t0 + warp) * E;
+        topk_one_token<VPL>([&](int ee) { return __ldcg(lrow + ee); }, bias, cfg, selected + (int64_t)(t0 + warp) * cfg.n_used,
+                            weights + (int64_t)(t0 + warp) * cfg.n_used, s_score + warp * E, s_sel + (t0 + warp) * cfg.n_used,
+                            s_wsel + (t0 + warp) * cfg.n_used);
     }
-    // ---- last tile of the launch?
-    __threadfence();
+    const int P = T * cfg.n_used;
+    if (gridDim.y > 1) {
+        // ---- last tile of the launch?
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_flag = (atomicAdd(&counters[0], 1u) == gridDim.y - 1) ? 1 : 0;
+        __syncthreads();
+        if (!s_flag) return;
+        if (threadIdx.x == 0) counters[0] = 0u;
+        __threadfence();
+        for (int i = threadIdx.x; i < P; i += kFusedWarps * 32) {   // the other tiles' picks
+            s_sel[i] = __ldcg(selected + i);
+            s_wsel[i] = __ldcg(weights + i);
+        }
+    }
     __syncthreads();
-    if (threadIdx.x == 0) s_flag = (atomicAdd(&counters[0], 1u) == gridDim.y - 1) ? 1 : 0;
-    __syncthreads();
-    if (!s_flag) return;
-    if (threadIdx.x == 0) counters[0] = 0u;
-    __threadfence();
-    int* wh = reinterpret_cast<int*>(fsm);
-    groupdev::build_small<kLogitWarps * 32>(selected, (int64_t)T * cfg.n_used, E, 0, chunk, shared_T, hist, offsets, perm, work_items,
-                                            n_work_items, work_cap, wh, s_warp);
+    if (item_recs != nullptr)
+        groupdev::build_small_with_recs<kFusedWarps * 32, kFusedMaxPicks>(s_sel, s_wsel, T, cfg.n_used, E, shared_T, hist, offsets, perm,
+                                                                          work_items, n_work_items, min(work_cap, kFusedMaxItems),
+                                                                          item_recs, reinterpret_cast<int*>(fsm), s_warp);
+    else
+        groupdev::build_small<kFusedWarps * 32, kFusedMaxPicks>(s_sel, P, E, 0, chunk, shared_T, hist, offsets, perm, work_items,
+                                                                n_work_items, work_cap, reinterpret_cast<int*>(fsm), s_warp);
 }
 
 }  // namespace
@@ -310,8 +400,8 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
 // Shapes the one-launch decode router covers (everything else takes the three separate kernels).
 bool router_fused_ok(int64_t T, const dsx_router_config& cfg, int64_t H) {
     const int v = cfg.n_expert / 32;
-    return T >= 1 && T <= 64 && cfg.n_expert % 32 == 0 && (v == 1 || v == 2 || v == 4 || v == 8) && H % 128 == 0 &&
-           (size_t)kLogitTokens * H * 2 <= 96 * 1024 && T * cfg.n_used <= kGroupChunk && cfg.n_used <= kMaxUsed &&
+    return T >= 1 && T <= 64 && cfg.n_expert % 32 == 0 && (v == 1 || v == 2 || v == 4 || v == 8) && H % 256 == 0 &&
+           (size_t)(kFusedRows * 4 + 8 * 2) * H <= 200 * 1024 && T * cfg.n_used <= kFusedMaxPicks && cfg.n_used <= kMaxUsed &&
            (cfg.n_group <= 1 || (cfg.n_group <= 32 && cfg.n_expert % cfg.n_group == 0));
 }
 
@@ -325,35 +415,75 @@ int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int 
     return DSX_OK;
 }
 
+namespace {
+size_t fused_smem(int64_t H, int nt_per_warp, int n_expert) {
+    return std::max<size_t>(std::max<size_t>((size_t)(kFusedRows * 4 + 2 * nt_per_warp * 2) * H, (size_t)kFusedWarps * n_expert * 4), kFusedScratch);
+}
+template <int V, int NT>
+cudaError_t launch_fused_variant(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* x, int T, const float* W,
+                                 const float* bias, int H, const dsx_router_config& cfg, float* logits, int32_t* selected,
+                                 float* weights, int chunk, int shared_T, int32_t* hist, int32_t* offsets, int32_t* perm,
+                                 int32_t* work_items, int32_t* n_work_items, int32_t work_cap, ItemRec* item_recs, unsigned int* counters,
+                                 uint32_t* error_word) {
+    return launch_pdl(router_fused_kernel<V, NT>, grid, dim3(kFusedWarps * 32), smem, stream, x, T, W, bias, H, cfg, logits, selected,
+                      weights, chunk, shared_T, hist, offsets, perm, work_items, n_work_items, work_cap, item_recs, counters, error_word);
+}
+template <int V>
+cudaError_t launch_fused_v(int nt_per_warp, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* x, int T, const float* W,
+                           const float* bias, int H, const dsx_router_config& cfg, float* logits, int32_t* selected, float* weights,
+                           int chunk, int shared_T, int32_t* hist, int32_t* offsets, int32_t* perm, int32_t* work_items,
+                           int32_t* n_work_items, int32_t work_cap, ItemRec* item_recs, unsigned int* counters, uint32_t* error_word) {
+#define DSX_FUSED_NT(N)                                                                                                         \
+    case N:                                                                                                                      \
+        return launch_fused_variant<V, N>(grid, smem, stream, x, T, W, bias, H, cfg, logits, selected, weights, chunk, shared_T, \
+                                          hist, offsets, perm, work_items, n_work_items, work_cap, item_recs, counters, error_word);
+    switch (nt_per_warp) {
+        DSX_FUSED_NT(1) DSX_FUSED_NT(2) DSX_FUSED_NT(4)
+    }
+#undef DSX_FUSED_NT
+    return cudaErrorInvalidValue;
+}
+template <int V, int NT>
+cudaError_t configure_fused_variant() {
+    return cudaFuncSetAttribute(router_fused_kernel<V, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+}
+}  // namespace
+
 int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const float* bias, int64_t H, const dsx_router_config& cfg,
                         float* logits, int32_t* selected, float* weights, int chunk, int shared_T, int32_t* hist, int32_t* offsets,
-                        int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap, unsigned int* counters,
-                        cudaStream_t stream) {
-    DSX_REQUIRE(router_fused_ok(T, cfg, H), "router_fused: shape not covered");
-    const size_t smem = std::max<size_t>((size_t)kLogitTokens * H * 2, (size_t)kLogitWarps * cfg.n_expert * 4);
-    dim3 grid((unsigned)(cfg.n_expert / kLogitWarps), (unsigned)((T + kLogitTokens - 1) / kLogitTokens));
+                        int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap, ItemRec* item_recs,
+                        unsigned int* counters, uint32_t* error_word, cudaStream_t stream) {
+    DSX_REQUIRE(router_fused_ok(T, cfg, H) && chunk == 8, "router_fused: shape not covered");
+    DSX_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "router_fused: token rows and router weights must be 16-byte aligned");
+    const int nt_per_warp = T <= 2 ? 1 : (T <= 4 ? 2 : 4);
+    const int tile = 2 * nt_per_warp;
+    const size_t smem = fused_smem(H, nt_per_warp, cfg.n_expert);
+    dim3 grid((unsigned)(cfg.n_expert / kFusedRows), (unsigned)((T + tile - 1) / tile));
+    cudaError_t err = cudaErrorInvalidValue;
     switch (cfg.n_expert / 32) {
-#define DSX_FUSED_CASE(V)                                                                                                     \
-    case V:                                                                                                                   \
-        DSX_CUDA(launch_pdl(router_fused_kernel<V>, grid, dim3(kLogitWarps * 32), smem, stream, x, (int)T, W, bias, (int)H, cfg,     \
-                            logits, selected, weights, chunk, shared_T, hist, offsets, perm, work_items, n_work_items, work_cap,  \
-                            counters));                                                                                       \
+#define DSX_FUSED_CASE(V)                                                                                                      \
+    case V:                                                                                                                    \
+        err = launch_fused_v<V>(nt_per_warp, grid, smem, stream, x, (int)T, W, bias, (int)H, cfg, logits, selected, weights, chunk, \
+                                shared_T, hist, offsets, perm, work_items, n_work_items, work_cap, item_recs, counters, error_word); \
         break;
         DSX_FUSED_CASE(1) DSX_FUSED_CASE(2) DSX_FUSED_CASE(4) DSX_FUSED_CASE(8)
 #undef DSX_FUSED_CASE
         default:
             return set_error(DSX_ERR_UNSUPPORTED, "router_fused: n_expert %d not instantiated", cfg.n_expert);
     }
+    DSX_CUDA(err);
     DSX_LAUNCHED();
     return DSX_OK;
 }
 
-// Opt the fused router in to 96 KB of dynamic shared memory (once per device, at layer creation).
+// Opt the fused router in to its dynamic shared memory (once per device, at layer creation).
 int router_configure() {
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+#define DSX_FUSED_CFG(V)                                  \
+    DSX_CUDA((configure_fused_variant<V, 1>()));          \
+    DSX_CUDA((configure_fused_variant<V, 2>()));          \
+    DSX_CUDA((configure_fused_variant<V, 4>()));
+    DSX_FUSED_CFG(1) DSX_FUSED_CFG(2) DSX_FUSED_CFG(4) DSX_FUSED_CFG(8)
+#undef DSX_FUSED_CFG
     return DSX_OK;
 }
 

@@ -188,6 +188,34 @@ def test_layer_config1_decode(torch_cuda, moe, oracle, T):
         assert np.array_equal(alone[0], out[0])
 
 
+def test_fused_decode_router_every_batch_size(torch_cuda, moe, oracle):
+    """The one-launch decode router (logits + top-k + group build) at every tile shape it has:
+    routing bit-exact with the oracle given its logits, logits the same bits as the stand-alone
+    logits kernel (which the larger batches use)."""
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS
+    cfg = CONFIGS[0]
+    r = cfg.router
+    w = synth.make_layer(cfg, 0)
+    layer = moe.build_layer_from_host(cfg, w, max_tokens=64)
+    router = moe.RouterTopk(r)
+    rw = torch_cuda.from_numpy(w["router_w"]).cuda()
+    for T in (1, 2, 3, 4, 5, 7, 8, 9, 16, 33, 64):
+        xb = synth.make_tokens(cfg, 0, T, stream=T)
+        x = torch_cuda.from_numpy(xb.view(np.int16)).cuda().view(torch_cuda.bfloat16)
+        layer.forward(x)
+        assert layer.check() == 0
+        got = layer.routing(T)
+        alone = router.logits(x, rw).cpu().numpy()
+        assert np.array_equal(got["logits"].view(np.uint32), alone.view(np.uint32)), T
+        osel, ow = oracle.router_topk(got["logits"], w["router_bias"], r.n_used, r.n_group, r.topk_group, r.score_fn, r.route_scale, r.weight_eps)
+        assert np.array_equal(got["selected"], osel), T
+        assert np.array_equal(got["weights"].view(np.uint32), ow.view(np.uint32)), T
+        oh, oo, op = oracle.group_build(osel, r.n_expert)
+        assert np.array_equal(got["hist"], oh) and np.array_equal(got["offsets"], oo) and np.array_equal(got["perm"], op), T
+    layer.close()
+
+
 def test_layer_q8_0_small(torch_cuda, moe, oracle):
     from deepstrix_b200.config import CONFIGS, FMT_Q8_0
     cfg = CONFIGS[0].with_(fmt=FMT_Q8_0)
