@@ -395,6 +395,139 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
                                                                 n_work_items, work_cap, reinterpret_cast<int*>(fsm), s_warp);
 }
 
+
+// ---- The same for 9..64 tokens: two router rows per block stay in shared memory while the token
+// rows stream past them in tiles of 8 (double buffered bulk copies), so the grid is E/2 blocks
+// whatever the batch size and the router weights are read once.  Warp w works on row w/4 and on
+// tokens 2*(w%4), +1 of the tile, in the f32 operation order of router_logits_kernel.
+// Then one barrier across the grid (every block is resident: the launcher checks E/2 against the
+// SM count, and the next kernel of the chain cannot start before every block of this one has
+// passed its release point; the wait is bounded and reports through error_word), the blocks share
+// out the tokens' top-k, one warp per token, and the last block to finish (ticket) builds the groups.
+// counters[0]: barrier arrivals, counters[1]: ticket; both return to zero.
+constexpr int kWideRows = 2;
+constexpr int kWideWarps = 8;
+constexpr int kWideTile = 8;
+
+template <int VPL>
+__global__ void __launch_bounds__(kWideWarps * 32)
+router_fused_wide_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __restrict__ W, const float* __restrict__ bias, int H,
+                         dsx_router_config cfg, float* __restrict__ logits, int32_t* __restrict__ selected, float* __restrict__ weights,
+                         int chunk, int shared_T, int32_t* hist, int32_t* offsets, int32_t* perm, int32_t* work_items,
+                         int32_t* n_work_items, int32_t work_cap, unsigned int* counters, uint32_t* error_word) {
+    extern __shared__ __align__(128) uint8_t fsm[];
+    __shared__ __align__(8) uint64_t s_bar[3];   // router rows, token buffer 0, token buffer 1
+    __shared__ int s_flag;
+    __shared__ int s_warp[kWideWarps + 1];
+    __shared__ int32_t s_sel[kFusedMaxPicks];
+    constexpr int E = VPL * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = warp >> 2, q = warp & 3;
+    const int vec = H >> 2;
+    const int n_tiles = (T + kWideTile - 1) / kWideTile;
+    float* ws = reinterpret_cast<float*>(fsm);                                   // [2][H] f32
+    uint2* xs = reinterpret_cast<uint2*>(fsm + (size_t)kWideRows * H * 4);       // [2 buffers][8][H/4] of 4 x bf16
+    const uint32_t bar_w = r_smem_u32(&s_bar[0]);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 3; i++) r_mbar_init(r_smem_u32(&s_bar[i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // router weights are constants of the layer: the copy may start before the previous kernel ends
+        const uint32_t bytes = (uint32_t)kWideRows * (uint32_t)H * 4u;
+        r_mbar_expect_tx(bar_w, bytes);
+        r_bulk_g2s(r_smem_u32(ws), W + (int64_t)blockIdx.x * kWideRows * H, bytes, bar_w);
+    }
+    __syncthreads();
+    pdl_wait();   // the token rows come from the previous kernel; the routing buffers written below may still be read by it
+    pdl_launch_dependents();
+    // blocks walk the tiles in rotated order, so that at any moment they read different token rows
+    auto tile_of = [&](int i) { return (i + (int)blockIdx.x) % n_tiles; };
+    auto load_tile = [&](int i) {   // thread 0: the i-th tile of this block into buffer i & 1 (a tile's rows are contiguous)
+        const int t = tile_of(i);
+        const int nt = min(kWideTile, T - t * kWideTile);
+        const uint32_t bar = r_smem_u32(&s_bar[1 + (i & 1)]);
+        r_mbar_expect_tx(bar, (uint32_t)nt * (uint32_t)H * 2u);
+        r_bulk_g2s(r_smem_u32(xs + (size_t)(i & 1) * kWideTile * vec), x + (int64_t)t * kWideTile * H, (uint32_t)nt * (uint32_t)H * 2u, bar);
+    };
+    if (threadIdx.x == 0) {
+        load_tile(0);
+        if (n_tiles > 1) load_tile(1);
+    }
+    const int e = blockIdx.x * kWideRows + row;
+    bool ok = r_mbar_wait(bar_w, 0);
+    for (int i = 0; i < n_tiles; i++) {
+        const int t = tile_of(i);
+        const int nt = min(kWideTile, T - t * kWideTile);
+        ok = ok && r_mbar_wait(r_smem_u32(&s_bar[1 + (i & 1)]), (uint32_t)((i >> 1) & 1));
+        if (ok && 2 * q < nt) {
+            const uint2* xb = xs + (size_t)(i & 1) * kWideTile * vec + lane;
+            const uint2* x0p = xb + (size_t)(2 * q) * vec;
+            const uint2* x1p = xb + (size_t)min(2 * q + 1, nt - 1) * vec;   // a slot past the batch aliases the last valid row
+            const float4* wrow = reinterpret_cast<const float4*>(ws + (size_t)row * H) + lane;
+            float a0 = 0.0f, a1 = 0.0f;
+            const int n_iter = H >> 7;
+#pragma unroll 4
+            for (int c = 0; c < n_iter; c++) {
+                const float4 w = wrow[c * 32];
+                const uint2 u = x0p[c * 32], v = x1p[c * 32];
+                a0 = __fmaf_rn(w.x, __uint_as_float(u.x << 16), a0);
+                a0 = __fmaf_rn(w.y, __uint_as_float(u.x & 0xFFFF0000u), a0);
+                a0 = __fmaf_rn(w.z, __uint_as_float(u.y << 16), a0);
+                a0 = __fmaf_rn(w.w, __uint_as_float(u.y & 0xFFFF0000u), a0);
+                a1 = __fmaf_rn(w.x, __uint_as_float(v.x << 16), a1);
+                a1 = __fmaf_rn(w.y, __uint_as_float(v.x & 0xFFFF0000u), a1);
+                a1 = __fmaf_rn(w.z, __uint_as_float(v.y << 16), a1);
+                a1 = __fmaf_rn(w.w, __uint_as_float(v.y & 0xFFFF0000u), a1);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                a0 = __fadd_rn(a0, __shfl_xor_sync(0xFFFFFFFFu, a0, off));
+                a1 = __fadd_rn(a1, __shfl_xor_sync(0xFFFFFFFFu, a1, off));
+            }
+            if (lane == 0) {
+                const int tok = t * kWideTile + 2 * q;
+                logits[(int64_t)tok * E + e] = a0;
+                if (2 * q + 1 < nt) logits[(int64_t)(tok + 1) * E + e] = a1;
+            }
+        }
+        __syncthreads();   // every warp is done with this buffer
+        if (threadIdx.x == 0 && i + 2 < n_tiles) load_tile(i + 2);
+    }
+    if (!ok && lane == 0) atomicOr(error_word, 4u);
+    // ---- barrier across the grid: all logits are written
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        atomicAdd(&counters[0], 1u);
+        bool arrived = false;
+        for (uint32_t i = 0; i < kRouterWaitSpins && !arrived; i++) {
+            arrived = __ldcg(&counters[0]) >= gridDim.x;
+            if (!arrived) __nanosleep(64);
+        }
+        if (!arrived) atomicOr(error_word, 8u);
+        __threadfence();
+    }
+    __syncthreads();
+    float* s_score = reinterpret_cast<float*>(fsm);   // rows and tokens are no longer needed
+    for (int tok = blockIdx.x + warp * gridDim.x; tok < T; tok += kWideWarps * gridDim.x) {
+        const float* lrow = logits + (int64_t)tok * E;
+        topk_one_token<VPL>([&](int ee) { return __ldcg(lrow + ee); }, bias, cfg, selected + (int64_t)tok * cfg.n_used,
+                            weights + (int64_t)tok * cfg.n_used, s_score + warp * E);
+    }
+    // ---- last block of the launch?
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_flag = (atomicAdd(&counters[1], 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_flag) return;
+    if (threadIdx.x == 0) { counters[0] = 0u; counters[1] = 0u; }   // every block has left the barrier: it took a ticket
+    __threadfence();
+    const int P = T * cfg.n_used;
+    for (int i = threadIdx.x; i < P; i += kWideWarps * 32) s_sel[i] = __ldcg(selected + i);
+    __syncthreads();
+    groupdev::build_small<kWideWarps * 32, kFusedMaxPicks>(s_sel, P, E, 0, chunk, shared_T, hist, offsets, perm, work_items, n_work_items,
+                                                           work_cap, reinterpret_cast<int*>(fsm), s_warp);
+}
+
 }  // namespace
 
 // Shapes the one-launch decode router covers (everything else takes the three separate kernels).
@@ -447,6 +580,10 @@ template <int V, int NT>
 cudaError_t configure_fused_variant() {
     return cudaFuncSetAttribute(router_fused_kernel<V, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
 }
+size_t wide_smem(int64_t H, int n_expert) {
+    return std::max<size_t>(std::max<size_t>((size_t)(kWideRows * 4 + 2 * kWideTile * 2) * H, (size_t)kWideWarps * n_expert * 4), kFusedScratch);
+}
+int g_sm_count = 0;   // of the device router_configure ran on
 }  // namespace
 
 int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const float* bias, int64_t H, const dsx_router_config& cfg,
@@ -455,6 +592,27 @@ int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const
                         unsigned int* counters, uint32_t* error_word, cudaStream_t stream) {
     DSX_REQUIRE(router_fused_ok(T, cfg, H) && chunk == 8, "router_fused: shape not covered");
     DSX_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "router_fused: token rows and router weights must be 16-byte aligned");
+    if (T > kWideTile && cfg.n_expert / kWideRows <= g_sm_count && wide_smem(H, cfg.n_expert) <= 200 * 1024 && item_recs == nullptr) {
+        // resident router rows, streamed tokens, one barrier across a grid that fits the device
+        cudaError_t werr = cudaErrorInvalidValue;
+        const dim3 wgrid((unsigned)(cfg.n_expert / kWideRows));
+        const size_t wsmem = wide_smem(H, cfg.n_expert);
+        switch (cfg.n_expert / 32) {
+#define DSX_WIDE_CASE(V)                                                                                                          \
+    case V:                                                                                                                       \
+        werr = launch_pdl(router_fused_wide_kernel<V>, wgrid, dim3(kWideWarps * 32), wsmem, stream, x, (int)T, W, bias, (int)H, cfg,   \
+                          logits, selected, weights, chunk, shared_T, hist, offsets, perm, work_items, n_work_items, work_cap,    \
+                          counters, error_word);                                                                                  \
+        break;
+            DSX_WIDE_CASE(1) DSX_WIDE_CASE(2) DSX_WIDE_CASE(4) DSX_WIDE_CASE(8)
+#undef DSX_WIDE_CASE
+            default:
+                return set_error(DSX_ERR_UNSUPPORTED, "router_fused: n_expert %d not instantiated", cfg.n_expert);
+        }
+        DSX_CUDA(werr);
+        DSX_LAUNCHED();
+        return DSX_OK;
+    }
     const int nt_per_warp = T <= 2 ? 1 : (T <= 4 ? 2 : 4);
     const int tile = 2 * nt_per_warp;
     const size_t smem = fused_smem(H, nt_per_warp, cfg.n_expert);
@@ -484,6 +642,13 @@ int router_configure() {
     DSX_CUDA((configure_fused_variant<V, 4>()));
     DSX_FUSED_CFG(1) DSX_FUSED_CFG(2) DSX_FUSED_CFG(4) DSX_FUSED_CFG(8)
 #undef DSX_FUSED_CFG
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    int dev = 0;
+    DSX_CUDA(cudaGetDevice(&dev));
+    DSX_CUDA(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
     return DSX_OK;
 }
 
