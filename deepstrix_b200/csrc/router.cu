@@ -77,6 +77,89 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, const float
     }
 }
 
+// Same logits for prefill-size batches, tiled like a GEMM so that router rows and token rows are
+// re-read from L2 16 and 32 times less: a block of 16 warps computes 16 router rows x 32 tokens,
+// a warp 4 rows x 8 tokens.  The reduction runs in chunks of 128 columns staged in shared memory
+// by 16-byte async copies (three stages); lane l still owns columns 4l..4l+3 of every chunk and
+// adds them in increasing column order, then the warp folds with the xor butterfly: the f32
+// operation sequence of a (token, expert) pair is the one of router_logits_kernel, same bits.
+constexpr int kTileRowsR = 16, kTileTok = 32, kTileStages = 3;
+constexpr int kTileThreads = 512;
+constexpr int kTileStageBytes = kTileRowsR * 128 * 4 + kTileTok * 128 * 2;   // 16 KB
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+__global__ void __launch_bounds__(kTileThreads)
+router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, const float* __restrict__ W, int n_expert, int64_t H,
+                           float* __restrict__ logits) {
+    extern __shared__ __align__(128) uint8_t tsm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rg = warp >> 2, tg = warp & 3;              // row group (4 rows), token group (8 tokens)
+    const int e0 = blockIdx.x * kTileRowsR;
+    const int64_t t0 = (int64_t)blockIdx.y * kTileTok;
+    const int n_iter = (int)(H >> 7);
+    // this thread's two 16-byte pieces of every stage (rows past the batch alias the last valid row)
+    const int wr = threadIdx.x >> 5, wc = threadIdx.x & 31;
+    const float* wsrc = W + (int64_t)(e0 + wr) * H + wc * 4;
+    const int xr = threadIdx.x >> 4, xc = threadIdx.x & 15;
+    const __nv_bfloat16* xsrc = x + min(t0 + xr, T - 1) * H + xc * 8;
+    auto stage_w = [&](int s) { return reinterpret_cast<float*>(tsm + (size_t)s * kTileStageBytes); };
+    auto stage_x = [&](int s) { return reinterpret_cast<__nv_bfloat16*>(tsm + (size_t)s * kTileStageBytes + kTileRowsR * 128 * 4); };
+    auto issue = [&](int i) {
+        const int s = i % kTileStages;
+        cp_async16(stage_w(s) + wr * 128 + wc * 4, wsrc + (int64_t)i * 128);
+        cp_async16(stage_x(s) + xr * 128 + xc * 8, xsrc + (int64_t)i * 128);
+    };
+    float acc[4][8];
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+        for (int t = 0; t < 8; t++) acc[r][t] = 0.0f;
+    issue(0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (n_iter > 1) issue(1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int i = 0; i < n_iter; i++) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();   // chunk i has landed for every thread; everyone is done with chunk i - 1
+        if (i + 2 < n_iter) issue(i + 2);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int s = i % kTileStages;
+        const float4* wp = reinterpret_cast<const float4*>(stage_w(s) + (rg * 4) * 128) + lane;
+        const uint2* xp = reinterpret_cast<const uint2*>(stage_x(s) + (tg * 8) * 128) + lane;
+        float4 w[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) w[r] = wp[r * 32];
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            const uint2 xv = xp[t * 32];
+            const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
+            const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                float a = acc[r][t];
+                a = __fmaf_rn(w[r].x, x0, a);
+                a = __fmaf_rn(w[r].y, x1, a);
+                a = __fmaf_rn(w[r].z, x2, a);
+                a = __fmaf_rn(w[r].w, x3, a);
+                acc[r][t] = a;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            float a = acc[r][t];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, off));
+            const int64_t tok = t0 + tg * 8 + t;
+            if (lane == 0 && tok < T) logits[tok * n_expert + e0 + rg * 4 + r] = a;
+        }
+}
+
 __device__ __forceinline__ uint32_t ordered_bits(float f) {
     const uint32_t b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -542,8 +625,13 @@ int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int 
                          cudaStream_t stream) {
     DSX_REQUIRE(H % 128 == 0, "router_logits: hidden %lld must be a multiple of 128", (long long)H);
     if (T == 0) return DSX_OK;
-    dim3 grid((unsigned)((n_expert + kLogitWarps - 1) / kLogitWarps), (unsigned)((T + kLogitTokens - 1) / kLogitTokens));
-    router_logits_kernel<<<grid, kLogitWarps * 32, 0, stream>>>(x, T, W, n_expert, H, logits);
+    if (n_expert % kTileRowsR == 0 && T >= 512 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0)) {   // enough 16 x 32 tiles for every SM
+        dim3 grid2((unsigned)(n_expert / kTileRowsR), (unsigned)((T + kTileTok - 1) / kTileTok));
+        router_logits_tiled_kernel<<<grid2, kTileThreads, kTileStages * kTileStageBytes, stream>>>(x, T, W, n_expert, H, logits);
+    } else {
+        dim3 grid((unsigned)((n_expert + kLogitWarps - 1) / kLogitWarps), (unsigned)((T + kLogitTokens - 1) / kLogitTokens));
+        router_logits_kernel<<<grid, kLogitWarps * 32, 0, stream>>>(x, T, W, n_expert, H, logits);
+    }
     DSX_LAUNCHED();
     return DSX_OK;
 }
@@ -642,6 +730,7 @@ int router_configure() {
     DSX_CUDA((configure_fused_variant<V, 4>()));
     DSX_FUSED_CFG(1) DSX_FUSED_CFG(2) DSX_FUSED_CFG(4) DSX_FUSED_CFG(8)
 #undef DSX_FUSED_CFG
+    DSX_CUDA(cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileStages * kTileStageBytes));
     DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));

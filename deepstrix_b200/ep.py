@@ -156,3 +156,148 @@ class ExpertParallelMoe:
         self._mark("combine_exchange_and_sum")
         self.last_stats = {"sent_rows": int(tok.numel()), "received_rows": R, "fanout": float(tok.numel()) / max(T, 1)}
         return out.to(x.dtype)
+
+
+# --------------------------------------------------------------------------
+# The same step over peer memory: rows go straight into the owner's device memory (CUDA IPC
+# mapping of one slab per rank), slots come from a scan on the device, and nothing in the step
+# synchronises with the host.  The arithmetic (what is sent, the rank-order f32 sum) is the one
+# above, so both transports give the same bits.
+class _DeviceView:
+    """A device pointer as a zero-copy torch tensor (through __cuda_array_interface__)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+def _as_tensor(ptr: int, shape, typestr: str, dtype=None) -> torch.Tensor:
+    t = torch.as_tensor(_DeviceView(ptr, shape, typestr), device="cuda")
+    return t if dtype is None else t.view(dtype)
+
+
+class PeerMemoryComm:
+    """One rank's end of the exchange (``dsx_ep_*`` of the C ABI)."""
+
+    def __init__(self, world: int, rank: int, cap: int, hidden: int, n_used: int):
+        import ctypes as C
+        from . import moe
+        self._C, self._moe = C, moe
+        self.world, self.rank, self.cap, self.hidden, self.k = world, rank, cap, hidden, n_used
+        h = C.c_void_p()
+        moe._check(moe.lib().dsx_ep_create(world, rank, C.c_int64(cap), C.c_int64(hidden), n_used, C.byref(h)))
+        self._h = h
+
+    def export_handle(self) -> bytes:
+        buf = (self._C.c_uint8 * 64)()
+        self._moe._check(self._moe.lib().dsx_ep_export(self._h, buf))
+        return bytes(buf)
+
+    def connect(self, handles: list):
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.world
+        self._moe._check(self._moe.lib().dsx_ep_connect(self._h, (self._C.c_uint8 * len(blob)).from_buffer_copy(blob)))
+
+    def connect_local(self, ranks: list):
+        arr = (self._C.c_void_p * self.world)(*[r._h for r in ranks])
+        self._moe._check(self._moe.lib().dsx_ep_connect_local(self._h, arr))
+
+    def connect_group(self, group=None):
+        """Exchange the slab handles over the process group (ranks are processes on one node)."""
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.export_handle(), group=group)
+        self.connect(handles)
+
+    def dispatch(self, x, selected, weights, n_expert: int):
+        m, C = self._moe, self._C
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and selected.dtype == torch.int32 and weights.dtype == torch.float32
+        assert selected.is_contiguous() and weights.is_contiguous()
+        m._check(m.lib().dsx_ep_dispatch(self._h, m._dptr(x), m._dptr(selected), m._dptr(weights), C.c_int64(x.shape[0]), n_expert, m._stream()))
+
+    def barrier(self):
+        self._moe._check(self._moe.lib().dsx_ep_barrier(self._h, self._moe._stream()))
+
+    def prepare(self):
+        """(rows [world*cap, hidden] bf16, picks [world*cap, k] int32, weights [world*cap, k] f32), views of library memory."""
+        m, C = self._moe, self._C
+        px, ps, pw, n = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_int64()
+        m._check(m.lib().dsx_ep_prepare(self._h, C.byref(px), C.byref(ps), C.byref(pw), C.byref(n), m._stream()))
+        slots = n.value
+        rows = _as_tensor(px.value, (slots, self.hidden), "<i2", torch.bfloat16)
+        return rows, _as_tensor(ps.value, (slots, self.k), "<i4"), _as_tensor(pw.value, (slots, self.k), "<f4")
+
+    def give_back(self, part):
+        assert part.dtype == torch.bfloat16 and part.is_contiguous() and part.shape == (self.world * self.cap, self.hidden)
+        self._moe._check(self._moe.lib().dsx_ep_give_back(self._h, self._moe._dptr(part), self._moe._stream()))
+
+    def sum(self, shared, T: int, out=None):
+        m, C = self._moe, self._C
+        if out is None:
+            out = torch.empty((T, self.hidden), dtype=torch.bfloat16, device="cuda")
+        m._check(m.lib().dsx_ep_sum(self._h, m._dptr(shared), C.c_int64(T), m._dptr(out), m._stream()))
+        return out
+
+    def counts(self) -> torch.Tensor:
+        p = self._C.c_void_p()
+        self._moe._check(self._moe.lib().dsx_ep_counts(self._h, self._C.byref(p)))
+        return _as_tensor(p.value, (self.world,), "<i4")
+
+    def check(self) -> int:
+        w = self._C.c_uint32()
+        self._moe._check(self._moe.lib().dsx_ep_check(self._h, self._moe._stream(), self._C.byref(w)))
+        return int(w.value)
+
+    def close(self):
+        if self._h:
+            self._moe.lib().dsx_ep_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ExpertParallelPeerMemory:
+    """ExpertParallelMoe's step with the peer-memory transport (GPU ranks of one node).
+
+    local_compute(rows, selected, weights) must accept world*cap rows whose unused slots carry picks of -1
+    (``MoeLayer.forward_picks`` does) and return one bf16 row per slot."""
+
+    def __init__(self, n_expert: int, comm: PeerMemoryComm, local_compute: Callable, shared_compute: Callable = None):
+        self.n_expert, self.comm = n_expert, comm
+        self.local_compute, self.shared_compute = local_compute, shared_compute
+        self._side = None
+        self.profile = False
+        self._events = []
+        self.last_stats = {}
+
+    _mark = ExpertParallelMoe._mark
+    phase_ms = ExpertParallelMoe.phase_ms
+
+    def forward(self, x: torch.Tensor, selected: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        c = self.comm
+        T = x.shape[0]
+        self._mark("start")
+        c.dispatch(x, selected, weights, self.n_expert)
+        sh = None
+        if self.shared_compute is not None:   # beside the exchange, on a side stream
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            main = torch.cuda.current_stream()
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                sh = self.shared_compute(x)
+                sh.record_stream(main)
+        c.barrier()
+        self._mark("dispatch_and_barrier")
+        rows, sel, w = c.prepare()
+        part = self.local_compute(rows, sel, w)
+        self._mark("owned_experts")
+        c.give_back(part)
+        c.barrier()
+        if sh is not None:
+            torch.cuda.current_stream().wait_stream(self._side)
+        out = c.sum(sh, T)
+        self._mark("give_back_barrier_and_sum")
+        return out

@@ -1,6 +1,8 @@
 """Expert-parallel benchmark leg (configuration 4): a stack of 8 full-size MoE
 layers, 256 experts sharded evenly over the GPUs of one node, the shared expert
-replicated, 4096 bf16 tokens per GPU, dispatch and combine over NCCL.
+replicated, 4096 bf16 tokens per GPU.  Dispatch and combine go over peer memory
+(rows stored straight into the owner's HBM through NVLink, no host round trip);
+``DSX_EP_TRANSPORT=nccl`` selects per-peer NCCL send/recv instead.
 
 Launched by ``bench.py`` under ``torch.distributed.run`` (one rank per GPU).
 """
@@ -20,8 +22,7 @@ TOKENS_PER_GPU = 4096
 
 def _rms_normalise(x: torch.Tensor) -> torch.Tensor:
     """Stand-in for the model's norm between layers: keeps the stack's activations at unit scale."""
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(dim=1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+    return torch.nn.functional.rms_norm(x, (x.shape[1],), eps=1e-6)
 
 
 def selfcheck(rank: int, world: int):
@@ -29,7 +30,7 @@ def selfcheck(rank: int, world: int):
     unsharded layer computed on the same GPU (configuration 4's check, at a size that takes a
     second).  Covers both kernel families: 16 tokens (GEMV kernels) and 160 (tensor-core path)."""
     from deepstrix_b200 import CONFIGS, moe, synth
-    from deepstrix_b200.ep import ExpertParallelMoe
+    from deepstrix_b200.ep import ExpertParallelMoe, ExpertParallelPeerMemory, PeerMemoryComm
     cfg = CONFIGS[0]
     E, k, H = cfg.router.n_expert, cfg.router.n_used, cfg.hidden
     per, lo = E // world, rank * (E // world)
@@ -40,6 +41,8 @@ def selfcheck(rank: int, world: int):
     rw, rb = torch.from_numpy(w["router_w"]).cuda(), torch.from_numpy(w["router_bias"]).cuda()
     part = moe.MoeLayer(cfg, shard, shared, rw, rb, max_tokens=160 * world)
     router = moe.RouterTopk(cfg.router)
+    comm = PeerMemoryComm(world, rank, 160, H, k)
+    comm.connect_group()
     worst = 0.0
     for T in (16, 160):
         x = torch.from_numpy(synth.make_tokens(cfg, 0, T, stream=50 + rank).view(np.int16)).cuda().view(torch.bfloat16)
@@ -47,10 +50,18 @@ def selfcheck(rank: int, world: int):
         none_sel = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
         ep = ExpertParallelMoe(E, None, lambda xr, s, ww: part.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False),
                                lambda xr: part.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
-        got = ep.forward(x, sel, wt).float()
+        got = ep.forward(x, sel, wt)
+        # the peer-memory transport moves the same rows and adds in the same order; the owner sees all
+        # world*cap slots at once, so it may take the other kernel family: compare both with the unsharded layer
+        ep2 = ExpertParallelPeerMemory(E, comm, lambda xr, s, ww: part.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False),
+                                       lambda xr: part.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
+        got2 = ep2.forward(x, sel.contiguous(), wt.contiguous()).float()
+        got = got.float()
         ref = full.forward(x).float()
-        worst = max(worst, float((got - ref).norm() / ref.norm()))
-    assert part.check() == 0 and full.check() == 0
+        worst = max(worst, float((got - ref).norm() / ref.norm()), float((got2 - ref).norm() / ref.norm()))
+    assert part.check() == 0 and full.check() == 0 and comm.check() == 0
+    dist.barrier()
+    comm.close()
     t = torch.tensor([worst], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     worst = float(t.item())
@@ -60,7 +71,7 @@ def selfcheck(rank: int, world: int):
 
 def run(args):
     from deepstrix_b200 import CONFIGS, moe, synth
-    from deepstrix_b200.ep import ExpertParallelMoe
+    from deepstrix_b200.ep import ExpertParallelMoe, ExpertParallelPeerMemory, PeerMemoryComm
     import bench as B
 
     rank = int(os.environ.get("RANK", "0"))
@@ -105,16 +116,24 @@ def run(args):
     def shared_compute(xr):
         return layer_sh.forward_picks(xr, none_sel, none_w, expert_lo=lo, with_shared=True)
 
-    ep = ExpertParallelMoe(E, None, local_compute, shared_compute)
+    transport = os.environ.get("DSX_EP_TRANSPORT", "peer")
+    comm = None
+    if transport == "nccl":
+        ep = ExpertParallelMoe(E, None, local_compute, shared_compute)
+    else:
+        comm = PeerMemoryComm(world, rank, T, H, k)
+        comm.connect_group()
+        ep = ExpertParallelPeerMemory(E, comm, local_compute, shared_compute)
     stats = {"received_rows": [], "fanout": []}
 
     def step(x):
         for rw, rb in routers:
             logits = router.logits(x, rw)
             sel, wt = router.launch_batched(logits, rb)
-            out = ep.forward(x, sel, wt)
-            stats["received_rows"].append(ep.last_stats["received_rows"])
-            stats["fanout"].append(ep.last_stats["fanout"])
+            out = ep.forward(x, sel.contiguous(), wt.contiguous())
+            if comm is None:
+                stats["received_rows"].append(ep.last_stats["received_rows"])
+                stats["fanout"].append(ep.last_stats["fanout"])
             x = _rms_normalise(out)
         return x
 
@@ -142,7 +161,7 @@ def run(args):
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
-    assert layer.check() == 0 and layer_sh.check() == 0
+    assert layer.check() == 0 and layer_sh.check() == 0 and (comm is None or comm.check() == 0)
 
     # end to end: tokens start in pinned host memory, the stack's output returns to the host
     xh = [t.cpu().pin_memory() for t in xs]
@@ -169,7 +188,11 @@ def run(args):
     phases = ep.phase_ms()
     phases["step_total"] = t_r0.elapsed_time(t_r1)
     ep.profile = False
-    rows = torch.tensor([float(np.mean(stats["received_rows"])), float(np.mean(stats["fanout"]))], device="cuda")
+    if comm is not None:   # rows received in the last layer of the last step; every sent row is received once
+        got_rows = float(comm.counts().sum().item())
+        rows = torch.tensor([got_rows, got_rows / T], device="cuda")
+    else:
+        rows = torch.tensor([float(np.mean(stats["received_rows"])), float(np.mean(stats["fanout"]))], device="cuda")
     dist.all_reduce(rows, op=dist.ReduceOp.SUM)
     if sampler:
         sampler.stop()
@@ -185,8 +208,10 @@ def run(args):
             "config": {"workload": f"config4: stack of {N_LAYERS} full-size MoE layers, 256 experts sharded over {world} GPUs "
                                    f"({per} per GPU), shared expert replicated, {T} bf16 tokens per GPU; value counts tokens x layers",
                        "tokens_per_gpu": T, "layers": N_LAYERS, "parallelism": f"ep{world}",
-                       "exchange": "per-peer NCCL send/recv batches (dispatch: token rows + picks + weights once per owner rank; "
-                                   "combine: one weighted partial row per token and owner)",
+                       "exchange": ("peer memory: rows, picks and weights stored straight into the owner's HBM over NVLink (CUDA IPC mapping), "
+                                    "slots by a device-side scan, two device-side barriers per layer, no host round trip"
+                                    if comm is not None else
+                                    "per-peer NCCL send/recv batches (token rows + picks + weights once per owner rank; one partial row back)"),
                        "l2": "each layer streams the rank's expert shard (%.0f MB) and %d token rows: far above L2" % (routed.device_bytes / 1e6, T)},
             "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16_peak, "unit": "TFLOP/s", "frac": tf / bf16_peak, "traffic": None,
                          "kernel": "prefill_gemm_kernel (tcgen05, f16 operands)", "peak_kind": peak_kind,

@@ -57,6 +57,7 @@ def lib() -> C.CDLL:
         _lib.dsx_launch_count.restype = C.c_uint64
         _lib.dsx_wi_upper_bound.restype = C.c_uint32
         _lib.dsx_wi_upper_bound.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint64]
+        _lib.dsx_ep_connect_local.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
     return _lib
 
 

@@ -294,6 +294,49 @@ DSX_API int dsx_moe_layer_stage_ms(dsx_moe_layer* layer, float* ms);
  * reset (per-thread launch audit, crates/v4flash-hip/src/module.rs:97-131). */
 DSX_API uint64_t dsx_launch_count(int reset);
 
+/* ------------------------------------------------------------------------
+ * 3. Expert-parallel exchange over peer memory
+ *
+ * Replaces the transport of the reference's remote-expert path (TCP "DSXP",
+ * het/remote_experts.rs: RemoteExpertClient::submit_dispatch :10060, the
+ * executor's NO_PICK skipping :7428-7442; docs/v41/REMOTE_EXPERTS.md:163-164,
+ * 196-229) for ranks that are processes on the GPUs of one node: what is sent
+ * and returned is the same (a token row once per owning rank with all its
+ * picks and weights; one weighted partial row back per received token; the
+ * sender adds in rank order), but the rows are stored straight into the
+ * owner's device memory, mapped through CUDA IPC, and nothing synchronises
+ * with the host.  One step on one stream:
+ *   dsx_ep_dispatch, dsx_ep_barrier, dsx_ep_prepare,
+ *   dsx_moe_layer_forward_picks on the prepared rows (expert_lo = rank's first expert),
+ *   dsx_ep_give_back, dsx_ep_barrier, dsx_ep_sum.
+ * ---------------------------------------------------------------------- */
+typedef struct dsx_ep_comm dsx_ep_comm;
+/* cap: most tokens a rank dispatches in one step; at most 8 ranks. */
+DSX_API int dsx_ep_create(int world, int rank, int64_t cap, int64_t hidden, int n_used, dsx_ep_comm** comm);
+DSX_API int dsx_ep_destroy(dsx_ep_comm* comm);
+/* 64-byte handle of this rank's receive slab; every rank passes all world handles, in rank order, to connect. */
+DSX_API int dsx_ep_export(dsx_ep_comm* comm, uint8_t* handle64);
+DSX_API int dsx_ep_connect(dsx_ep_comm* comm, const uint8_t* handles);
+/* Ranks that live in one process on one device (tests): peers are plain pointers; the caller runs each
+ * phase for every rank before the next phase and leaves the barriers out. */
+DSX_API int dsx_ep_connect_local(dsx_ep_comm* comm, dsx_ep_comm* const* ranks);
+/* Slots by exclusive scan over the tokens, rows + picks + weights stored into the owners' slabs. */
+DSX_API int dsx_ep_dispatch(dsx_ep_comm* comm, const void* x_bf16, const int32_t* selected, const float* weights,
+                            int64_t T, int n_expert, dsx_stream_t stream);
+/* All ranks' earlier stores are visible after it.  The wait is bounded (error bit 1, see dsx_ep_check). */
+DSX_API int dsx_ep_barrier(dsx_ep_comm* comm, dsx_stream_t stream);
+/* Received rows [world*cap, hidden] bf16, their picks [world*cap, n_used] (-1 in unused slots) and weights. */
+DSX_API int dsx_ep_prepare(dsx_ep_comm* comm, const void** x_rows, const int32_t** selected, const float** weights,
+                           int64_t* n_slots, dsx_stream_t stream);
+/* partial_rows [world*cap, hidden] bf16 (row i: weighted sum of slot i's owned picks) back to their sources. */
+DSX_API int dsx_ep_give_back(dsx_ep_comm* comm, const void* partial_rows_bf16, dsx_stream_t stream);
+/* out[t] = shared[t] (or 0 when NULL) + the partial rows of token t in rank order, f32 adds, bf16 result. */
+DSX_API int dsx_ep_sum(dsx_ep_comm* comm, const void* shared_bf16, int64_t T, void* out_bf16, dsx_stream_t stream);
+/* Device array of `world` ints: rows received from every source this step (valid after the first barrier). */
+DSX_API int dsx_ep_counts(dsx_ep_comm* comm, const int32_t** counts);
+/* Reads and clears the error word (bit 1: a barrier gave up waiting); synchronises the stream. */
+DSX_API int dsx_ep_check(dsx_ep_comm* comm, dsx_stream_t stream, uint32_t* error_word);
+
 #ifdef __cplusplus
 }
 #endif
