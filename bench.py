@@ -330,6 +330,36 @@ def run_single_gpu(args):
                    "frac_of_measured_bf16_peak": fl / (ms_p * 1e-3) / 1e12 / bf16_peak,
                    "frac_of_nominal_fp4_peak_9pf": fl / (ms_p * 1e-3) / 9e15}
         layer_p.close()
+    # configuration 4's stack on ONE GPU (all 256 experts resident, no exchange): the reference point for
+    # the expert-parallel lines of `--gpus N`, which run the same stack with 4096 tokens per GPU
+    stack1 = None
+    if not args.no_prefill:
+        Ts, n_layers = 4096, 8
+        layer_s = moe.MoeLayer(cfg, base, base_sh, rw, rb, max_tokens=Ts)
+        xs4 = [torch.from_numpy(synth.make_tokens(cfg, 4, Ts, stream=i).view(np.int16)).cuda().view(torch.bfloat16) for i in range(2)]
+
+        def stack_step(x):
+            for li in range(n_layers):
+                layer_s.set_weights(stores[li % len(stores)], shared[li % len(stores)], rw, rb)
+                x = torch.nn.functional.rms_norm(layer_s.forward(x), (H,), eps=1e-6)
+            return x
+
+        n_s = max(4, args.steps // 8)
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                stack_step(xs4[i % 2])
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(n_s):
+                stack_step(xs4[i % 2])
+            e1.record(stream)
+            stream.synchronize()
+        assert layer_s.check() == 0
+        ms_s = e0.elapsed_time(e1) / n_s
+        stack1 = {"workload": "config4 on one GPU: stack of 8 full-size MoE layers, all 256 experts resident, 4096 bf16 tokens, router included",
+                  "tokens": Ts, "layers": n_layers, "steps": n_s, "ms_per_step": ms_s, "value": Ts * n_layers / (ms_s * 1e-3),
+                  "unit": UNIT + " (tokens x layers)"}
+        layer_s.close()
     # configuration 3: Q8_0 experts, 2048 tokens, Zipf(1.1)-skewed expert popularity
     q8 = None
     if not args.no_q8:
@@ -410,6 +440,7 @@ def run_single_gpu(args):
         "clocks": clocks,
         "series": series,
         "prefill": prefill,
+        "stack_one_gpu": stack1,
         "q8_0_zipf": q8,
     }
     print(json.dumps(line))

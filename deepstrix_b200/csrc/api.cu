@@ -353,7 +353,13 @@ int dsx_router_logits(const void* x_bf16, int64_t T, const float* W, int n_exper
 int dsx_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg, int32_t* selected,
                     float* weights, dsx_stream_t stream) {
     DSX_REQUIRE(logits && cfg && selected && weights && T >= 0, "router_topk: null argument");
-    return launch_router_topk(logits, bias, T, *cfg, selected, weights, (cudaStream_t)stream);
+    return launch_router_topk(logits, bias, T, *cfg, selected, weights, 0, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+int dsx_router_topk_ex(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg, int32_t* selected,
+                       float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, dsx_stream_t stream) {
+    DSX_REQUIRE(logits && cfg && selected && weights && T >= 0, "router_topk_ex: null argument");
+    DSX_REQUIRE(alts != nullptr || alt_w == nullptr, "router_topk_ex: alt_w without alts");
+    return launch_router_topk(logits, bias, T, *cfg, selected, weights, n_alt, alts, alt_w, range_out, (cudaStream_t)stream);
 }
 
 uint32_t dsx_wi_upper_bound(uint64_t members, uint32_t groups, uint32_t chunk, uint64_t cap) {
@@ -593,7 +599,7 @@ int dsx_moe_layer_forward(dsx_moe_layer* L, const void* x_bf16, int64_t T, void*
     }
     {
         StageTimer tm(L, DSX_STAGE_ROUTER_TOPK, stream);
-        if (int rc = launch_router_topk(logits, L->router_bias, T, L->cfg.router, L->selected, L->weights, stream)) return rc;
+        if (int rc = launch_router_topk(logits, L->router_bias, T, L->cfg.router, L->selected, L->weights, 0, nullptr, nullptr, nullptr, stream)) return rc;
     }
     L->last_logits = logits; L->last_selected = L->selected; L->last_weights = L->weights;
     return forward_core(L, x, T, L->selected, L->weights, 0, false, 1, (__nv_bfloat16*)out_bf16, stream);

@@ -192,7 +192,7 @@ int launch_max_byte(const uint8_t* p, int64_t bytes, uint32_t* out, cudaStream_t
 int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int n_expert, int64_t H, float* logits,
                          cudaStream_t stream);
 int launch_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg,
-                       int32_t* selected, float* weights, cudaStream_t stream);
+                       int32_t* selected, float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, cudaStream_t stream);
 int router_configure();
 bool router_fused_ok(int64_t T, const dsx_router_config& cfg, int64_t H);
 int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const float* bias, int64_t H, const dsx_router_config& cfg,
@@ -246,6 +246,7 @@ struct GemvArgs {
 int launch_gemv_gate_up(const GemvArgs& a, int sm_count, cudaStream_t stream);
 int launch_gemv_down(const GemvArgs& a, int sm_count, cudaStream_t stream);
 int gemv_configure();  // opt in to large dynamic shared memory (once per device)
+bool gemv_fits(int64_t K);  // the kernels' shared memory holds a reduction of this length
 
 // combine.cu
 int launch_combine(const float* partial, int64_t T, int n_used, int64_t H, int with_shared, const int32_t* selected,

@@ -475,6 +475,8 @@ int check_args(const GemvArgs& a) {
 
 }  // namespace
 
+bool gemv_fits(int64_t K) { return K % 256 == 0 && gemv_smem_bytes(K) <= kMaxSmem; }
+
 int launch_gemv_gate_up(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     if (int rc = check_args(a)) return rc;
     return a.fmt == DSX_FMT_MXFP4 ? launch_one<DSX_FMT_MXFP4, true>(a, sm_count, stream)

@@ -531,25 +531,34 @@ __device__ __forceinline__ int seg_size(int cnt) {  // even split into <= 256-ro
 }
 
 // One block.  Segments sorted by expert; the shared expert's segments (expert id
-// n_local) follow and cover rows P .. P+T-1.
+// n_local) follow and cover rows P .. P+T-1.  Experts with at most small_max rows get no
+// segment: a tile would spend a full pass of weight conversion on a handful of tokens, while the
+// grouped GEMV streams the same weights at HBM speed, so they become GEMV work items instead.
 __global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t P, int T_shared,
-                                      PrefillSeg* __restrict__ segs, int32_t* __restrict__ n_segs, int cap) {
+                                      PrefillSeg* __restrict__ segs, int32_t* __restrict__ n_segs, int cap, int small_max,
+                                      int32_t* __restrict__ small_items, int32_t* __restrict__ n_small) {
     __shared__ int s_base[513];
     if (threadIdx.x == 0) {
-        int run = 0;
+        int run = 0, small = 0;
         for (int e = 0; e < n_local; e++) {
             s_base[e] = run;
             const int cnt = offsets[e + 1] - offsets[e];
+            if (cnt > 0 && cnt <= small_max) {
+                small_items[small++] = (int32_t)((uint32_t)e << 16);
+                continue;
+            }
             const int sz = seg_size(cnt);
             run += sz ? (cnt + sz - 1) / sz : 0;
         }
         s_base[n_local] = run;
         const int sz = seg_size(T_shared);
         n_segs[0] = min(cap, run + (sz ? (T_shared + sz - 1) / sz : 0));
+        if (n_small != nullptr) n_small[0] = small;
     }
     __syncthreads();
     for (int e = threadIdx.x; e <= n_local; e += blockDim.x) {
         const int cnt = e < n_local ? offsets[e + 1] - offsets[e] : T_shared;
+        if (e < n_local && cnt <= small_max) continue;
         const int row0 = e < n_local ? offsets[e] : (int)P;
         const int sz = seg_size(cnt);
         for (int i = 0, st = 0; st < cnt; i++, st += sz) {
@@ -662,6 +671,11 @@ int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, in
     DSX_CUDA(cudaMalloc((void**)&ws->xperm, (size_t)ws->cap_rows * (size_t)cfg.hidden * 2));
     DSX_CUDA(cudaMalloc((void**)&ws->segs, sizeof(PrefillSeg) * (size_t)ws->seg_cap));
     DSX_CUDA(cudaMalloc((void**)&ws->n_segs, 256));
+    DSX_CUDA(cudaMalloc((void**)&ws->small_items, sizeof(int32_t) * (size_t)(cfg.router.n_expert + 8)));
+    DSX_CUDA(cudaMalloc((void**)&ws->n_small, 256));
+    DSX_CUDA(cudaMemset(ws->n_small, 0, 256));
+    // a work item of the grouped GEMV holds at most 8 tokens; both reductions must fit its shared memory
+    ws->small_max = (gemv_fits(cfg.hidden) && gemv_fits(cfg.ffn) && cfg.hidden % 128 == 0 && cfg.ffn % 128 == 0) ? 8 : 0;
     if (int rc = encode_rows_map(&ws->tmap_x, ws->xperm, ws->cap_rows, cfg.hidden)) return rc;
     if (int rc = encode_rows_map(&ws->tmap_mid, mid, ws->cap_rows, cfg.ffn)) return rc;
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
@@ -677,7 +691,9 @@ void prefill_workspace_free(PrefillWorkspace* ws) {
     cudaFree(ws->xperm);
     cudaFree(ws->segs);
     cudaFree(ws->n_segs);
-    ws->xperm = nullptr; ws->segs = nullptr; ws->n_segs = nullptr; ws->ready = false;
+    cudaFree(ws->small_items);
+    cudaFree(ws->n_small);
+    ws->xperm = nullptr; ws->segs = nullptr; ws->n_segs = nullptr; ws->small_items = nullptr; ws->n_small = nullptr; ws->ready = false;
 }
 
 bool prefill_wanted(const PrefillWorkspace& ws, const dsx_moe_config&, int fmt, int64_t T) {
@@ -691,7 +707,8 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     if (int rc = launch_group_build(c.selected, c.T, c.n_used, c.n_local, c.expert_lo, kSegRows, 0, c.hist, c.offsets, c.perm,
                                     nullptr, nullptr, 0, c.gs, stream))
         return rc;
-    build_segments_kernel<<<1, 512, 0, stream>>>(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, ws->segs, ws->n_segs, ws->seg_cap);
+    build_segments_kernel<<<1, 512, 0, stream>>>(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, ws->segs, ws->n_segs, ws->seg_cap,
+                                                 ws->small_max, ws->small_items, ws->n_small);
     DSX_LAUNCHED();
     const int64_t rows = P + c.T;
     gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(c.x, c.perm, c.offsets, c.n_local, c.n_used, P, c.T,
@@ -706,6 +723,12 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
         if (int rc = map_weights(ws, 1, c.sh_gu_nib, c.sh_gu_sc, c.sh_dn_nib, c.sh_dn_sc, c.gu_nib_stride, c.gu_sc_stride,
                                  c.dn_nib_stride, c.dn_sc_stride, 1))
             return rc;
+    // experts with a handful of rows: the decode kernels, over the same sorted rows and partial rows
+    GemvArgs v{};
+    v.fmt = c.fmt; v.shared_fmt = c.fmt; v.n_expert = c.n_local;
+    v.work_items = ws->small_items; v.n_work_items = ws->n_small; v.item_recs = nullptr; v.offsets = c.offsets; v.perm = c.perm;
+    v.route_w = c.route_w; v.n_used = c.n_used; v.T = c.T; v.clamp = cfg.clamp; v.x = c.x; v.mid = c.mid; v.mid_stride = cfg.ffn;
+    v.partial = c.partial; v.error_word = c.error_word;
     GemmArgs g{};
     g.segs = ws->segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
     g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.error_word = c.error_word;
@@ -718,6 +741,11 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
         prefill_gemm_kernel<DSX_FMT_Q8_0, true><<<c.sm_count, kThreads, Shape<DSX_FMT_Q8_0>::kSmemTotal, stream>>>(
             ws->tmap_x, ws->tmap_gu_nib[0], ws->tmap_gu_sc[0], ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
     DSX_LAUNCHED();
+    if (ws->small_max > 0) {
+        v.K = cfg.hidden; v.rows = cfg.ffn; v.sh_rows = cfg.ffn;
+        v.nib = c.gu_nib; v.sc = c.gu_sc; v.nib_slot_stride = c.gu_nib_stride; v.sc_slot_stride = c.gu_sc_stride;
+        if (int rc = launch_gemv_gate_up(v, c.sm_count, stream)) return rc;
+    }
     // down: K = ffn, rows = hidden
     g.K = cfg.ffn; g.rows = cfg.hidden;
     if (c.fmt == DSX_FMT_MXFP4)
@@ -727,6 +755,11 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
         prefill_gemm_kernel<DSX_FMT_Q8_0, false><<<c.sm_count, kThreads, Shape<DSX_FMT_Q8_0>::kSmemTotal, stream>>>(
             ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0], ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
     DSX_LAUNCHED();
+    if (ws->small_max > 0) {
+        v.K = cfg.ffn; v.rows = cfg.hidden; v.sh_rows = cfg.hidden;
+        v.nib = c.dn_nib; v.sc = c.dn_sc; v.nib_slot_stride = c.dn_nib_stride; v.sc_slot_stride = c.dn_sc_stride;
+        if (int rc = launch_gemv_down(v, c.sm_count, stream)) return rc;
+    }
     return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr,
                           c.expert_lo, c.n_local, c.out, stream);
 }

@@ -23,6 +23,9 @@ struct PrefillWorkspace {
     PrefillSeg* segs = nullptr;
     int32_t* n_segs = nullptr;
     int32_t seg_cap = 0;
+    int small_max = 0;         // experts with at most this many rows go to the grouped GEMV instead (0: none)
+    int32_t* small_items = nullptr;   // their work items (expert << 16 | first member), one per expert
+    int32_t* n_small = nullptr;
     CUtensorMap tmap_x;        // xperm as [cap_rows, H], box 64 x 256, 128-byte swizzle
     CUtensorMap tmap_mid;      // mid   as [cap_rows, F]
     // packed-weight planes as 4-D tensors [slot][row tile][column tile][bytes as u32]; index 0 routed, 1 shared

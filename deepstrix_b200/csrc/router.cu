@@ -173,7 +173,9 @@ constexpr int kMaxUsed = 16;
 template <int VPL, typename LoadLogit>
 __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float* __restrict__ bias, const dsx_router_config& cfg,
                                                int32_t* __restrict__ sel_out, float* __restrict__ w_out, float* s_score,
-                                               int32_t* s_sel = nullptr, float* s_wsel = nullptr /* optional copies in shared memory */) {
+                                               int32_t* s_sel = nullptr, float* s_wsel = nullptr /* optional copies in shared memory */,
+                                               int n_alt = 0, int32_t* __restrict__ alt_out = nullptr, float* __restrict__ altw_out = nullptr,
+                                               float* __restrict__ range_out = nullptr) {
     const int lane = threadIdx.x & 31;
     const int E = VPL * 32;
     float p[VPL], s[VPL];
@@ -182,6 +184,17 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
         const int e = lane * VPL + j;
         p[j] = router_prob(load_logit(e), cfg.score_fn);
         s[j] = bias ? __fadd_rn(p[j], bias[e]) : p[j];
+    }
+    if (range_out != nullptr) {   // max - min of the selection scores over all experts (router_topk_par.hip:140-160)
+        float mx = s[0], mn = s[0];
+#pragma unroll
+        for (int j = 1; j < VPL; j++) { mx = fmaxf(mx, s[j]); mn = fminf(mn, s[j]); }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+            mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, off));
+        }
+        if (lane == 0) *range_out = __fsub_rn(mx, mn);
     }
     if (cfg.n_group > 1) {
         // group score = sum of the two largest selection scores of the group;
@@ -242,7 +255,7 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
     int esel[kMaxUsed];
 #pragma unroll
     for (int r = 0; r < kMaxUsed; r++) {
-        if (r < cfg.n_used) {
+        if (r < cfg.n_used + n_alt) {   // rounds past n_used are the alternatives: they only mask further
             // the lane's best by a tournament (depth log2 VPL); `>` keeps the lower j on ties
             uint32_t v[VPL];
             int ix[VPL];
@@ -278,11 +291,15 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
     int my_e = 0;
 #pragma unroll
     for (int r = 0; r < kMaxUsed; r++)
-        if (r < cfg.n_used) {
-            sum = __fadd_rn(sum, psel[r]);
+        if (r < cfg.n_used + n_alt) {
+            if (r < cfg.n_used) sum = __fadd_rn(sum, psel[r]);
             if (lane == r) { my_p = psel[r]; my_e = esel[r]; }
         }
     if (sum < cfg.weight_eps) sum = cfg.weight_eps;
+    if (lane >= cfg.n_used && lane < cfg.n_used + n_alt) {   // prob(alt) / (sum of the picks' probs) * scale
+        alt_out[lane - cfg.n_used] = my_e;
+        if (altw_out != nullptr) altw_out[lane - cfg.n_used] = __fmul_rn(__fdiv_rn(my_p, sum), cfg.route_scale);
+    }
     if (lane < cfg.n_used) {
         const float wv = __fmul_rn(__fdiv_rn(my_p, sum), cfg.route_scale);
         sel_out[lane] = my_e;
@@ -294,13 +311,16 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
 template <int VPL>
 __global__ void __launch_bounds__(kTopkWarps * 32)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, dsx_router_config cfg,
-                   int32_t* __restrict__ selected, float* __restrict__ weights) {
+                   int32_t* __restrict__ selected, float* __restrict__ weights, int n_alt, int32_t* __restrict__ alts,
+                   float* __restrict__ alt_w, float* __restrict__ range_out) {
     __shared__ float s_score[kTopkWarps][VPL * 32];
     const int warp = threadIdx.x >> 5;
     const int64_t t = (int64_t)blockIdx.x * kTopkWarps + warp;
     if (t >= T) return;
     const float* row = logits + t * (VPL * 32);
-    topk_one_token<VPL>([&](int e) { return row[e]; }, bias, cfg, selected + t * cfg.n_used, weights + t * cfg.n_used, s_score[warp]);
+    topk_one_token<VPL>([&](int e) { return row[e]; }, bias, cfg, selected + t * cfg.n_used, weights + t * cfg.n_used, s_score[warp], nullptr,
+                        nullptr, n_alt, alts ? alts + t * n_alt : nullptr, alt_w ? alt_w + t * n_alt : nullptr,
+                        range_out ? range_out + t : nullptr);
 }
 
 // ---- Decode router in ONE launch (T <= 64, E <= 256): logits, top-k and the group build.
@@ -742,7 +762,10 @@ int router_configure() {
 }
 
 int launch_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg,
-                       int32_t* selected, float* weights, cudaStream_t stream) {
+                       int32_t* selected, float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, cudaStream_t stream) {
+    if (alts == nullptr) n_alt = 0;
+    DSX_REQUIRE(n_alt >= 0 && cfg.n_used + n_alt <= kMaxUsed && cfg.n_used + n_alt <= cfg.n_expert,
+                "router_topk: %d picks + %d alternatives (at most %d together)", cfg.n_used, n_alt, kMaxUsed);
     DSX_REQUIRE(cfg.n_expert > 0 && cfg.n_expert % 32 == 0 && cfg.n_expert <= 512,
                 "router_topk: n_expert %d must be a multiple of 32, at most 512", cfg.n_expert);
     DSX_REQUIRE(cfg.n_used >= 1 && cfg.n_used <= kMaxUsed && cfg.n_used <= cfg.n_expert, "router_topk: n_used %d out of range", cfg.n_used);
@@ -755,7 +778,7 @@ int launch_router_topk(const float* logits, const float* bias, int64_t T, const 
     switch (cfg.n_expert / 32) {
 #define DSX_TOPK_CASE(V)                                                                                   \
     case V:                                                                                                \
-        router_topk_kernel<V><<<grid, kTopkWarps * 32, 0, stream>>>(logits, bias, T, cfg, selected, weights); \
+        router_topk_kernel<V><<<grid, kTopkWarps * 32, 0, stream>>>(logits, bias, T, cfg, selected, weights, n_alt, alts, alt_w, range_out); \
         break;
         DSX_TOPK_CASE(1) DSX_TOPK_CASE(2) DSX_TOPK_CASE(3) DSX_TOPK_CASE(4) DSX_TOPK_CASE(6) DSX_TOPK_CASE(8)
         DSX_TOPK_CASE(12) DSX_TOPK_CASE(16)

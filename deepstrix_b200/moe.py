@@ -186,6 +186,23 @@ class RouterTopk:
         _check(lib().dsx_router_topk(_dptr(logits), _dptr(bias), C.c_int64(T), C.byref(rc), _dptr(sel), _dptr(w), _stream()))
         return sel, w
 
+    def launch_batched_ex(self, logits: torch.Tensor, bias: torch.Tensor | None, n_alt: int = 0, want_range: bool = False):
+        """``launch_batched`` plus the reference's extras (src/router_topk.rs:245-364): the n_alt next-ranked
+        experts per token with their weights, and the selection-score range.  Returns
+        (selected, weights, alts, alt_weights, score_range); the last three are None when not asked for."""
+        T, E = logits.shape
+        assert E == self.cfg.n_expert and logits.dtype == torch.float32 and logits.is_contiguous()
+        dev = logits.device
+        sel = torch.empty((T, self.cfg.n_used), dtype=torch.int32, device=dev)
+        w = torch.empty((T, self.cfg.n_used), dtype=torch.float32, device=dev)
+        alts = torch.empty((T, n_alt), dtype=torch.int32, device=dev) if n_alt else None
+        alt_w = torch.empty((T, n_alt), dtype=torch.float32, device=dev) if n_alt else None
+        rng = torch.empty((T,), dtype=torch.float32, device=dev) if want_range else None
+        rc = _router_struct(self.cfg)
+        _check(lib().dsx_router_topk_ex(_dptr(logits), _dptr(bias), C.c_int64(T), C.byref(rc), _dptr(sel), _dptr(w), n_alt,
+                                        _dptr(alts), _dptr(alt_w), _dptr(rng), _stream()))
+        return sel, w, alts, alt_w, rng
+
 
 class MoeGroupBuilder:
     """Histogram / offsets / stable permutation / work items."""

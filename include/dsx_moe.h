@@ -176,6 +176,17 @@ typedef struct {
  * bias may be NULL.  selected: int32 [T, n_used] in rank order; weights f32. */
 DSX_API int dsx_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg,
                             int32_t* selected, float* weights, dsx_stream_t stream);
+/* RouterTopk::launch_batched_ex (src/router_topk.rs:245-364; router_topk_par.hip:18-21,75-81,140-160,
+ * 231-236): the same picks and weights, plus
+ *   alts      int32 [T, n_alt]  ranks n_used+1 .. n_used+n_alt (further argmax passes; what box 2
+ *                               substitutes for a pick it does not hold); NULL -> no alternatives
+ *   alt_w     f32 [T, n_alt]    prob(alt) / (sum of the picks' probs) * scale; may be NULL
+ *   range_out f32 [T]           max - min of the selection scores over all experts; may be NULL
+ * n_used + n_alt <= 16.  The cache-prior arguments of the reference (prior, n_protect, orig_sel)
+ * are not part of this entry point. */
+DSX_API int dsx_router_topk_ex(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg,
+                               int32_t* selected, float* weights, int n_alt, int32_t* alts, float* alt_w,
+                               float* range_out, dsx_stream_t stream);
 
 /* --- Histogram / permute / work items ------------------------------------
  * MoeGroupBuilder::launch + launch_work_items_split (src/moe_group_builder.rs:72-259;

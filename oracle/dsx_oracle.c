@@ -406,18 +406,30 @@ DSXO_API float dsxo_router_prob(float logit, int score_fn) {
  *   largest s in the group; the topk_group best groups (ties -> lower group)
  *   stay, all other experts are masked to -inf before the top-k.
  *   n_group <= 1 gives the reference algorithm unchanged. */
-DSXO_API void dsxo_router_topk(const float* logits, const float* bias, int64_t T, int n_expert,
-                               int n_used, int n_group, int topk_group, int score_fn,
-                               float scale, float eps, int32_t* selected, float* weights) {
+/* Top-k with the reference's extras (kernels/router_topk_par.hip:18-21,75-81,140-160,164-171,
+ * 231-236): n_alt further argmax passes after the first n_used ("alternatives", ranks
+ * n_used+1 .. n_used+n_alt; the picks and weights do not depend on n_alt), their weights
+ * prob(alt) / (sum of the n_used picks' probs) * scale, and the token's selection-score range
+ * max - min over all experts (taken before the group limit masks anything).  alts, alt_w and
+ * range_out may be NULL. */
+DSXO_API void dsxo_router_topk_ex(const float* logits, const float* bias, int64_t T, int n_expert,
+                                  int n_used, int n_group, int topk_group, int score_fn,
+                                  float scale, float eps, int32_t* selected, float* weights,
+                                  int n_alt, int32_t* alts, float* alt_w, float* range_out) {
+    if (!alts) n_alt = 0;
 #pragma omp parallel for schedule(static)
     for (int64_t t = 0; t < T; t++) {
         float* p = (float*)malloc(sizeof(float) * (size_t)n_expert * 2);
         float* s = p + n_expert;
         const float* lg = logits + t * n_expert;
+        float mx = -INFINITY, mn = INFINITY;
         for (int e = 0; e < n_expert; e++) {
             p[e] = dsxo_router_prob(lg[e], score_fn);
             s[e] = bias ? (p[e] + bias[e]) : p[e];
+            mx = fmaxf(mx, s[e]);
+            mn = fminf(mn, s[e]);
         }
+        if (range_out) range_out[t] = mx - mn;
         if (n_group > 1) {
             int per = n_expert / n_group;
             float gs[64];
@@ -440,24 +452,36 @@ DSXO_API void dsxo_router_topk(const float* logits, const float* bias, int64_t T
             for (int e = 0; e < n_expert; e++)
                 if (!keep[e / per]) s[e] = -INFINITY;
         }
-        int32_t* sel = selected + t * n_used;
-        for (int j = 0; j < n_used; j++) {
+        int32_t all[64];
+        for (int j = 0; j < n_used + n_alt; j++) {
             int best = -1;
             float bv = -INFINITY;
             for (int e = 0; e < n_expert; e++) {
                 int taken = 0;
-                for (int q = 0; q < j; q++) if (sel[q] == e) taken = 1;
+                for (int q = 0; q < j; q++) if (all[q] == e) taken = 1;
                 if (taken) continue;
                 if (best < 0 || s[e] > bv) { best = e; bv = s[e]; }
             }
-            sel[j] = best;
+            all[j] = best;
         }
+        int32_t* sel = selected + t * n_used;
+        for (int j = 0; j < n_used; j++) sel[j] = all[j];
         float sum = 0.0f;
         for (int j = 0; j < n_used; j++) sum += p[sel[j]];
         if (sum < eps) sum = eps;
         for (int j = 0; j < n_used; j++) weights[t * n_used + j] = p[sel[j]] / sum * scale;
+        for (int j = 0; j < n_alt; j++) {
+            alts[t * n_alt + j] = all[n_used + j];
+            if (alt_w) alt_w[t * n_alt + j] = p[all[n_used + j]] / sum * scale;
+        }
         free(p);
     }
+}
+
+DSXO_API void dsxo_router_topk(const float* logits, const float* bias, int64_t T, int n_expert,
+                               int n_used, int n_group, int topk_group, int score_fn,
+                               float scale, float eps, int32_t* selected, float* weights) {
+    dsxo_router_topk_ex(logits, bias, T, n_expert, n_used, n_group, topk_group, score_fn, scale, eps, selected, weights, 0, NULL, NULL, NULL);
 }
 
 /* Router logits: x[T,H] (f32) . W[E,H]^T, f32 inputs, accumulated in double

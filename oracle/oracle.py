@@ -229,6 +229,23 @@ def router_topk(logits, bias, n_used, n_group=1, topk_group=1, score_fn=SCORE_SI
     return sel, w
 
 
+def router_topk_ex(logits, bias, n_used, n_alt, n_group=1, topk_group=1, score_fn=SCORE_SIGMOID,
+                   scale=1.0, eps=ROUTER_EPS):
+    """router_topk plus the alternatives (ranks n_used+1 .. n_used+n_alt), their weights and the score range."""
+    logits = _c(logits, np.float32)
+    T, E = logits.shape
+    b = None if bias is None else _c(bias, np.float32)
+    sel = np.empty((T, n_used), np.int32)
+    w = np.empty((T, n_used), np.float32)
+    alts = np.empty((T, max(n_alt, 1)), np.int32)
+    alt_w = np.empty((T, max(n_alt, 1)), np.float32)
+    rng = np.empty((T,), np.float32)
+    lib().dsxo_router_topk_ex(_p(logits), _p(b), C.c_int64(T), C.c_int(E), C.c_int(n_used),
+                              C.c_int(n_group), C.c_int(topk_group), C.c_int(score_fn),
+                              C.c_float(scale), C.c_float(eps), _p(sel), _p(w), C.c_int(n_alt), _p(alts), _p(alt_w), _p(rng))
+    return sel, w, alts[:, :n_alt], alt_w[:, :n_alt], rng
+
+
 def group_build(selected: np.ndarray, n_expert: int):
     selected = _c(selected, np.int32)
     T, k = selected.shape

@@ -103,6 +103,44 @@ def test_router_topk_bitexact(torch_cuda, moe, oracle, E, k, n_group, topk_group
         assert np.array_equal(w.cpu().numpy().view(np.uint32), ow.view(np.uint32))
 
 
+@pytest.mark.parametrize("E,k,n_alt,n_group,topk_group,score_fn", [(256, 8, 4, 8, 4, 1), (384, 6, 4, 1, 1, 0), (64, 6, 2, 8, 4, 1)])
+def test_router_alternatives_and_range_bitexact(torch_cuda, moe, oracle, E, k, n_alt, n_group, topk_group, score_fn):
+    """The reference's extras of the top-k (router_topk_par.hip:18-21,140-160,231-236): alternatives are the
+    ranks k+1..k+n_alt, they leave picks and weights untouched, and the score range is max - min."""
+    from deepstrix_b200.config import RouterConfig
+    rng = np.random.Generator(np.random.PCG64(77 + E))
+    T = 97
+    logits = rng.normal(0.0, 1.3, size=(T, E)).astype(np.float32)
+    logits[3, 10] = logits[3, 200 % E]   # a tie among the leaders
+    bias = rng.normal(0.0, 0.01, size=(E,)).astype(np.float32)
+    cfg = RouterConfig(n_expert=E, n_used=k, n_group=n_group, topk_group=topk_group, score_fn=score_fn, route_scale=2.5)
+    router = moe.RouterTopk(cfg)
+    lg, b = torch_cuda.from_numpy(logits).cuda(), torch_cuda.from_numpy(bias).cuda()
+    sel, w, alts, alt_w, srange = router.launch_batched_ex(lg, b, n_alt=n_alt, want_range=True)
+    sel0, w0 = router.launch_batched(lg, b)
+    assert torch_cuda.equal(sel, sel0) and torch_cuda.equal(w, w0)
+    osel, ow, oalts, oalt_w, orange = oracle.router_topk_ex(logits, bias, k, n_alt, n_group, topk_group, score_fn, 2.5, cfg.weight_eps)
+    assert np.array_equal(sel.cpu().numpy(), osel)
+    assert np.array_equal(w.cpu().numpy().view(np.uint32), ow.view(np.uint32))
+    assert np.array_equal(alts.cpu().numpy(), oalts)
+    assert np.array_equal(alt_w.cpu().numpy().view(np.uint32), oalt_w.view(np.uint32))
+    assert np.array_equal(srange.cpu().numpy().view(np.uint32), orange.view(np.uint32))
+    # the alternatives are what a longer top-k would have picked next
+    longer, _ = oracle.router_topk(logits, bias, k + n_alt, n_group, topk_group, score_fn, 2.5, cfg.weight_eps)
+    assert np.array_equal(longer[:, k:], oalts)
+
+
+def test_layer_drafter_shape(torch_cuda, moe, oracle):
+    """The drafter's grouped MoE shape (128 experts, top-3, a 5-token block, no group limit,
+    sqrt-softplus scores; mxfp4_pair_matvec.hip:566-596): every distinct expert's weights are read
+    once for all the tokens that picked it."""
+    from deepstrix_b200.config import CONFIGS, RouterConfig
+    cfg = CONFIGS[0].with_(router=RouterConfig(n_expert=128, n_used=3, n_group=1, topk_group=1, score_fn=0, route_scale=1.5))
+    out, ref, layer, w, x, routing = _layer_case(torch_cuda, moe, oracle, cfg, 0, 5)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+    assert int((routing["hist"] > 0).sum()) <= 15
+
+
 def test_router_logits_close_and_batch_invariant(torch_cuda, moe, oracle):
     torch = torch_cuda
     from deepstrix_b200 import synth
