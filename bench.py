@@ -426,9 +426,9 @@ def run_single_gpu(args):
                          % (len(stores), len(stores) * (base.device_bytes + base_sh.device_bytes) / 1e9),
                    "launch": "one captured CUDA graph per step"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     # dram__bytes_read + write of this kernel from the ncu capture of a 41-item launch
-                     # (370.21 MB, profiles/gemv_decode_t8_64experts.md), scaled by the items of this launch
-                     "traffic": int(370.21e6 / 41 * (sum(gu_items) / len(gu_items))),
+                     # dram__bytes_read + write of this kernel from the ncu capture of a 57-item launch
+                     # (512.94 MB, profiles/gemv_decode_t16_64experts.md), scaled by the items of this launch
+                     "traffic": int(512.94e6 / 57 * (sum(gu_items) / len(gu_items))),
                      "kernel": "gemv_kernel<MXFP4, pair> (gate/up + SwiGLU)", "peak_kind": peak_kind,
                      "avg_launch_ms": gu_ms, "layer_frac": head["layer_frac_of_hbm_peak"]},
         "stage_ms": stage_ms,
