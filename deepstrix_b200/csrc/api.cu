@@ -347,7 +347,9 @@ int dsx_expert_store_info(const dsx_expert_store* st, int* fmt, int* n_slots, in
 
 // ------------------------------------------------------------------ router
 int dsx_router_logits(const void* x_bf16, int64_t T, const float* W, int n_expert, int64_t hidden, float* logits, dsx_stream_t stream) {
-    DSX_REQUIRE(x_bf16 && W && logits && T >= 0, "router_logits: null argument");
+    DSX_REQUIRE(T >= 0, "router_logits: negative token count");
+    if (T == 0) return DSX_OK;   // an empty batch has no rows to point at
+    DSX_REQUIRE(x_bf16 && W && logits, "router_logits: null argument");
     return launch_router_logits((const __nv_bfloat16*)x_bf16, T, W, n_expert, hidden, logits, (cudaStream_t)stream);
 }
 int dsx_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg, int32_t* selected,
@@ -547,7 +549,8 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
     GemvArgs a{};
     a.fmt = L->routed->fmt; a.shared_fmt = shared ? L->shared->fmt : a.fmt; a.n_expert = n_local;
     a.work_items = L->work_items; a.n_work_items = L->n_work_items; a.offsets = L->offsets; a.perm = L->perm;
-    a.item_recs = (groups_ready && T < 8) ? L->item_recs : nullptr;   // the decode router writes them for small batches only
+    // the decode router writes them for batches below 8 tokens; both kernels must have a small-batch form
+    a.item_recs = (groups_ready && T < 8 && gemv_small_batch_ok(L->routed->fmt, c.hidden, c.ffn, T)) ? L->item_recs : nullptr;
     a.route_w = weights; a.n_used = k; a.T = T; a.clamp = c.clamp; a.x = x; a.mid = L->mid; a.mid_stride = c.ffn;
     a.partial = L->partial; a.error_word = L->error_word;
     // gate/up: rows = ffn, K = hidden
@@ -572,8 +575,10 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
 
 int dsx_moe_layer_forward(dsx_moe_layer* L, const void* x_bf16, int64_t T, void* out_bf16, const float* logits_in, dsx_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    DSX_REQUIRE(L && x_bf16 && out_bf16, "moe_layer_forward: null argument");
+    DSX_REQUIRE(L, "moe_layer_forward: null layer");
     DSX_REQUIRE(T >= 0 && T <= L->cfg.max_tokens, "moe_layer_forward: %lld tokens, workspace holds %d", (long long)T, L->cfg.max_tokens);
+    if (T == 0) return DSX_OK;   // an empty batch has no rows to point at
+    DSX_REQUIRE(x_bf16 && out_bf16, "moe_layer_forward: null argument");
     DSX_REQUIRE(L->routed->n_slots == L->cfg.router.n_expert, "moe_layer_forward: store holds %d of %d experts; use forward_picks",
                 L->routed->n_slots, L->cfg.router.n_expert);
     if (T == 0) return DSX_OK;
@@ -619,9 +624,10 @@ int dsx_moe_layer_forward_host(dsx_moe_layer* L, const void* x_host, int64_t T, 
 
 int dsx_moe_layer_forward_picks(dsx_moe_layer* L, const void* x_bf16, int64_t T, const int32_t* selected, const float* weights,
                                 int expert_lo, int with_shared, void* out_bf16, dsx_stream_t stream) {
-    DSX_REQUIRE(L && x_bf16 && selected && weights && out_bf16, "moe_layer_forward_picks: null argument");
+    DSX_REQUIRE(L, "moe_layer_forward_picks: null layer");
     DSX_REQUIRE(T >= 0 && T <= L->cfg.max_tokens, "moe_layer_forward_picks: %lld tokens, workspace holds %d", (long long)T, L->cfg.max_tokens);
     if (T == 0) return DSX_OK;
+    DSX_REQUIRE(x_bf16 && selected && weights && out_bf16, "moe_layer_forward_picks: null argument");
     L->last_logits = nullptr; L->last_selected = selected; L->last_weights = weights;
     return forward_core(L, (const __nv_bfloat16*)x_bf16, T, selected, weights, expert_lo, true, with_shared, (__nv_bfloat16*)out_bf16,
                         (cudaStream_t)stream);

@@ -247,6 +247,7 @@ int launch_gemv_gate_up(const GemvArgs& a, int sm_count, cudaStream_t stream);
 int launch_gemv_down(const GemvArgs& a, int sm_count, cudaStream_t stream);
 int gemv_configure();  // opt in to large dynamic shared memory (once per device)
 bool gemv_fits(int64_t K);  // the kernels' shared memory holds a reduction of this length
+bool gemv_small_batch_ok(int fmt, int64_t hidden, int64_t ffn, int64_t T);  // item records may be used for this chain
 
 // combine.cu
 int launch_combine(const float* partial, int64_t T, int n_used, int64_t H, int with_shared, const int32_t* selected,

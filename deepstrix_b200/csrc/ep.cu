@@ -318,7 +318,8 @@ int dsx_ep_connect_local(dsx_ep_comm* c, dsx_ep_comm* const* ranks) {
 int dsx_ep_dispatch(dsx_ep_comm* c, const void* x_bf16, const int32_t* selected, const float* weights, int64_t T, int n_expert,
                     dsx_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    DSX_REQUIRE(c && x_bf16 && selected && weights, "ep_dispatch: null argument");
+    DSX_REQUIRE(c, "ep_dispatch: null argument");
+    DSX_REQUIRE(T == 0 || (x_bf16 && selected && weights), "ep_dispatch: null argument");
     DSX_REQUIRE(c->connected || c->world == 1, "ep_dispatch: not connected");
     DSX_REQUIRE(T >= 0 && T <= c->cap, "ep_dispatch: %lld tokens, capacity %lld", (long long)T, (long long)c->cap);
     DSX_REQUIRE(n_expert > 0 && n_expert % c->world == 0, "ep_dispatch: %d experts over %d ranks", n_expert, c->world);

@@ -438,27 +438,48 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
     }
 }
 
-size_t gemv_smem_bytes(int64_t K) {
+// Shared memory of one block: 8 activation rows, the rings, barriers, the item and (two warps per row
+// tile only) the exchange buffer of the two halves.
+size_t gemv_smem_bytes(int64_t K, bool with_halves) {
     const size_t act = (((size_t)kMaxTok * (size_t)(K + kActPad) * 2) + 127) & ~(size_t)127;
     return act + (size_t)kRingStagesPerBlock * kStageBytes + sizeof(uint64_t) * kRingStagesPerBlock + ((sizeof(ItemRec) + 127) & ~(size_t)127) +
-           (size_t)2 * 8 * 32 * 8 * sizeof(float) + 128;
+           (with_halves ? (size_t)2 * 8 * 32 * 8 * sizeof(float) : 0) + 128;
 }
 
 constexpr size_t kMaxSmem = 227 * 1024;
 
+struct Variant {
+    int warps, ksplit;   // 0 warps: nothing fits
+    size_t smem;
+};
+
+// Which instantiation a launch takes.  256-row units (one row tile per warp) need enough (item, unit)
+// pairs for every SM: the item count lives on the device, so the batch size decides (>= 8 tokens x
+// top-k picks is plenty).  Below that two warps share a row tile when the stage count is even, else
+// 8 warps own one each; a reduction too long for the exchange buffer falls back to 256-row units.
+Variant pick_variant(int fmt, bool pair, int64_t K, int64_t rows, int64_t T) {
+    const int tile_k = fmt == DSX_FMT_MXFP4 ? 64 : 32, ct_per_stage = pair ? kSubPerStage / 2 : kSubPerStage;
+    const int n_stage = (int)((K / tile_k + ct_per_stage - 1) / ct_per_stage);
+    const bool can_wide = rows % (kTileRows * 16) == 0;
+    const size_t plain = gemv_smem_bytes(K, false), split = gemv_smem_bytes(K, true);
+    if (can_wide && T >= 8 && plain <= kMaxSmem) return {16, 1, plain};
+    if (n_stage % 2 == 0 && split <= kMaxSmem) return {16, 2, split};
+    if (n_stage % 2 != 0 && plain <= kMaxSmem) return {8, 1, plain};
+    if (can_wide && plain <= kMaxSmem) return {16, 1, plain};
+    return {0, 0, plain};
+}
+
 template <int FMT, bool PAIR>
 int launch_one(const GemvArgs& a, int sm_count, cudaStream_t stream) {
-    const size_t smem = gemv_smem_bytes(a.K);
-    DSX_REQUIRE(smem <= kMaxSmem, "gemv: reduction length %lld needs %zu B of shared memory (max %zu)", (long long)a.K, smem, kMaxSmem);
-    // 256-row blocks need enough (item, block) units to occupy every SM twice over; the item count
-    // lives on the device, so decide on the batch size (>= 8 tokens x top-k picks is plenty)
-    const bool wide = a.rows % (kTileRows * 16) == 0 && a.T >= 8;
-    const int tile_k = FMT == DSX_FMT_MXFP4 ? 64 : 32, ct_per_stage = PAIR ? kSubPerStage / 2 : kSubPerStage;
-    const int n_stage = (int)((a.K / tile_k + ct_per_stage - 1) / ct_per_stage);
+    const Variant v = pick_variant(FMT, PAIR, a.K, a.rows, a.T);
+    DSX_REQUIRE(v.warps != 0, "gemv: reduction length %lld needs %zu B of shared memory (max %zu)", (long long)a.K, v.smem, kMaxSmem);
+    const size_t smem = v.smem;
     const bool small = a.item_recs != nullptr && a.T < kMaxTok;
 #define DSX_GEMV_LAUNCH(W, S, SM) DSX_CUDA(launch_pdl(gemv_kernel<FMT, PAIR, W, S, SM>, dim3(sm_count), dim3(W * 32), smem, stream, a))
-    if (wide) DSX_GEMV_LAUNCH(16, 1, false);
-    else if (n_stage % 2 == 0) { if (small) DSX_GEMV_LAUNCH(16, 2, true); else DSX_GEMV_LAUNCH(16, 2, false); }
+    if (v.warps == 16 && v.ksplit == 1) {
+        DSX_REQUIRE(!small, "gemv: item records need the small-batch kernels (see gemv_small_batch_ok)");
+        DSX_GEMV_LAUNCH(16, 1, false);
+    } else if (v.warps == 16) { if (small) DSX_GEMV_LAUNCH(16, 2, true); else DSX_GEMV_LAUNCH(16, 2, false); }
     else { if (small) DSX_GEMV_LAUNCH(8, 1, true); else DSX_GEMV_LAUNCH(8, 1, false); }
 #undef DSX_GEMV_LAUNCH
     DSX_LAUNCHED();
@@ -475,7 +496,14 @@ int check_args(const GemvArgs& a) {
 
 }  // namespace
 
-bool gemv_fits(int64_t K) { return K % 256 == 0 && gemv_smem_bytes(K) <= kMaxSmem; }
+bool gemv_fits(int64_t K) { return K % 256 == 0 && gemv_smem_bytes(K, false) <= kMaxSmem; }
+
+// Batches below 8 tokens may use item records only when both kernels of the chain take a small-batch
+// instantiation (they rely on each other's release order).
+bool gemv_small_batch_ok(int fmt, int64_t hidden, int64_t ffn, int64_t T) {
+    const Variant gu = pick_variant(fmt, true, hidden, ffn, T), dn = pick_variant(fmt, false, ffn, hidden, T);
+    return T < kMaxTok && gu.warps != 0 && dn.warps != 0 && !(gu.warps == 16 && gu.ksplit == 1) && !(dn.warps == 16 && dn.ksplit == 1);
+}
 
 int launch_gemv_gate_up(const GemvArgs& a, int sm_count, cudaStream_t stream) {
     if (int rc = check_args(a)) return rc;

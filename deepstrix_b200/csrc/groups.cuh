@@ -219,5 +219,104 @@ __device__ void build_small_with_recs(const int32_t* sel, const float* s_w, int 
     }
 }
 
+// The same result for at most 32 picks (a handful of decode tokens), in four block barriers instead of
+// a dozen: every thread counts the picks of, and below, its own expert directly (the picks are in
+// shared memory), one block scan numbers the work items, and one warp places the picks (position =
+// picks of smaller experts + earlier picks of the same expert, by match_any).  Needs E <= NT.
+// scratch: shared memory for 32 + work_cap + E + 2 ints.
+template <int NT>
+__device__ void build_tiny_with_recs(const int32_t* sel, const float* s_w, int T, int n_used, int E, int shared_T, int32_t* hist,
+                                     int32_t* offsets, int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap,
+                                     ItemRec* recs, int* scratch, int* s_warp) {
+    const int P = T * n_used;   // <= 32
+    int32_t* s_perm = scratch;
+    int32_t* s_items = s_perm + 32;
+    int32_t* s_off = s_items + work_cap;
+    int* s_n_items = s_off + E + 1;
+    const int e = threadIdx.x;
+    int h = 0, below = 0, valid = 0;
+    for (int i = 0; i < P; i++) {
+        const int v = sel[i];
+        h += (v == e) ? 1 : 0;
+        below += (v >= 0 && v < e) ? 1 : 0;
+        valid += (v >= 0 && v < E) ? 1 : 0;
+    }
+    if (e < E) {
+        hist[e] = h;
+        offsets[e] = below;
+        s_off[e] = below;
+    }
+    if (e == 0) {
+        offsets[E] = valid;
+        s_off[E] = valid;
+    }
+    const int ni = (e < E) ? (h + 7) >> 3 : 0;
+    int n_items;
+    const int ibase = block_exclusive_scan<NT>(ni, &n_items, s_warp);   // its barriers also publish s_off
+    for (int c = 0; c < ni; c++) {
+        const int p = ibase + c;
+        if (p < work_cap) {
+            const int32_t wi = (int32_t)(((uint32_t)e << 16) | (uint32_t)(c * 8));
+            work_items[p] = wi;
+            s_items[p] = wi;
+        }
+    }
+    const int n_sh = (shared_T + 7) >> 3;   // the shared expert is appended as pseudo expert id E over all tokens
+    for (int c = threadIdx.x; c < n_sh; c += NT) {
+        const int p = n_items + c;
+        if (p < work_cap) {
+            const int32_t wi = (int32_t)(((uint32_t)E << 16) | (uint32_t)(c * 8));
+            work_items[p] = wi;
+            s_items[p] = wi;
+        }
+    }
+    if (threadIdx.x == 0) {
+        n_work_items[0] = n_items + n_sh;
+        *s_n_items = min(n_items + n_sh, work_cap);
+    }
+    if (threadIdx.x < 32) {   // stable placement by one warp
+        const int i = threadIdx.x;
+        const int v = i < P ? sel[i] : -1;
+        const bool ok = v >= 0 && v < E;
+        const int key = ok ? v : (0x40000000 | i);
+        const uint32_t mask = __match_any_sync(0xFFFFFFFFu, key);
+        if (ok) {
+            const int pos = s_off[v] + __popc(mask & ((1u << i) - 1u));
+            perm[pos] = i;
+            s_perm[pos] = i;
+        }
+    }
+    __syncthreads();
+    const int total = *s_n_items;
+    for (int idx = threadIdx.x; idx < total * 8; idx += NT) {
+        const int i = idx >> 3, j = idx & 7;
+        const uint32_t wi = (uint32_t)s_items[i];
+        const int ex = (int)(wi >> 16), start = (int)(wi & 0xFFFFu);
+        int n, tok, mid_row, out_row;
+        float w;
+        if (ex == E) {   // shared expert: tokens start..start+7, weight 1
+            n = min(8, shared_T - start);
+            tok = start + j;
+            mid_row = out_row = P + start + j;
+            w = 1.0f;
+        } else {
+            const int seg0 = s_off[ex];
+            n = min(8, s_off[ex + 1] - seg0 - start);
+            const int p = seg0 + start + min(j, n - 1);
+            const int ts = s_perm[p];
+            tok = ts / n_used;
+            mid_row = p;
+            out_row = ts;
+            w = s_w[ts];
+        }
+        ItemRec* r = recs + i;
+        if (j == 0) { r->expert = ex; r->n_tok = n; }
+        r->tok[j] = tok;
+        r->mid_row[j] = mid_row;
+        r->out_row[j] = out_row;
+        r->w[j] = w;
+    }
+}
+
 }  // namespace groupdev
 }  // namespace dsx

@@ -489,7 +489,11 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
         }
     }
     __syncthreads();
-    if (item_recs != nullptr)
+    if (item_recs != nullptr && P <= 32)
+        groupdev::build_tiny_with_recs<kFusedWarps * 32>(s_sel, s_wsel, T, cfg.n_used, E, shared_T, hist, offsets, perm, work_items,
+                                                         n_work_items, min(work_cap, kFusedMaxItems), item_recs, reinterpret_cast<int*>(fsm),
+                                                         s_warp);
+    else if (item_recs != nullptr)
         groupdev::build_small_with_recs<kFusedWarps * 32, kFusedMaxPicks>(s_sel, s_wsel, T, cfg.n_used, E, shared_T, hist, offsets, perm,
                                                                           work_items, n_work_items, min(work_cap, kFusedMaxItems),
                                                                           item_recs, reinterpret_cast<int*>(fsm), s_warp);

@@ -405,6 +405,54 @@ def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
     assert rel_l2(acc, out_full) < 8e-3   # three bf16 roundings instead of one
 
 
+@pytest.mark.parametrize("T", [3, 16, 80])
+def test_layer_v41_widths(torch_cuda, moe, oracle, T):
+    """The reference model's own widths (hidden 5120, expert FFN 2304, top-6, sqrt-softplus scores, no
+    group limit; 32 of its 384 experts to keep the test small): the 5120-long reduction does not fit
+    the two-warps-per-row-tile form of the decode kernel, so batches below 8 tokens take 256-row units."""
+    from deepstrix_b200.config import CONFIGS, RouterConfig
+    cfg = CONFIGS[1].with_(hidden=5120, ffn=2304, shared_ffn=2304,
+                           router=RouterConfig(n_expert=32, n_used=6, n_group=1, topk_group=1, score_fn=0, route_scale=1.5))
+    out, ref, layer, w, x, routing = _layer_case(torch_cuda, moe, oracle, cfg, 1, T, max_tokens=80)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+    layer.close()
+
+
+def test_empty_batches(torch_cuda, moe, oracle):
+    """Zero tokens is a valid call everywhere (the reference's wrappers return early on an empty batch,
+    src/moe_group_builder.rs:144-150): nothing is launched, nothing is written, no error."""
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS
+    from deepstrix_b200.ep import PeerMemoryComm
+    cfg = CONFIGS[0]
+    r = cfg.router
+    w = synth.make_layer(cfg, 0)
+    layer = moe.build_layer_from_host(cfg, w, max_tokens=16)
+    x0 = torch_cuda.empty((0, cfg.hidden), dtype=torch_cuda.bfloat16, device="cuda")
+    out = layer.forward(x0)
+    assert out.shape == (0, cfg.hidden) and layer.check() == 0
+    sel0 = torch_cuda.empty((0, r.n_used), dtype=torch_cuda.int32, device="cuda")
+    w0 = torch_cuda.empty((0, r.n_used), dtype=torch_cuda.float32, device="cuda")
+    assert layer.forward_picks(x0, sel0, w0).shape == (0, cfg.hidden)
+    router = moe.RouterTopk(r)
+    rw = torch_cuda.from_numpy(w["router_w"]).cuda()
+    assert router.logits(x0, rw).shape == (0, r.n_expert)
+    # an empty batch after a real one leaves the layer usable
+    x = torch_cuda.from_numpy(synth.make_tokens(cfg, 0, 4).view(np.int16)).cuda().view(torch_cuda.bfloat16)
+    a = layer.forward(x).clone()
+    layer.forward(x0)
+    assert torch_cuda.equal(layer.forward(x), a)
+    # a rank with nothing to send still takes part in the exchange
+    comm = PeerMemoryComm(1, 0, 8, cfg.hidden, r.n_used)
+    comm.connect_local([comm])
+    comm.dispatch(x0, sel0, w0, r.n_expert)
+    rows, sel, wt = comm.prepare()
+    torch_cuda.cuda.synchronize()
+    assert int(comm.counts().cpu()[0]) == 0 and bool((sel == -1).all())
+    comm.close()
+    layer.close()
+
+
 def test_launcher_validation(torch_cuda, moe):
     torch = torch_cuda
     from deepstrix_b200.config import RouterConfig
