@@ -250,51 +250,45 @@ __device__ __forceinline__ void topk_one_token(LoadLogit load_logit, const float
     uint32_t ob[VPL];
 #pragma unroll
     for (int j = 0; j < VPL; j++) ob[j] = ordered_bits(__fadd_rn(s[j], 0.0f));   // adding +0 turns -0 into +0
-    // 0 marks "already taken": every non-NaN score maps to at least 0x007FFFFF (-inf)
-    float psel[kMaxUsed];
-    int esel[kMaxUsed];
-#pragma unroll
-    for (int r = 0; r < kMaxUsed; r++) {
-        if (r < cfg.n_used + n_alt) {   // rounds past n_used are the alternatives: they only mask further
-            // the lane's best by a tournament (depth log2 VPL); `>` keeps the lower j on ties
-            uint32_t v[VPL];
-            int ix[VPL];
-            float pp[VPL];
-#pragma unroll
-            for (int j = 0; j < VPL; j++) { v[j] = ob[j]; ix[j] = j; pp[j] = p[j]; }
-#pragma unroll
-            for (int lvl = 0; lvl < 5; lvl++) {
-                const int w = 1 << lvl;
-#pragma unroll
-                for (int j = 0; j < VPL; j++) {
-                    if (w < VPL && (j & (2 * w - 1)) == 0 && j + w < VPL) {
-                        const bool take = v[j + w] > v[j];
-                        v[j] = take ? v[j + w] : v[j];
-                        ix[j] = take ? ix[j + w] : ix[j];
-                        pp[j] = take ? pp[j + w] : pp[j];
-                    }
-                }
-            }
-            const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, v[0]);
-            const uint32_t cand = (v[0] == mx) ? (uint32_t)(lane * VPL + ix[0]) : 0xFFFFFFFFu;
-            const int e = (int)__reduce_min_sync(0xFFFFFFFFu, cand);
-            const bool mine = cand == (uint32_t)e;
-#pragma unroll
-            for (int j = 0; j < VPL; j++)
-                ob[j] = (mine && ix[0] == j) ? 0u : ob[j];
-            psel[r] = __shfl_sync(0xFFFFFFFFu, pp[0], e / VPL);
-            esel[r] = e;
-        }
-    }
-    // weights from the unbiased probabilities, summed in slot order; lane r writes slot r
+    // 0 marks "already taken": every non-NaN score maps to at least 0x007FFFFF (-inf).
+    // The rounds run as a real loop: this code executes once per token on one warp, where fetching the
+    // instructions of sixteen unrolled rounds costs more than running them.  Lane r keeps round r's
+    // pick; the weights' sum is accumulated in slot order over the first n_used rounds.
     float sum = 0.0f, my_p = 0.0f;
     int my_e = 0;
+    const int n_rounds = cfg.n_used + n_alt;   // rounds past n_used are the alternatives: they only mask further
+#pragma unroll 1
+    for (int r = 0; r < n_rounds; r++) {
+        // the lane's best by a tournament (depth log2 VPL); `>` keeps the lower j on ties
+        uint32_t v[VPL];
+        int ix[VPL];
+        float pp[VPL];
 #pragma unroll
-    for (int r = 0; r < kMaxUsed; r++)
-        if (r < cfg.n_used + n_alt) {
-            if (r < cfg.n_used) sum = __fadd_rn(sum, psel[r]);
-            if (lane == r) { my_p = psel[r]; my_e = esel[r]; }
+        for (int j = 0; j < VPL; j++) { v[j] = ob[j]; ix[j] = j; pp[j] = p[j]; }
+#pragma unroll
+        for (int lvl = 0; lvl < 5; lvl++) {
+            const int w = 1 << lvl;
+#pragma unroll
+            for (int j = 0; j < VPL; j++) {
+                if (w < VPL && (j & (2 * w - 1)) == 0 && j + w < VPL) {
+                    const bool take = v[j + w] > v[j];
+                    v[j] = take ? v[j + w] : v[j];
+                    ix[j] = take ? ix[j + w] : ix[j];
+                    pp[j] = take ? pp[j + w] : pp[j];
+                }
+            }
         }
+        const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, v[0]);
+        const uint32_t cand = (v[0] == mx) ? (uint32_t)(lane * VPL + ix[0]) : 0xFFFFFFFFu;
+        const int e = (int)__reduce_min_sync(0xFFFFFFFFu, cand);
+        const bool mine = cand == (uint32_t)e;
+#pragma unroll
+        for (int j = 0; j < VPL; j++)
+            ob[j] = (mine && ix[0] == j) ? 0u : ob[j];
+        const float pv = __shfl_sync(0xFFFFFFFFu, pp[0], e / VPL);
+        if (r < cfg.n_used) sum = __fadd_rn(sum, pv);
+        if (lane == r) { my_p = pv; my_e = e; }
+    }
     if (sum < cfg.weight_eps) sum = cfg.weight_eps;
     if (lane >= cfg.n_used && lane < cfg.n_used + n_alt) {   // prob(alt) / (sum of the picks' probs) * scale
         alt_out[lane - cfg.n_used] = my_e;
@@ -511,12 +505,15 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
 // SM count, and the next kernel of the chain cannot start before every block of this one has
 // passed its release point; the wait is bounded and reports through error_word), the blocks share
 // out the tokens' top-k, one warp per token, and the last block to finish (ticket) builds the groups.
+// NI = H / 128 when the launcher knows it (0 otherwise): a warp then keeps its router row in NI x 4
+// registers for the whole kernel and the tile loop reads only tokens from shared memory, whose
+// bandwidth is what bounds this phase.
 // counters[0]: barrier arrivals, counters[1]: ticket; both return to zero.
 constexpr int kWideRows = 2;
 constexpr int kWideWarps = 8;
 constexpr int kWideTile = 8;
 
-template <int VPL>
+template <int VPL, int NI>
 __global__ void __launch_bounds__(kWideWarps * 32)
 router_fused_wide_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __restrict__ W, const float* __restrict__ bias, int H,
                          dsx_router_config cfg, float* __restrict__ logits, int32_t* __restrict__ selected, float* __restrict__ weights,
@@ -561,6 +558,12 @@ router_fused_wide_kernel(const __nv_bfloat16* __restrict__ x, int T, const float
     }
     const int e = blockIdx.x * kWideRows + row;
     bool ok = r_mbar_wait(bar_w, 0);
+    float4 wreg[NI > 0 ? NI : 1];
+    if constexpr (NI > 0) {
+        const float4* wsrc = reinterpret_cast<const float4*>(ws + (size_t)row * H) + lane;
+#pragma unroll
+        for (int c = 0; c < NI; c++) wreg[c] = wsrc[c * 32];
+    }
     for (int i = 0; i < n_tiles; i++) {
         const int t = tile_of(i);
         const int nt = min(kWideTile, T - t * kWideTile);
@@ -571,10 +574,7 @@ router_fused_wide_kernel(const __nv_bfloat16* __restrict__ x, int T, const float
             const uint2* x1p = xb + (size_t)min(2 * q + 1, nt - 1) * vec;   // a slot past the batch aliases the last valid row
             const float4* wrow = reinterpret_cast<const float4*>(ws + (size_t)row * H) + lane;
             float a0 = 0.0f, a1 = 0.0f;
-            const int n_iter = H >> 7;
-#pragma unroll 4
-            for (int c = 0; c < n_iter; c++) {
-                const float4 w = wrow[c * 32];
+            auto step = [&](const float4& w, int c) {
                 const uint2 u = x0p[c * 32], v = x1p[c * 32];
                 a0 = __fmaf_rn(w.x, __uint_as_float(u.x << 16), a0);
                 a0 = __fmaf_rn(w.y, __uint_as_float(u.x & 0xFFFF0000u), a0);
@@ -584,6 +584,14 @@ router_fused_wide_kernel(const __nv_bfloat16* __restrict__ x, int T, const float
                 a1 = __fmaf_rn(w.y, __uint_as_float(v.x & 0xFFFF0000u), a1);
                 a1 = __fmaf_rn(w.z, __uint_as_float(v.y << 16), a1);
                 a1 = __fmaf_rn(w.w, __uint_as_float(v.y & 0xFFFF0000u), a1);
+            };
+            if constexpr (NI > 0) {
+#pragma unroll
+                for (int c = 0; c < NI; c++) step(wreg[c], c);
+            } else {
+                const int n_iter = H >> 7;
+#pragma unroll 4
+                for (int c = 0; c < n_iter; c++) step(wrow[c * 32], c);
             }
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) {
@@ -709,18 +717,24 @@ int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const
         cudaError_t werr = cudaErrorInvalidValue;
         const dim3 wgrid((unsigned)(cfg.n_expert / kWideRows));
         const size_t wsmem = wide_smem(H, cfg.n_expert);
-        switch (cfg.n_expert / 32) {
-#define DSX_WIDE_CASE(V)                                                                                                          \
-    case V:                                                                                                                       \
-        werr = launch_pdl(router_fused_wide_kernel<V>, wgrid, dim3(kWideWarps * 32), wsmem, stream, x, (int)T, W, bias, (int)H, cfg,   \
-                          logits, selected, weights, chunk, shared_T, hist, offsets, perm, work_items, n_work_items, work_cap,    \
-                          counters, error_word);                                                                                  \
+        const int ni = (H == 4096) ? 32 : (H == 2048 ? 16 : 0);   // widths whose router row lives in registers
+#define DSX_WIDE_LAUNCH(V, N)                                                                                                     \
+    werr = launch_pdl(router_fused_wide_kernel<V, N>, wgrid, dim3(kWideWarps * 32), wsmem, stream, x, (int)T, W, bias, (int)H, cfg,   \
+                      logits, selected, weights, chunk, shared_T, hist, offsets, perm, work_items, n_work_items, work_cap,        \
+                      counters, error_word)
+#define DSX_WIDE_CASE(V)                                                  \
+    case V:                                                               \
+        if (ni == 32) DSX_WIDE_LAUNCH(V, 32);                             \
+        else if (ni == 16) DSX_WIDE_LAUNCH(V, 16);                        \
+        else DSX_WIDE_LAUNCH(V, 0);                                       \
         break;
+        switch (cfg.n_expert / 32) {
             DSX_WIDE_CASE(1) DSX_WIDE_CASE(2) DSX_WIDE_CASE(4) DSX_WIDE_CASE(8)
-#undef DSX_WIDE_CASE
             default:
                 return set_error(DSX_ERR_UNSUPPORTED, "router_fused: n_expert %d not instantiated", cfg.n_expert);
         }
+#undef DSX_WIDE_CASE
+#undef DSX_WIDE_LAUNCH
         DSX_CUDA(werr);
         DSX_LAUNCHED();
         return DSX_OK;
@@ -755,10 +769,12 @@ int router_configure() {
     DSX_FUSED_CFG(1) DSX_FUSED_CFG(2) DSX_FUSED_CFG(4) DSX_FUSED_CFG(8)
 #undef DSX_FUSED_CFG
     DSX_CUDA(cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileStages * kTileStageBytes));
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    DSX_CUDA(cudaFuncSetAttribute(router_fused_wide_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+#define DSX_WIDE_CFG(V)                                                                                                        \
+    DSX_CUDA((cudaFuncSetAttribute(router_fused_wide_kernel<V, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));  \
+    DSX_CUDA((cudaFuncSetAttribute(router_fused_wide_kernel<V, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024))); \
+    DSX_CUDA((cudaFuncSetAttribute(router_fused_wide_kernel<V, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
+    DSX_WIDE_CFG(1) DSX_WIDE_CFG(2) DSX_WIDE_CFG(4) DSX_WIDE_CFG(8)
+#undef DSX_WIDE_CFG
     int dev = 0;
     DSX_CUDA(cudaGetDevice(&dev));
     DSX_CUDA(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
