@@ -85,9 +85,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
     for (uint32_t i = 0; i < kSpinLimit; i++) {
         if (mbar_try(bar, parity)) return true;
-#ifdef DSX_X_BACKOFF
-        __nanosleep(DSX_X_BACKOFF);
-#endif
         if ((i & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1u;
@@ -426,9 +423,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 if (!ok) break;
                 const uint8_t* raw = smem + C::kSmemRaw + sr * C::kRawBytes;
                 uint8_t* A = smem + C::kSmemA + sa * kABytes;
-#ifdef DSX_X_NOCONV
-                if (true) {} else
-#endif
                 if constexpr (FMT == DSX_FMT_MXFP4) {
                     // both sub-tiles of this warp: loads first, then the conversions
                     uint4 wq[2];
@@ -492,9 +486,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                         *reinterpret_cast<uint4*>(arow + off + 1024u) = r1;
                     }
                 }
-#ifndef DSX_X_NOFENCE
                 fence_proxy_async();
-#endif
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(bar(AB_FULL + sa));
