@@ -360,6 +360,36 @@ def run_single_gpu(args):
                   "tokens": Ts, "layers": n_layers, "steps": n_s, "ms_per_step": ms_s, "value": Ts * n_layers / (ms_s * 1e-3),
                   "unit": UNIT + " (tokens x layers)"}
         layer_s.close()
+    # the steps either side of the layer (RMSNorm producing its bf16 input, residual mix consuming its output)
+    glue = None
+    if not args.no_prefill:
+        Tg, n_hc = 16384, 4   # 268 MB of f32 rows (norm) and 1 GB of residual streams (mix): every launch misses L2
+        xg = torch.randn((Tg, H), device="cuda", dtype=torch.float32)
+        wg = torch.ones((H,), device="cuda", dtype=torch.float32)
+        rh = torch.randn((Tg, n_hc, H), device="cuda", dtype=torch.float32)
+        post = torch.randn((Tg, n_hc), device="cuda", dtype=torch.float32)
+        comb = torch.randn((Tg, n_hc * n_hc), device="cuda", dtype=torch.float32)
+        bo = torch.randn((Tg, H), device="cuda", dtype=torch.float32).to(torch.bfloat16)
+
+        def timed(fn, reps=6):
+            with torch.cuda.stream(stream):
+                for i in range(3):
+                    fn()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for i in range(reps):
+                    fn()
+                b.record(stream)
+                stream.synchronize()
+            return a.elapsed_time(b) / reps
+
+        ms_n = timed(lambda: moe.RmsNorm.launch_weighted_batched(xg, wg))
+        ms_h = timed(lambda: moe.HcPost.launch_batched(bo, rh, post, comb))
+        by_n, by_h = Tg * H * 6, Tg * H * (2 + 4 * n_hc * 2)
+        glue = {"workload": "16384 rows of 4096 columns, launches back to back (each streams more than L2 holds)",
+                "rms_norm_rows": {"us": ms_n * 1e3, "gbs": by_n / (ms_n * 1e-3) / 1e9, "frac_of_hbm_peak": by_n / (ms_n * 1e-3) / 1e9 / hbm_peak},
+                "hc_post": {"us": ms_h * 1e3, "gbs": by_h / (ms_h * 1e-3) / 1e9, "frac_of_hbm_peak": by_h / (ms_h * 1e-3) / 1e9 / hbm_peak}}
+        del xg, rh
     # configuration 3: Q8_0 experts, 2048 tokens, Zipf(1.1)-skewed expert popularity
     q8 = None
     if not args.no_q8:
@@ -441,6 +471,7 @@ def run_single_gpu(args):
         "series": series,
         "prefill": prefill,
         "stack_one_gpu": stack1,
+        "glue": glue,
         "q8_0_zipf": q8,
     }
     print(json.dumps(line))

@@ -1,0 +1,198 @@
+// The two steps either side of the MoE path: the RMSNorm that produces the layer's input rows and
+// the residual mix that consumes its output.
+//
+// Reference counterparts (paths relative to the deepstrix repository):
+//   crates/v4flash-kernels/kernels/rms_norm.hip:12-84   rms_norm_weighted[_batched]
+//       out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i]; thread t of 256 sums x[t + 256 j]^2 in
+//       double, the 256 partials are cast to f32 and folded by a shared-memory tree (stride 128..1)
+//       wrapper RmsNorm::launch_weighted_batched, crates/v4flash-kernels/src/rms_norm.rs:161-205
+//   crates/v4flash-kernels/kernels/hc_post.hip:15-68    hc_post[_batched]
+//       out_hc[dst, d] = block_out[d] * post[dst] + sum_src comb[dst + src * n_hc] * residual_hc[src, d]
+//       wrapper crates/v4flash-kernels/src/head.rs:267-372; call het/forward_layer.rs:3130-3152
+//
+// Both keep the reference's order of operations.  Where the reference's compiler is free to choose
+// (rsqrtf, contraction of a * b + c) this file fixes one choice, the same as the CPU oracle:
+// 1 / sqrt with IEEE division and square root, and a fused multiply-add per mixing term.
+// Here the norm writes the bf16 rows the MoE layer reads (and, optionally, the f32 rows as the
+// reference does), and the mix reads the layer's bf16 output directly: one pass over HBM each.
+#include "dsx_common.cuh"
+
+namespace dsx {
+namespace {
+
+constexpr int kNormThreads = 256;
+
+// kNormRegs: values a thread keeps in registers (rows up to 256 * kNormRegs columns are read once; 0 = re-read
+// the row).  Instantiated for a few sizes so that a 4096-column row does not pay the registers of an 8192-column one.
+template <int kNormRegs>
+__global__ void __launch_bounds__(kNormThreads)
+rms_norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight, int n, float eps, float* __restrict__ out_f32,
+                     __nv_bfloat16* __restrict__ out_bf16) {
+    __shared__ float sdata[kNormThreads];
+    const int tid = threadIdx.x;
+    const float* xb = x + (int64_t)blockIdx.x * n;
+    constexpr bool in_regs = kNormRegs > 0;
+    float v[kNormRegs > 0 ? kNormRegs : 1];
+    double partial = 0.0;
+    if constexpr (in_regs) {
+#pragma unroll
+        for (int j = 0; j < kNormRegs; j++) {
+            const int i = tid + kNormThreads * j;
+            v[j] = i < n ? xb[i] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < kNormRegs; j++)
+            if (tid + kNormThreads * j < n) partial += (double)v[j] * (double)v[j];
+    } else {
+        for (int i = tid; i < n; i += kNormThreads) {
+            const float a = xb[i];
+            partial += (double)a * (double)a;
+        }
+    }
+    // the reference's tree: sdata[t] += sdata[t + stride] for stride 128, 64, ..., 1.  Strides 128..32 go
+    // through shared memory; 16..1 are the same additions as shuffles inside the first warp.
+    sdata[tid] = (float)partial;
+    __syncthreads();
+    if (tid < 128) sdata[tid] = __fadd_rn(sdata[tid], sdata[tid + 128]);
+    __syncthreads();
+    if (tid < 64) sdata[tid] = __fadd_rn(sdata[tid], sdata[tid + 64]);
+    __syncthreads();
+    if (tid < 32) {
+        float s = __fadd_rn(sdata[tid], sdata[tid + 32]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, s, off));
+        if (tid == 0) sdata[0] = s;
+    }
+    __syncthreads();
+    const float mean_sq = __fdiv_rn(sdata[0], (float)n);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
+    auto emit = [&](int i, float a) {
+        const float r = __fmul_rn(__fmul_rn(a, scale), weight[i]);
+        if (out_f32 != nullptr) out_f32[(int64_t)blockIdx.x * n + i] = r;
+        if (out_bf16 != nullptr) out_bf16[(int64_t)blockIdx.x * n + i] = __float2bfloat16_rn(r);
+    };
+    if constexpr (in_regs) {
+#pragma unroll
+        for (int j = 0; j < kNormRegs; j++) {
+            const int i = tid + kNormThreads * j;
+            if (i < n) emit(i, v[j]);
+        }
+    } else {
+        for (int i = tid; i < n; i += kNormThreads) emit(i, xb[i]);
+    }
+}
+
+// One thread per (token, destination stream, column): any number of streams.
+template <bool BF16_IN>
+__global__ void __launch_bounds__(256)
+hc_post_kernel(const void* __restrict__ block_out, const float* __restrict__ residual_hc, const float* __restrict__ post,
+               const float* __restrict__ comb, int n_embd, int n_hc, float* __restrict__ out_hc) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= n_embd) return;
+    const int dst = blockIdx.y;
+    const int64_t b = blockIdx.z;
+    float bo;
+    if (BF16_IN) bo = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(block_out)[b * n_embd + d]);
+    else bo = reinterpret_cast<const float*>(block_out)[b * n_embd + d];
+    const float* rh = residual_hc + b * n_hc * n_embd;
+    const float* cb = comb + b * n_hc * n_hc;
+    float acc = __fmul_rn(bo, post[b * n_hc + dst]);
+    for (int src = 0; src < n_hc; src++) acc = __fmaf_rn(cb[dst + src * n_hc], rh[(int64_t)src * n_embd + d], acc);
+    out_hc[(b * n_hc + dst) * n_embd + d] = acc;
+}
+
+// The reference's four streams: one thread per (token, 4 columns) reads every residual stream once
+// (16-byte loads) and writes all four destinations.  Same operations per element as above.
+template <bool BF16_IN>
+__global__ void __launch_bounds__(256)
+hc_post4_kernel(const void* __restrict__ block_out, const float* __restrict__ residual_hc, const float* __restrict__ post,
+                const float* __restrict__ comb, int n_embd, int64_t n_tok, float* __restrict__ out_hc) {
+    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_row = n_embd >> 2;
+    if (gid >= n_tok * per_row) return;
+    const int64_t b = gid / per_row;
+    const int c = (int)(gid - b * per_row);
+    float bo[4];
+    if (BF16_IN) {
+        const uint2 v = *(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(block_out) + b * n_embd) + c);
+        bo[0] = __uint_as_float(v.x << 16); bo[1] = __uint_as_float(v.x & 0xFFFF0000u);
+        bo[2] = __uint_as_float(v.y << 16); bo[3] = __uint_as_float(v.y & 0xFFFF0000u);
+    } else {
+        const float4 v = *(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(block_out) + b * n_embd) + c);
+        bo[0] = v.x; bo[1] = v.y; bo[2] = v.z; bo[3] = v.w;
+    }
+    float4 r[4];
+#pragma unroll
+    for (int src = 0; src < 4; src++) r[src] = *(reinterpret_cast<const float4*>(residual_hc + (b * 4 + src) * n_embd) + c);
+    const float* cb = comb + b * 16;
+#pragma unroll
+    for (int dst = 0; dst < 4; dst++) {
+        const float p = post[b * 4 + dst];
+        float a[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) a[i] = __fmul_rn(bo[i], p);
+#pragma unroll
+        for (int src = 0; src < 4; src++) {
+            const float k = cb[dst + src * 4];
+            a[0] = __fmaf_rn(k, r[src].x, a[0]);
+            a[1] = __fmaf_rn(k, r[src].y, a[1]);
+            a[2] = __fmaf_rn(k, r[src].z, a[2]);
+            a[3] = __fmaf_rn(k, r[src].w, a[3]);
+        }
+        *(reinterpret_cast<float4*>(out_hc + (b * 4 + dst) * n_embd) + c) = make_float4(a[0], a[1], a[2], a[3]);
+    }
+}
+
+}  // namespace
+}  // namespace dsx
+
+using namespace dsx;
+
+extern "C" {
+
+int dsx_rms_norm_rows(const float* x, const float* weight, int64_t T, int64_t n, float eps, float* out_f32, void* out_bf16,
+                      dsx_stream_t stream) {
+    DSX_REQUIRE(T >= 0 && n >= 1 && n <= (1 << 30), "rms_norm_rows: %lld rows of %lld columns", (long long)T, (long long)n);
+    if (T == 0) return DSX_OK;
+    DSX_REQUIRE(x && weight && (out_f32 || out_bf16), "rms_norm_rows: null argument");
+    DSX_REQUIRE(T <= 0x7FFFFFFF, "rms_norm_rows: too many rows");
+    const int per_thread = (int)((n + kNormThreads - 1) / kNormThreads);
+#define DSX_NORM_LAUNCH(R) rms_norm_rows_kernel<R><<<(unsigned)T, kNormThreads, 0, (cudaStream_t)stream>>>(x, weight, (int)n, eps, out_f32, (__nv_bfloat16*)out_bf16)
+    if (per_thread <= 8) DSX_NORM_LAUNCH(8);
+    else if (per_thread <= 16) DSX_NORM_LAUNCH(16);
+    else if (per_thread <= 24) DSX_NORM_LAUNCH(24);
+    else if (per_thread <= 32) DSX_NORM_LAUNCH(32);
+    else DSX_NORM_LAUNCH(0);
+#undef DSX_NORM_LAUNCH
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+int dsx_hc_post(const void* block_out, int block_out_is_bf16, const float* residual_hc, const float* post, const float* comb, int64_t T,
+                int64_t n_embd, int n_hc, float* out_hc, dsx_stream_t stream) {
+    DSX_REQUIRE(T >= 0 && n_embd >= 1 && n_hc >= 1 && n_hc <= 65535, "hc_post: %lld tokens, %lld columns, %d streams", (long long)T,
+                (long long)n_embd, n_hc);
+    if (T == 0) return DSX_OK;
+    DSX_REQUIRE(block_out && residual_hc && post && comb && out_hc, "hc_post: null argument");
+    const bool vec = n_hc == 4 && n_embd % 4 == 0 && (((uintptr_t)block_out | (uintptr_t)residual_hc | (uintptr_t)out_hc) & 15) == 0;
+    if (vec) {
+        const int64_t nthr = T * (n_embd / 4);
+        const unsigned blocks = (unsigned)((nthr + 255) / 256);
+        if (block_out_is_bf16)
+            hc_post4_kernel<true><<<blocks, 256, 0, (cudaStream_t)stream>>>(block_out, residual_hc, post, comb, (int)n_embd, T, out_hc);
+        else
+            hc_post4_kernel<false><<<blocks, 256, 0, (cudaStream_t)stream>>>(block_out, residual_hc, post, comb, (int)n_embd, T, out_hc);
+        DSX_LAUNCHED();
+        return DSX_OK;
+    }
+    DSX_REQUIRE(T <= 65535, "hc_post: at most 65535 tokens per call unless n_hc == 4 with 16-byte aligned rows");
+    const dim3 grid((unsigned)((n_embd + 255) / 256), (unsigned)n_hc, (unsigned)T);
+    if (block_out_is_bf16)
+        hc_post_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(block_out, residual_hc, post, comb, (int)n_embd, n_hc, out_hc);
+    else
+        hc_post_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(block_out, residual_hc, post, comb, (int)n_embd, n_hc, out_hc);
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+}  // extern "C"

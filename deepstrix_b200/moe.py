@@ -89,6 +89,37 @@ def bytes_per_expert(fmt: int, k: int, rows: int) -> int:
 
 
 # --------------------------------------------------------------------------
+class RmsNorm:
+    """``RmsNorm::launch_weighted_batched`` (src/rms_norm.rs:161-205): rows of f32 -> normalised rows,
+    as the bf16 input of the MoE layer and / or as f32."""
+
+    @staticmethod
+    def launch_weighted_batched(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, want_f32: bool = False, want_bf16: bool = True):
+        assert x.dtype == torch.float32 and weight.dtype == torch.float32 and x.is_contiguous() and weight.is_contiguous()
+        T, n = x.shape
+        assert weight.numel() == n
+        o32 = torch.empty_like(x) if want_f32 else None
+        o16 = torch.empty((T, n), dtype=torch.bfloat16, device=x.device) if want_bf16 else None
+        _check(lib().dsx_rms_norm_rows(_dptr(x), _dptr(weight), C.c_int64(T), C.c_int64(n), C.c_float(eps), _dptr(o32), _dptr(o16), _stream()))
+        return o32, o16
+
+
+class HcPost:
+    """``hc_post_batched`` (src/head.rs:267-372): mixes the layer's output into the residual streams."""
+
+    @staticmethod
+    def launch_batched(block_out: torch.Tensor, residual_hc: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+        T, n_hc, n = residual_hc.shape
+        assert block_out.shape == (T, n) and block_out.dtype in (torch.bfloat16, torch.float32) and block_out.is_contiguous()
+        assert residual_hc.dtype == torch.float32 and residual_hc.is_contiguous()
+        assert post.shape == (T, n_hc) and comb.numel() == T * n_hc * n_hc and post.is_contiguous() and comb.is_contiguous()
+        out = torch.empty_like(residual_hc)
+        _check(lib().dsx_hc_post(_dptr(block_out), 1 if block_out.dtype == torch.bfloat16 else 0, _dptr(residual_hc), _dptr(post), _dptr(comb),
+                                 C.c_int64(T), C.c_int64(n), n_hc, _dptr(out), _stream()))
+        return out
+
+
+# --------------------------------------------------------------------------
 class RoutedExpertWeights:
     """Expert store: n_slots experts (gate, up, down) resident in HBM in the
     library's tile layout."""

@@ -305,6 +305,22 @@ DSX_API int dsx_moe_layer_stage_ms(dsx_moe_layer* layer, float* ms);
  * reset (per-thread launch audit, crates/v4flash-hip/src/module.rs:97-131). */
 DSX_API uint64_t dsx_launch_count(int reset);
 
+/* --- The steps either side of the layer -------------------------------------
+ * RmsNorm::launch_weighted_batched (src/rms_norm.rs:161-205; kernels/rms_norm.hip:48-84):
+ *   out[t, i] = x[t, i] * (1 / sqrt(mean_i(x[t, i]^2) + eps)) * weight[i]
+ * with the reference's summation order (thread j of 256 adds x[j + 256 m]^2 in double, the 256
+ * partials are folded as f32 by a stride-128..1 tree).  Writes the bf16 rows the MoE layer reads
+ * (out_bf16) and / or the f32 rows the reference writes (out_f32); either may be NULL. */
+DSX_API int dsx_rms_norm_rows(const float* x, const float* weight, int64_t T, int64_t n, float eps, float* out_f32,
+                              void* out_bf16, dsx_stream_t stream);
+/* hc_post_batched (kernels/hc_post.hip:36-68; src/head.rs:267-372; het/forward_layer.rs:3130-3152):
+ *   out_hc[t, dst, d] = block_out[t, d] * post[t, dst] + sum_src comb[t, dst + src * n_hc] * residual_hc[t, src, d]
+ * (one fused multiply-add per src, in src order).  block_out is the layer's bf16 output
+ * (block_out_is_bf16 != 0) or f32 rows.  n_hc == 4 with 16-byte aligned rows takes a vectorised kernel;
+ * other shapes are limited to 65535 tokens per call. */
+DSX_API int dsx_hc_post(const void* block_out, int block_out_is_bf16, const float* residual_hc, const float* post,
+                        const float* comb, int64_t T, int64_t n_embd, int n_hc, float* out_hc, dsx_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * 3. Expert-parallel exchange over peer memory
  *

@@ -484,6 +484,42 @@ DSXO_API void dsxo_router_topk(const float* logits, const float* bias, int64_t T
     dsxo_router_topk_ex(logits, bias, T, n_expert, n_used, n_group, topk_group, score_fn, scale, eps, selected, weights, 0, NULL, NULL, NULL);
 }
 
+/* RMSNorm of rows (kernels/rms_norm.hip:48-84): partial j (of 256) = sum over m of x[j + 256 m]^2 in
+ * double, cast to f32; the 256 partials fold by a stride-128..1 tree; scale = 1 / sqrt(mean + eps);
+ * out = (x * scale) * weight.  The reference's rsqrtf is an approximation of the same value. */
+DSXO_API void dsxo_rms_norm_rows(const float* x, const float* weight, int64_t T, int64_t n, float eps, float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < T; t++) {
+        const float* xb = x + t * n;
+        float sd[256];
+        for (int j = 0; j < 256; j++) {
+            double partial = 0.0;
+            for (int64_t i = j; i < n; i += 256) partial += (double)xb[i] * (double)xb[i];
+            sd[j] = (float)partial;
+        }
+        for (int stride = 128; stride > 0; stride >>= 1)
+            for (int j = 0; j < stride; j++) sd[j] = sd[j] + sd[j + stride];
+        const float mean_sq = sd[0] / (float)n;
+        const float scale = 1.0f / sqrtf(mean_sq + eps);
+        for (int64_t i = 0; i < n; i++) out[t * n + i] = (xb[i] * scale) * weight[i];
+    }
+}
+
+/* Residual mix (kernels/hc_post.hip:36-68): acc = block_out * post[dst]; acc = fma(comb[dst + src*n_hc],
+ * residual[src], acc) for src ascending. */
+DSXO_API void dsxo_hc_post(const float* block_out, const float* residual_hc, const float* post, const float* comb,
+                           int64_t T, int64_t n_embd, int n_hc, float* out_hc) {
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < T; t++)
+        for (int dst = 0; dst < n_hc; dst++)
+            for (int64_t d = 0; d < n_embd; d++) {
+                float acc = block_out[t * n_embd + d] * post[t * n_hc + dst];
+                for (int src = 0; src < n_hc; src++)
+                    acc = fmaf(comb[t * n_hc * n_hc + dst + src * n_hc], residual_hc[(t * n_hc + src) * n_embd + d], acc);
+                out_hc[(t * n_hc + dst) * n_embd + d] = acc;
+            }
+}
+
 /* Router logits: x[T,H] (f32) . W[E,H]^T, f32 inputs, accumulated in double
  * (kernels/f16_matvec.hip:26-45 accumulates f32 per lane then a wave
  * reduction; any f32 association is within 1e-6 of this). */

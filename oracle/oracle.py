@@ -246,6 +246,24 @@ def router_topk_ex(logits, bias, n_used, n_alt, n_group=1, topk_group=1, score_f
     return sel, w, alts[:, :n_alt], alt_w[:, :n_alt], rng
 
 
+def rms_norm_rows(x, weight, eps=1e-6):
+    x = _c(x, np.float32)
+    w = _c(weight, np.float32)
+    T, n = x.shape
+    out = np.empty((T, n), np.float32)
+    lib().dsxo_rms_norm_rows(_p(x), _p(w), C.c_int64(T), C.c_int64(n), C.c_float(eps), _p(out))
+    return out
+
+
+def hc_post(block_out, residual_hc, post, comb):
+    bo = _c(block_out, np.float32)
+    rh = _c(residual_hc, np.float32)
+    T, n_hc, n = rh.shape
+    out = np.empty((T, n_hc, n), np.float32)
+    lib().dsxo_hc_post(_p(bo), _p(rh), _p(_c(post, np.float32)), _p(_c(comb, np.float32)), C.c_int64(T), C.c_int64(n), C.c_int(n_hc), _p(out))
+    return out
+
+
 def group_build(selected: np.ndarray, n_expert: int):
     selected = _c(selected, np.int32)
     T, k = selected.shape

@@ -418,6 +418,38 @@ def test_layer_v41_widths(torch_cuda, moe, oracle, T):
     layer.close()
 
 
+@pytest.mark.parametrize("T,n", [(1, 4096), (37, 5120), (3, 512), (2, 10000)])
+def test_rms_norm_rows_bitexact(torch_cuda, moe, oracle, T, n):
+    """The norm that produces the layer's input rows: f32 result bit-exact with the oracle's restatement of
+    rms_norm.hip (double partials per thread, f32 tree), bf16 result = that value rounded to nearest even."""
+    rng = np.random.Generator(np.random.PCG64(900 + n))
+    x = (rng.standard_normal((T, n)) * 3.0).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    o32, o16 = moe.RmsNorm.launch_weighted_batched(torch_cuda.from_numpy(x).cuda(), torch_cuda.from_numpy(w).cuda(), 1e-6, want_f32=True)
+    ref = oracle.rms_norm_rows(x, w, 1e-6)
+    assert np.array_equal(o32.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    want16 = torch_cuda.from_numpy(ref).to(torch_cuda.bfloat16)
+    assert torch_cuda.equal(o16.cpu(), want16)
+
+
+@pytest.mark.parametrize("bf16_in,n_hc", [(True, 4), (False, 4), (True, 3)])
+def test_hc_post_bitexact(torch_cuda, moe, oracle, bf16_in, n_hc):
+    """The residual mix that consumes the layer's output (hc_post.hip), reading it as bf16 or f32."""
+    rng = np.random.Generator(np.random.PCG64(911))
+    T, n = 9, 4096
+    bo = rng.standard_normal((T, n)).astype(np.float32)
+    rh = rng.standard_normal((T, n_hc, n)).astype(np.float32)
+    post = rng.standard_normal((T, n_hc)).astype(np.float32)
+    comb = rng.standard_normal((T, n_hc * n_hc)).astype(np.float32)
+    bo_t = torch_cuda.from_numpy(bo).cuda()
+    if bf16_in:
+        bo_t = bo_t.to(torch_cuda.bfloat16)
+        bo = bo_t.float().cpu().numpy()
+    out = moe.HcPost.launch_batched(bo_t, torch_cuda.from_numpy(rh).cuda(), torch_cuda.from_numpy(post).cuda(), torch_cuda.from_numpy(comb).cuda())
+    ref = oracle.hc_post(bo, rh, post, comb)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+
+
 def test_empty_batches(torch_cuda, moe, oracle):
     """Zero tokens is a valid call everywhere (the reference's wrappers return early on an empty batch,
     src/moe_group_builder.rs:144-150): nothing is launched, nothing is written, no error."""

@@ -222,3 +222,21 @@ def test_moe_layer_slot_order_and_reference_int_path(oracle):
                                           (w["down"][0][e], w["down"][1][e]), cfg.hidden, cfg.ffn, x[0], 0.3)
     d = np.abs(ref_int - partials[1]) / np.abs(partials[1]).max()
     assert d.max() < 5e-2 and d.mean() < 5e-3
+
+
+def test_glue_restatements_match_plain_formulas(oracle):
+    """RMSNorm and the residual mix: the order-preserving restatements agree with the textbook formulas
+    in float64 (no golden vector exists for these two in the reference: parity unpinned beyond this)."""
+    rng = np.random.Generator(np.random.PCG64(31))
+    x = (rng.standard_normal((6, 5120)) * 2.0).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(5120)).astype(np.float32)
+    got = oracle.rms_norm_rows(x, w, 1e-6)
+    ref = x / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-6) * w
+    assert np.abs(got - ref).max() < 2e-6 * np.abs(ref).max()
+    bo = rng.standard_normal((3, 64)).astype(np.float32)
+    rh = rng.standard_normal((3, 4, 64)).astype(np.float32)
+    post = rng.standard_normal((3, 4)).astype(np.float32)
+    comb = rng.standard_normal((3, 16)).astype(np.float32)
+    got = oracle.hc_post(bo, rh, post, comb)
+    ref = bo[:, None, :].astype(np.float64) * post[:, :, None] + np.einsum("tsd,tsk->tkd", rh.astype(np.float64), comb.reshape(3, 4, 4))
+    assert np.abs(got - ref).max() < 1e-5
