@@ -15,7 +15,10 @@
  *   - scripts/v41_oracle/kernel.py (dequant_fp4 / act_quant / fp4_gemm outputs)
  * Parts with no counterpart in the reference (group-limited routing, Q8_0
  * routed experts, bf16 activations) are "parity unpinned": defined here under
- * the reference's conventions.
+ * the reference's conventions.  So are the router's alternatives / score range
+ * and the two steps either side of the layer (RMSNorm, residual mix): the
+ * reference has kernels for them but no known-answer vector, so they are
+ * restated from the kernel text alone.
  *
  * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (see Makefile).
  * -ffp-contract=off matters: the router arithmetic must round exactly like the
