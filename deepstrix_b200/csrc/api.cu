@@ -363,6 +363,14 @@ int dsx_router_topk_ex(const float* logits, const float* bias, int64_t T, const 
     DSX_REQUIRE(alts != nullptr || alt_w == nullptr, "router_topk_ex: alt_w without alts");
     return launch_router_topk(logits, bias, T, *cfg, selected, weights, n_alt, alts, alt_w, range_out, (cudaStream_t)stream);
 }
+int dsx_router_topk_prior(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg, int32_t* selected,
+                          float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, const float* prior, int n_protect,
+                          int prior_dry, int32_t* orig_sel, dsx_stream_t stream) {
+    DSX_REQUIRE(logits && cfg && selected && weights && prior && T >= 0, "router_topk_prior: null argument");
+    DSX_REQUIRE(alts != nullptr || alt_w == nullptr, "router_topk_prior: alt_w without alts");
+    return launch_router_topk_prior(logits, bias, T, *cfg, selected, weights, n_alt, alts, alt_w, range_out, prior, n_protect, prior_dry,
+                                    orig_sel, (cudaStream_t)stream);
+}
 
 uint32_t dsx_wi_upper_bound(uint64_t members, uint32_t groups, uint32_t chunk, uint64_t cap) {
     const uint64_t m = members, g = std::min<uint64_t>(m, groups), c = chunk ? chunk : 1;

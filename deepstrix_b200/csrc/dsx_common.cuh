@@ -193,6 +193,9 @@ int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int 
                          cudaStream_t stream);
 int launch_router_topk(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg,
                        int32_t* selected, float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, cudaStream_t stream);
+int launch_router_topk_prior(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg, int32_t* selected,
+                             float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, const float* prior, int n_protect,
+                             int prior_dry, int32_t* orig_sel, cudaStream_t stream);
 int router_configure();
 bool router_fused_ok(int64_t T, const dsx_router_config& cfg, int64_t H);
 int launch_router_fused(const __nv_bfloat16* x, int64_t T, const float* W, const float* bias, int64_t H, const dsx_router_config& cfg,

@@ -317,6 +317,107 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
                         range_out ? range_out + t : nullptr);
 }
 
+// ---- Top-k with the reference's cache prior (router_topk_par.hip:82-99,173-210): a per-expert prior is
+// added to the SELECTION score; the first n_protect picks of the plain ranking are always kept, the
+// remaining slots and the alternatives are the argmax of score + prior; weights still come from the
+// unbiased probabilities of the emitted set.  orig_sel receives the plain top-n_used.  With
+// prior_dry the roles swap: the plain picks are emitted (and weighted) and orig_sel carries what
+// the prior would have chosen.  One warp per token; no group limit (the reference has none here).
+template <int VPL>
+__device__ __forceinline__ int prior_argmax_round(uint32_t (&ob)[VPL], int lane) {
+    uint32_t best = ob[0];
+    int bj = 0;
+#pragma unroll
+    for (int j = 1; j < VPL; j++)
+        if (ob[j] > best) { best = ob[j]; bj = j; }   // `>` keeps the lower j on ties
+    const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, best);
+    const uint32_t cand = (best == mx) ? (uint32_t)(lane * VPL + bj) : 0xFFFFFFFFu;
+    const int e = (int)__reduce_min_sync(0xFFFFFFFFu, cand);
+#pragma unroll
+    for (int j = 0; j < VPL; j++)
+        ob[j] = (cand == (uint32_t)e && bj == j) ? 0u : ob[j];
+    return e;
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(kTopkWarps * 32)
+router_topk_prior_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, dsx_router_config cfg,
+                         int32_t* __restrict__ selected, float* __restrict__ weights, int n_alt, int32_t* __restrict__ alts,
+                         float* __restrict__ alt_w, float* __restrict__ range_out, const float* __restrict__ prior, int n_protect,
+                         int prior_dry, int32_t* __restrict__ orig_sel) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * kTopkWarps + warp;
+    if (t >= T) return;
+    const float* row = logits + t * (VPL * 32);
+    float p[VPL], s[VPL];
+    uint32_t ob[VPL], ob2[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; j++) {
+        const int e = lane * VPL + j;
+        p[j] = router_prob(row[e], cfg.score_fn);
+        s[j] = bias ? __fadd_rn(p[j], bias[e]) : p[j];
+        ob[j] = ordered_bits(__fadd_rn(s[j], 0.0f));
+        ob2[j] = ordered_bits(__fadd_rn(__fadd_rn(s[j], prior[e]), 0.0f));
+    }
+    if (range_out != nullptr) {
+        float mx = s[0], mn = s[0];
+#pragma unroll
+        for (int j = 1; j < VPL; j++) { mx = fmaxf(mx, s[j]); mn = fminf(mn, s[j]); }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+            mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, off));
+        }
+        if (lane == 0) range_out[t] = __fsub_rn(mx, mn);
+    }
+    // lane r keeps rank r of both rankings
+    int my_orig = -1, my_sel = -1;
+#pragma unroll 1
+    for (int r = 0; r < cfg.n_used; r++) {   // the ORIGINAL top-n_used, on the plain scores
+        const int e = prior_argmax_round<VPL>(ob, lane);
+        if (lane == r) my_orig = e;
+    }
+#pragma unroll 1
+    for (int r = 0; r < n_protect; r++) {    // protected picks stay and leave the boosted pool
+        const int e = __shfl_sync(0xFFFFFFFFu, my_orig, r);
+        if (lane == r) my_sel = e;
+#pragma unroll
+        for (int j = 0; j < VPL; j++)
+            ob2[j] = (lane * VPL + j == e) ? 0u : ob2[j];
+    }
+#pragma unroll 1
+    for (int r = n_protect; r < cfg.n_used + n_alt; r++) {
+        const int e = prior_argmax_round<VPL>(ob2, lane);
+        if (lane == r) my_sel = e;
+    }
+    // dry run: emit the plain picks, report the prior's
+    int emit = my_sel, other = my_orig;
+    if (prior_dry && lane < cfg.n_used) { emit = my_orig; other = my_sel; }
+    // unbiased probability of this lane's emitted expert: from the lane that owns it
+    float my_p = 0.0f;
+    for (int r = 0; r < cfg.n_used + n_alt; r++) {
+        const int e = __shfl_sync(0xFFFFFFFFu, emit, r);
+        float pv = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPL; j++)
+            if (lane * VPL + j == e) pv = p[j];
+        pv = __shfl_sync(0xFFFFFFFFu, pv, (e >= 0 ? e : 0) / VPL);
+        if (lane == r) my_p = (e >= 0) ? pv : 0.0f;
+    }
+    float sum = 0.0f;
+    for (int r = 0; r < cfg.n_used; r++) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, my_p, r));
+    if (sum < cfg.weight_eps) sum = cfg.weight_eps;
+    const float wv = __fmul_rn(__fdiv_rn(my_p, sum), cfg.route_scale);
+    if (lane < cfg.n_used) {
+        selected[t * cfg.n_used + lane] = emit;
+        weights[t * cfg.n_used + lane] = wv;
+        if (orig_sel != nullptr) orig_sel[t * cfg.n_used + lane] = other;
+    } else if (lane < cfg.n_used + n_alt) {
+        alts[t * n_alt + lane - cfg.n_used] = emit;
+        if (alt_w != nullptr) alt_w[t * n_alt + lane - cfg.n_used] = wv;
+    }
+}
+
 // ---- Decode router in ONE launch (T <= 64, E <= 256): logits, top-k and the group build.
 //
 // Grid (E/4, token tiles), 8 warps.  A tile is 2*NT tokens (NT = 1, 2 or 4, chosen from T).  The
@@ -805,6 +906,34 @@ int launch_router_topk(const float* logits, const float* bias, int64_t T, const 
 #undef DSX_TOPK_CASE
         default:
             return set_error(DSX_ERR_UNSUPPORTED, "router_topk: n_expert %d not instantiated", cfg.n_expert);
+    }
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+int launch_router_topk_prior(const float* logits, const float* bias, int64_t T, const dsx_router_config& cfg, int32_t* selected,
+                             float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, const float* prior, int n_protect,
+                             int prior_dry, int32_t* orig_sel, cudaStream_t stream) {
+    if (alts == nullptr) n_alt = 0;
+    DSX_REQUIRE(cfg.n_expert > 0 && cfg.n_expert % 32 == 0 && cfg.n_expert <= 512, "router_topk_prior: n_expert %d must be a multiple of 32, at most 512",
+                cfg.n_expert);
+    DSX_REQUIRE(cfg.n_used >= 1 && n_alt >= 0 && cfg.n_used + n_alt <= 32 && cfg.n_used + n_alt <= cfg.n_expert,
+                "router_topk_prior: %d picks + %d alternatives", cfg.n_used, n_alt);
+    DSX_REQUIRE(cfg.n_group <= 1, "router_topk_prior: the cache prior is defined without a group limit");
+    DSX_REQUIRE(n_protect >= 0 && n_protect <= cfg.n_used, "router_topk_prior: n_protect %d of %d picks", n_protect, cfg.n_used);
+    if (T == 0) return DSX_OK;
+    const unsigned grid = (unsigned)((T + kTopkWarps - 1) / kTopkWarps);
+    switch (cfg.n_expert / 32) {
+#define DSX_PRIOR_CASE(V)                                                                                                         \
+    case V:                                                                                                                       \
+        router_topk_prior_kernel<V><<<grid, kTopkWarps * 32, 0, stream>>>(logits, bias, T, cfg, selected, weights, n_alt, alts, alt_w, \
+                                                                          range_out, prior, n_protect, prior_dry, orig_sel);      \
+        break;
+        DSX_PRIOR_CASE(1) DSX_PRIOR_CASE(2) DSX_PRIOR_CASE(3) DSX_PRIOR_CASE(4) DSX_PRIOR_CASE(6) DSX_PRIOR_CASE(8)
+        DSX_PRIOR_CASE(12) DSX_PRIOR_CASE(16)
+#undef DSX_PRIOR_CASE
+        default:
+            return set_error(DSX_ERR_UNSUPPORTED, "router_topk_prior: n_expert %d not instantiated", cfg.n_expert);
     }
     DSX_LAUNCHED();
     return DSX_OK;

@@ -234,6 +234,24 @@ class RouterTopk:
                                         _dptr(alts), _dptr(alt_w), _dptr(rng), _stream()))
         return sel, w, alts, alt_w, rng
 
+    def launch_batched_prior(self, logits: torch.Tensor, bias: torch.Tensor | None, prior: torch.Tensor, n_protect: int, n_alt: int = 0,
+                             prior_dry: bool = False):
+        """The cache-prior form of ``launch_batched_ex`` (router_topk_par.hip:82-99,173-210).
+        Returns (selected, weights, alts, alt_weights, orig_sel)."""
+        T, E = logits.shape
+        assert E == self.cfg.n_expert and logits.dtype == torch.float32 and logits.is_contiguous()
+        assert prior.dtype == torch.float32 and prior.numel() == E and prior.is_contiguous()
+        dev = logits.device
+        sel = torch.empty((T, self.cfg.n_used), dtype=torch.int32, device=dev)
+        w = torch.empty((T, self.cfg.n_used), dtype=torch.float32, device=dev)
+        alts = torch.empty((T, n_alt), dtype=torch.int32, device=dev) if n_alt else None
+        alt_w = torch.empty((T, n_alt), dtype=torch.float32, device=dev) if n_alt else None
+        orig = torch.empty((T, self.cfg.n_used), dtype=torch.int32, device=dev)
+        rc = _router_struct(self.cfg)
+        _check(lib().dsx_router_topk_prior(_dptr(logits), _dptr(bias), C.c_int64(T), C.byref(rc), _dptr(sel), _dptr(w), n_alt, _dptr(alts),
+                                           _dptr(alt_w), C.c_void_p(0), _dptr(prior), n_protect, 1 if prior_dry else 0, _dptr(orig), _stream()))
+        return sel, w, alts, alt_w, orig
+
 
 class MoeGroupBuilder:
     """Histogram / offsets / stable permutation / work items."""

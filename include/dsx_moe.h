@@ -182,11 +182,21 @@ DSX_API int dsx_router_topk(const float* logits, const float* bias, int64_t T, c
  *                               substitutes for a pick it does not hold); NULL -> no alternatives
  *   alt_w     f32 [T, n_alt]    prob(alt) / (sum of the picks' probs) * scale; may be NULL
  *   range_out f32 [T]           max - min of the selection scores over all experts; may be NULL
- * n_used + n_alt <= 16.  The cache-prior arguments of the reference (prior, n_protect, orig_sel)
- * are not part of this entry point. */
+ * n_used + n_alt <= 16.  The cache prior of the reference has its own entry point below. */
 DSX_API int dsx_router_topk_ex(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg,
                                int32_t* selected, float* weights, int n_alt, int32_t* alts, float* alt_w,
                                float* range_out, dsx_stream_t stream);
+
+/* The cache prior of RouterTopk::launch_batched_ex (router_topk_par.hip:82-99,173-210): prior[n_expert] is
+ * added to the SELECTION score; the first n_protect picks of the plain ranking are always kept, the other
+ * slots and the alternatives are the argmax of score + prior; weights come from the unbiased probabilities
+ * of the emitted picks.  orig_sel (may be NULL): int32 [T, n_used], the plain top-n_used.  prior_dry != 0
+ * swaps the roles: the plain picks are emitted and weighted, orig_sel carries the prior's choice.
+ * No group limit (cfg->n_group <= 1); n_used + n_alt <= 32. */
+DSX_API int dsx_router_topk_prior(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg,
+                                  int32_t* selected, float* weights, int n_alt, int32_t* alts, float* alt_w,
+                                  float* range_out, const float* prior, int n_protect, int prior_dry, int32_t* orig_sel,
+                                  dsx_stream_t stream);
 
 /* --- Histogram / permute / work items ------------------------------------
  * MoeGroupBuilder::launch + launch_work_items_split (src/moe_group_builder.rs:72-259;

@@ -15,8 +15,8 @@
  *   - scripts/v41_oracle/kernel.py (dequant_fp4 / act_quant / fp4_gemm outputs)
  * Parts with no counterpart in the reference (group-limited routing, Q8_0
  * routed experts, bf16 activations) are "parity unpinned": defined here under
- * the reference's conventions.  So are the router's alternatives / score range
- * and the two steps either side of the layer (RMSNorm, residual mix): the
+ * the reference's conventions.  So are the router's alternatives / score range /
+ * cache prior and the two steps either side of the layer (RMSNorm, residual mix): the
  * reference has kernels for them but no known-answer vector, so they are
  * restated from the kernel text alone.
  *
@@ -485,6 +485,64 @@ DSXO_API void dsxo_router_topk(const float* logits, const float* bias, int64_t T
                                int n_used, int n_group, int topk_group, int score_fn,
                                float scale, float eps, int32_t* selected, float* weights) {
     dsxo_router_topk_ex(logits, bias, T, n_expert, n_used, n_group, topk_group, score_fn, scale, eps, selected, weights, 0, NULL, NULL, NULL);
+}
+
+/* Top-k with the cache prior (kernels/router_topk_par.hip:82-99,173-210).  No group limit. */
+DSXO_API void dsxo_router_topk_prior(const float* logits, const float* bias, int64_t T, int n_expert, int n_used, int score_fn,
+                                     float scale, float eps, int32_t* selected, float* weights, int n_alt, int32_t* alts,
+                                     float* alt_w, const float* prior, int n_protect, int prior_dry, int32_t* orig_sel) {
+    if (!alts) n_alt = 0;
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < T; t++) {
+        float* p = (float*)malloc(sizeof(float) * (size_t)n_expert * 3);
+        float* s = p + n_expert;
+        float* boost = s + n_expert;
+        const float* lg = logits + t * n_expert;
+        for (int e = 0; e < n_expert; e++) {
+            p[e] = dsxo_router_prob(lg[e], score_fn);
+            s[e] = bias ? (p[e] + bias[e]) : p[e];
+            boost[e] = s[e] + prior[e];
+        }
+        int32_t orig[64], sel[64];
+        for (int j = 0; j < n_used; j++) {          /* the original top-n_used on the plain scores */
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < n_expert; e++) {
+                int taken = 0;
+                for (int q = 0; q < j; q++) if (orig[q] == e) taken = 1;
+                if (taken) continue;
+                if (best < 0 || s[e] > bv) { best = e; bv = s[e]; }
+            }
+            orig[j] = best;
+        }
+        for (int j = 0; j < n_protect; j++) sel[j] = orig[j];
+        for (int j = n_protect; j < n_used + n_alt; j++) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < n_expert; e++) {
+                int taken = 0;
+                for (int q = 0; q < j; q++) if (sel[q] == e) taken = 1;
+                if (taken) continue;
+                if (best < 0 || boost[e] > bv) { best = e; bv = boost[e]; }
+            }
+            sel[j] = best;
+        }
+        if (prior_dry)
+            for (int j = 0; j < n_used; j++) { int32_t tmp = sel[j]; sel[j] = orig[j]; orig[j] = tmp; }
+        float sum = 0.0f;
+        for (int j = 0; j < n_used; j++) sum += p[sel[j]];
+        if (sum < eps) sum = eps;
+        for (int j = 0; j < n_used; j++) {
+            selected[t * n_used + j] = sel[j];
+            weights[t * n_used + j] = p[sel[j]] / sum * scale;
+            if (orig_sel) orig_sel[t * n_used + j] = orig[j];
+        }
+        for (int j = 0; j < n_alt; j++) {
+            alts[t * n_alt + j] = sel[n_used + j];
+            if (alt_w) alt_w[t * n_alt + j] = p[sel[n_used + j]] / sum * scale;
+        }
+        free(p);
+    }
 }
 
 /* RMSNorm of rows (kernels/rms_norm.hip:48-84): partial j (of 256) = sum over m of x[j + 256 m]^2 in

@@ -246,6 +246,23 @@ def router_topk_ex(logits, bias, n_used, n_alt, n_group=1, topk_group=1, score_f
     return sel, w, alts[:, :n_alt], alt_w[:, :n_alt], rng
 
 
+def router_topk_prior(logits, bias, n_used, n_alt, prior, n_protect, prior_dry=False, score_fn=SCORE_SIGMOID, scale=1.0, eps=ROUTER_EPS):
+    """Top-k with the reference's cache prior: (selected, weights, alts, alt_weights, orig_sel)."""
+    logits = _c(logits, np.float32)
+    T, E = logits.shape
+    b = None if bias is None else _c(bias, np.float32)
+    pr = _c(prior, np.float32)
+    sel = np.empty((T, n_used), np.int32)
+    w = np.empty((T, n_used), np.float32)
+    alts = np.empty((T, max(n_alt, 1)), np.int32)
+    alt_w = np.empty((T, max(n_alt, 1)), np.float32)
+    orig = np.empty((T, n_used), np.int32)
+    lib().dsxo_router_topk_prior(_p(logits), _p(b), C.c_int64(T), C.c_int(E), C.c_int(n_used), C.c_int(score_fn), C.c_float(scale),
+                                 C.c_float(eps), _p(sel), _p(w), C.c_int(n_alt), _p(alts), _p(alt_w), _p(pr), C.c_int(n_protect),
+                                 C.c_int(1 if prior_dry else 0), _p(orig))
+    return sel, w, alts[:, :n_alt], alt_w[:, :n_alt], orig
+
+
 def rms_norm_rows(x, weight, eps=1e-6):
     x = _c(x, np.float32)
     w = _c(weight, np.float32)

@@ -130,6 +130,35 @@ def test_router_alternatives_and_range_bitexact(torch_cuda, moe, oracle, E, k, n
     assert np.array_equal(longer[:, k:], oalts)
 
 
+@pytest.mark.parametrize("E,k,n_alt,n_protect,dry,score_fn", [(256, 8, 4, 2, False, 0), (384, 6, 4, 2, True, 0), (64, 6, 0, 0, False, 1), (128, 8, 2, 8, False, 0)])
+def test_router_cache_prior_bitexact(torch_cuda, moe, oracle, E, k, n_alt, n_protect, dry, score_fn):
+    """The cache prior of the reference's router (router_topk_par.hip:82-99,173-210): protected picks stay,
+    the rest follows score + prior, weights come from the unbiased probabilities of what is emitted."""
+    from deepstrix_b200.config import RouterConfig
+    rng = np.random.Generator(np.random.PCG64(500 + E + n_protect))
+    T = 61
+    logits = rng.normal(0.0, 1.3, size=(T, E)).astype(np.float32)
+    bias = rng.normal(0.0, 0.01, size=(E,)).astype(np.float32)
+    prior = np.where(rng.random(E) < 0.3, 0.2, 0.0).astype(np.float32)   # a boost on the experts "held locally"
+    cfg = RouterConfig(n_expert=E, n_used=k, n_group=1, topk_group=1, score_fn=score_fn, route_scale=1.5)
+    router = moe.RouterTopk(cfg)
+    lg, b, pr = (torch_cuda.from_numpy(a).cuda() for a in (logits, bias, prior))
+    sel, w, alts, alt_w, orig = router.launch_batched_prior(lg, b, pr, n_protect, n_alt=n_alt, prior_dry=dry)
+    osel, ow, oalts, oalt_w, oorig = oracle.router_topk_prior(logits, bias, k, n_alt, prior, n_protect, dry, score_fn, 1.5, cfg.weight_eps)
+    assert np.array_equal(sel.cpu().numpy(), osel) and np.array_equal(orig.cpu().numpy(), oorig)
+    assert np.array_equal(w.cpu().numpy().view(np.uint32), ow.view(np.uint32))
+    if n_alt:
+        assert np.array_equal(alts.cpu().numpy(), oalts)
+        assert np.array_equal(alt_w.cpu().numpy().view(np.uint32), oalt_w.view(np.uint32))
+    # what must hold whatever the prior: the plain ranking is the plain router's, protected picks survive
+    psel, _ = oracle.router_topk(logits, bias, k, 1, 1, score_fn, 1.5, cfg.weight_eps)
+    plain, prior_pick = (osel, oorig) if dry else (oorig, osel)
+    assert np.array_equal(plain, psel)
+    assert np.array_equal(prior_pick[:, :n_protect], psel[:, :n_protect])
+    if n_protect == k:
+        assert np.array_equal(prior_pick, psel)
+
+
 def test_layer_drafter_shape(torch_cuda, moe, oracle):
     """The drafter's grouped MoE shape (128 experts, top-3, a 5-token block, no group limit,
     sqrt-softplus scores; mxfp4_pair_matvec.hip:566-596): every distinct expert's weights are read
