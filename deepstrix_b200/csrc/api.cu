@@ -363,6 +363,13 @@ int dsx_router_topk_ex(const float* logits, const float* bias, int64_t T, const 
     DSX_REQUIRE(alts != nullptr || alt_w == nullptr, "router_topk_ex: alt_w without alts");
     return launch_router_topk(logits, bias, T, *cfg, selected, weights, n_alt, alts, alt_w, range_out, (cudaStream_t)stream);
 }
+int dsx_expert_sel_count(uint32_t* counts, const int32_t* selected, uint32_t layer_off, uint32_t n_expert, int64_t total,
+                         dsx_stream_t stream) {
+    DSX_REQUIRE(total >= 0 && n_expert > 0, "expert_sel_count: %lld picks, %u experts", (long long)total, n_expert);
+    if (total == 0) return DSX_OK;
+    DSX_REQUIRE(counts && selected, "expert_sel_count: null argument");
+    return launch_expert_sel_count(counts, selected, layer_off, n_expert, total, (cudaStream_t)stream);
+}
 int dsx_router_topk_prior(const float* logits, const float* bias, int64_t T, const dsx_router_config* cfg, int32_t* selected,
                           float* weights, int n_alt, int32_t* alts, float* alt_w, float* range_out, const float* prior, int n_protect,
                           int prior_dry, int32_t* orig_sel, dsx_stream_t stream) {

@@ -213,6 +213,8 @@ int launch_group_build(const int32_t* selected, int64_t T, int n_used, int n_exp
                        int shared_items_for_T, int32_t* hist, int32_t* offsets, int32_t* perm, int32_t* work_items,
                        int32_t* n_work_items, int32_t work_cap, GroupScratch scratch, cudaStream_t stream);
 
+int launch_expert_sel_count(unsigned int* counts, const int32_t* selected, unsigned int layer_off, unsigned int n_expert, int64_t total,
+                            cudaStream_t stream);
 int launch_group_build_static(const int32_t* selected, int64_t T, int n_used, int n_expert, int chunk, int32_t* hist,
                               int32_t* offsets, int32_t* perm, int32_t* work_items, int32_t* n_work_items, int32_t work_cap,
                               cudaStream_t stream);

@@ -149,4 +149,27 @@ int launch_group_build(const int32_t* selected, int64_t T, int n_used, int n_exp
     return DSX_OK;
 }
 
+
+// Expert-selection statistics bank (crates/v4flash-kernels/kernels/expert_sel_count.hip:17-28,
+// src/expert_sel_count.rs:34): counts[layer_off + sel[i]] += 1 for every pick; ids outside
+// [0, n_expert) are dropped.  Integer atomics: the totals do not depend on the order.
+namespace {
+__global__ void expert_sel_count_kernel(unsigned int* __restrict__ counts, const int32_t* __restrict__ selected, unsigned int layer_off,
+                                        unsigned int n_expert, int64_t total) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int e = selected[i];
+    if (e < 0 || (unsigned int)e >= n_expert) return;
+    atomicAdd(&counts[layer_off + (unsigned int)e], 1u);
+}
+}  // namespace
+
+int launch_expert_sel_count(unsigned int* counts, const int32_t* selected, unsigned int layer_off, unsigned int n_expert, int64_t total,
+                            cudaStream_t stream) {
+    if (total == 0) return DSX_OK;
+    expert_sel_count_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(counts, selected, layer_off, n_expert, total);
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
 }  // namespace dsx

@@ -89,6 +89,17 @@ def bytes_per_expert(fmt: int, k: int, rows: int) -> int:
 
 
 # --------------------------------------------------------------------------
+class ExpertSelCount:
+    """``ExpertSelCount::launch`` (src/expert_sel_count.rs:34): accumulate the picks of one layer into the bank."""
+
+    @staticmethod
+    def launch(counts: torch.Tensor, selected: torch.Tensor, layer: int, n_expert: int):
+        assert counts.dtype == torch.int32 and selected.dtype == torch.int32 and counts.is_contiguous() and selected.is_contiguous()
+        assert counts.numel() >= (layer + 1) * n_expert
+        _check(lib().dsx_expert_sel_count(_dptr(counts), _dptr(selected), layer * n_expert, n_expert, C.c_int64(selected.numel()), _stream()))
+
+
+# --------------------------------------------------------------------------
 class RmsNorm:
     """``RmsNorm::launch_weighted_batched`` (src/rms_norm.rs:161-205): rows of f32 -> normalised rows,
     as the bf16 input of the MoE layer and / or as f32."""

@@ -198,6 +198,12 @@ DSX_API int dsx_router_topk_prior(const float* logits, const float* bias, int64_
                                   float* range_out, const float* prior, int n_protect, int prior_dry, int32_t* orig_sel,
                                   dsx_stream_t stream);
 
+/* ExpertSelCount::launch (src/expert_sel_count.rs:34; kernels/expert_sel_count.hip:17-28): the selection
+ * statistics bank, counts[layer_off + selected[i]] += 1 for every pick (u32, n_layer x n_expert, kept across
+ * steps and harvested by the caller); ids outside [0, n_expert) are dropped. */
+DSX_API int dsx_expert_sel_count(uint32_t* counts, const int32_t* selected, uint32_t layer_off, uint32_t n_expert,
+                                 int64_t total, dsx_stream_t stream);
+
 /* --- Histogram / permute / work items ------------------------------------
  * MoeGroupBuilder::launch + launch_work_items_split (src/moe_group_builder.rs:72-259;
  * kernels/moe_group_builder.hip:32-51, moe_work_items_builder.hip:61-145) with the

@@ -159,6 +159,21 @@ def test_router_cache_prior_bitexact(torch_cuda, moe, oracle, E, k, n_alt, n_pro
         assert np.array_equal(prior_pick, psel)
 
 
+def test_expert_sel_count_bank(torch_cuda, moe):
+    """The selection statistics bank accumulates over calls and layers; out-of-range ids are dropped
+    (expert_sel_count.hip:17-28)."""
+    rng = np.random.Generator(np.random.PCG64(41))
+    E, n_layer = 256, 3
+    bank = torch_cuda.zeros((n_layer * E,), dtype=torch_cuda.int32, device="cuda")
+    want = np.zeros((n_layer, E), np.int64)
+    for layer, T in ((1, 700), (1, 33), (2, 5000)):
+        sel = rng.integers(-2, E + 3, size=(T, 8)).astype(np.int32)
+        moe.ExpertSelCount.launch(bank, torch_cuda.from_numpy(sel).cuda(), layer, E)
+        ok = (sel >= 0) & (sel < E)
+        want[layer] += np.bincount(sel[ok], minlength=E)
+    assert np.array_equal(bank.cpu().numpy().reshape(n_layer, E), want)
+
+
 def test_layer_drafter_shape(torch_cuda, moe, oracle):
     """The drafter's grouped MoE shape (128 experts, top-3, a 5-token block, no group limit,
     sqrt-softplus scores; mxfp4_pair_matvec.hip:566-596): every distinct expert's weights are read
