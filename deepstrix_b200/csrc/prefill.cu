@@ -534,6 +534,11 @@ __device__ __forceinline__ int seg_size(int cnt) {  // even split into <= 256-ro
 // n_local) follow and cover rows P .. P+T-1.  Experts with at most small_max rows get no
 // segment: a tile would spend a full pass of weight conversion on a handful of tokens, while the
 // grouped GEMV streams the same weights at HBM speed, so they become GEMV work items instead.
+#ifndef DSX_SMALL_MAX
+#define DSX_SMALL_MAX 8
+#endif
+constexpr int kSmallMax = DSX_SMALL_MAX;   // at most 32 (4 work items of 8 rows per expert)
+
 __global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t P, int T_shared,
                                       PrefillSeg* __restrict__ segs, int32_t* __restrict__ n_segs, int cap, int small_max,
                                       int32_t* __restrict__ small_items, int32_t* __restrict__ n_small) {
@@ -544,7 +549,7 @@ __global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n
             s_base[e] = run;
             const int cnt = offsets[e + 1] - offsets[e];
             if (cnt > 0 && cnt <= small_max) {
-                small_items[small++] = (int32_t)((uint32_t)e << 16);
+                for (int st = 0; st < cnt; st += 8) small_items[small++] = (int32_t)(((uint32_t)e << 16) | (uint32_t)st);
                 continue;
             }
             const int sz = seg_size(cnt);
@@ -671,11 +676,11 @@ int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, in
     DSX_CUDA(cudaMalloc((void**)&ws->xperm, (size_t)ws->cap_rows * (size_t)cfg.hidden * 2));
     DSX_CUDA(cudaMalloc((void**)&ws->segs, sizeof(PrefillSeg) * (size_t)ws->seg_cap));
     DSX_CUDA(cudaMalloc((void**)&ws->n_segs, 256));
-    DSX_CUDA(cudaMalloc((void**)&ws->small_items, sizeof(int32_t) * (size_t)(cfg.router.n_expert + 8)));
+    DSX_CUDA(cudaMalloc((void**)&ws->small_items, sizeof(int32_t) * (size_t)(cfg.router.n_expert * 4 + 8)));   // up to 32 rows = 4 items per expert
     DSX_CUDA(cudaMalloc((void**)&ws->n_small, 256));
     DSX_CUDA(cudaMemset(ws->n_small, 0, 256));
     // a work item of the grouped GEMV holds at most 8 tokens; both reductions must fit its shared memory
-    ws->small_max = (gemv_fits(cfg.hidden) && gemv_fits(cfg.ffn) && cfg.hidden % 128 == 0 && cfg.ffn % 128 == 0) ? 8 : 0;
+    ws->small_max = (gemv_fits(cfg.hidden) && gemv_fits(cfg.ffn) && cfg.hidden % 128 == 0 && cfg.ffn % 128 == 0) ? kSmallMax : 0;
     if (int rc = encode_rows_map(&ws->tmap_x, ws->xperm, ws->cap_rows, cfg.hidden)) return rc;
     if (int rc = encode_rows_map(&ws->tmap_mid, mid, ws->cap_rows, cfg.ffn)) return rc;
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
