@@ -448,6 +448,10 @@ size_t gemv_smem_bytes(int64_t K, bool with_halves) {
 
 constexpr size_t kMaxSmem = 227 * 1024;
 
+#ifndef DSX_PAIR_WIDE_FROM
+#define DSX_PAIR_WIDE_FROM 10
+#endif
+
 struct Variant {
     int warps, ksplit;   // 0 warps: nothing fits
     size_t smem;
@@ -462,7 +466,10 @@ Variant pick_variant(int fmt, bool pair, int64_t K, int64_t rows, int64_t T) {
     const int n_stage = (int)((K / tile_k + ct_per_stage - 1) / ct_per_stage);
     const bool can_wide = rows % (kTileRows * 16) == 0;
     const size_t plain = gemv_smem_bytes(K, false), split = gemv_smem_bytes(K, true);
-    if (can_wide && T >= 8 && plain <= kMaxSmem) return {16, 1, plain};
+    // gate/up of 8 or 9 tokens: ~60 items x 8 wide units leave some blocks a fourth unit while most have
+    // three; 128-row units halve that tail (measured 108 -> 104 us at 8 tokens, a loss from 12 tokens on)
+    const int64_t wide_from = (pair && n_stage % 2 == 0 && split <= kMaxSmem) ? DSX_PAIR_WIDE_FROM : 8;
+    if (can_wide && T >= wide_from && plain <= kMaxSmem) return {16, 1, plain};
     if (n_stage % 2 == 0 && split <= kMaxSmem) return {16, 2, split};
     if (n_stage % 2 != 0 && plain <= kMaxSmem) return {8, 1, plain};
     if (can_wide && plain <= kMaxSmem) return {16, 1, plain};
