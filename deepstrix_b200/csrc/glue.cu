@@ -15,6 +15,8 @@
 // 1 / sqrt with IEEE division and square root, and a fused multiply-add per mixing term.
 // Here the norm writes the bf16 rows the MoE layer reads (and, optionally, the f32 rows as the
 // reference does), and the mix reads the layer's bf16 output directly: one pass over HBM each.
+#include <algorithm>
+
 #include "dsx_common.cuh"
 
 namespace dsx {
@@ -79,6 +81,97 @@ rms_norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weig
         }
     } else {
         for (int i = tid; i < n; i += kNormThreads) emit(i, xb[i]);
+    }
+}
+
+// The same arithmetic at HBM speed: persistent blocks, every block walks rows b, b + grid, ... with two
+// row buffers in shared memory; one thread fetches the next row with a bulk async copy (mbarrier
+// complete_tx) while the block reduces and stores the current one.  Every thread still takes ITS
+// elements (t + 256 j, the reference's assignment) from shared memory, so sums and results are the
+// same bits; results go back through the buffer and leave 16 bytes per lane.  The wait on a row is
+// bounded; a block whose wait runs out stops (its remaining rows stay unwritten).
+__device__ __forceinline__ uint32_t g_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__global__ void __launch_bounds__(kNormThreads)
+rms_norm_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ weight, int n, int64_t T, float eps,
+                         float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16) {
+    extern __shared__ __align__(16) float sbuf[];   // [2][n]
+    __shared__ float sdata[kNormThreads];
+    __shared__ __align__(8) uint64_t s_bar[2];
+    const int tid = threadIdx.x;
+    const uint32_t row_bytes = (uint32_t)n * 4u;
+    auto fetch = [&](int64_t r, int b) {   // thread 0
+        const uint32_t bar = g_smem_u32(&s_bar[b]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         g_smem_u32(sbuf + (size_t)b * n)),
+                     "l"(x + r * n), "r"(row_bytes), "r"(bar)
+                     : "memory");
+    };
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(g_smem_u32(&s_bar[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(g_smem_u32(&s_bar[1])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if ((int64_t)blockIdx.x < T) fetch(blockIdx.x, 0);
+    }
+    __syncthreads();
+    int k = 0;
+    for (int64_t r = blockIdx.x; r < T; r += gridDim.x, k++) {
+        const int b = k & 1;
+        if (tid == 0 && r + gridDim.x < T) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the other buffer was last written by this block's threads
+            fetch(r + gridDim.x, b ^ 1);
+        }
+        {   // bounded wait for this row
+            const uint32_t bar = g_smem_u32(&s_bar[b]), parity = (uint32_t)((k >> 1) & 1);
+            uint32_t ok = 0;
+            for (uint32_t i = 0; i < (1u << 22) && !ok; i++)
+                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(ok)
+                             : "r"(bar), "r"(parity)
+                             : "memory");
+            if (!ok) return;
+        }
+        float* srow = sbuf + (size_t)b * n;
+        double partial = 0.0;
+        for (int i = tid; i < n; i += kNormThreads) {
+            const float a = srow[i];
+            partial += (double)a * (double)a;
+        }
+        sdata[tid] = (float)partial;
+        __syncthreads();
+        if (tid < 128) sdata[tid] = __fadd_rn(sdata[tid], sdata[tid + 128]);
+        __syncthreads();
+        if (tid < 64) sdata[tid] = __fadd_rn(sdata[tid], sdata[tid + 64]);
+        __syncthreads();
+        if (tid < 32) {
+            float s = __fadd_rn(sdata[tid], sdata[tid + 32]);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_down_sync(0xFFFFFFFFu, s, off));
+            if (tid == 0) sdata[0] = s;
+        }
+        __syncthreads();
+        const float mean_sq = __fdiv_rn(sdata[0], (float)n);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
+        for (int i = tid; i < n; i += kNormThreads) srow[i] = __fmul_rn(__fmul_rn(srow[i], scale), __ldg(weight + i));   // own elements only
+        __syncthreads();
+        if (out_f32 != nullptr) {
+            float4* o4 = reinterpret_cast<float4*>(out_f32 + r * n);
+            for (int i = tid; i < (n >> 2); i += kNormThreads) o4[i] = reinterpret_cast<const float4*>(srow)[i];
+        }
+        if (out_bf16 != nullptr) {
+            uint4* o8 = reinterpret_cast<uint4*>(out_bf16 + r * n);
+            for (int i = tid; i < (n >> 3); i += kNormThreads) {
+                const float4 a = reinterpret_cast<const float4*>(srow)[2 * i], c = reinterpret_cast<const float4*>(srow)[2 * i + 1];
+                const __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x, a.y), h1 = __floats2bfloat162_rn(a.z, a.w);
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(c.x, c.y), h3 = __floats2bfloat162_rn(c.z, c.w);
+                uint4 o;
+                o.x = *reinterpret_cast<const uint32_t*>(&h0); o.y = *reinterpret_cast<const uint32_t*>(&h1);
+                o.z = *reinterpret_cast<const uint32_t*>(&h2); o.w = *reinterpret_cast<const uint32_t*>(&h3);
+                o8[i] = o;
+            }
+        }
+        __syncthreads();   // everyone is done with this buffer (and with sdata) before it is fetched into again
     }
 }
 
@@ -156,6 +249,22 @@ int dsx_rms_norm_rows(const float* x, const float* weight, int64_t T, int64_t n,
     if (T == 0) return DSX_OK;
     DSX_REQUIRE(x && weight && (out_f32 || out_bf16), "rms_norm_rows: null argument");
     DSX_REQUIRE(T <= 0x7FFFFFFF, "rms_norm_rows: too many rows");
+    const bool vec = n % 8 == 0 && n * 8 <= 96 * 1024 && (((uintptr_t)x | (uintptr_t)out_f32 | (uintptr_t)out_bf16) & 15) == 0;
+    if (vec) {
+        static int sm_count = 0;   // persistent grid: a few blocks per SM
+        if (sm_count == 0) {
+            int dev = 0;
+            DSX_CUDA(cudaGetDevice(&dev));
+            DSX_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+            DSX_CUDA(cudaFuncSetAttribute(rms_norm_rows_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        }
+        const size_t smem = (size_t)n * 8;
+        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(6, (200 * 1024) / (smem + 2048)));
+        const unsigned blocks = (unsigned)std::min<int64_t>(T, (int64_t)sm_count * per_sm);
+        rms_norm_rows_vec_kernel<<<blocks, kNormThreads, smem, (cudaStream_t)stream>>>(x, weight, (int)n, T, eps, out_f32, (__nv_bfloat16*)out_bf16);
+        DSX_LAUNCHED();
+        return DSX_OK;
+    }
     const int per_thread = (int)((n + kNormThreads - 1) / kNormThreads);
 #define DSX_NORM_LAUNCH(R) rms_norm_rows_kernel<R><<<(unsigned)T, kNormThreads, 0, (cudaStream_t)stream>>>(x, weight, (int)n, eps, out_f32, (__nv_bfloat16*)out_bf16)
     if (per_thread <= 8) DSX_NORM_LAUNCH(8);
