@@ -180,10 +180,11 @@ struct ItemInfo {
 //
 // SMALL (batches below 8 tokens routed by the one-launch decode router, where the kernels' fixed
 // costs are a large share): an item is one ready-made ItemRec, and what does not depend on the
-// previous kernel of the chain runs before the wait for it.  Gate/up stages every token row once,
+// previous kernel of the chain runs before the wait for it: gate/up stages every token row once,
 // as f16 (its predecessor releases it only after the token rows are complete); an item then only
-// selects rows.  The down kernel reads the routing and requests its first weights (gate/up
-// releases it after its own wait, when the routing is complete).  Otherwise the kernel derives an
+// selects rows.  In every variant the down kernel reads the work list and requests its first weights
+// before it waits for gate/up (gate/up releases it after its own wait, when the routing is complete;
+// worth 3 us per layer step at every batch size).  Otherwise the kernel derives an
 // item from offsets / perm / weights and stages its rows when the block reaches it; that code is
 // kept apart at compile time because the streaming loop's schedule is sensitive to it.
 template <int FMT, bool PAIR, int WARPS, int KSPLIT, bool SMALL>
@@ -230,10 +231,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
         }
     }
     __syncthreads();
-    if (!SMALL) {
-        pdl_launch_dependents();
-        pdl_wait();   // work items, routing and activations come from the previous kernels of the chain
-    } else if (PAIR) {
+    if (PAIR) {
         pdl_wait();   // work items and routing come from the previous kernel of the chain
         // the next kernel (down) reads the routing before its own wait: release it only now
         pdl_launch_dependents();
@@ -285,7 +283,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
 
     if (lane == 0)
         for (int i = 0; i < total && i < kStages; i++) issue();
-    if (SMALL && !PAIR) pdl_wait();   // the rows of mid come from the gate/up kernel
+    if (!PAIR) pdl_wait();   // the rows of mid come from the gate/up kernel
 
     int item = u0 / bpi, rb = u0 - item * bpi, ls = 0;
     int cur_item = -1;
