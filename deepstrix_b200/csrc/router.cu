@@ -7,6 +7,7 @@
 //           `(ord(score) << 32) | ~index` is reused here)
 //   sigmoid crates/v4flash-kernels/kernels/laguna_ops.hip:55-62
 #include <algorithm>
+#include <atomic>
 
 #include "groups.cuh"
 
@@ -78,86 +79,137 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, const float
 }
 
 // Same logits for prefill-size batches, tiled like a GEMM so that router rows and token rows are
-// re-read from L2 16 and 32 times less: a block of 16 warps computes 16 router rows x 32 tokens,
-// a warp 4 rows x 8 tokens.  The reduction runs in chunks of 128 columns staged in shared memory
-// by 16-byte async copies (three stages); lane l still owns columns 4l..4l+3 of every chunk and
-// adds them in increasing column order, then the warp folds with the xor butterfly: the f32
-// operation sequence of a (token, expert) pair is the one of router_logits_kernel, same bits.
+// re-read from L2 16 and 32 times less: a block of 8 warps computes 16 router rows x 32 tokens,
+// a warp 8 rows x 8 tokens (64 accumulators a lane; 0.75 bytes of shared memory read per FMA), two
+// blocks to an SM.  The reduction runs in chunks of 128 columns, two per stage of shared memory
+// filled by 16-byte async copies (three stages); lane l still owns columns 4l..4l+3 of every chunk and
+// adds them in increasing column order, then the warp folds with the operand pairs of the xor
+// butterfly: the f32 operation sequence of a (token, expert) pair is the one of router_logits_kernel,
+// same bits.
 constexpr int kTileRowsR = 16, kTileTok = 32, kTileStages = 3;
-constexpr int kTileThreads = 512;
-constexpr int kTileStageBytes = kTileRowsR * 128 * 4 + kTileTok * 128 * 2;   // 16 KB
+constexpr int kTileThreads = 256;
+constexpr int kTileWarpRows = 8, kTileWarpTok = 8;
+constexpr int kTileCols = 256;   // columns per stage: two 128-column chunks per block barrier
+constexpr int kTileStageBytes = kTileRowsR * kTileCols * 4 + kTileTok * kTileCols * 2;   // 32 KB
+static_assert((kTileRowsR / kTileWarpRows) * (kTileTok / kTileWarpTok) * 32 == kTileThreads, "warps must cover the block tile");
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
 }
 
-__global__ void __launch_bounds__(kTileThreads)
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+// (d.lo, d.hi) = (a.lo * b.lo + c.lo, a.hi * b.hi + c.hi), each half one IEEE fused multiply-add
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__global__ void __launch_bounds__(kTileThreads, 2)
 router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, const float* __restrict__ W, int n_expert, int64_t H,
                            float* __restrict__ logits) {
     extern __shared__ __align__(128) uint8_t tsm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rg = warp >> 2, tg = warp & 3;              // row group (4 rows), token group (8 tokens)
+    const int rg = warp >> 2, tg = warp & 3;              // row group (8 rows), token group (8 tokens)
     const int e0 = blockIdx.x * kTileRowsR;
     const int64_t t0 = (int64_t)blockIdx.y * kTileTok;
-    const int n_iter = (int)(H >> 7);
-    // this thread's two 16-byte pieces of every stage (rows past the batch alias the last valid row)
-    const int wr = threadIdx.x >> 5, wc = threadIdx.x & 31;
+    const int n_iter = (int)(H / kTileCols);
+    // this thread's eight 16-byte pieces of every stage (rows past the batch alias the last valid row)
+    const int wr = threadIdx.x >> 4, wc = threadIdx.x & 15;
     const float* wsrc = W + (int64_t)(e0 + wr) * H + wc * 4;
-    const int xr = threadIdx.x >> 4, xc = threadIdx.x & 15;
+    const int xr = threadIdx.x >> 3, xc = threadIdx.x & 7;
     const __nv_bfloat16* xsrc = x + min(t0 + xr, T - 1) * H + xc * 8;
     auto stage_w = [&](int s) { return reinterpret_cast<float*>(tsm + (size_t)s * kTileStageBytes); };
-    auto stage_x = [&](int s) { return reinterpret_cast<__nv_bfloat16*>(tsm + (size_t)s * kTileStageBytes + kTileRowsR * 128 * 4); };
+    auto stage_x = [&](int s) { return reinterpret_cast<__nv_bfloat16*>(tsm + (size_t)s * kTileStageBytes + kTileRowsR * kTileCols * 4); };
     auto issue = [&](int i) {
         const int s = i % kTileStages;
-        cp_async16(stage_w(s) + wr * 128 + wc * 4, wsrc + (int64_t)i * 128);
-        cp_async16(stage_x(s) + xr * 128 + xc * 8, xsrc + (int64_t)i * 128);
+#pragma unroll
+        for (int j = 0; j < kTileCols / 64; j++) {
+            cp_async16(stage_w(s) + wr * kTileCols + j * 64 + wc * 4, wsrc + (int64_t)i * kTileCols + j * 64);
+            cp_async16(stage_x(s) + xr * kTileCols + j * 64 + xc * 8, xsrc + (int64_t)i * kTileCols + j * 64);
+        }
     };
-    float acc[4][8];
+    // accumulators of token pairs (t, t + 1) share a 64-bit register: one packed instruction performs
+    // the two round-to-nearest fused multiply-adds, each exactly the scalar one
+    uint64_t acc[kTileWarpRows][kTileWarpTok / 2];
 #pragma unroll
-    for (int r = 0; r < 4; r++)
+    for (int r = 0; r < kTileWarpRows; r++)
 #pragma unroll
-        for (int t = 0; t < 8; t++) acc[r][t] = 0.0f;
+        for (int t = 0; t < kTileWarpTok / 2; t++) acc[r][t] = 0ull;
     issue(0);
     asm volatile("cp.async.commit_group;" ::: "memory");
     if (n_iter > 1) issue(1);
     asm volatile("cp.async.commit_group;" ::: "memory");
     for (int i = 0; i < n_iter; i++) {
         asm volatile("cp.async.wait_group 1;" ::: "memory");
-        __syncthreads();   // chunk i has landed for every thread; everyone is done with chunk i - 1
+        __syncthreads();   // stage i has landed for every thread; everyone is done with stage i - 1
         if (i + 2 < n_iter) issue(i + 2);
         asm volatile("cp.async.commit_group;" ::: "memory");
         const int s = i % kTileStages;
-        const float4* wp = reinterpret_cast<const float4*>(stage_w(s) + (rg * 4) * 128) + lane;
-        const uint2* xp = reinterpret_cast<const uint2*>(stage_x(s) + (tg * 8) * 128) + lane;
-        float4 w[4];
 #pragma unroll
-        for (int r = 0; r < 4; r++) w[r] = wp[r * 32];
+        for (int h = 0; h < kTileCols / 128; h++) {   // 128-column chunks in increasing column order
+            const float4* wp = reinterpret_cast<const float4*>(stage_w(s) + (rg * kTileWarpRows) * kTileCols + h * 128) + lane;
+            const uint2* xp = reinterpret_cast<const uint2*>(stage_x(s) + (tg * kTileWarpTok) * kTileCols + h * 128) + lane;
+            uint64_t xq[kTileWarpTok / 2][4];   // columns 4l..4l+3 of tokens (2p, 2p + 1), widened to f32
 #pragma unroll
-        for (int t = 0; t < 8; t++) {
-            const uint2 xv = xp[t * 32];
-            const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xFFFF0000u);
-            const float x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xFFFF0000u);
+            for (int t = 0; t < kTileWarpTok / 2; t++) {
+                const uint2 xa = xp[(2 * t) * (kTileCols / 4)], xb = xp[(2 * t + 1) * (kTileCols / 4)];
+                xq[t][0] = pack2(xa.x << 16, xb.x << 16);
+                xq[t][1] = pack2(xa.x & 0xFFFF0000u, xb.x & 0xFFFF0000u);
+                xq[t][2] = pack2(xa.y << 16, xb.y << 16);
+                xq[t][3] = pack2(xa.y & 0xFFFF0000u, xb.y & 0xFFFF0000u);
+            }
 #pragma unroll
-            for (int r = 0; r < 4; r++) {
-                float a = acc[r][t];
-                a = __fmaf_rn(w[r].x, x0, a);
-                a = __fmaf_rn(w[r].y, x1, a);
-                a = __fmaf_rn(w[r].z, x2, a);
-                a = __fmaf_rn(w[r].w, x3, a);
-                acc[r][t] = a;
+            for (int r = 0; r < kTileWarpRows; r++) {
+                const float4 w = wp[r * (kTileCols / 4)];
+                const uint64_t w0 = pack2(__float_as_uint(w.x), __float_as_uint(w.x)), w1 = pack2(__float_as_uint(w.y), __float_as_uint(w.y));
+                const uint64_t w2 = pack2(__float_as_uint(w.z), __float_as_uint(w.z)), w3 = pack2(__float_as_uint(w.w), __float_as_uint(w.w));
+#pragma unroll
+                for (int t = 0; t < kTileWarpTok / 2; t++) {
+                    uint64_t a = acc[r][t];
+                    a = fma2(w0, xq[t][0], a);
+                    a = fma2(w1, xq[t][1], a);
+                    a = fma2(w2, xq[t][2], a);
+                    a = fma2(w3, xq[t][3], a);
+                    acc[r][t] = a;
+                }
             }
         }
     }
+    // The butterfly of router_logits_kernel, folded: at the step with lane distance d a lane keeps the
+    // half of its values its bit d selects and adds the partner's partial sums of the same values, so
+    // every addition has the butterfly's two operands (f32 addition commutes) and each step halves the
+    // work.  Value r * 8 + t ends, fully summed, in lane (r * 8 + t) / 2.
+    float v[kTileWarpRows * kTileWarpTok];
 #pragma unroll
-    for (int r = 0; r < 4; r++)
+    for (int r = 0; r < kTileWarpRows; r++)
 #pragma unroll
-        for (int t = 0; t < 8; t++) {
-            float a = acc[r][t];
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, off));
-            const int64_t tok = t0 + tg * 8 + t;
-            if (lane == 0 && tok < T) logits[tok * n_expert + e0 + rg * 4 + r] = a;
+        for (int t = 0; t < kTileWarpTok; t++) {
+            const uint64_t q = acc[r][t >> 1];
+            v[r * kTileWarpTok + t] = __uint_as_float((t & 1) ? (uint32_t)(q >> 32) : (uint32_t)q);
         }
+#pragma unroll
+    for (int half = kTileWarpRows * kTileWarpTok / 2, off = 16; off > 0; half >>= 1, off >>= 1) {
+        const bool up = (lane & off) != 0;
+#pragma unroll
+        for (int j = 0; j < half; j++) {
+            const float keep = up ? v[j + half] : v[j];
+            const float give = up ? v[j] : v[j + half];
+            v[j] = __fadd_rn(keep, __shfl_xor_sync(0xFFFFFFFFu, give, off));
+        }
+    }
+    static_assert(kTileWarpRows * kTileWarpTok == 64, "two finished values a lane");
+    {
+        const int r = lane >> 2;
+        const int64_t tok = t0 + tg * kTileWarpTok + 2 * (lane & 3);
+        float* out = logits + tok * n_expert + e0 + rg * kTileWarpRows + r;
+        if (tok < T) out[0] = v[0];
+        if (tok + 1 < T) out[n_expert] = v[1];
+    }
 }
 
 __device__ __forceinline__ uint32_t ordered_bits(float f) {
@@ -758,7 +810,16 @@ int launch_router_logits(const __nv_bfloat16* x, int64_t T, const float* W, int 
                          cudaStream_t stream) {
     DSX_REQUIRE(H % 128 == 0, "router_logits: hidden %lld must be a multiple of 128", (long long)H);
     if (T == 0) return DSX_OK;
-    if (n_expert % kTileRowsR == 0 && T >= 512 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0)) {   // enough 16 x 32 tiles for every SM
+    if (n_expert % kTileRowsR == 0 && T >= 128 && H % kTileCols == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0)) {   // a 16 x 32 tile finishes in about the time the warp-per-row kernel needs for 128 tokens
+        // this entry point is also reached without a layer handle, so the opt-in to 96 KB of shared
+        // memory is made here, once per device
+        static std::atomic<uint64_t> opted_in{0};
+        int dev = 0;
+        DSX_CUDA(cudaGetDevice(&dev));
+        if (!((opted_in.load(std::memory_order_relaxed) >> (dev & 63)) & 1)) {
+            DSX_CUDA(cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileStages * kTileStageBytes));
+            opted_in.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
+        }
         dim3 grid2((unsigned)(n_expert / kTileRowsR), (unsigned)((T + kTileTok - 1) / kTileTok));
         router_logits_tiled_kernel<<<grid2, kTileThreads, kTileStages * kTileStageBytes, stream>>>(x, T, W, n_expert, H, logits);
     } else {
@@ -869,7 +930,6 @@ int router_configure() {
     DSX_CUDA((configure_fused_variant<V, 4>()));
     DSX_FUSED_CFG(1) DSX_FUSED_CFG(2) DSX_FUSED_CFG(4) DSX_FUSED_CFG(8)
 #undef DSX_FUSED_CFG
-    DSX_CUDA(cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileStages * kTileStageBytes));
 #define DSX_WIDE_CFG(V)                                                                                                        \
     DSX_CUDA((cudaFuncSetAttribute(router_fused_wide_kernel<V, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));  \
     DSX_CUDA((cudaFuncSetAttribute(router_fused_wide_kernel<V, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024))); \
