@@ -204,6 +204,28 @@ def test_router_logits_close_and_batch_invariant(torch_cuda, moe, oracle):
     assert np.array_equal(one[0].view(np.uint32), lg[17].view(np.uint32))
 
 
+@pytest.mark.parametrize("T,E,H", [(128, 256, 4096), (129, 256, 4096), (191, 64, 2048), (257, 384, 5120), (1000, 256, 4096)])
+def test_router_logits_tiled_same_bits_as_row_kernel(torch_cuda, moe, oracle, T, E, H):
+    """Large batches take the tiled kernel (ragged last tile, odd token counts); slices of at most
+    64 tokens take the warp-per-row kernel.  Same f32 operation order, so the bits must agree."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS, RouterConfig
+    rng = np.random.default_rng(T + E)
+    W = rng.normal(0, 0.02, (E, H)).astype(np.float32)
+    xf = rng.normal(0, 1.0, (T, H)).astype(np.float32)
+    x = torch.from_numpy(xf).cuda().to(torch.bfloat16)
+    Wd = torch.from_numpy(W).cuda()
+    r = moe.RouterTopk(RouterConfig(n_expert=E, n_used=6, n_group=1, topk_group=1, route_scale=2.5))
+    big = r.logits(x, Wd).cpu().numpy()
+    assert big.shape == (T, E)
+    small = np.concatenate([r.logits(x[a:a + 50].contiguous(), Wd).cpu().numpy() for a in range(0, T, 50)])
+    assert np.array_equal(big.view(np.uint32), small.view(np.uint32))
+    rows = [0, T // 2, T - 2, T - 1]
+    ref = oracle.router_logits(x[rows].float().cpu().numpy(), W)
+    assert np.abs(big[rows] - ref).max() < 5e-5
+
+
 # ------------------------------------------------------------------ groups
 @pytest.mark.parametrize("T,k,E,chunk", [(1, 8, 256, 8), (16, 6, 64, 8), (64, 8, 256, 8), (300, 8, 256, 32), (2048, 8, 256, 128), (5000, 6, 384, 32)])
 def test_group_build_bitexact(torch_cuda, moe, oracle, T, k, E, chunk):
