@@ -225,6 +225,9 @@ int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int6
     if (e == cudaSuccess) e = cudaMalloc(&s->dn_sc, n * s->dn_sc_stride);
     if (e == cudaSuccess) e = cudaMalloc((void**)&s->d_scale_max, 256);
     if (e == cudaSuccess) e = cudaMemset(s->d_scale_max, 0, 256);
+    // scale planes start at zero: the largest-scale scan covers whole planes, slots not loaded yet included
+    if (e == cudaSuccess) e = cudaMemset(s->gu_sc, 0, n * s->gu_sc_stride);
+    if (e == cudaSuccess) e = cudaMemset(s->dn_sc, 0, n * s->dn_sc_stride);
     if (e != cudaSuccess) {
         dsx_expert_store_destroy(s);
         return set_error((int)e, "expert_store: cudaMalloc failed: %s", cudaGetErrorString(e));
@@ -268,10 +271,9 @@ int dsx_expert_store_load(dsx_expert_store* st, int slot, int which, int src_lay
     const int64_t nstr = down ? st->dn_nib_stride : st->gu_nib_stride, sstr = down ? st->dn_sc_stride : st->gu_sc_stride;
     const int pair_stride = down ? 1 : 2, pair_index = which == DSX_MAT_UP ? 1 : 0;
     const int first = slot < 0 ? 0 : slot, count = slot < 0 ? st->n_slots : 1;
-    auto fold_scales = [&]() -> int {  // MXFP4 scale planes hold nothing but E8M0 bytes
+    auto fold_scales = [&]() -> int {  // the largest scale is recomputed over the whole planes before the next use
         st->scale_dirty = true;
-        if (st->fmt != DSX_FMT_MXFP4) return DSX_OK;
-        return launch_max_byte(sc + first * sstr, (int64_t)count * sstr, st->d_scale_max, stream);
+        return DSX_OK;
     };
     if (src_on_device) {
         if (int rc = launch_repack(st->fmt, src_layout, (const uint8_t*)q, (const uint8_t*)s, rows, K, nib + first * nstr,
@@ -517,6 +519,9 @@ int dsx_moe_layer_set_weights(dsx_moe_layer* L, const dsx_expert_store* routed, 
     if (int rc = check_weights(L->cfg, routed, shared, router_w)) return rc;
     L->routed = routed; L->shared = L->cfg.shared_ffn > 0 ? shared : nullptr;
     L->router_w = router_w; L->router_bias = router_bias;
+    // the tensor maps of the prefill path describe the previous stores (a new store may even sit at a freed
+    // store's address with another slot count): encode them again on the next use
+    for (int i = 0; i < 2; i++) L->pf.mapped_gu_nib[i] = L->pf.mapped_dn_nib[i] = nullptr;
     return DSX_OK;
 }
 
@@ -525,7 +530,13 @@ int dsx_moe_layer_set_weights(dsx_moe_layer* L, const dsx_expert_store* routed, 
 static bool scales_fit_f16(const dsx_expert_store* st) {
     if (st->fmt != DSX_FMT_MXFP4) return true;
     if (st->scale_dirty) {
+        // MXFP4 scale planes hold nothing but E8M0 bytes: one maximum over both planes as they are now
+        // (a slot reloaded with smaller scales lowers it again)
         uint32_t v = 255;
+        const size_t n = (size_t)st->n_slots;
+        if (cudaMemset(st->d_scale_max, 0, 4) != cudaSuccess) return false;
+        if (launch_max_byte(st->gu_sc, (int64_t)(n * st->gu_sc_stride), st->d_scale_max, nullptr) != DSX_OK) return false;
+        if (launch_max_byte(st->dn_sc, (int64_t)(n * st->dn_sc_stride), st->d_scale_max, nullptr) != DSX_OK) return false;
         if (cudaMemcpy(&v, st->d_scale_max, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
         st->h_scale_max = v;
         st->scale_dirty = false;
@@ -596,7 +607,6 @@ int dsx_moe_layer_forward(dsx_moe_layer* L, const void* x_bf16, int64_t T, void*
     DSX_REQUIRE(x_bf16 && out_bf16, "moe_layer_forward: null argument");
     DSX_REQUIRE(L->routed->n_slots == L->cfg.router.n_expert, "moe_layer_forward: store holds %d of %d experts; use forward_picks",
                 L->routed->n_slots, L->cfg.router.n_expert);
-    if (T == 0) return DSX_OK;
     const __nv_bfloat16* x = (const __nv_bfloat16*)x_bf16;
     const float* logits = logits_in;
     if (L->profile) for (bool& u : L->ev_used) u = false;

@@ -134,7 +134,8 @@ ep_send_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
 }
 
 // ---- barrier across the ranks
-__global__ void ep_barrier_kernel(PeerTable peers, size_t flags_off, int world, int rank, uint32_t epoch, uint32_t* error_word) {
+__global__ void ep_barrier_kernel(PeerTable peers, size_t flags_off, int world, int rank, uint32_t epoch, uint32_t polls,
+                                  uint32_t* error_word) {
     const int p = threadIdx.x;
     if (p >= world) return;
     __threadfence_system();
@@ -143,7 +144,7 @@ __global__ void ep_barrier_kernel(PeerTable peers, size_t flags_off, int world, 
     __threadfence_system();
     volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(peers.slab[rank] + flags_off) + p;
     bool seen = false;
-    for (uint32_t i = 0; i < kBarrierPolls && !seen; i++) {
+    for (uint32_t i = 0; i < polls && !seen; i++) {
         seen = (int32_t)(*mine - epoch) >= 0;
         if (!seen) __nanosleep(100);
     }
@@ -233,6 +234,7 @@ struct dsx_ep_comm {
     float* w = nullptr;                // [world*cap][k]
     uint32_t* error_word = nullptr;
     uint32_t epoch = 0;
+    uint32_t barrier_polls = kBarrierPolls;   // polls (>= 100 ns each) before a barrier gives up
     bool connected = false;
 };
 
@@ -335,10 +337,17 @@ int dsx_ep_dispatch(dsx_ep_comm* c, const void* x_bf16, const int32_t* selected,
     return DSX_OK;
 }
 
+int dsx_ep_set_barrier_polls(dsx_ep_comm* c, uint32_t polls) {
+    DSX_REQUIRE(c && polls >= 1, "ep_set_barrier_polls: bad argument");
+    c->barrier_polls = polls;
+    return DSX_OK;
+}
+
 int dsx_ep_barrier(dsx_ep_comm* c, dsx_stream_t stream_) {
     DSX_REQUIRE(c && c->connected, "ep_barrier: not connected");
     c->epoch++;
-    ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream_>>>(c->peers, c->lay.flags, c->world, c->rank, c->epoch, c->error_word);
+    ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream_>>>(c->peers, c->lay.flags, c->world, c->rank, c->epoch, c->barrier_polls,
+                                                            c->error_word);
     DSX_LAUNCHED();
     return DSX_OK;
 }
@@ -400,6 +409,7 @@ int dsx_ep_check(dsx_ep_comm* c, dsx_stream_t stream_, uint32_t* error_word) {
     DSX_CUDA(cudaStreamSynchronize((cudaStream_t)stream_));
     if (w) DSX_CUDA(cudaMemsetAsync(c->error_word, 0, 4, (cudaStream_t)stream_));
     if (error_word) *error_word = w;
+    if (w) return set_error(DSX_ERR_DEVICE, "an exchange kernel reported error word 0x%x (a bounded wait ran out)", w);
     return DSX_OK;
 }
 

@@ -16,6 +16,7 @@
 // Here the norm writes the bf16 rows the MoE layer reads (and, optionally, the f32 rows as the
 // reference does), and the mix reads the layer's bf16 output directly: one pass over HBM each.
 #include <algorithm>
+#include <atomic>
 
 #include "dsx_common.cuh"
 
@@ -23,6 +24,9 @@ namespace dsx {
 namespace {
 
 constexpr int kNormThreads = 256;
+// Error word of the kernels in this file (bit 1: a row's bulk copy never arrived); read and
+// cleared by dsx_glue_check.
+__device__ uint32_t g_glue_error = 0;
 
 // kNormRegs: values a thread keeps in registers (rows up to 256 * kNormRegs columns are read once; 0 = re-read
 // the row).  Instantiated for a few sizes so that a 4096-column row does not pay the registers of an 8192-column one.
@@ -130,7 +134,10 @@ rms_norm_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ 
                              : "=r"(ok)
                              : "r"(bar), "r"(parity)
                              : "memory");
-            if (!ok) return;
+            if (!ok) {   // the row never arrived: report it and stop (this block's remaining rows stay unwritten)
+                if (tid == 0) atomicOr(&g_glue_error, 1u);
+                return;
+            }
         }
         float* srow = sbuf + (size_t)b * n;
         double partial = 0.0;
@@ -251,12 +258,18 @@ int dsx_rms_norm_rows(const float* x, const float* weight, int64_t T, int64_t n,
     DSX_REQUIRE(T <= 0x7FFFFFFF, "rms_norm_rows: too many rows");
     const bool vec = n % 8 == 0 && n * 8 <= 96 * 1024 && (((uintptr_t)x | (uintptr_t)out_f32 | (uintptr_t)out_bf16) & 15) == 0;
     if (vec) {
-        static int sm_count = 0;   // persistent grid: a few blocks per SM
+        // persistent grid: a few blocks per SM.  The opt-in to 96 KB of shared memory is a per-device
+        // setting, so it is made (and the SM count read) once for every device this entry point meets.
+        constexpr int kMaxDevices = 64;
+        static std::atomic<int> sm_counts[kMaxDevices];
+        int dev = 0;
+        DSX_CUDA(cudaGetDevice(&dev));
+        DSX_REQUIRE(dev >= 0 && dev < kMaxDevices, "rms_norm_rows: device index %d out of range", dev);
+        int sm_count = sm_counts[dev].load(std::memory_order_acquire);
         if (sm_count == 0) {
-            int dev = 0;
-            DSX_CUDA(cudaGetDevice(&dev));
             DSX_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
             DSX_CUDA(cudaFuncSetAttribute(rms_norm_rows_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+            sm_counts[dev].store(sm_count, std::memory_order_release);
         }
         const size_t smem = (size_t)n * 8;
         const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(6, (200 * 1024) / (smem + 2048)));
@@ -274,6 +287,21 @@ int dsx_rms_norm_rows(const float* x, const float* weight, int64_t T, int64_t n,
     else DSX_NORM_LAUNCH(0);
 #undef DSX_NORM_LAUNCH
     DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+int dsx_glue_check(dsx_stream_t stream_, uint32_t* error_word) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    uint32_t w = 0;
+    DSX_CUDA(cudaMemcpyFromSymbolAsync(&w, g_glue_error, 4, 0, cudaMemcpyDeviceToHost, stream));
+    DSX_CUDA(cudaStreamSynchronize(stream));
+    if (w) {
+        const uint32_t zero = 0;
+        DSX_CUDA(cudaMemcpyToSymbolAsync(g_glue_error, &zero, 4, 0, cudaMemcpyHostToDevice, stream));
+        DSX_CUDA(cudaStreamSynchronize(stream));
+    }
+    if (error_word) *error_word = w;
+    if (w) return set_error(DSX_ERR_DEVICE, "a norm / residual-mix kernel reported error word 0x%x (a bounded wait ran out)", w);
     return DSX_OK;
 }
 

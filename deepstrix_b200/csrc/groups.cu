@@ -110,6 +110,9 @@ int launch_group_build_static(const int32_t* selected, int64_t T, int n_used, in
                               cudaStream_t stream) {
     const int64_t P = T * n_used;
     const int64_t n_chunks = (P + kGroupChunk - 1) / kGroupChunk;
+    if (n_expert > kMaxExperts)
+        return set_error(DSX_ERR_UNSUPPORTED, "group_build_static: %d experts exceed the built-in scratch (at most %d)", n_expert,
+                         kMaxExperts);
     if (n_chunks > kStaticMaxChunks)
         return set_error(DSX_ERR_UNSUPPORTED,
                          "group_build_static: %lld picks exceed the built-in scratch (at most %d picks); use dsx_moe_group_build",

@@ -661,7 +661,7 @@ router_fused_kernel(const __nv_bfloat16* __restrict__ x, int T, const float* __r
 // NI = H / 128 when the launcher knows it (0 otherwise): a warp then keeps its router row in NI x 4
 // registers for the whole kernel and the tile loop reads only tokens from shared memory, whose
 // bandwidth is what bounds this phase.
-// counters[0]: barrier arrivals, counters[1]: ticket; both return to zero.
+// counters[0]: barrier arrivals, counters[1]: ticket, counters[2]: a block gave up waiting; all return to zero.
 constexpr int kWideRows = 2;
 constexpr int kWideWarps = 8;
 constexpr int kWideTile = 8;
@@ -771,24 +771,41 @@ router_fused_wide_kernel(const __nv_bfloat16* __restrict__ x, int T, const float
             arrived = __ldcg(&counters[0]) >= gridDim.x;
             if (!arrived) __nanosleep(64);
         }
-        if (!arrived) atomicOr(error_word, 8u);
+        if (!arrived) {   // some blocks of the grid never became resident: the logits are incomplete
+            atomicOr(error_word, 8u);
+            atomicExch(&counters[2], 1u);
+        }
+        s_flag = arrived ? 1 : 0;
         __threadfence();
     }
     __syncthreads();
     float* s_score = reinterpret_cast<float*>(fsm);   // rows and tokens are no longer needed
-    for (int tok = blockIdx.x + warp * gridDim.x; tok < T; tok += kWideWarps * gridDim.x) {
-        const float* lrow = logits + (int64_t)tok * E;
-        topk_one_token<VPL>([&](int ee) { return __ldcg(lrow + ee); }, bias, cfg, selected + (int64_t)tok * cfg.n_used,
-                            weights + (int64_t)tok * cfg.n_used, s_score + warp * E);
-    }
+    if (s_flag)
+        for (int tok = blockIdx.x + warp * gridDim.x; tok < T; tok += kWideWarps * gridDim.x) {
+            const float* lrow = logits + (int64_t)tok * E;
+            topk_one_token<VPL>([&](int ee) { return __ldcg(lrow + ee); }, bias, cfg, selected + (int64_t)tok * cfg.n_used,
+                                weights + (int64_t)tok * cfg.n_used, s_score + warp * E);
+        }
     // ---- last block of the launch?
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_flag = (atomicAdd(&counters[1], 1u) == gridDim.x - 1) ? 1 : 0;
     __syncthreads();
     if (!s_flag) return;
-    if (threadIdx.x == 0) { counters[0] = 0u; counters[1] = 0u; }   // every block has left the barrier: it took a ticket
+    const bool failed = __ldcg(&counters[2]) != 0u;
+    __syncthreads();
+    if (threadIdx.x == 0) { counters[0] = 0u; counters[1] = 0u; counters[2] = 0u; }   // every block has left the barrier: it took a ticket
     __threadfence();
+    if (failed) {
+        // a barrier wait ran out: no picks are trustworthy, so the expert kernels get an empty work list
+        // (the error word tells the host; the output rows of this call are undefined)
+        for (int i = threadIdx.x; i <= E; i += kWideWarps * 32) {
+            if (i < E) hist[i] = 0;
+            offsets[i] = 0;
+        }
+        if (threadIdx.x == 0) n_work_items[0] = 0;
+        return;
+    }
     const int P = T * cfg.n_used;
     for (int i = threadIdx.x; i < P; i += kWideWarps * 32) s_sel[i] = __ldcg(selected + i);
     __syncthreads();

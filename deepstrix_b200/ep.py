@@ -241,9 +241,16 @@ class PeerMemoryComm:
         self._moe._check(self._moe.lib().dsx_ep_counts(self._h, self._C.byref(p)))
         return _as_tensor(p.value, (self.world,), "<i4")
 
+    def set_barrier_polls(self, polls: int):
+        """Polls (>= 100 ns each) a barrier waits for its peers before it gives up with error bit 1."""
+        self._moe._check(self._moe.lib().dsx_ep_set_barrier_polls(self._h, self._C.c_uint32(polls)))
+
     def check(self) -> int:
+        """The exchange kernels' error word (0 = clean; bit 1 = a barrier gave up waiting).  Clears it."""
         w = self._C.c_uint32()
-        self._moe._check(self._moe.lib().dsx_ep_check(self._h, self._moe._stream(), self._C.byref(w)))
+        rc = self._moe.lib().dsx_ep_check(self._h, self._moe._stream(), self._C.byref(w))
+        if rc != -3:   # DSX_ERR_DEVICE only says that the word is non-zero
+            self._moe._check(rc)
         return int(w.value)
 
     def close(self):
@@ -262,7 +269,9 @@ class ExpertParallelPeerMemory:
     """ExpertParallelMoe's step with the peer-memory transport (GPU ranks of one node).
 
     local_compute(rows, selected, weights) must accept world*cap rows whose unused slots carry picks of -1
-    (``MoeLayer.forward_picks`` does) and return one bf16 row per slot."""
+    (``MoeLayer.forward_picks`` does) and return one bf16 row per slot.  shared_compute runs on a side
+    stream at the same time as local_compute: the two callables must not share a ``MoeLayer`` (a layer's
+    workspace serves one call at a time)."""
 
     def __init__(self, n_expert: int, comm: PeerMemoryComm, local_compute: Callable, shared_compute: Callable = None):
         self.n_expert, self.comm = n_expert, comm

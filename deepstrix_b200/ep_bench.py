@@ -72,6 +72,9 @@ def selfcheck(rank: int, world: int, use_peer: bool = True):
     shared = moe.RoutedExpertWeights.from_host(cfg.fmt, H, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
     rw, rb = torch.from_numpy(w["router_w"]).cuda(), torch.from_numpy(w["router_bias"]).cuda()
     part = moe.MoeLayer(cfg, shard, shared, rw, rb, max_tokens=160 * world)
+    # the shared expert runs on a side stream while the owned experts run on the main one: a layer's
+    # workspace (groups, mid, partial rows) serves one call at a time, so the shared pass gets its own
+    part_sh = moe.MoeLayer(cfg, shard, shared, rw, rb, max_tokens=160)
     router = moe.RouterTopk(cfg.router)
     comm = open_peer_memory(world, rank, 160, H, k) if use_peer else None
     worst = 0.0
@@ -80,7 +83,7 @@ def selfcheck(rank: int, world: int, use_peer: bool = True):
         sel, wt = router.launch_batched(router.logits(x, rw), rb)
         none_sel = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
         ep = ExpertParallelMoe(E, None, lambda xr, s, ww: part.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False),
-                               lambda xr: part.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
+                               lambda xr: part_sh.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
         got = ep.forward(x, sel, wt)
         # the peer-memory transport moves the same rows and adds in the same order; the owner sees all
         # world*cap slots at once, so it may take the other kernel family: compare both with the unsharded layer
@@ -89,10 +92,10 @@ def selfcheck(rank: int, world: int, use_peer: bool = True):
         worst = max(worst, float((got - ref).norm() / ref.norm()))
         if comm is not None:
             ep2 = ExpertParallelPeerMemory(E, comm, lambda xr, s, ww: part.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False),
-                                           lambda xr: part.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
+                                           lambda xr: part_sh.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
             got2 = ep2.forward(x, sel.contiguous(), wt.contiguous()).float()
             worst = max(worst, float((got2 - ref).norm() / ref.norm()))
-    assert part.check() == 0 and full.check() == 0 and (comm is None or comm.check() == 0)
+    assert part.check() == 0 and part_sh.check() == 0 and full.check() == 0 and (comm is None or comm.check() == 0)
     dist.barrier()
     if comm is not None:
         comm.close()

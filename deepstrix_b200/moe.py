@@ -377,8 +377,11 @@ class MoeLayer:
         return {n: float(v) for n, v in zip(self.STAGES, ms)}
 
     def check(self) -> int:
+        """The layer's device-side error word (0 = clean).  Clears it."""
         w = C.c_uint32()
-        _check(lib().dsx_moe_layer_check(self._h, _stream(), C.byref(w)))
+        rc = lib().dsx_moe_layer_check(self._h, _stream(), C.byref(w))
+        if rc != -3:   # DSX_ERR_DEVICE only says that the word is non-zero
+            _check(rc)
         return w.value
 
 

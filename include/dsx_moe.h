@@ -276,7 +276,12 @@ DSX_API int dsx_moe_layer_set_weights(dsx_moe_layer* layer, const dsx_expert_sto
 
 /* x, out: DEVICE bf16 [T, hidden].  logits_in: optional DEVICE f32 [T, n_expert];
  * when given the router GEMV is skipped and these logits drive the routing
- * (the "pinned routing" of het/fidelity_tap.rs).  Asynchronous on `stream`. */
+ * (the "pinned routing" of het/fidelity_tap.rs).  Asynchronous on `stream`.
+ * Batches of 9..64 tokens route with one kernel whose n_expert/2 blocks meet at a barrier: they must all
+ * be resident at once, so no other stream may occupy the device's SMs with long-running kernels while
+ * this call runs.  If some blocks cannot start, the waiting ones give up after a bounded time, error
+ * bit 8 is set (dsx_moe_layer_check returns DSX_ERR_DEVICE), the expert kernels of that call get an
+ * empty work list and its output rows are undefined. */
 DSX_API int dsx_moe_layer_forward(dsx_moe_layer* layer, const void* x_bf16, int64_t T, void* out_bf16,
                                   const float* logits_in, dsx_stream_t stream);
 /* Same, with HOST buffers: copies x in, runs, copies out back, synchronises. */
@@ -329,6 +334,11 @@ DSX_API uint64_t dsx_launch_count(int reset);
  * (out_bf16) and / or the f32 rows the reference writes (out_f32); either may be NULL. */
 DSX_API int dsx_rms_norm_rows(const float* x, const float* weight, int64_t T, int64_t n, float eps, float* out_f32,
                               void* out_bf16, dsx_stream_t stream);
+/* Reads (and clears) the device-side error word of the two kernels of this section on the current
+ * device; synchronises the stream.  Non-zero (bit 1: a row copy inside dsx_rms_norm_rows never
+ * arrived within its bounded wait, rows of that call are missing) returns DSX_ERR_DEVICE.
+ * The reference has no such word: its kernels use no bounded waits. */
+DSX_API int dsx_glue_check(dsx_stream_t stream, uint32_t* error_word);
 /* hc_post_batched (kernels/hc_post.hip:36-68; src/head.rs:267-372; het/forward_layer.rs:3130-3152):
  *   out_hc[t, dst, d] = block_out[t, d] * post[t, dst] + sum_src comb[t, dst + src * n_hc] * residual_hc[t, src, d]
  * (one fused multiply-add per src, in src order).  block_out is the layer's bf16 output
@@ -368,6 +378,11 @@ DSX_API int dsx_ep_dispatch(dsx_ep_comm* comm, const void* x_bf16, const int32_t
                             int64_t T, int n_expert, dsx_stream_t stream);
 /* All ranks' earlier stores are visible after it.  The wait is bounded (error bit 1, see dsx_ep_check). */
 DSX_API int dsx_ep_barrier(dsx_ep_comm* comm, dsx_stream_t stream);
+/* How long a barrier waits for its peers before it gives up: `polls` polls of at least 100 ns each
+ * (default 2^24, seconds).  A short limit lets a supervisor (or a test) see a missing rank as error
+ * bit 1 within milliseconds; the kernel returns normally and the context stays usable.  The reference's
+ * counterpart is the request timeout of its TCP transport (het/remote_experts.rs, RemoteExpertClient). */
+DSX_API int dsx_ep_set_barrier_polls(dsx_ep_comm* comm, uint32_t polls);
 /* Received rows [world*cap, hidden] bf16, their picks [world*cap, n_used] (-1 in unused slots) and weights. */
 DSX_API int dsx_ep_prepare(dsx_ep_comm* comm, const void** x_rows, const int32_t** selected, const float** weights,
                            int64_t* n_slots, dsx_stream_t stream);
@@ -377,7 +392,8 @@ DSX_API int dsx_ep_give_back(dsx_ep_comm* comm, const void* partial_rows_bf16, d
 DSX_API int dsx_ep_sum(dsx_ep_comm* comm, const void* shared_bf16, int64_t T, void* out_bf16, dsx_stream_t stream);
 /* Device array of `world` ints: rows received from every source this step (valid after the first barrier). */
 DSX_API int dsx_ep_counts(dsx_ep_comm* comm, const int32_t** counts);
-/* Reads and clears the error word (bit 1: a barrier gave up waiting); synchronises the stream. */
+/* Reads and clears the error word (bit 1: a barrier gave up waiting); synchronises the stream.
+ * Returns DSX_ERR_DEVICE when the word is non-zero, like dsx_moe_layer_check. */
 DSX_API int dsx_ep_check(dsx_ep_comm* comm, dsx_stream_t stream, uint32_t* error_word);
 
 #ifdef __cplusplus

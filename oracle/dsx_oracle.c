@@ -704,11 +704,27 @@ static void expert_ffn(int fmt, const uint8_t* gq, const uint8_t* gs, const uint
         for (int64_t r = 0; r < F; r++) {
             dequant_row(fmt, gq, gs, H, r, row);
             dequant_row(fmt, uq, us, H, r, row2);
+            /* four tokens at a time: eight independent sums in flight, each still added in k order */
+            double ag4[4], au4[4];
             for (int i = 0; i < n; i++) {
-                double ag = 0.0, au = 0.0;
-                const float* x = xs[i];
-                for (int64_t k = 0; k < H; k++) { ag += (double)row[k] * x[k]; au += (double)row2[k] * x[k]; }
-                float g = (float)ag, u = (float)au;
+                if ((i & 3) == 0) {
+                    const int m4 = n - i < 4 ? n - i : 4;
+                    const float* x0 = xs[i];
+                    const float* x1 = xs[i + (m4 > 1 ? 1 : 0)];
+                    const float* x2 = xs[i + (m4 > 2 ? 2 : 0)];
+                    const float* x3 = xs[i + (m4 > 3 ? 3 : 0)];
+                    double g0 = 0.0, g1 = 0.0, g2 = 0.0, g3 = 0.0, u0 = 0.0, u1 = 0.0, u2 = 0.0, u3 = 0.0;
+                    for (int64_t k = 0; k < H; k++) {
+                        const double a = (double)row[k], b = (double)row2[k];
+                        g0 += a * x0[k]; u0 += b * x0[k];
+                        g1 += a * x1[k]; u1 += b * x1[k];
+                        g2 += a * x2[k]; u2 += b * x2[k];
+                        g3 += a * x3[k]; u3 += b * x3[k];
+                    }
+                    ag4[0] = g0; ag4[1] = g1; ag4[2] = g2; ag4[3] = g3;
+                    au4[0] = u0; au4[1] = u1; au4[2] = u2; au4[3] = u3;
+                }
+                float g = (float)ag4[i & 3], u = (float)au4[i & 3];
                 if (clamp > 1.0e-6f) {
                     if (g > clamp) g = clamp;
                     if (u > clamp) u = clamp;
@@ -724,11 +740,21 @@ static void expert_ffn(int fmt, const uint8_t* gq, const uint8_t* gs, const uint
 #pragma omp for schedule(static)
         for (int64_t r = 0; r < H; r++) {
             dequant_row(fmt, dq, ds, F, r, row);
-            for (int i = 0; i < n; i++) {
-                double a = 0.0;
-                const float* m = mid + (int64_t)i * F;
-                for (int64_t k = 0; k < F; k++) a += (double)row[k] * m[k];
-                outs[i][r] = (float)a;
+            for (int i = 0; i < n; i += 4) {
+                const int m4 = n - i < 4 ? n - i : 4;
+                const float* m0 = mid + (int64_t)i * F;
+                const float* m1 = mid + (int64_t)(i + (m4 > 1 ? 1 : 0)) * F;
+                const float* m2 = mid + (int64_t)(i + (m4 > 2 ? 2 : 0)) * F;
+                const float* m3 = mid + (int64_t)(i + (m4 > 3 ? 3 : 0)) * F;
+                double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+                for (int64_t k = 0; k < F; k++) {
+                    const double w = (double)row[k];
+                    a0 += w * m0[k]; a1 += w * m1[k]; a2 += w * m2[k]; a3 += w * m3[k];
+                }
+                outs[i][r] = (float)a0;
+                if (m4 > 1) outs[i + 1][r] = (float)a1;
+                if (m4 > 2) outs[i + 2][r] = (float)a2;
+                if (m4 > 3) outs[i + 3][r] = (float)a3;
             }
         }
         free(row);

@@ -31,3 +31,23 @@ def oracle():
     from oracle import oracle as o
     o.build()
     return o
+
+
+@pytest.fixture(scope="session")
+def full_mxfp4():
+    """The full-size MXFP4 layer (hidden 4096, 256 + 1 experts of width 2048) resident on the GPU, built once
+    per test session: generating its 3.4 GB of synthetic weights takes most of a minute.  The decode,
+    prefill and mid-batch configurations share these weights, as the workload definition says."""
+    import torch
+
+    from deepstrix_b200 import moe, synth
+    from deepstrix_b200.config import CONFIGS
+    cfg = CONFIGS[1]
+    w = synth.make_layer(cfg, 1)
+    routed = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, w["gate"], w["up"], w["down"])
+    shared = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
+    rw = torch.from_numpy(w["router_w"]).cuda()
+    rb = torch.from_numpy(w["router_bias"]).cuda()
+    yield {"cfg": cfg, "w": w, "routed": routed, "shared": shared, "rw": rw, "rb": rb}
+    routed.close()
+    shared.close()

@@ -22,7 +22,7 @@ def _picks(rng, T, k, E):
     return sel
 
 
-def test_static_scratch_matches_allocating_entry_point_twice_in_a_row():
+def test_static_scratch_matches_allocating_entry_point_twice_in_a_row(oracle):
     import torch
     from deepstrix_b200 import moe
     assert torch.cuda.is_available()
@@ -40,6 +40,12 @@ def test_static_scratch_matches_allocating_entry_point_twice_in_a_row():
         for name, g, w, m in (("hist", got[0], want[0], E), ("offsets", got[1], want[1], E + 1),
                               ("perm", got[2], want[2], n), ("work_items", got[3], want[3], ni)):
             assert torch.equal(g[:m], w[:m]), name
+        # and against the CPU oracle's group inversion and work items
+        oh, oo, op = oracle.group_build(sel.cpu().numpy(), E)
+        assert np.array_equal(got[0].cpu().numpy(), oh) and np.array_equal(got[1].cpu().numpy(), oo)
+        assert np.array_equal(got[2].cpu().numpy()[: op.size], op)
+        oi, on = oracle.work_items(oh, chunk)
+        assert on == ni and np.array_equal(got[3].cpu().numpy()[:on], oi)
 
 
 def test_static_scratch_refuses_oversized_input():
@@ -50,3 +56,7 @@ def test_static_scratch_refuses_oversized_input():
     with pytest.raises(moe.DsxError) as e:
         moe.MoeGroupBuilder.launch_static(sel, 256, 32)
     assert e.value.code == -2 and "131072" in str(e.value)
+    sel = torch.zeros((4, 8), dtype=torch.int32, device="cuda")
+    with pytest.raises(moe.DsxError) as e:
+        moe.MoeGroupBuilder.launch_static(sel, 544, 32)               # more experts than the scratch has columns for
+    assert e.value.code == -2
