@@ -12,6 +12,9 @@ import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libdsx_moe.so")
+# one of the library's kernels as a stand-alone code object, for callers that load kernels by name
+# (dsx_module_load_data / dsx_module_get_function / dsx_function_launch)
+CUBIN_PATH = os.path.join(_HERE, "kernels", "dsx_combine.cubin")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 EXTRA = os.environ.get("DSX_NVCC_EXTRA", "").split()
 FLAGS = EXTRA + [
@@ -25,7 +28,7 @@ def sources():
 
 
 def stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+    if not os.path.exists(LIB_PATH) or not os.path.exists(CUBIN_PATH):
         return True
     t = os.path.getmtime(LIB_PATH)
     deps = sources() + glob.glob(os.path.join(_HERE, "csrc", "*.cuh")) + glob.glob(os.path.join(_HERE, "..", "include", "*.h"))
@@ -56,6 +59,9 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         raise RuntimeError("nvcc failed")
     cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH] + objs
     subprocess.run(cmd, check=True)
+    os.makedirs(os.path.dirname(CUBIN_PATH), exist_ok=True)
+    subprocess.run([NVCC, "-cubin", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+                    os.path.join(_HERE, "csrc", "combine.cu"), "-o", CUBIN_PATH], check=True)
     return LIB_PATH
 
 

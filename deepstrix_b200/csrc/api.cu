@@ -33,6 +33,11 @@ struct dsx_expert_store {
     int64_t H = 0, F = 0;
     uint8_t *gu_nib = nullptr, *gu_sc = nullptr, *dn_nib = nullptr, *dn_sc = nullptr;
     int64_t gu_nib_stride = 0, gu_sc_stride = 0, dn_nib_stride = 0, dn_sc_stride = 0;  // bytes per slot
+    // MXFP4 only (null for a decode-only store): the tensor-core planes of prefill_mx.cu.  Codes K-major
+    // ([slot][gate|up][ffn][hidden/2] and [slot][hidden][ffn/2], the HF byte layout) and the block scales as
+    // 512-byte scale-factor chunks (layout: kmajor_mxfp4_kernel in repack.cu).
+    uint8_t *km_gu = nullptr, *km_dn = nullptr, *sf_gu = nullptr, *sf_dn = nullptr;
+    int64_t km_gu_stride = 0, km_dn_stride = 0, sf_gu_stride = 0, sf_dn_stride = 0;  // bytes per slot
     uint8_t* stage = nullptr;  // device staging for host sources
     size_t stage_bytes = 0;
     size_t device_bytes = 0;
@@ -207,7 +212,12 @@ int dsx_bytes_per_expert(int fmt, int64_t k, int64_t rows, size_t* bytes) {
 }
 
 int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int64_t hidden, int64_t ffn) {
+    return dsx_expert_store_create_ex(store, fmt, n_slots, hidden, ffn, 0);
+}
+
+int dsx_expert_store_create_ex(dsx_expert_store** store, int fmt, int n_slots, int64_t hidden, int64_t ffn, uint32_t flags) {
     DSX_REQUIRE(fmt == DSX_FMT_MXFP4 || fmt == DSX_FMT_Q8_0, "expert_store: format %d", fmt);
+    DSX_REQUIRE((flags & ~(uint32_t)DSX_STORE_DECODE_ONLY) == 0, "expert_store: unknown flags 0x%x", flags);
     DSX_REQUIRE(n_slots >= 1 && hidden > 0 && ffn > 0 && hidden % 256 == 0 && ffn % 256 == 0,
                 "expert_store: %d slots, hidden %lld, ffn %lld (both must be multiples of 256)", n_slots, (long long)hidden, (long long)ffn);
     dsx_expert_store* s = new (std::nothrow) dsx_expert_store();
@@ -223,6 +233,17 @@ int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int6
     if (e == cudaSuccess) e = cudaMalloc(&s->gu_sc, n * s->gu_sc_stride);
     if (e == cudaSuccess) e = cudaMalloc(&s->dn_nib, n * s->dn_nib_stride);
     if (e == cudaSuccess) e = cudaMalloc(&s->dn_sc, n * s->dn_sc_stride);
+    const bool tensor_planes = fmt == DSX_FMT_MXFP4 && !(flags & DSX_STORE_DECODE_ONLY);
+    if (tensor_planes) {
+        s->km_gu_stride = ffn * hidden;          // two matrices of ffn x hidden / 2 bytes
+        s->km_dn_stride = hidden * ffn / 2;
+        s->sf_gu_stride = ffn * hidden / 16;     // one byte per 32 weights, two matrices
+        s->sf_dn_stride = hidden * ffn / 32;
+        if (e == cudaSuccess) e = cudaMalloc(&s->km_gu, n * s->km_gu_stride);
+        if (e == cudaSuccess) e = cudaMalloc(&s->km_dn, n * s->km_dn_stride);
+        if (e == cudaSuccess) e = cudaMalloc(&s->sf_gu, n * s->sf_gu_stride);
+        if (e == cudaSuccess) e = cudaMalloc(&s->sf_dn, n * s->sf_dn_stride);
+    }
     if (e == cudaSuccess) e = cudaMalloc((void**)&s->d_scale_max, 256);
     if (e == cudaSuccess) e = cudaMemset(s->d_scale_max, 0, 256);
     // scale planes start at zero: the largest-scale scan covers whole planes, slots not loaded yet included
@@ -232,7 +253,8 @@ int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int6
         dsx_expert_store_destroy(s);
         return set_error((int)e, "expert_store: cudaMalloc failed: %s", cudaGetErrorString(e));
     }
-    s->device_bytes = n * (size_t)(s->gu_nib_stride + s->gu_sc_stride + s->dn_nib_stride + s->dn_sc_stride);
+    s->device_bytes = n * (size_t)(s->gu_nib_stride + s->gu_sc_stride + s->dn_nib_stride + s->dn_sc_stride + s->km_gu_stride +
+                                   s->km_dn_stride + s->sf_gu_stride + s->sf_dn_stride);
     *store = s;
     return DSX_OK;
 }
@@ -240,6 +262,7 @@ int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int6
 int dsx_expert_store_destroy(dsx_expert_store* s) {
     if (!s) return DSX_OK;
     cudaFree(s->gu_nib); cudaFree(s->gu_sc); cudaFree(s->dn_nib); cudaFree(s->dn_sc); cudaFree(s->stage); cudaFree(s->d_scale_max);
+    cudaFree(s->km_gu); cudaFree(s->km_dn); cudaFree(s->sf_gu); cudaFree(s->sf_dn);
     delete s;
     return DSX_OK;
 }
@@ -275,10 +298,20 @@ int dsx_expert_store_load(dsx_expert_store* st, int slot, int which, int src_lay
         st->scale_dirty = true;
         return DSX_OK;
     };
+    // the same source once more into the tensor-core planes (MXFP4 stores that keep them)
+    auto tensor_planes = [&](const uint8_t* dq, const uint8_t* ds, int slot0, int n_mats) -> int {
+        if (!st->km_gu) return DSX_OK;
+        uint8_t* km = down ? st->km_dn : st->km_gu;
+        uint8_t* sf = down ? st->sf_dn : st->sf_gu;
+        const int64_t kstr = down ? st->km_dn_stride : st->km_gu_stride, fstr = down ? st->sf_dn_stride : st->sf_gu_stride;
+        return launch_kmajor_mxfp4(src_layout, dq, ds, rows, K, down ? -1 : pair_index, n_mats, (int64_t)qb, (int64_t)sb, km + slot0 * kstr, kstr,
+                                   sf + slot0 * fstr, fstr, stream);
+    };
     if (src_on_device) {
         if (int rc = launch_repack(st->fmt, src_layout, (const uint8_t*)q, (const uint8_t*)s, rows, K, nib + first * nstr,
                                    sc + first * sstr, pair_stride, pair_index, count, (int64_t)qb, (int64_t)sb, nstr, sstr, stream))
             return rc;
+        if (int rc = tensor_planes((const uint8_t*)q, (const uint8_t*)s, first, count)) return rc;
         return fold_scales();
     }
     // host source: stage through device memory in batches
@@ -302,6 +335,7 @@ int dsx_expert_store_load(dsx_expert_store* st, int slot, int which, int src_lay
         if (int rc = launch_repack(st->fmt, src_layout, dq, sb ? ds : nullptr, rows, K, nib + (first + b0) * nstr,
                                    sc + (first + b0) * sstr, pair_stride, pair_index, nb, (int64_t)qb, (int64_t)sb, nstr, sstr, stream))
             return rc;
+        if (int rc = tensor_planes(dq, sb ? ds : nullptr, first + b0, nb)) return rc;
         DSX_CUDA(cudaStreamSynchronize(stream));  // the staging buffer is reused
     }
     return fold_scales();
@@ -321,12 +355,20 @@ int dsx_expert_store_clone(const dsx_expert_store* src, dsx_expert_store** dst, 
     cudaStream_t stream = (cudaStream_t)stream_;
     DSX_REQUIRE(src && dst, "expert_store_clone: null argument");
     dsx_expert_store* d = nullptr;
-    if (int rc = dsx_expert_store_create(&d, src->fmt, src->n_slots, src->H, src->F)) return rc;
+    if (int rc = dsx_expert_store_create_ex(&d, src->fmt, src->n_slots, src->H, src->F,
+                                            (src->fmt == DSX_FMT_MXFP4 && !src->km_gu) ? DSX_STORE_DECODE_ONLY : 0))
+        return rc;
     const size_t n = (size_t)src->n_slots;
     cudaError_t e = cudaMemcpyAsync(d->gu_nib, src->gu_nib, n * src->gu_nib_stride, cudaMemcpyDeviceToDevice, stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(d->gu_sc, src->gu_sc, n * src->gu_sc_stride, cudaMemcpyDeviceToDevice, stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(d->dn_nib, src->dn_nib, n * src->dn_nib_stride, cudaMemcpyDeviceToDevice, stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(d->dn_sc, src->dn_sc, n * src->dn_sc_stride, cudaMemcpyDeviceToDevice, stream);
+    if (src->km_gu) {
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d->km_gu, src->km_gu, n * src->km_gu_stride, cudaMemcpyDeviceToDevice, stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d->km_dn, src->km_dn, n * src->km_dn_stride, cudaMemcpyDeviceToDevice, stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d->sf_gu, src->sf_gu, n * src->sf_gu_stride, cudaMemcpyDeviceToDevice, stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d->sf_dn, src->sf_dn, n * src->sf_dn_stride, cudaMemcpyDeviceToDevice, stream);
+    }
     if (e == cudaSuccess) e = cudaMemcpyAsync(d->d_scale_max, src->d_scale_max, 4, cudaMemcpyDeviceToDevice, stream);
     d->scale_dirty = true;
     if (e != cudaSuccess) {
@@ -412,6 +454,16 @@ int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n_used, i
                                      (cudaStream_t)stream);
 }
 
+int dsx_reduce_partials(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared, const int32_t* selected,
+                        int expert_lo, int n_local, void* out_bf16, dsx_stream_t stream) {
+    DSX_REQUIRE(T >= 0 && n_used >= 1 && hidden >= 4, "reduce_partials: %lld tokens, %d slots, %lld columns", (long long)T, n_used, (long long)hidden);
+    if (T == 0) return DSX_OK;
+    DSX_REQUIRE(partial && out_bf16, "reduce_partials: null argument");
+    DSX_REQUIRE((((uintptr_t)partial | (uintptr_t)out_bf16) & 15) == 0, "reduce_partials: rows must be 16-byte aligned");
+    return launch_combine(partial, T, n_used, hidden, with_shared ? 1 : 0, selected, expert_lo, n_local, (__nv_bfloat16*)out_bf16,
+                          (cudaStream_t)stream);
+}
+
 // ------------------------------------------------------------------- layer
 struct StageTimer {  // brackets one stage with an event pair when profiling is on
     dsx_moe_layer* L; int stage; cudaStream_t stream;
@@ -426,6 +478,7 @@ static void layer_free(dsx_moe_layer* L) {
     cudaFree(L->logits); cudaFree(L->selected); cudaFree(L->weights); cudaFree(L->hist); cudaFree(L->offsets);
     cudaFree(L->perm); cudaFree(L->work_items); cudaFree(L->n_work_items); cudaFree(L->gs.chunk_hist); cudaFree(L->mid);
     cudaFree(L->partial); cudaFree(L->error_word); cudaFree(L->router_counters); cudaFree(L->item_recs); cudaFree(L->x_stage); cudaFree(L->out_stage);
+    prefill_mx_workspace_free(&L->pf);
     prefill_workspace_free(&L->pf);
 }
 
@@ -502,6 +555,12 @@ int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const
         delete L;
         return rc;
     }
+    if (L->pf.ready && routed->km_gu != nullptr)
+        if (int rc = prefill_mx_workspace_create(&L->pf, c, c.router.n_used)) {
+            layer_free(L);
+            delete L;
+            return rc;
+        }
     *layer = L;
     return DSX_OK;
 }
@@ -521,7 +580,7 @@ int dsx_moe_layer_set_weights(dsx_moe_layer* L, const dsx_expert_store* routed, 
     L->router_w = router_w; L->router_bias = router_bias;
     // the tensor maps of the prefill path describe the previous stores (a new store may even sit at a freed
     // store's address with another slot count): encode them again on the next use
-    for (int i = 0; i < 2; i++) L->pf.mapped_gu_nib[i] = L->pf.mapped_dn_nib[i] = nullptr;
+    for (int i = 0; i < 2; i++) L->pf.mapped_gu_nib[i] = L->pf.mapped_dn_nib[i] = L->pf.mapped_km_gu[i] = L->pf.mapped_km_dn[i] = nullptr;
     return DSX_OK;
 }
 
@@ -551,7 +610,11 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
     const dsx_moe_config& c = L->cfg;
     const int k = c.router.n_used, n_local = L->routed->n_slots;
     const bool shared = with_shared && L->shared != nullptr;
-    if (prefill_wanted(L->pf, c, L->routed->fmt, T) && scales_fit_f16(L->routed) && (!shared || scales_fit_f16(L->shared))) {
+    // MXFP4 stores with tensor-core planes: block-scaled FP4 MMAs on the stored codes and scales (any E8M0 scale);
+    // otherwise f16 operands expanded in shared memory (Q8_0; MXFP4 scales must then fit f16)
+    const bool mx = L->pf.mx_ready && L->routed->fmt == DSX_FMT_MXFP4 && L->routed->km_gu != nullptr &&
+                    (!shared || (L->shared->fmt == DSX_FMT_MXFP4 && L->shared->km_gu != nullptr));
+    if (prefill_wanted(L->pf, c, L->routed->fmt, T) && (mx || (scales_fit_f16(L->routed) && (!shared || scales_fit_f16(L->shared))))) {
         PrefillCall pc{};
         pc.x = x; pc.T = T; pc.selected = selected; pc.route_w = weights; pc.expert_lo = expert_lo; pc.n_local = n_local;
         pc.filter_picks = filter_picks; pc.with_shared = shared; pc.out = out;
@@ -564,6 +627,13 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
         if (shared) { pc.sh_gu_nib = L->shared->gu_nib; pc.sh_gu_sc = L->shared->gu_sc; pc.sh_dn_nib = L->shared->dn_nib; pc.sh_dn_sc = L->shared->dn_sc; }
         pc.fmt = L->routed->fmt;
         StageTimer tm(L, DSX_STAGE_GATE_UP, stream);
+        if (mx) {
+            pc.km_gu = L->routed->km_gu; pc.km_dn = L->routed->km_dn; pc.sf_gu = L->routed->sf_gu; pc.sf_dn = L->routed->sf_dn;
+            pc.km_gu_stride = L->routed->km_gu_stride; pc.km_dn_stride = L->routed->km_dn_stride;
+            pc.sf_gu_stride = L->routed->sf_gu_stride; pc.sf_dn_stride = L->routed->sf_dn_stride;
+            if (shared) { pc.sh_km_gu = L->shared->km_gu; pc.sh_km_dn = L->shared->km_dn; pc.sh_sf_gu = L->shared->sf_gu; pc.sh_sf_dn = L->shared->sf_dn; }
+            return prefill_mx_forward(&L->pf, c, pc, stream);
+        }
         return prefill_forward(&L->pf, c, pc, stream);
     }
     if (!groups_ready) {   // the one-launch decode router has already built them

@@ -8,15 +8,14 @@
 // No float atomics: the order of additions is fixed, so the result is reproducible.
 #include "dsx_common.cuh"
 
-namespace dsx {
-namespace {
-
-// One thread per (token, 4 consecutive rows).
-__global__ void __launch_bounds__(256)
-combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int64_t H, int with_shared,
+// One thread per (token, 4 consecutive rows).  Unmangled name: the kernel is also shipped as a stand-alone
+// code object (deepstrix_b200/kernels/dsx_combine.cubin) for callers that load kernels through
+// dsx_module_load_data / dsx_module_get_function, the way the reference embeds its kernels.
+extern "C" __global__ void __launch_bounds__(256)
+dsx_combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int64_t H, int with_shared,
                const int32_t* __restrict__ selected, int expert_lo, int n_local, __nv_bfloat16* __restrict__ out) {
-    pdl_launch_dependents();
-    pdl_wait();   // partial rows come from the down kernel
+    dsx::pdl_launch_dependents();
+    dsx::pdl_wait();   // partial rows come from the down kernel
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t per_row = H >> 2;
     if (gid >= T * per_row) return;
@@ -47,14 +46,14 @@ combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int64_t
     *(reinterpret_cast<uint2*>(out + t * H) + c) = o;
 }
 
-}  // namespace
+namespace dsx {
 
 int launch_combine(const float* partial, int64_t T, int n_used, int64_t H, int with_shared, const int32_t* selected,
                    int expert_lo, int n_local, __nv_bfloat16* out, cudaStream_t stream) {
     DSX_REQUIRE(H % 4 == 0, "combine: hidden must be a multiple of 4");
     if (T == 0) return DSX_OK;
     const int64_t n = T * (H / 4);
-    DSX_CUDA(launch_pdl(combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, partial, T, n_used, H, with_shared,
+    DSX_CUDA(launch_pdl(dsx_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, partial, T, n_used, H, with_shared,
                         selected, expert_lo, n_local, out));
     DSX_LAUNCHED();
     return DSX_OK;

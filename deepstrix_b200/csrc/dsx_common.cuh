@@ -186,6 +186,11 @@ int launch_repack(int fmt, int src_layout, const uint8_t* q, const uint8_t* s, i
 int launch_unpack(int fmt, const uint8_t* nib, const uint8_t* sc, int64_t rows, int64_t K, int pair_stride,
                   int pair_index, uint8_t* q_out, uint8_t* s_out, cudaStream_t stream);
 
+// MXFP4 source layout -> the tensor-core planes (K-major codes + scale-factor chunks); pair_index 0 / 1 = gate / up,
+// -1 = down (256-row tiles).
+int launch_kmajor_mxfp4(int src_layout, const uint8_t* q, const uint8_t* s, int64_t rows, int64_t K, int pair_index, int n_mats,
+                        int64_t src_q_stride, int64_t src_s_stride, uint8_t* km, int64_t km_stride, uint8_t* sf, int64_t sf_stride,
+                        cudaStream_t stream);
 int launch_max_byte(const uint8_t* p, int64_t bytes, uint32_t* out, cudaStream_t stream);
 
 // router.cu

@@ -525,9 +525,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
 }
 
 // ---------------------------------------------------------------- helpers
-__device__ __forceinline__ int seg_size(int cnt) {  // even split into <= 256-row segments, multiples of 16
-    const int n = (cnt + kSegRows - 1) / kSegRows;
-    return n == 0 ? 0 : min(kSegRows, (((cnt + n - 1) / n) + 15) & ~15);
+__device__ __forceinline__ int seg_size(int cnt, int seg_rows) {  // even split into segments of at most seg_rows rows, multiples of 16
+    const int n = (cnt + seg_rows - 1) / seg_rows;
+    return n == 0 ? 0 : min(seg_rows, (((cnt + n - 1) / n) + 15) & ~15);
 }
 
 // One block.  Segments sorted by expert; the shared expert's segments (expert id
@@ -543,7 +543,7 @@ __device__ __forceinline__ int seg_size(int cnt) {  // even split into <= 256-ro
 constexpr int kSmallMax = DSX_SMALL_MAX;   // at most 32 (4 work items of 8 rows per expert)
 static_assert(kSmallMax <= 32, "the work-item list holds 4 items per expert");
 
-__global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t P, int T_shared,
+__global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t P, int T_shared, int seg_rows,
                                       PrefillSeg* __restrict__ segs, int32_t* __restrict__ n_segs, int cap, int small_max,
                                       int32_t* __restrict__ small_items, int32_t* __restrict__ n_small) {
     __shared__ int s_base[513];
@@ -559,11 +559,11 @@ __global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n
                 for (int st = 0; st < cnt; st += 8) small_items[small++] = (int32_t)(((uint32_t)e << 16) | (uint32_t)st);
                 continue;
             }
-            const int sz = seg_size(cnt);
+            const int sz = seg_size(cnt, seg_rows);
             run += sz ? (cnt + sz - 1) / sz : 0;
         }
         s_base[n_local] = run;
-        const int sz = seg_size(T_shared);
+        const int sz = seg_size(T_shared, seg_rows);
         n_segs[0] = min(cap, run + (sz ? (T_shared + sz - 1) / sz : 0));
         if (n_small != nullptr) n_small[0] = small;
     }
@@ -572,7 +572,7 @@ __global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n
         const int cnt = e < n_local ? offsets[e + 1] - offsets[e] : T_shared;
         if (e < n_local && cnt <= small_max) continue;
         const int row0 = e < n_local ? offsets[e] : (int)P;
-        const int sz = seg_size(cnt);
+        const int sz = seg_size(cnt, seg_rows);
         for (int i = 0, st = 0; st < cnt; i++, st += sz) {
             const int idx = s_base[e] + i;
             if (idx < cap) segs[idx] = PrefillSeg{e, row0 + st, min(sz, cnt - st), 0};
@@ -610,6 +610,35 @@ gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library links no libcuda).
+int tmap_encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims, const cuuint64_t* strides,
+                const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        DSX_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !p) return set_error(DSX_ERR_UNSUPPORTED, "driver has no cuTensorMapEncodeTiled");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUresult r = fn(map, type, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(DSX_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return DSX_OK;
+}
+
+int launch_build_segments(const int32_t* offsets, int n_local, int64_t P, int T_shared, int seg_rows, PrefillSeg* segs, int32_t* n_segs,
+                          int cap, int small_max, int32_t* small_items, int32_t* n_small, cudaStream_t stream) {
+    build_segments_kernel<<<1, 512, 0, stream>>>(offsets, n_local, P, T_shared, seg_rows, segs, n_segs, cap, small_max, small_items, n_small);
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+namespace {
 
 int encode_rows_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
     static EncodeTiledFn fn = nullptr;
@@ -719,9 +748,9 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     if (int rc = launch_group_build(c.selected, c.T, c.n_used, c.n_local, c.expert_lo, kSegRows, 0, c.hist, c.offsets, c.perm,
                                     nullptr, nullptr, 0, c.gs, stream))
         return rc;
-    build_segments_kernel<<<1, 512, 0, stream>>>(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, ws->segs, ws->n_segs, ws->seg_cap,
-                                                 ws->small_max, ws->small_items, ws->n_small);
-    DSX_LAUNCHED();
+    if (int rc = launch_build_segments(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, kSegRows, ws->segs, ws->n_segs, ws->seg_cap,
+                                       ws->small_max, ws->small_items, ws->n_small, stream))
+        return rc;
     const int64_t rows = P + c.T;
     gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(c.x, c.perm, c.offsets, c.n_local, c.n_used, P, c.T,
                                                                       c.with_shared ? 1 : 0, cfg.hidden, ws->xperm);

@@ -32,6 +32,18 @@ struct PrefillWorkspace {
     CUtensorMap tmap_gu_nib[2], tmap_gu_sc[2], tmap_dn_nib[2], tmap_dn_sc[2];
     const void* mapped_gu_nib[2] = {nullptr, nullptr};   // planes the maps above were encoded for
     const void* mapped_dn_nib[2] = {nullptr, nullptr};
+    // ---- block-scaled MXFP4 path (prefill_mx.cu)
+    bool mx_ready = false;
+    uint8_t* xq = nullptr;          // [3 terms][cap_rows][K/2]: the sorted rows (then mid) as packed E2M1 terms
+    int64_t mx_term_stride = 0;     // bytes between terms
+    uint8_t* sfb = nullptr;         // their block scales: [segment][K/128][term][2][512]
+    PrefillSeg* mx_segs = nullptr;  // segments of at most 240 rows
+    int32_t mx_seg_cap = 0;
+    CUtensorMap tmap_xq, tmap_mq;   // xq as (bytes, row, term) for K = hidden / K = ffn
+    CUtensorMap tmap_km_gu[2], tmap_km_dn[2];            // K-major code planes; index 0 routed, 1 shared
+    const void* mapped_km_gu[2] = {nullptr, nullptr};
+    const void* mapped_km_dn[2] = {nullptr, nullptr};
+    int mapped_km_slots[2] = {0, 0};
 };
 
 struct PrefillCall {
@@ -54,11 +66,24 @@ struct PrefillCall {
     const uint8_t *gu_nib, *gu_sc, *dn_nib, *dn_sc;
     int64_t gu_nib_stride, gu_sc_stride, dn_nib_stride, dn_sc_stride;
     const uint8_t *sh_gu_nib, *sh_gu_sc, *sh_dn_nib, *sh_dn_sc;
+    // tensor-core planes of an MXFP4 store (null otherwise)
+    const uint8_t *km_gu, *km_dn, *sf_gu, *sf_dn;
+    int64_t km_gu_stride, km_dn_stride, sf_gu_stride, sf_dn_stride;
+    const uint8_t *sh_km_gu, *sh_km_dn, *sh_sf_gu, *sh_sf_dn;
 };
 
 int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid);
 void prefill_workspace_free(PrefillWorkspace* ws);
 bool prefill_wanted(const PrefillWorkspace& ws, const dsx_moe_config& cfg, int fmt, int64_t T);
 int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& call, cudaStream_t stream);
+// shared by the two tensor-core files
+int tmap_encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims, const cuuint64_t* strides,
+                const cuuint32_t* box, CUtensorMapSwizzle swizzle);
+int launch_build_segments(const int32_t* offsets, int n_local, int64_t P, int T_shared, int seg_rows, PrefillSeg* segs, int32_t* n_segs,
+                          int cap, int small_max, int32_t* small_items, int32_t* n_small, cudaStream_t stream);
+// block-scaled MXFP4 path (prefill_mx.cu); the workspace must have been through prefill_workspace_create
+int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used);
+void prefill_mx_workspace_free(PrefillWorkspace* ws);
+int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& call, cudaStream_t stream);
 
 }  // namespace dsx

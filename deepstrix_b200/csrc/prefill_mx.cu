@@ -1,0 +1,626 @@
+// Prefill-size grouped GEMM for MXFP4 experts on the block-scaled FP4 tensor cores
+// (tcgen05.mma.kind::mxf4.block_scale), weights and scales consumed as stored.
+//
+// Reference counterparts (paths relative to the deepstrix repository): the by-expert prefill kernels
+// and their matrix-core arms,
+//   gate/up  crates/v4flash-kernels/kernels/mxfp4_pair_matvec.hip:293-564, mxfp4_moe_wmma.hip:137-368
+//   down     crates/v4flash-kernels/kernels/mxfp4_matvec.hip:219-369,      mxfp4_moe_wmma.hip:370-388
+//   activation quantiser  crates/v4flash-kernels/kernels/q8_k_quantize.hip:23-90 (the reference turns
+//            activations into int8 blocks for its integer dot; here they become MXFP4 terms, see below)
+//
+// Operands.  The weights are E2M1 codes with one E8M0 scale per 32: exactly what kind::mxf4 multiplies,
+// so they go from HBM to shared memory by TMA (K-major rows, 64-byte swizzle) and their scales to tensor
+// memory by tcgen05.cp, untouched.  The other operand of kind::mxf4 is FP4 too, and one FP4 value per
+// activation is far too coarse (rel-L2 0.2 on the layer).  So an activation row x is written as a SUM of
+// three MXFP4 rows, x ~ t1 + t2 + t3: t1 = x rounded to E2M1 with a power-of-two scale per 32, t2 the
+// same rounding of the residual x - t1 with its own scales, t3 of x - t1 - t2 (mx_quantize_rows_kernel;
+// every step exact in f32, so the CPU can restate it bit for bit).  Each term is one more MMA into the same
+// accumulator.  Three terms leave a relative error of about 3e-3 on the layer output (two terms 2.5e-2,
+// a single E4M3 term 4.6e-2), for 1.5 times the tensor-core time of one FP8 pass.
+//
+// Tiling.  Expert-sorted rows are cut into segments of at most 240 rows of one expert.  A tile =
+// (segment, 256 weight rows): two M = 128 halves (gate rows f0.. and up rows f0.. for the first product,
+// so that a tensor-memory lane holds gate and up of one output row) with the segment's rows as N.  Tensor
+// memory: two accumulators of 240 columns, 8 columns of weight scales, 24 of activation scales = 512.
+// A pipeline stage is 128 reduction columns: 16 KB of weight codes, 3 x 16 KB of activation terms, 1 KB +
+// 3 KB of scale chunks, all arriving on one mbarrier; per stage the issuing thread copies the eight scale
+// chunks to tensor memory and issues 2 (k steps of 64) x 3 (terms) x 2 (halves) MMAs.
+// Warp roles: one producer thread, one MMA thread, 12 epilogue warps that read the accumulators
+// (tcgen05.ld), apply clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows
+// (f32).  Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
+// is freed and bit 2 of the layer's error word is set.
+#include "prefill.cuh"
+
+namespace dsx {
+namespace {
+
+constexpr int kEpiWarps = 12;
+constexpr int kThreads = (2 + kEpiWarps) * 32;
+constexpr int kSegRows = 240;                 // most rows of a segment (MMA N)
+constexpr int kBoxRows = 256;                 // rows a token-tile copy brings (rows past the segment are never multiplied)
+constexpr int kTerms = 3;                     // MXFP4 terms per activation row
+constexpr int kStageK = 128;                  // reduction columns per pipeline stage (4 scale blocks)
+constexpr int kRowBytes = kStageK / 2;        // packed bytes per row and stage: one 64-byte swizzle row
+constexpr int kStages = 3;
+constexpr int kABytes = 256 * kRowBytes;                 // 16384: two halves of 128 weight rows
+constexpr int kBTermBytes = kBoxRows * kRowBytes;        // 16384
+constexpr int kBBytes = kTerms * kBTermBytes;            // 49152
+constexpr int kSfChunk = 512;                            // 128 rows x 4 scale blocks
+constexpr int kSfaBytes = 2 * kSfChunk;
+constexpr int kSfbBytes = kTerms * 2 * kSfChunk;
+constexpr int kStageTx = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+constexpr int kSmemA = 0;
+constexpr int kSmemB = kSmemA + kStages * kABytes;
+constexpr int kSmemSfa = kSmemB + kStages * kBBytes;
+constexpr int kSmemSfb = kSmemSfa + kStages * kSfaBytes;
+constexpr int kSmemBar = kSmemSfb + kStages * kSfbBytes;
+constexpr int kNumBars = 2 * kStages + 2;
+constexpr int kSmemMisc = kSmemBar + kNumBars * 8;
+constexpr int kSmemTotal = kSmemMisc + 16 + 1024;        // + alignment slack
+static_assert(kSmemTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
+// tensor-memory columns
+constexpr uint32_t kAcc1Col = kSegRows;       // second accumulator
+constexpr uint32_t kSfaCol = 2 * kSegRows;    // 4 columns per 128-row half
+constexpr uint32_t kSfbCol = kSfaCol + 8;     // 8 columns per term (two chunks of 128 rows)
+static_assert(kSfbCol + 8 * kTerms <= 512, "tensor memory holds 512 columns");
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait that also gives up when another role of the block has aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; i++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 512 bytes of scale factors (32 rows of 16 bytes) from shared memory into 4 tensor-memory columns, the
+// same 16 bytes in all four lane quarters.
+__device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[128 x N] (+)= A[128 x 64] . B[N x 64]^T, E2M1 operands, one E8M0 scale per 32 columns of either operand.
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile with 64-byte rows and 64-byte swizzle: 8-row groups of 512 bytes.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);       // start address
+    d |= (uint64_t)(512u >> 4) << 32;               // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                         // descriptor version (sm_100)
+    d |= (uint64_t)4 << 61;                         // 64-byte swizzle
+    return d;
+}
+// Unswizzled 32 rows x 16 bytes (one scale-factor chunk): 8-row groups of 128 bytes.
+__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(128u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// kind::mxf4: E2M1 x E2M1 -> f32, E8M0 scales, both operands K-major, M = 128, K = 64; sf = byte (0 or 2) of the
+// 4-byte scale words that holds this k step's first block.
+__device__ __forceinline__ uint32_t mxf4_idesc(int n, uint32_t sf) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf << 4) | (sf << 29);
+}
+
+struct MxGemmArgs {
+    const PrefillSeg* segs;
+    const int32_t* n_segs;
+    int n_local;               // seg.expert == n_local -> shared expert
+    int K;                     // reduction length (hidden for gate/up, ffn for down)
+    int rows;                  // output rows of the matrix (ffn for gate/up, hidden for down)
+    int n_used;
+    int64_t P;                 // T * n_used: first row of the shared expert's rows
+    const int32_t* perm;
+    const float* route_w;
+    float clamp;
+    __half* mid;               // gate/up output [rows_total, ffn]
+    int64_t mid_stride;
+    float* partial;            // down output [rows_total, hidden]
+    const uint8_t* sfa;        // weight scale chunks, routed: [slot][row tile][K/128][2][512]
+    int64_t sfa_slot_stride;
+    const uint8_t* sfa_shared;
+    const uint8_t* sfb;        // activation scale chunks: [segment][K/128][term][2][512]
+    uint32_t* error_word;
+};
+
+template <bool GATE_UP>
+__global__ void __launch_bounds__(kThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
+               const __grid_constant__ CUtensorMap tmap_w_shared, const MxGemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = sbase + kSmemBar;
+    // FULL[s]: the stage's codes and scales have landed (TMA bytes); EMPTY[s]: the MMAs and scale copies reading
+    // stage s have completed (one tcgen05.commit); ACC_FULL / ACC_EMPTY: a tile's accumulators are complete / drained.
+    constexpr int FULL = 0, EMPTY = FULL + kStages, ACC_FULL = EMPTY + kStages, ACC_EMPTY = ACC_FULL + 1;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; i++) { mbar_init(bar(FULL + i), 1); mbar_init(bar(EMPTY + i), 1); }
+        mbar_init(bar(ACC_FULL), 1);
+        mbar_init(bar(ACC_EMPTY), kEpiWarps);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // all 512 columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32((const void*)tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_segs = a.n_segs[0];
+    const int n_mb = a.rows / (GATE_UP ? 128 : 256);   // 256-row tiles (gate/up: 128 gate + 128 up)
+    const int n_tiles = n_segs * n_mb;
+    const int n_kc = a.K / kStageK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t cnt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int si = tile / n_mb, mb = tile % n_mb;
+                const PrefillSeg seg = a.segs[si];
+                const bool sh = seg.expert == a.n_local;
+                const CUtensorMap* m_w = sh ? &tmap_w_shared : &tmap_w;
+                const int slot = sh ? 0 : seg.expert;
+                const uint8_t* sfa = (sh ? a.sfa_shared : a.sfa + (int64_t)slot * a.sfa_slot_stride) + (int64_t)mb * n_kc * kSfaBytes;
+                const uint8_t* sfb = a.sfb + (int64_t)si * n_kc * kSfbBytes;
+                // weights of this tile into L2 a few stages ahead of the ring
+                constexpr int kAhead = 6;
+                if (tile == (int)blockIdx.x)
+                    for (int kc = 0; kc < kAhead && kc < n_kc; kc++)
+                        tma_prefetch_4d(m_w, kc * kRowBytes, GATE_UP ? mb * 128 : mb * 256, 0, slot);
+                const int ntile = tile + gridDim.x;
+                PrefillSeg nseg = seg;
+                int nmb = mb;
+                if (ntile < n_tiles) { nseg = a.segs[ntile / n_mb]; nmb = ntile % n_mb; }
+                const bool nsh = nseg.expert == a.n_local;
+                for (int kc = 0; kc < n_kc && ok; kc++) {
+                    const int pk = kc + kAhead;
+                    if (pk < n_kc) tma_prefetch_4d(m_w, pk * kRowBytes, GATE_UP ? mb * 128 : mb * 256, 0, slot);
+                    else if (ntile < n_tiles)
+                        tma_prefetch_4d(nsh ? &tmap_w_shared : &tmap_w, (pk - n_kc) * kRowBytes, GATE_UP ? nmb * 128 : nmb * 256, 0,
+                                        nsh ? 0 : nseg.expert);
+                    const int s = cnt % kStages;
+                    ok = mbar_wait(bar(EMPTY + s), ((cnt / kStages) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(FULL + s), kStageTx);
+                    // weights: gate/up map = (bytes, row, matrix, slot) with a box of 64 x 128 x 2; down map = (bytes, row, 1, slot) with 64 x 256 x 1
+                    tma_load_4d(sbase + kSmemA + s * kABytes, m_w, kc * kRowBytes, GATE_UP ? mb * 128 : mb * 256, 0, slot, bar(FULL + s));
+                    // activation terms: (bytes, row, term), box 64 x 256 x 3
+                    tma_load_3d(sbase + kSmemB + s * kBBytes, &tmap_b, kc * kRowBytes, seg.row0, 0, bar(FULL + s));
+                    bulk_load(sbase + kSmemSfa + s * kSfaBytes, sfa + (int64_t)kc * kSfaBytes, kSfaBytes, bar(FULL + s));
+                    bulk_load(sbase + kSmemSfb + s * kSfbBytes, sfb + (int64_t)kc * kSfbBytes, kSfbBytes, bar(FULL + s));
+                    cnt++;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ----------------------------------------------------------- MMA issue
+        if (lane == 0) {
+            uint32_t tcnt = 0, s = 0, ph = 0;   // ring stage and its phase parity
+            bool ok = true;
+            const uint64_t a_desc0 = operand_desc(sbase + kSmemA), b_desc0 = operand_desc(sbase + kSmemB);
+            const uint64_t sfa_desc0 = scale_desc(sbase + kSmemSfa), sfb_desc0 = scale_desc(sbase + kSmemSfb);
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const PrefillSeg seg = a.segs[tile / n_mb];
+                const int n16 = max(16, (seg.n + 15) & ~15);
+                const uint32_t idesc0 = mxf4_idesc(n16, 0u), idesc1 = mxf4_idesc(n16, 2u);
+                ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // the previous tile's accumulators are drained
+                if (!ok) break;
+                tc_fence_after();
+                for (int kc = 0; kc < n_kc; kc++) {
+                    const uint32_t full = bar(FULL) + 8u * s;
+                    if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    // scales of this stage: 2 weight chunks, then 2 chunks for each of the 3 terms (16-byte units in the descriptor)
+                    const uint64_t sfa_d = sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4));
+                    const uint64_t sfb_d = sfb_desc0 + (uint64_t)(s * (kSfbBytes >> 4));
+                    tc_cp_scales(tmem_base + kSfaCol, sfa_d);
+                    tc_cp_scales(tmem_base + kSfaCol + 4, sfa_d + (kSfChunk >> 4));
+#pragma unroll
+                    for (int c = 0; c < 2 * kTerms; c++) tc_cp_scales(tmem_base + kSfbCol + 4 * c, sfb_d + (uint64_t)(c * (kSfChunk >> 4)));
+                    const uint64_t a_d = a_desc0 + (uint64_t)(s * (kABytes >> 4));
+                    const uint64_t b_d = b_desc0 + (uint64_t)(s * (kBBytes >> 4));
+#pragma unroll
+                    for (int ks = 0; ks < 2; ks++) {
+                        const uint32_t idesc = ks ? idesc1 : idesc0;
+#pragma unroll
+                        for (int t = 0; t < kTerms; t++) {
+                            const uint64_t bd = b_d + (uint64_t)(t * (kBTermBytes >> 4) + ks * 2);   // + 32 bytes per k step
+                            const uint32_t acc = (kc | ks | t) != 0 ? 1u : 0u;
+                            tc_mma_mxf4(tmem_base, a_d + (uint64_t)(ks * 2), bd, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol + 8 * t, acc);
+                            tc_mma_mxf4(tmem_base + kAcc1Col, a_d + (uint64_t)((kABytes >> 5) + ks * 2), bd, idesc, tmem_base + kSfaCol + 4,
+                                        tmem_base + kSfbCol + 8 * t, acc);
+                        }
+                    }
+                    tc_commit(bar(EMPTY) + 8u * s);   // arrives when the copies and MMAs above have read their operands
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+                if (ok) tc_commit(bar(ACC_FULL));
+                tcnt++;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        // Warp w may read lanes 32 * (w % 4) .. + 31 of tensor memory; the three warps of a lane quarter split
+        // the tile's 32-column chunks between them.
+        const int q = warp & 3, rank = (warp - 2) >> 2;
+        uint32_t tcnt = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const PrefillSeg seg = a.segs[tile / n_mb];
+            const int mb = tile % n_mb;
+            const bool sh = seg.expert == a.n_local;
+            ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const int r_in = q * 32 + lane;           // row inside a 128-row half
+            for (int c0 = 32 * rank; c0 < seg.n; c0 += 96) {
+                // lane j of the warp fetches the routing weight / output row of column c0 + j
+                float wv = 0.f;
+                int orow = 0;
+                if (c0 + lane < seg.n) {
+                    if (sh) { wv = 1.0f; orow = seg.row0 + c0 + lane; }
+                    else { const int ts = a.perm[seg.row0 + c0 + lane]; wv = a.route_w[ts]; orow = ts; }
+                }
+                uint32_t v0[32], v1[32];
+                tc_ld32(lane_addr + (uint32_t)c0, v0);
+                tc_ld32(lane_addr + kAcc1Col + (uint32_t)c0, v1);
+                tc_wait_ld();
+                if (GATE_UP) {
+                    __half* dst = a.mid + (int64_t)(seg.row0 + c0) * a.mid_stride + mb * 128 + r_in;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float wj = __shfl_sync(0xFFFFFFFFu, wv, j);
+                        if (c0 + j < seg.n) {
+                            float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
+                            if (a.clamp > 1.0e-6f) {
+                                gv = fminf(gv, a.clamp);
+                                uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
+                            }
+                            const float sig = __fdividef(1.0f, 1.0f + __expf(-gv));
+                            dst[(int64_t)j * a.mid_stride] = __float2half_rn(gv * sig * uv * wj);
+                        }
+                    }
+                } else {
+                    const int h = mb * 256 + r_in;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int rj = __shfl_sync(0xFFFFFFFFu, orow, j);
+                        if (c0 + j < seg.n) {
+                            float* dst = a.partial + (int64_t)rj * a.rows + h;
+                            dst[0] = __uint_as_float(v0[j]);
+                            dst[128] = __uint_as_float(v1[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
+            tcnt++;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error_word, 2u);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+// ------------------------------------------------------- activation terms
+// E8M0 byte of the block scale for a block whose largest magnitude is amax: the smallest power of two 2^(e-127)
+// with amax / 2^(e-127) <= 6 (the largest E2M1 value), kept inside [1, 253] so that the scale and its inverse are
+// normal floats.  amax = m * 2^E with m in [1, 2): e - 127 = E - 2, one more when m > 1.5.
+__device__ __forceinline__ uint32_t mx_scale_byte(float amax) {
+    const uint32_t b = __float_as_uint(amax);
+    const int e = (int)(b >> 23) - 2 + ((b & 0x7FFFFFu) > 0x400000u ? 1 : 0);
+    return (uint32_t)min(max(e, 1), 253);
+}
+// Eight floats -> eight E2M1 codes (round to nearest even, saturating), element i in nibble i.
+__device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8]) {
+    uint32_t out;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+        : "=r"(out)
+        : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+    return out;
+}
+// The eight values those codes stand for (exact).
+__device__ __forceinline__ void e2m1_unpack8(uint32_t q, float (&d)[8]) {
+    uint32_t h[4];
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(q));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+        d[2 * i] = f.x;
+        d[2 * i + 1] = f.y;
+    }
+}
+
+// One warp per expert-sorted row that lies inside a segment: the row (a token's bf16 row, found through the
+// permutation, or a row of f16 mid) becomes kTerms MXFP4 rows -- codes [term][row][K/2], scales into the
+// segment's scale-factor chunks.  A lane holds 8 consecutive values; four lanes make a 32-value block.
+template <bool FROM_TOKENS>
+__global__ void __launch_bounds__(256)
+mx_quantize_rows_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm, int n_used, int64_t P, int64_t rows_total, int K,
+                        const PrefillSeg* __restrict__ segs, const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq,
+                        int64_t term_stride, uint8_t* __restrict__ sfb) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows_total) return;
+    // the segment holding this row: the last one that starts at or before it (segments are sorted by first row)
+    const int n_segs = n_segs_p[0];
+    int lo = 0, hi = n_segs;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((int64_t)segs[mid].row0 <= row) lo = mid; else hi = mid;
+    }
+    if (n_segs == 0) return;
+    const PrefillSeg seg = segs[lo];
+    if (row < seg.row0 || row >= (int64_t)seg.row0 + seg.n) return;   // a row of an expert the grouped GEMV takes
+    const int r = (int)(row - seg.row0);
+    const int n_kc = K / kStageK;
+    uint8_t* sf_row = sfb + (int64_t)lo * n_kc * kSfbBytes + (r >> 7) * kSfChunk + (r & 31) * 16 + ((r >> 5) & 3) * 4;
+    const uint4* in;
+    if (FROM_TOKENS) {
+        const int64_t tok = row < P ? perm[row] / n_used : row - P;
+        in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + tok * K);
+    } else {
+        in = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(src) + row * K);
+    }
+    uint8_t* out_row = xq + row * (K >> 1) + lane * 4;
+    for (int i = 0; i < (K >> 8); i++) {
+        const uint4 raw = __ldg(in + i * 32 + lane);
+        const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (FROM_TOKENS) {
+                v[2 * j] = __uint_as_float(wds[j] << 16);
+                v[2 * j + 1] = __uint_as_float(wds[j] & 0xFFFF0000u);
+            } else {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wds[j]));
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kTerms; t++) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+            const uint32_t e = mx_scale_byte(amax);
+            const float inv = __uint_as_float((254u - e) << 23), scl = __uint_as_float(e << 23);
+            float sv[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) sv[j] = v[j] * inv;
+            const uint32_t codes = e2m1_pack8(sv);
+            *reinterpret_cast<uint32_t*>(out_row + (int64_t)t * term_stride + i * 128) = codes;
+            if (t + 1 < kTerms) {
+                float d[8];
+                e2m1_unpack8(codes, d);
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = __fmaf_rn(-d[j], scl, v[j]);   // exact: the residual
+            }
+            // the scales of 4 consecutive blocks (lanes 0,4,8,12 / 16,20,24,28) form one word of the chunk of stage 2i / 2i+1
+            const int base = lane & 16;
+            const uint32_t w = __shfl_sync(0xFFFFFFFFu, e, base) | (__shfl_sync(0xFFFFFFFFu, e, base + 4) << 8) |
+                               (__shfl_sync(0xFFFFFFFFu, e, base + 8) << 16) | (__shfl_sync(0xFFFFFFFFu, e, base + 12) << 24);
+            if ((lane & 15) == 0)
+                *reinterpret_cast<uint32_t*>(sf_row + ((int64_t)(2 * i + (lane >> 4)) * kTerms + t) * (2 * kSfChunk)) = w;
+        }
+    }
+}
+
+// (Re-)encode the weight maps when the layer points at other planes: gate/up as (bytes, row, matrix, slot)
+// with a box of 64 bytes x 128 rows x both matrices, down as (bytes, row, 1, slot) with 64 x 256.
+int map_weights(PrefillWorkspace* ws, int which, const uint8_t* km_gu, const uint8_t* km_dn, int64_t gu_stride, int64_t dn_stride,
+                int n_slots) {
+    if (ws->mapped_km_gu[which] == km_gu && ws->mapped_km_dn[which] == km_dn && ws->mapped_km_slots[which] == n_slots) return DSX_OK;
+    const int64_t H = ws->H, F = ws->F;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)(H / 2), (cuuint64_t)F, 2, (cuuint64_t)n_slots};
+        const cuuint64_t strides[3] = {(cuuint64_t)(H / 2), (cuuint64_t)(F * (H / 2)), (cuuint64_t)gu_stride};
+        const cuuint32_t box[4] = {(cuuint32_t)kRowBytes, 128, 2, 1};
+        if (int rc = tmap_encode(&ws->tmap_km_gu[which], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, km_gu, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
+            return rc;
+    }
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)(F / 2), (cuuint64_t)H, 1, (cuuint64_t)n_slots};
+        const cuuint64_t strides[3] = {(cuuint64_t)(F / 2), (cuuint64_t)(H * (F / 2)), (cuuint64_t)dn_stride};
+        const cuuint32_t box[4] = {(cuuint32_t)kRowBytes, 256, 1, 1};
+        if (int rc = tmap_encode(&ws->tmap_km_dn[which], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, km_dn, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
+            return rc;
+    }
+    ws->mapped_km_gu[which] = km_gu;
+    ws->mapped_km_dn[which] = km_dn;
+    ws->mapped_km_slots[which] = n_slots;
+    return DSX_OK;
+}
+
+}  // namespace
+
+int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used) {
+    ws->mx_ready = false;
+    // shapes the tiles cover: 128 gate + 128 up rows per tile, 256 down rows per tile, 128-column stages
+    if (cfg.ffn % 256 != 0 || cfg.hidden % 256 != 0 || (cfg.shared_ffn != 0 && cfg.shared_ffn != cfg.ffn)) return DSX_OK;
+    const int64_t Kmax = std::max(cfg.hidden, cfg.ffn);
+    ws->mx_seg_cap = cfg.router.n_expert + (int)((ws->cap_rows + kSegRows - 1) / kSegRows) + 8;
+    ws->mx_term_stride = ws->cap_rows * (Kmax / 2);
+    DSX_CUDA(cudaMalloc((void**)&ws->xq, (size_t)kTerms * (size_t)ws->mx_term_stride));
+    DSX_CUDA(cudaMalloc((void**)&ws->sfb, (size_t)ws->mx_seg_cap * (size_t)(Kmax / kStageK) * kSfbBytes));
+    DSX_CUDA(cudaMalloc((void**)&ws->mx_segs, sizeof(PrefillSeg) * (size_t)ws->mx_seg_cap));
+    // activation terms as (bytes, row, term): box 64 bytes x 256 rows x 3 terms
+    for (int g = 0; g < 2; g++) {
+        const int64_t K = g == 0 ? cfg.hidden : cfg.ffn;
+        const cuuint64_t dims[3] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->cap_rows, (cuuint64_t)kTerms};
+        const cuuint64_t strides[2] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->mx_term_stride};
+        const cuuint32_t box[3] = {(cuuint32_t)kRowBytes, (cuuint32_t)kBoxRows, (cuuint32_t)kTerms};
+        if (int rc = tmap_encode(g == 0 ? &ws->tmap_xq : &ws->tmap_mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ws->xq, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_64B))
+            return rc;
+    }
+    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    ws->mx_ready = true;
+    return DSX_OK;
+}
+
+void prefill_mx_workspace_free(PrefillWorkspace* ws) {
+    cudaFree(ws->xq);
+    cudaFree(ws->sfb);
+    cudaFree(ws->mx_segs);
+    ws->xq = nullptr; ws->sfb = nullptr; ws->mx_segs = nullptr; ws->mx_ready = false;
+}
+
+int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& c, cudaStream_t stream) {
+    const int64_t P = c.T * c.n_used, rows = P + c.T;
+    DSX_REQUIRE(rows <= ws->cap_rows, "prefill: %lld rows exceed the workspace (%lld)", (long long)rows, (long long)ws->cap_rows);
+    if (int rc = launch_group_build(c.selected, c.T, c.n_used, c.n_local, c.expert_lo, 256, 0, c.hist, c.offsets, c.perm, nullptr, nullptr, 0,
+                                    c.gs, stream))
+        return rc;
+    if (int rc = launch_build_segments(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, kSegRows, ws->mx_segs, ws->n_segs, ws->mx_seg_cap,
+                                       ws->small_max, ws->small_items, ws->n_small, stream))
+        return rc;
+    if (int rc = map_weights(ws, 0, c.km_gu, c.km_dn, c.km_gu_stride, c.km_dn_stride, c.n_local)) return rc;
+    const int shi = c.with_shared ? 1 : 0;   // without a shared expert the shared map aliases the routed one (never used)
+    if (c.with_shared)
+        if (int rc = map_weights(ws, 1, c.sh_km_gu, c.sh_km_dn, c.km_gu_stride, c.km_dn_stride, 1)) return rc;
+    const int64_t quant_rows = c.with_shared ? rows : P;
+    const unsigned qblocks = (unsigned)((quant_rows + 7) / 8);
+    // experts with a handful of rows: the decode kernels, over the same sorted rows and partial rows
+    GemvArgs v{};
+    v.fmt = c.fmt; v.shared_fmt = c.fmt; v.n_expert = c.n_local;
+    v.work_items = ws->small_items; v.n_work_items = ws->n_small; v.item_recs = nullptr; v.offsets = c.offsets; v.perm = c.perm;
+    v.route_w = c.route_w; v.n_used = c.n_used; v.T = c.T; v.clamp = cfg.clamp; v.x = c.x; v.mid = c.mid; v.mid_stride = cfg.ffn;
+    v.partial = c.partial; v.error_word = c.error_word;
+    MxGemmArgs g{};
+    g.segs = ws->mx_segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
+    g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.sfb = ws->sfb;
+    g.error_word = c.error_word;
+
+    // first product: K = hidden, rows = ffn
+    mx_quantize_rows_kernel<true><<<qblocks, 256, 0, stream>>>(c.x, c.perm, c.n_used, P, quant_rows, (int)cfg.hidden, ws->mx_segs, ws->n_segs,
+                                                               ws->xq, ws->mx_term_stride, ws->sfb);
+    DSX_LAUNCHED();
+    g.K = cfg.hidden; g.rows = cfg.ffn;
+    g.sfa = c.sf_gu; g.sfa_slot_stride = c.sf_gu_stride; g.sfa_shared = c.sh_sf_gu;
+    mx_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_xq, ws->tmap_km_gu[0], ws->tmap_km_gu[shi], g);
+    DSX_LAUNCHED();
+    if (ws->small_max > 0) {
+        v.K = cfg.hidden; v.rows = cfg.ffn; v.sh_rows = cfg.ffn;
+        v.nib = c.gu_nib; v.sc = c.gu_sc; v.nib_slot_stride = c.gu_nib_stride; v.sc_slot_stride = c.gu_sc_stride;
+        if (int rc = launch_gemv_gate_up(v, c.sm_count, stream)) return rc;
+    }
+    // second product: K = ffn, rows = hidden, over the terms of mid
+    mx_quantize_rows_kernel<false><<<qblocks, 256, 0, stream>>>(c.mid, nullptr, c.n_used, P, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs,
+                                                                ws->xq, ws->mx_term_stride, ws->sfb);
+    DSX_LAUNCHED();
+    g.K = cfg.ffn; g.rows = cfg.hidden;
+    g.sfa = c.sf_dn; g.sfa_slot_stride = c.sf_dn_stride; g.sfa_shared = c.sh_sf_dn;
+    mx_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mq, ws->tmap_km_dn[0], ws->tmap_km_dn[shi], g);
+    DSX_LAUNCHED();
+    if (ws->small_max > 0) {
+        v.K = cfg.ffn; v.rows = cfg.hidden; v.sh_rows = cfg.hidden;
+        v.nib = c.dn_nib; v.sc = c.dn_sc; v.nib_slot_stride = c.dn_nib_stride; v.sc_slot_stride = c.dn_sc_stride;
+        if (int rc = launch_gemv_down(v, c.sm_count, stream)) return rc;
+    }
+    return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr, c.expert_lo,
+                          c.n_local, c.out, stream);
+}
+
+}  // namespace dsx

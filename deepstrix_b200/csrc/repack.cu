@@ -162,6 +162,38 @@ __global__ void unpack_kernel(int fmt, const uint8_t* __restrict__ nib, const ui
     }
 }
 
+// The tensor-core planes of an MXFP4 matrix (prefill_mx.cu): codes K-major, i.e. the HF byte layout
+// [row][K/2] with element 2i in the low nibble, and the E8M0 block scales cut into the 512-byte chunks
+// the block-scaled MMA takes its scale factors from: chunk = 128 rows x 4 blocks (128 columns), byte
+// (row % 32) * 16 + (row / 32 % 4) * 4 + (block % 4).  Chunks are ordered [row tile][K / 128][2]: for gate
+// and up the pair index is the matrix (a tile of 128 gate rows and the same 128 up rows is one MMA
+// tile), for down it is the 128-row half of a 256-row tile.  One thread per (row, 32-column block).
+__global__ void kmajor_mxfp4_kernel(int layout, const uint8_t* __restrict__ q, const uint8_t* __restrict__ s, int64_t rows, int64_t K,
+                                    int pair_index, int64_t src_q_stride, int64_t src_s_stride, uint8_t* __restrict__ km,
+                                    int64_t km_stride, uint8_t* __restrict__ sf, int64_t sf_stride) {
+    const int64_t nb = K >> 5;
+    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= rows * nb) return;
+    const int64_t row = gid / nb, blk = gid - row * nb;
+    const int64_t mat = blockIdx.y;
+    q += mat * src_q_stride;
+    if (s) s += mat * src_s_stride;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) v |= mxfp4_src_code(layout, q, K, row, blk * 32 + i * 8 + j) << (4 * j);
+        w[i] = v;
+    }
+    uint8_t* kdst = km + mat * km_stride + (pair_index > 0 ? rows * (K >> 1) : 0) + row * (K >> 1) + blk * 16;
+    *reinterpret_cast<uint4*>(kdst) = make_uint4(w[0], w[1], w[2], w[3]);
+    const int64_t n_kc = K >> 7;
+    const int64_t chunk = pair_index >= 0 ? ((row >> 7) * n_kc + (blk >> 2)) * 2 + pair_index
+                                          : ((row >> 8) * n_kc + (blk >> 2)) * 2 + ((row >> 7) & 1);
+    sf[mat * sf_stride + chunk * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (blk & 3)] = mxfp4_src_scale(layout, q, s, K, row, blk);
+}
+
 // Largest byte of a scale plane (E8M0 exponents), folded into *out with atomicMax.
 __global__ void max_byte_kernel(const uint8_t* __restrict__ p, int64_t n_words, uint32_t* out) {
     uint32_t m = 0;
@@ -180,6 +212,20 @@ int launch_max_byte(const uint8_t* p, int64_t bytes, uint32_t* out, cudaStream_t
     const int64_t n_words = bytes / 4;
     if (n_words == 0) return DSX_OK;
     max_byte_kernel<<<(unsigned)std::min<int64_t>(1024, (n_words + 255) / 256), 256, 0, stream>>>(p, n_words, out);
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
+int launch_kmajor_mxfp4(int src_layout, const uint8_t* q, const uint8_t* s, int64_t rows, int64_t K, int pair_index, int n_mats,
+                        int64_t src_q_stride, int64_t src_s_stride, uint8_t* km, int64_t km_stride, uint8_t* sf, int64_t sf_stride,
+                        cudaStream_t stream) {
+    DSX_REQUIRE(rows % 128 == 0 && K % 128 == 0 && (pair_index >= 0 || rows % 256 == 0), "kmajor: rows %lld / K %lld not tileable",
+                (long long)rows, (long long)K);
+    DSX_REQUIRE(src_layout >= DSX_SRC_MXFP4_HF && src_layout <= DSX_SRC_MXFP4_SB2, "kmajor: layout %d is not MXFP4", src_layout);
+    const int64_t n_threads = rows * (K >> 5);
+    dim3 grid((unsigned)((n_threads + 255) / 256), (unsigned)n_mats);
+    kmajor_mxfp4_kernel<<<grid, 256, 0, stream>>>(src_layout, q, s, rows, K, pair_index, src_q_stride, src_s_stride, km, km_stride, sf,
+                                                  sf_stride);
     DSX_LAUNCHED();
     return DSX_OK;
 }

@@ -89,6 +89,62 @@ def bytes_per_expert(fmt: int, k: int, rows: int) -> int:
 
 
 # --------------------------------------------------------------------------
+class Module:
+    """``Module::load_data`` / ``get_function`` / ``Function::launch_raw``
+    (crates/v4flash-hip/src/module.rs:28-57,141-171): a code object loaded from bytes, kernels by name,
+    launches with one pointer per argument."""
+
+    def __init__(self, image: bytes):
+        self._image = C.create_string_buffer(image, len(image))
+        h = C.c_void_p()
+        _check(lib().dsx_module_load_data(self._image, C.byref(h)))
+        self._h = h
+
+    def get_function(self, name: str) -> C.c_void_p:
+        f = C.c_void_p()
+        _check(lib().dsx_module_get_function(self._h, name.encode(), C.byref(f)))
+        return f
+
+    @staticmethod
+    def launch_raw(fn, grid, block, shared_bytes: int, args: list):
+        """args: ctypes values, one per kernel parameter, in order."""
+        g = (C.c_uint32 * 3)(*grid)
+        b = (C.c_uint32 * 3)(*block)
+        ptrs = (C.c_void_p * len(args))(*[C.cast(C.pointer(a), C.c_void_p) for a in args])
+        _check(lib().dsx_function_launch(fn, g, b, C.c_uint32(shared_bytes), _stream(), ptrs))
+
+    def close(self):
+        if self._h:
+            lib().dsx_module_unload(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def reduce_partials(partial: torch.Tensor, T: int, n_used: int, with_shared: bool, selected=None, expert_lo: int = 0, n_local: int = 0):
+    """``launch_reduce_partials`` + ``VecAddInplace`` (q2_k_accumulate_matvec_par.hip:705-766, src/ffn.rs:118-151):
+    slot-order f32 sum of the per-pick partial rows (+ the shared expert's row) -> bf16 [T, hidden]."""
+    assert partial.dtype == torch.float32 and partial.is_contiguous()
+    H = partial.shape[1]
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=partial.device)
+    _check(lib().dsx_reduce_partials(_dptr(partial), C.c_int64(T), n_used, C.c_int64(H), 1 if with_shared else 0, _dptr(selected),
+                                     expert_lo, n_local, _dptr(out), _stream()))
+    return out
+
+
+def stream_write_value32(addr: int, value: int):
+    _check(lib().dsx_stream_write_value32(_stream(), C.c_void_p(addr), C.c_uint32(value)))
+
+
+def stream_wait_value32(addr: int, value: int, flags: int = 0):
+    _check(lib().dsx_stream_wait_value32(_stream(), C.c_void_p(addr), C.c_uint32(value), C.c_uint32(flags)))
+
+
+# --------------------------------------------------------------------------
 class ExpertSelCount:
     """``ExpertSelCount::launch`` (src/expert_sel_count.rs:34): accumulate the picks of one layer into the bank."""
 
@@ -135,11 +191,13 @@ class RoutedExpertWeights:
     """Expert store: n_slots experts (gate, up, down) resident in HBM in the
     library's tile layout."""
 
-    def __init__(self, fmt: int, n_slots: int, hidden: int, ffn: int, _handle=None):
+    def __init__(self, fmt: int, n_slots: int, hidden: int, ffn: int, _handle=None, decode_only: bool = False):
+        """decode_only: keep only the decode kernels' tile layout (an MXFP4 store otherwise also holds the
+        K-major planes of the block-scaled tensor-core kernel, twice the bytes)."""
         self.fmt, self.n_slots, self.hidden, self.ffn = fmt, n_slots, hidden, ffn
         if _handle is None:
             h = C.c_void_p()
-            _check(lib().dsx_expert_store_create(C.byref(h), fmt, n_slots, C.c_int64(hidden), C.c_int64(ffn)))
+            _check(lib().dsx_expert_store_create_ex(C.byref(h), fmt, n_slots, C.c_int64(hidden), C.c_int64(ffn), C.c_uint32(1 if decode_only else 0)))
             _handle = h
         self._h = _handle
 
@@ -192,11 +250,11 @@ class RoutedExpertWeights:
         return RoutedExpertWeights(self.fmt, self.n_slots, self.hidden, self.ffn, _handle=h)
 
     @classmethod
-    def from_host(cls, fmt: int, hidden: int, ffn: int, gate, up, down) -> "RoutedExpertWeights":
+    def from_host(cls, fmt: int, hidden: int, ffn: int, gate, up, down, decode_only: bool = False) -> "RoutedExpertWeights":
         """gate/up/down: (q, s) numpy pairs in the canonical host layout
         (HF for MXFP4, split for Q8_0), leading dimension = slots."""
         n = gate[0].shape[0]
-        st = cls(fmt, n, hidden, ffn)
+        st = cls(fmt, n, hidden, ffn, decode_only=decode_only)
         layout = SRC_MXFP4_HF if fmt == FMT_MXFP4 else SRC_Q8_0_SPLIT
         st.load(MAT_GATE, layout, gate[0], gate[1])
         st.load(MAT_UP, layout, up[0], up[1])
@@ -385,13 +443,13 @@ class MoeLayer:
         return w.value
 
 
-def build_layer_from_host(cfg: MoeConfig, weights: dict, max_tokens: int = 64):
+def build_layer_from_host(cfg: MoeConfig, weights: dict, max_tokens: int = 64, decode_only: bool = False):
     """weights: the dict of :func:`deepstrix_b200.synth.make_layer`."""
-    routed = RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, weights["gate"], weights["up"], weights["down"])
+    routed = RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, weights["gate"], weights["up"], weights["down"], decode_only=decode_only)
     shared = None
     if cfg.shared_ffn:
         shared = RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.shared_ffn, weights["shared_gate"],
-                                               weights["shared_up"], weights["shared_down"])
+                                               weights["shared_up"], weights["shared_down"], decode_only=decode_only)
     rw = torch.from_numpy(weights["router_w"]).cuda()
     rb = torch.from_numpy(weights["router_bias"]).cuda() if weights.get("router_bias") is not None else None
     return MoeLayer(cfg, routed, shared, rw, rb, max_tokens=max_tokens)

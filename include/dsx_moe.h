@@ -97,6 +97,30 @@ DSX_API int dsx_graph_end_capture(dsx_stream_t stream, dsx_graph_t* graph_exec);
 DSX_API int dsx_graph_launch(dsx_graph_t graph_exec, dsx_stream_t stream);
 DSX_API int dsx_graph_destroy(dsx_graph_t graph_exec);
 
+/* Code objects -- module.rs:28-57,141-171, launch.rs:25-40, sys.rs:317-330 (hipModuleLoadData / Unload /
+ * GetFunction / LaunchKernel).  `image` is a cubin or fatbin in host memory (what `nvcc -cubin
+ * -gencode arch=compute_100a,code=sm_100a` writes; a Rust crate embeds it with include_bytes!, as
+ * crates/v4flash-kernels/build.rs:114-119 does for its code objects).  The module belongs to the device that
+ * is current at load.  get_function keeps a name -> handle table per module (module.rs:37-57), so a lookup
+ * per launch costs a map probe.  launch takes the CUDA "kernelParams" ABI: params[i] points at the i-th
+ * argument, read during the call.  Kernels that use more than 48 KB of dynamic shared memory need
+ * dsx_function_set_max_shared once.  deepstrix_b200/kernels/dsx_combine.cubin (kernel "dsx_combine_kernel")
+ * is built beside the library as a loadable example of the library's own kernels. */
+typedef struct dsx_module dsx_module;
+typedef void* dsx_function_t; /* CUfunction, owned by its module */
+DSX_API int dsx_module_load_data(const void* image, dsx_module** module);
+DSX_API int dsx_module_unload(dsx_module* module);
+DSX_API int dsx_module_get_function(dsx_module* module, const char* name, dsx_function_t* fn);
+DSX_API int dsx_function_set_max_shared(dsx_function_t fn, uint32_t bytes);
+DSX_API int dsx_function_launch(dsx_function_t fn, const uint32_t grid[3], const uint32_t block[3], uint32_t shared_bytes,
+                                dsx_stream_t stream, void** params);
+/* hipStreamWaitValue32 / hipStreamWriteValue32 -- sys.rs:290-302; used to gate one stream on a value another
+ * stream (or device) writes, het/forward_layer.rs:436-449.  The comparison happens when the stream reaches the
+ * operation, not at the call.  flags: 0 = *addr >= value, 1 = ==, 2 = (*addr & value) != 0, 3 = ~(*addr | value) != 0.
+ * addr is a 4-byte aligned device address. */
+DSX_API int dsx_stream_wait_value32(dsx_stream_t stream, void* addr, uint32_t value, uint32_t flags);
+DSX_API int dsx_stream_write_value32(dsx_stream_t stream, void* addr, uint32_t value);
+
 /* ------------------------------------------------------------------------
  * 2. MoE operators
  * ---------------------------------------------------------------------- */
@@ -136,6 +160,13 @@ DSX_API int dsx_bytes_per_expert(int fmt, int64_t k, int64_t rows, size_t* bytes
 typedef struct dsx_expert_store dsx_expert_store;
 
 DSX_API int dsx_expert_store_create(dsx_expert_store** store, int fmt, int n_slots, int64_t hidden, int64_t ffn);
+/* An MXFP4 store holds every matrix twice: in the decode kernels' tile layout, and K-major (the HF
+ * byte layout) with its E8M0 scales cut into the scale-factor chunks of the block-scaled tensor-core
+ * kernel that runs batches above 64 tokens -- 34 bytes per 32 weights in all.  DSX_STORE_DECODE_ONLY
+ * leaves the second copy out (17 bytes per 32 weights, the reference's byte count); large batches on
+ * such a store run on the grouped-GEMV kernels.  Q8_0 stores have one copy either way. */
+enum dsx_store_flags { DSX_STORE_DECODE_ONLY = 1 };
+DSX_API int dsx_expert_store_create_ex(dsx_expert_store** store, int fmt, int n_slots, int64_t hidden, int64_t ffn, uint32_t flags);
 DSX_API int dsx_expert_store_destroy(dsx_expert_store* store);
 /* Repack one matrix of one slot from a source layout into the tile layout
  * (the role of mxfp4_repack_hf_to_ggml, kernels/mxfp4_repack.hip:35-65 and
@@ -244,6 +275,14 @@ DSX_API int dsx_moe_group_build(const int32_t* selected, int64_t T, int n_used, 
 DSX_API int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n_used, int n_expert, int chunk,
                                        int32_t* hist, int32_t* offsets, int32_t* perm,
                                        int32_t* work_items, int32_t* n_work_items, dsx_stream_t stream);
+/* Q2KAccumulateMatvec::launch_reduce_partials[_hetsplit] (kernels/q2_k_accumulate_matvec_par.hip:705-766;
+ * b2_reduce_partials_zero, b2_fast_chain.hip:137-189) followed by VecAddInplace (src/ffn.rs:118-151):
+ *   out[t, :] = 0 + partial[t*n_used + 0, :] + ... + partial[t*n_used + n_used-1, :]   (slot order, f32 adds)
+ *             + partial[T*n_used + t, :]                                              (when with_shared != 0)
+ * written as bf16 [T, hidden].  partial: f32 [T*n_used (+ T), hidden].  selected (optional, int32 [T, n_used]):
+ * slots whose pick lies outside [expert_lo, expert_lo + n_local) are skipped (rows another owner computes). */
+DSX_API int dsx_reduce_partials(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared,
+                                const int32_t* selected, int expert_lo, int n_local, void* out_bf16, dsx_stream_t stream);
 /* moe_wi_upper_bound, het/dispatch.rs:444-454 */
 DSX_API uint32_t dsx_wi_upper_bound(uint64_t members, uint32_t groups, uint32_t chunk, uint64_t cap);
 

@@ -413,9 +413,10 @@ def test_layer_prefill_q8_0_zipf(torch_cuda, moe, oracle, T):
     assert rel_l2(out, ref) <= REL_L2_TOL
 
 
-def test_prefill_path_declines_scales_beyond_f16(torch_cuda, moe, oracle):
-    """Block scales above 2^13 do not fit the tensor-core path's f16 weights: the layer must take
-    the grouped-GEMV kernels instead and still match the oracle."""
+def test_prefill_block_scales_beyond_f16(torch_cuda, moe, oracle):
+    """Block scales above 2^13 (the most an f16 expansion of the weights could hold): the block-scaled
+    tensor-core path takes the E8M0 scales as stored and must match the oracle; a decode-only store (no
+    tensor-core planes) takes the grouped-GEMV kernels for the same batch and matches as well."""
     torch = torch_cuda
     from deepstrix_b200 import synth
     from deepstrix_b200.config import MoeConfig, RouterConfig
@@ -425,16 +426,23 @@ def test_prefill_path_declines_scales_beyond_f16(torch_cuda, moe, oracle):
     for name in ("gate", "up", "down"):
         w[name][1][...] = 127          # unit scales
     w["gate"][1][:, :, 0] = 143        # one block per row at 2^16 (the SwiGLU clamp bounds what follows)
-    layer = moe.build_layer_from_host(cfg, w, max_tokens=96)
     xb = synth.make_tokens(cfg, 5, 96)
     x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
-    moe.launch_count(reset=True)
-    out = layer.forward(x).float().cpu().numpy()
-    assert moe.launch_count() == 6     # logits, top-k, group build, gate/up GEMV, down GEMV, combine
-    r = layer.routing(96)
-    ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), r["selected"], r["weights"], w["gate"], w["up"], w["down"],
-                               clamp=cfg.clamp, n_expert=32)
-    assert np.isfinite(out).all() and rel_l2(out, ref) <= REL_L2_TOL
+    for decode_only in (False, True):
+        layer = moe.build_layer_from_host(cfg, w, max_tokens=96, decode_only=decode_only)
+        layer.forward(x)               # first call: one-time set-up
+        moe.launch_count(reset=True)
+        out = layer.forward(x).float().cpu().numpy()
+        if decode_only:
+            assert moe.launch_count() == 6     # logits, top-k, group build, gate/up GEMV, down GEMV, combine
+        else:
+            assert moe.launch_count() > 6      # segments, activation terms, two tensor-core kernels on top
+        assert layer.check() == 0
+        r = layer.routing(96)
+        ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), r["selected"], r["weights"], w["gate"], w["up"], w["down"],
+                                   clamp=cfg.clamp, n_expert=32)
+        assert np.isfinite(out).all() and rel_l2(out, ref) <= REL_L2_TOL
+        layer.close()
 
 
 def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
