@@ -496,9 +496,11 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1 or args.gpus > 1:
-        from deepstrix_b200 import ep_bench
-        return ep_bench.run(args)
+    # Under torch.distributed.run (RANK and WORLD_SIZE set) every N runs configuration 4, N = 1 included, so that
+    # the values of a 1 -> 8 GPU scaling run are the same workload; plain `python bench.py` is configuration 1.
+    if world > 1 or args.gpus > 1 or ("RANK" in os.environ and "WORLD_SIZE" in os.environ):
+        import bench_ep
+        return bench_ep.run(args)
     return run_single_gpu(args)
 
 

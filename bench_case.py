@@ -1,5 +1,6 @@
 """Runs one small, configurable MoE-layer case a few times: the command to put
-under a profiler (``ncu ... python -m deepstrix_b200.profile_case ...``).
+under a profiler (``ncu ... python bench_case.py ...``).  Harness, not product:
+it only drives the library through ``deepstrix_b200.moe``.
 
 The layer has the full-size shapes (hidden 4096, ffn 2048, top-8) but, by
 default, only 64 routed experts, so that the whole case holds under 1 GB on the
@@ -9,11 +10,18 @@ from __future__ import annotations
 
 import argparse
 
+import os
+import sys
+
 import numpy as np
 import torch
 
-from . import moe, synth
-from .config import CONFIGS, FMT_MXFP4, FMT_Q8_0, RouterConfig
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from deepstrix_b200 import moe, synth  # noqa: E402
+from deepstrix_b200.config import CONFIGS, FMT_MXFP4, FMT_Q8_0, RouterConfig  # noqa: E402
 
 
 def main():

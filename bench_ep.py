@@ -4,7 +4,9 @@ replicated, 4096 bf16 tokens per GPU.  Dispatch and combine go over peer memory
 (rows stored straight into the owner's HBM through NVLink, no host round trip);
 ``DSX_EP_TRANSPORT=nccl`` selects per-peer NCCL send/recv instead.
 
-Launched by ``bench.py`` under ``torch.distributed.run`` (one rank per GPU).
+Launched by ``bench.py`` under ``torch.distributed.run`` (one rank per GPU; with one rank the same stack
+runs with all 256 experts on that GPU, the point the expert-parallel lines are compared with).
+Harness, not product: it drives the library through ``deepstrix_b200.moe`` / ``deepstrix_b200.ep``.
 """
 from __future__ import annotations
 
@@ -40,6 +42,9 @@ def open_peer_memory(world: int, rank: int, cap: int, hidden: int, k: int):
         comm = PeerMemoryComm(world, rank, cap, hidden, k)
     except Exception as e:
         why = str(e)
+    if world == 1 and comm is not None:   # a process cannot open its own IPC handle, and has no peer to map
+        comm.connect_local([comm])
+        return comm
     if all_ok(comm is not None):
         handles = [None] * world
         dist.all_gather_object(handles, comm.export_handle())   # every rank takes part: all slabs exist

@@ -410,23 +410,14 @@ __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8]) {
         : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
     return out;
 }
-// The eight values those codes stand for (exact).
-__device__ __forceinline__ void e2m1_unpack8(uint32_t q, float (&d)[8]) {
-    uint32_t h[4];
-    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
-        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
-        : "r"(q));
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
-        d[2 * i] = f.x;
-        d[2 * i + 1] = f.y;
-    }
+// The value of E2M1 code n (sign, two exponent bits, one mantissa bit): {0, .5, 1, 1.5, 2, 3, 4, 6}, exact.
+// Plain integer arithmetic on the code, so that the residual is taken against exactly what the tensor core
+// will multiply, independent of any conversion instruction's operand order.
+__device__ __forceinline__ float e2m1_value(uint32_t n) {
+    const uint32_t mag = n & 7u;
+    const uint32_t doubled = mag < 2u ? mag : ((2u | (mag & 1u)) << ((mag >> 1) - 1u));   // 0 1 2 3 4 6 8 12
+    const float v = 0.5f * (float)doubled;
+    return (n & 8u) ? -v : v;
 }
 
 // One warp per expert-sorted row that lies inside a segment: the row (a token's bf16 row, found through the
@@ -491,10 +482,8 @@ mx_quantize_rows_kernel(const void* __restrict__ src, const int32_t* __restrict_
             const uint32_t codes = e2m1_pack8(sv);
             *reinterpret_cast<uint32_t*>(out_row + (int64_t)t * term_stride + i * 128) = codes;
             if (t + 1 < kTerms) {
-                float d[8];
-                e2m1_unpack8(codes, d);
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = __fmaf_rn(-d[j], scl, v[j]);   // exact: the residual
+                for (int j = 0; j < 8; j++) v[j] = __fmaf_rn(-e2m1_value(codes >> (4 * j)), scl, v[j]);   // exact: the residual
             }
             // the scales of 4 consecutive blocks (lanes 0,4,8,12 / 16,20,24,28) form one word of the chunk of stage 2i / 2i+1
             const int base = lane & 16;
