@@ -57,6 +57,7 @@ struct dsx_moe_layer {
     int sm_count = 0;
     // workspace (device)
     float* logits = nullptr;
+    int32_t* sel_local = nullptr;   // picks translated through an ownership table (dsx_moe_layer_forward_remap)
     int32_t *selected = nullptr, *hist = nullptr, *offsets = nullptr, *perm = nullptr, *work_items = nullptr, *n_work_items = nullptr;
     float* weights = nullptr;
     int32_t work_cap = 0;
@@ -475,6 +476,7 @@ struct StageTimer {  // brackets one stage with an event pair when profiling is 
 
 static void layer_free(dsx_moe_layer* L) {
     for (cudaEvent_t e : L->ev) if (e) cudaEventDestroy(e);
+    cudaFree(L->sel_local);
     cudaFree(L->logits); cudaFree(L->selected); cudaFree(L->weights); cudaFree(L->hist); cudaFree(L->offsets);
     cudaFree(L->perm); cudaFree(L->work_items); cudaFree(L->n_work_items); cudaFree(L->gs.chunk_hist); cudaFree(L->mid);
     cudaFree(L->partial); cudaFree(L->error_word); cudaFree(L->router_counters); cudaFree(L->item_recs); cudaFree(L->x_stage); cudaFree(L->out_stage);
@@ -519,6 +521,7 @@ int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const
     auto alloc = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, std::max<size_t>(bytes, 256)); };
     alloc((void**)&L->logits, Tm * E * 4);
     alloc((void**)&L->selected, P * 4);
+    alloc((void**)&L->sel_local, P * 4);
     alloc((void**)&L->weights, P * 4);
     alloc((void**)&L->hist, E * 4);
     alloc((void**)&L->offsets, (E + 1) * 4);
@@ -726,6 +729,36 @@ int dsx_moe_layer_forward_picks(dsx_moe_layer* L, const void* x_bf16, int64_t T,
     L->last_logits = nullptr; L->last_selected = selected; L->last_weights = weights;
     return forward_core(L, (const __nv_bfloat16*)x_bf16, T, selected, weights, expert_lo, true, with_shared, (__nv_bfloat16*)out_bf16,
                         (cudaStream_t)stream);
+}
+
+// picks (global expert ids) -> local slots of this owner: remap[e] < 0 means slot -(remap[e] + 1) is held here,
+// remap[e] >= 0 means another device holds e (its slot there), ids outside [0, n_expert) -- NO_PICK, or the
+// sentinel n_expert that pads fixed-shape launches -- are nobody's.  Everything not held here becomes -1.
+__global__ void remap_picks_kernel(const int32_t* __restrict__ selected, const int32_t* __restrict__ remap, int n_expert, int n_slots,
+                                   int64_t n, int32_t* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int e = selected[i];
+    int slot = -1;
+    if (e >= 0 && e < n_expert) {
+        const int r = remap[e];
+        if (r < 0 && -(r + 1) < n_slots) slot = -(r + 1);
+    }
+    out[i] = slot;
+}
+
+int dsx_moe_layer_forward_remap(dsx_moe_layer* L, const void* x_bf16, int64_t T, const int32_t* selected, const float* weights,
+                                const int32_t* remap, int n_expert, int with_shared, void* out_bf16, dsx_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    DSX_REQUIRE(L, "moe_layer_forward_remap: null layer");
+    DSX_REQUIRE(T >= 0 && T <= L->cfg.max_tokens, "moe_layer_forward_remap: %lld tokens, workspace holds %d", (long long)T, L->cfg.max_tokens);
+    if (T == 0) return DSX_OK;
+    DSX_REQUIRE(x_bf16 && selected && weights && remap && out_bf16 && n_expert >= 1, "moe_layer_forward_remap: null argument");
+    const int64_t n = T * L->cfg.router.n_used;
+    remap_picks_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(selected, remap, n_expert, L->routed->n_slots, n, L->sel_local);
+    DSX_LAUNCHED();
+    L->last_logits = nullptr; L->last_selected = L->sel_local; L->last_weights = weights;
+    return forward_core(L, (const __nv_bfloat16*)x_bf16, T, L->sel_local, weights, 0, true, with_shared, (__nv_bfloat16*)out_bf16, stream);
 }
 
 int dsx_moe_layer_routing(const dsx_moe_layer* L, const float** logits, const int32_t** selected, const float** weights,

@@ -16,6 +16,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "dsx_common.cuh"
 
@@ -134,6 +135,68 @@ int dsx_function_launch(dsx_function_t fn, const uint32_t grid[3], const uint32_
     count_launch();
     DSX_DRV(launch((CUfunction)fn, grid[0], grid[1], grid[2], block[0], block[1], block[2], shared_bytes, (CUstream)stream, params, nullptr),
             "cuLaunchKernel");
+    return DSX_OK;
+}
+
+// ---- executable graphs whose kernel nodes can be re-pointed (crates/v4flash-hip/src/sys.rs:360-382:
+// hipGraphGetNodes, hipGraphKernelNodeGetParams, hipGraphExecKernelNodeSetParams; src/graph.rs)
+int dsx_graph_end_capture_keep(dsx_stream_t stream, dsx_graph_t* graph_exec, void** graph) {
+    DSX_REQUIRE(graph_exec && graph, "graph_end_capture_keep: null argument");
+    cudaGraph_t g = nullptr;
+    DSX_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &g));
+    cudaGraphExec_t ge = nullptr;
+    const cudaError_t e = cudaGraphInstantiate(&ge, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        DSX_CUDA(e);
+    }
+    *graph_exec = ge;
+    *graph = g;
+    return DSX_OK;
+}
+
+int dsx_graph_template_destroy(void* graph) {
+    if (graph) DSX_CUDA(cudaGraphDestroy((cudaGraph_t)graph));
+    return DSX_OK;
+}
+
+int dsx_graph_kernel_nodes(void* graph, void** nodes, size_t* count) {
+    DSX_REQUIRE(graph && count, "graph_kernel_nodes: null argument");
+    size_t n = 0;
+    DSX_CUDA(cudaGraphGetNodes((cudaGraph_t)graph, nullptr, &n));
+    std::vector<cudaGraphNode_t> all(n);
+    if (n) DSX_CUDA(cudaGraphGetNodes((cudaGraph_t)graph, all.data(), &n));
+    size_t k = 0;
+    for (size_t i = 0; i < n; i++) {
+        cudaGraphNodeType ty;
+        DSX_CUDA(cudaGraphNodeGetType(all[i], &ty));
+        if (ty != cudaGraphNodeTypeKernel) continue;
+        if (nodes && k < *count) nodes[k] = all[i];
+        k++;
+    }
+    *count = k;   // kernel nodes in the graph (nodes[] received min(capacity, k) of them)
+    return DSX_OK;
+}
+
+int dsx_graph_exec_kernel_node_set_params(dsx_graph_t graph_exec, void* node, dsx_function_t fn, const uint32_t grid[3],
+                                          const uint32_t block[3], uint32_t shared_bytes, void** params) {
+    DSX_REQUIRE(graph_exec && node && params, "graph_exec_kernel_node_set_params: null argument");
+    typedef CUresult (*GetFn)(CUgraphNode, CUDA_KERNEL_NODE_PARAMS*);
+    typedef CUresult (*SetFn)(CUgraphExec, CUgraphNode, const CUDA_KERNEL_NODE_PARAMS*);
+    static GetFn get = nullptr;
+    static SetFn set = nullptr;
+    if (!get)
+        if (int rc = driver_fn("cuGraphKernelNodeGetParams", &get)) return rc;
+    if (!set)
+        if (int rc = driver_fn("cuGraphExecKernelNodeSetParams", &set)) return rc;
+    CUDA_KERNEL_NODE_PARAMS p;
+    DSX_DRV(get((CUgraphNode)node, &p), "cuGraphKernelNodeGetParams");
+    if (fn) p.func = (CUfunction)fn;   // null: keep the node's kernel
+    if (grid) { p.gridDimX = grid[0]; p.gridDimY = grid[1]; p.gridDimZ = grid[2]; }
+    if (block) { p.blockDimX = block[0]; p.blockDimY = block[1]; p.blockDimZ = block[2]; p.sharedMemBytes = shared_bytes; }
+    p.kernelParams = params;
+    p.extra = nullptr;
+    DSX_DRV(set((CUgraphExec)graph_exec, (CUgraphNode)node, &p), "cuGraphExecKernelNodeSetParams");
     return DSX_OK;
 }
 

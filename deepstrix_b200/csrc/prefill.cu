@@ -543,40 +543,44 @@ __device__ __forceinline__ int seg_size(int cnt, int seg_rows) {  // even split 
 constexpr int kSmallMax = DSX_SMALL_MAX;   // at most 32 (4 work items of 8 rows per expert)
 static_assert(kSmallMax <= 32, "the work-item list holds 4 items per expert");
 
-__global__ void build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t P, int T_shared, int seg_rows,
-                                      PrefillSeg* __restrict__ segs, int32_t* __restrict__ n_segs, int cap, int small_max,
-                                      int32_t* __restrict__ small_items, int32_t* __restrict__ n_small) {
-    __shared__ int s_base[513];
-    __shared__ int s_cnt[512];
-    for (int e = threadIdx.x; e < n_local; e += blockDim.x) s_cnt[e] = offsets[e + 1] - offsets[e];   // one round of loads, not a serial chain
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0, small = 0;
-        for (int e = 0; e < n_local; e++) {
-            s_base[e] = run;
-            const int cnt = s_cnt[e];
-            if (cnt > 0 && cnt <= small_max) {
-                for (int st = 0; st < cnt; st += 8) small_items[small++] = (int32_t)(((uint32_t)e << 16) | (uint32_t)st);
-                continue;
-            }
-            const int sz = seg_size(cnt, seg_rows);
-            run += sz ? (cnt + sz - 1) / sz : 0;
-        }
-        s_base[n_local] = run;
-        const int sz = seg_size(T_shared, seg_rows);
-        n_segs[0] = min(cap, run + (sz ? (T_shared + sz - 1) / sz : 0));
-        if (n_small != nullptr) n_small[0] = small;
+__global__ void __launch_bounds__(512)
+build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t P, int T_shared, int seg_rows,
+                      PrefillSeg* __restrict__ segs, int32_t* __restrict__ n_segs, int cap, int small_max,
+                      int32_t* __restrict__ small_items, int32_t* __restrict__ n_small) {
+    // thread e = expert e (n_local <= 512): its segment count and GEMV item count, then an exclusive scan of both
+    __shared__ int s_seg[512], s_small[512];
+    const int e = threadIdx.x;
+    int cnt = 0, sz = 0, nseg = 0, nsmall = 0;
+    if (e < n_local) {
+        cnt = offsets[e + 1] - offsets[e];
+        if (cnt > 0 && cnt <= small_max) nsmall = (cnt + 7) >> 3;
+        else { sz = seg_size(cnt, seg_rows); nseg = sz ? (cnt + sz - 1) / sz : 0; }
     }
+    s_seg[e] = nseg;
+    s_small[e] = nsmall;
     __syncthreads();
-    for (int e = threadIdx.x; e <= n_local; e += blockDim.x) {
-        const int cnt = e < n_local ? offsets[e + 1] - offsets[e] : T_shared;
-        if (e < n_local && cnt <= small_max) continue;
-        const int row0 = e < n_local ? offsets[e] : (int)P;
-        const int sz = seg_size(cnt, seg_rows);
-        for (int i = 0, st = 0; st < cnt; i++, st += sz) {
-            const int idx = s_base[e] + i;
-            if (idx < cap) segs[idx] = PrefillSeg{e, row0 + st, min(sz, cnt - st), 0};
-        }
+    for (int d = 1; d < 512; d <<= 1) {   // inclusive scan, 9 steps
+        const int a = e >= d ? s_seg[e - d] : 0, b = e >= d ? s_small[e - d] : 0;
+        __syncthreads();
+        s_seg[e] += a;
+        s_small[e] += b;
+        __syncthreads();
+    }
+    const int seg_base = s_seg[e] - nseg, small_base = s_small[e] - nsmall;
+    const int routed_segs = s_seg[511];
+    if (e < n_local) {
+        const int row0 = offsets[e];
+        for (int i = 0; i < nsmall; i++) small_items[small_base + i] = (int32_t)(((uint32_t)e << 16) | (uint32_t)(8 * i));
+        for (int i = 0, st = 0; i < nseg; i++, st += sz)
+            if (seg_base + i < cap) segs[seg_base + i] = PrefillSeg{e, row0 + st, min(sz, cnt - st), 0};
+    }
+    // the shared expert's segments follow, over rows P .. P + T_shared - 1, spread over the threads
+    const int ssz = seg_size(T_shared, seg_rows), sn = ssz ? (T_shared + ssz - 1) / ssz : 0;
+    for (int i = e; i < sn; i += 512)
+        if (routed_segs + i < cap) segs[routed_segs + i] = PrefillSeg{n_local, (int)P + i * ssz, min(ssz, T_shared - i * ssz), 0};
+    if (e == 0) {
+        n_segs[0] = min(cap, routed_segs + sn);
+        if (n_small != nullptr) n_small[0] = s_small[511];
     }
 }
 

@@ -36,8 +36,11 @@ struct PrefillWorkspace {
     bool mx_ready = false;
     uint8_t* xq = nullptr;          // [3 terms][cap_rows][K/2]: the sorted rows (then mid) as packed E2M1 terms
     int64_t mx_term_stride = 0;     // bytes between terms
-    uint8_t* sfb = nullptr;         // their block scales: [segment][K/128][term][2][512]
-    PrefillSeg* mx_segs = nullptr;  // segments of at most 240 rows
+    uint8_t* sfb = nullptr;         // their block scales: [segment][K/128][term][512]
+    uint8_t* xq_tok = nullptr;      // [3 terms][max_tokens][hidden/2]: every token expanded once
+    int64_t mx_tok_term_stride = 0;
+    uint8_t* sf_tok = nullptr;      // [max_tokens][3 terms][hidden/32] E8M0 bytes
+    PrefillSeg* mx_segs = nullptr;  // segments of at most 112 rows
     int32_t mx_seg_cap = 0;
     CUtensorMap tmap_xq, tmap_mq;   // xq as (bytes, row, term) for K = hidden / K = ffn
     CUtensorMap tmap_km_gu[2], tmap_km_dn[2];            // K-major code planes; index 0 routed, 1 shared

@@ -18,14 +18,19 @@
 // accumulator.  Three terms leave a relative error of about 3e-3 on the layer output (two terms 2.5e-2,
 // a single E4M3 term 4.6e-2), for 1.5 times the tensor-core time of one FP8 pass.
 //
-// Tiling.  Expert-sorted rows are cut into segments of at most 240 rows of one expert.  A tile =
-// (segment, 256 weight rows): two M = 128 halves (gate rows f0.. and up rows f0.. for the first product,
-// so that a tensor-memory lane holds gate and up of one output row) with the segment's rows as N.  Tensor
-// memory: two accumulators of 240 columns, 8 columns of weight scales, 24 of activation scales = 512.
-// A pipeline stage is 128 reduction columns: 16 KB of weight codes, 3 x 16 KB of activation terms, 1 KB +
-// 3 KB of scale chunks, all arriving on one mbarrier; per stage the issuing thread copies the eight scale
-// chunks to tensor memory and issues 2 (k steps of 64) x 3 (terms) x 2 (halves) MMAs.
-// Warp roles: one producer thread, one MMA thread, 12 epilogue warps that read the accumulators
+// Tiling.  Every activation row costs three operand rows, so a tile is tall on the weight side: expert-sorted
+// rows are cut into segments of at most 112 rows of one expert, and a tile = (segment, 512 weight rows) = four
+// M = 128 accumulators that share the segment's rows as N (first product: gate rows f0..f0+127, up rows
+// f0..f0+127, gate f0+128.., up f0+128.., so that a tensor-memory lane holds gate and up of one output row).
+// Tensor memory: 4 x 112 accumulator columns, 16 columns of weight scales, 12 of activation scales.
+// A pipeline stage is 128 reduction columns: 32 KB of weight codes, up to 3 x 8 KB of activation terms (only the
+// 32-row boxes the segment needs are fetched), 2 KB + 1.5 KB of scale chunks, all arriving on one mbarrier; per
+// stage the issuing thread copies the seven scale chunks to tensor memory and issues 2 (k steps of 64) x 3
+// (terms) x 4 (accumulators) MMAs.  Shared-memory traffic per MMA-clock is what bounds this kernel (the L2 ->
+// shared-memory path saturates near 10 TB/s on the device): 256-row tiles with 240-row segments moved 79 bytes
+// per MMA-clock on the 8192-token workload, whose experts hold ~256 rows and so split into two half-empty
+// segments; this shape moves 38.
+// Warp roles: one producer thread, one MMA thread, 16 epilogue warps that read the accumulators
 // (tcgen05.ld), apply clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows
 // (f32).  Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
 // is freed and bit 2 of the layer's error word is set.
@@ -34,21 +39,23 @@
 namespace dsx {
 namespace {
 
-constexpr int kEpiWarps = 12;
+constexpr int kEpiWarps = 16;
 constexpr int kThreads = (2 + kEpiWarps) * 32;
-constexpr int kSegRows = 240;                 // most rows of a segment (MMA N)
-constexpr int kBoxRows = 256;                 // rows a token-tile copy brings (rows past the segment are never multiplied)
+constexpr int kAccs = 4;                      // M = 128 accumulators per tile (512 weight rows)
+constexpr int kSegRows = 112;                 // most rows of a segment (MMA N)
+constexpr int kBRows = 128;                   // rows of a term plane in shared memory
+constexpr int kBoxRows = 32;                  // rows one token-tile copy brings
 constexpr int kTerms = 3;                     // MXFP4 terms per activation row
 constexpr int kStageK = 128;                  // reduction columns per pipeline stage (4 scale blocks)
 constexpr int kRowBytes = kStageK / 2;        // packed bytes per row and stage: one 64-byte swizzle row
 constexpr int kStages = 3;
-constexpr int kABytes = 256 * kRowBytes;                 // 16384: two halves of 128 weight rows
-constexpr int kBTermBytes = kBoxRows * kRowBytes;        // 16384
-constexpr int kBBytes = kTerms * kBTermBytes;            // 49152
+constexpr int kABytes = kAccs * 128 * kRowBytes;         // 32768
+constexpr int kBTermBytes = kBRows * kRowBytes;          // 8192
+constexpr int kBBoxBytes = kBoxRows * kRowBytes;         // 2048
+constexpr int kBBytes = kTerms * kBTermBytes;            // 24576
 constexpr int kSfChunk = 512;                            // 128 rows x 4 scale blocks
-constexpr int kSfaBytes = 2 * kSfChunk;
-constexpr int kSfbBytes = kTerms * 2 * kSfChunk;
-constexpr int kStageTx = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+constexpr int kSfaBytes = kAccs * kSfChunk;
+constexpr int kSfbBytes = kTerms * kSfChunk;
 constexpr int kSmemA = 0;
 constexpr int kSmemB = kSmemA + kStages * kABytes;
 constexpr int kSmemSfa = kSmemB + kStages * kBBytes;
@@ -59,10 +66,9 @@ constexpr int kSmemMisc = kSmemBar + kNumBars * 8;
 constexpr int kSmemTotal = kSmemMisc + 16 + 1024;        // + alignment slack
 static_assert(kSmemTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
 // tensor-memory columns
-constexpr uint32_t kAcc1Col = kSegRows;       // second accumulator
-constexpr uint32_t kSfaCol = 2 * kSegRows;    // 4 columns per 128-row half
-constexpr uint32_t kSfbCol = kSfaCol + 8;     // 8 columns per term (two chunks of 128 rows)
-static_assert(kSfbCol + 8 * kTerms <= 512, "tensor memory holds 512 columns");
+constexpr uint32_t kSfaCol = kAccs * kSegRows;    // accumulator h at column h * kSegRows; then 4 columns of weight scales per accumulator
+constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term (one chunk: at most 128 rows)
+static_assert(kSfbCol + 4 * kTerms <= 512, "tensor memory holds 512 columns");
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -134,14 +140,12 @@ __device__ __forceinline__ void tc_mma_mxf4(uint32_t d, uint64_t adesc, uint64_t
         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -223,7 +227,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
 
     const int n_segs = a.n_segs[0];
-    const int n_mb = a.rows / (GATE_UP ? 128 : 256);   // 256-row tiles (gate/up: 128 gate + 128 up)
+    const int n_mb = a.rows / (GATE_UP ? 256 : 512);   // 512-row tiles (gate/up: 256 gate + 256 up)
     const int n_tiles = n_segs * n_mb;
     const int n_kc = a.K / kStageK;
 
@@ -232,19 +236,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
         if (lane == 0) {
             uint32_t cnt = 0;
             bool ok = true;
+            // weight map: gate/up = (bytes, row, matrix, slot) with a box of 64 x 256 x 2 (lands as 256 gate rows, then 256 up
+            // rows); down = (bytes, row, 1, slot) with a box of 64 x 256 x 1, two boxes per stage
+            auto w_row = [&](int mb) { return GATE_UP ? mb * 256 : mb * 512; };
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int si = tile / n_mb, mb = tile % n_mb;
                 const PrefillSeg seg = a.segs[si];
                 const bool sh = seg.expert == a.n_local;
                 const CUtensorMap* m_w = sh ? &tmap_w_shared : &tmap_w;
                 const int slot = sh ? 0 : seg.expert;
-                const uint8_t* sfa = (sh ? a.sfa_shared : a.sfa + (int64_t)slot * a.sfa_slot_stride) + (int64_t)mb * n_kc * kSfaBytes;
+                // scale chunks of this tile: two runs of [K/128][2][512] (row tiles 2 mb and 2 mb + 1 of the plane)
+                const uint8_t* sfa = (sh ? a.sfa_shared : a.sfa + (int64_t)slot * a.sfa_slot_stride) + (int64_t)(2 * mb) * n_kc * (2 * kSfChunk);
                 const uint8_t* sfb = a.sfb + (int64_t)si * n_kc * kSfbBytes;
+                const int n_box = (max(16, (seg.n + 15) & ~15) + kBoxRows - 1) / kBoxRows;
+                const uint32_t stage_tx = (uint32_t)(kABytes + kSfaBytes + kSfbBytes + kTerms * n_box * kBBoxBytes);
                 // weights of this tile into L2 a few stages ahead of the ring
-                constexpr int kAhead = 6;
+                constexpr int kAhead = 4;
+                auto prefetch_w = [&](const CUtensorMap* m, int kc, int mb_, int slot_) {
+                    tma_prefetch_4d(m, kc * kRowBytes, w_row(mb_), 0, slot_);
+                    if (!GATE_UP) tma_prefetch_4d(m, kc * kRowBytes, w_row(mb_) + 256, 0, slot_);
+                };
                 if (tile == (int)blockIdx.x)
-                    for (int kc = 0; kc < kAhead && kc < n_kc; kc++)
-                        tma_prefetch_4d(m_w, kc * kRowBytes, GATE_UP ? mb * 128 : mb * 256, 0, slot);
+                    for (int kc = 0; kc < kAhead && kc < n_kc; kc++) prefetch_w(m_w, kc, mb, slot);
                 const int ntile = tile + gridDim.x;
                 PrefillSeg nseg = seg;
                 int nmb = mb;
@@ -252,20 +265,26 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                 const bool nsh = nseg.expert == a.n_local;
                 for (int kc = 0; kc < n_kc && ok; kc++) {
                     const int pk = kc + kAhead;
-                    if (pk < n_kc) tma_prefetch_4d(m_w, pk * kRowBytes, GATE_UP ? mb * 128 : mb * 256, 0, slot);
-                    else if (ntile < n_tiles)
-                        tma_prefetch_4d(nsh ? &tmap_w_shared : &tmap_w, (pk - n_kc) * kRowBytes, GATE_UP ? nmb * 128 : nmb * 256, 0,
-                                        nsh ? 0 : nseg.expert);
+                    if (pk < n_kc) prefetch_w(m_w, pk, mb, slot);
+                    else if (ntile < n_tiles) prefetch_w(nsh ? &tmap_w_shared : &tmap_w, pk - n_kc, nmb, nsh ? 0 : nseg.expert);
                     const int s = cnt % kStages;
                     ok = mbar_wait(bar(EMPTY + s), ((cnt / kStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(bar(FULL + s), kStageTx);
-                    // weights: gate/up map = (bytes, row, matrix, slot) with a box of 64 x 128 x 2; down map = (bytes, row, 1, slot) with 64 x 256 x 1
-                    tma_load_4d(sbase + kSmemA + s * kABytes, m_w, kc * kRowBytes, GATE_UP ? mb * 128 : mb * 256, 0, slot, bar(FULL + s));
-                    // activation terms: (bytes, row, term), box 64 x 256 x 3
-                    tma_load_3d(sbase + kSmemB + s * kBBytes, &tmap_b, kc * kRowBytes, seg.row0, 0, bar(FULL + s));
-                    bulk_load(sbase + kSmemSfa + s * kSfaBytes, sfa + (int64_t)kc * kSfaBytes, kSfaBytes, bar(FULL + s));
-                    bulk_load(sbase + kSmemSfb + s * kSfbBytes, sfb + (int64_t)kc * kSfbBytes, kSfbBytes, bar(FULL + s));
+                    const uint32_t full = bar(FULL + s);
+                    mbar_expect_tx(full, stage_tx);
+                    const uint32_t a_dst = sbase + kSmemA + s * kABytes;
+                    tma_load_4d(a_dst, m_w, kc * kRowBytes, w_row(mb), 0, slot, full);
+                    if (!GATE_UP) tma_load_4d(a_dst + kABytes / 2, m_w, kc * kRowBytes, w_row(mb) + 256, 0, slot, full);
+                    // activation terms: (bytes, row, term), boxes of 64 bytes x 32 rows, only as many as the segment has rows
+                    const uint32_t b_dst = sbase + kSmemB + s * kBBytes;
+#pragma unroll
+                    for (int t = 0; t < kTerms; t++)
+                        for (int c = 0; c < n_box; c++)
+                            tma_load_3d(b_dst + t * kBTermBytes + c * kBBoxBytes, &tmap_b, kc * kRowBytes, seg.row0 + c * kBoxRows, t, full);
+                    const uint32_t sfa_dst = sbase + kSmemSfa + s * kSfaBytes;
+                    bulk_load(sfa_dst, sfa + (int64_t)kc * (2 * kSfChunk), 2 * kSfChunk, full);
+                    bulk_load(sfa_dst + 2 * kSfChunk, sfa + (int64_t)(n_kc + kc) * (2 * kSfChunk), 2 * kSfChunk, full);
+                    bulk_load(sbase + kSmemSfb + s * kSfbBytes, sfb + (int64_t)kc * kSfbBytes, kSfbBytes, full);
                     cnt++;
                 }
             }
@@ -288,13 +307,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                     const uint32_t full = bar(FULL) + 8u * s;
                     if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    // scales of this stage: 2 weight chunks, then 2 chunks for each of the 3 terms (16-byte units in the descriptor)
+                    // scales of this stage: one chunk per accumulator, one per term (16-byte units in the descriptor)
                     const uint64_t sfa_d = sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4));
                     const uint64_t sfb_d = sfb_desc0 + (uint64_t)(s * (kSfbBytes >> 4));
-                    tc_cp_scales(tmem_base + kSfaCol, sfa_d);
-                    tc_cp_scales(tmem_base + kSfaCol + 4, sfa_d + (kSfChunk >> 4));
 #pragma unroll
-                    for (int c = 0; c < 2 * kTerms; c++) tc_cp_scales(tmem_base + kSfbCol + 4 * c, sfb_d + (uint64_t)(c * (kSfChunk >> 4)));
+                    for (int h = 0; h < kAccs; h++) tc_cp_scales(tmem_base + kSfaCol + 4 * h, sfa_d + (uint64_t)(h * (kSfChunk >> 4)));
+#pragma unroll
+                    for (int t = 0; t < kTerms; t++) tc_cp_scales(tmem_base + kSfbCol + 4 * t, sfb_d + (uint64_t)(t * (kSfChunk >> 4)));
                     const uint64_t a_d = a_desc0 + (uint64_t)(s * (kABytes >> 4));
                     const uint64_t b_d = b_desc0 + (uint64_t)(s * (kBBytes >> 4));
 #pragma unroll
@@ -304,9 +323,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                         for (int t = 0; t < kTerms; t++) {
                             const uint64_t bd = b_d + (uint64_t)(t * (kBTermBytes >> 4) + ks * 2);   // + 32 bytes per k step
                             const uint32_t acc = (kc | ks | t) != 0 ? 1u : 0u;
-                            tc_mma_mxf4(tmem_base, a_d + (uint64_t)(ks * 2), bd, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol + 8 * t, acc);
-                            tc_mma_mxf4(tmem_base + kAcc1Col, a_d + (uint64_t)((kABytes >> 5) + ks * 2), bd, idesc, tmem_base + kSfaCol + 4,
-                                        tmem_base + kSfbCol + 8 * t, acc);
+#pragma unroll
+                            for (int h = 0; h < kAccs; h++) {
+                                // accumulator h reads 128 rows of the stage's weights: gate/up stages hold 256 gate rows, then 256 up rows
+                                const int a_off = GATE_UP ? ((h & 1) * (kABytes / 2) + (h >> 1) * (kABytes / 4)) : h * (kABytes / 4);
+                                tc_mma_mxf4(tmem_base + (uint32_t)(h * kSegRows), a_d + (uint64_t)((a_off >> 4) + ks * 2), bd, idesc,
+                                            tmem_base + kSfaCol + 4 * h, tmem_base + kSfbCol + 4 * t, acc);
+                            }
                         }
                     }
                     tc_commit(bar(EMPTY) + 8u * s);   // arrives when the copies and MMAs above have read their operands
@@ -318,8 +341,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        // Warp w may read lanes 32 * (w % 4) .. + 31 of tensor memory; the three warps of a lane quarter split
-        // the tile's 32-column chunks between them.
+        // Warp w may read lanes 32 * (w % 4) .. + 31 of tensor memory; the four warps of a lane quarter take one
+        // 32-column chunk of the tile each.
         const int q = warp & 3, rank = (warp - 2) >> 2;
         uint32_t tcnt = 0;
         bool ok = true;
@@ -331,8 +354,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-            const int r_in = q * 32 + lane;           // row inside a 128-row half
-            for (int c0 = 32 * rank; c0 < seg.n; c0 += 96) {
+            const int r_in = q * 32 + lane;           // row inside a 128-row accumulator
+            const int c0 = 32 * rank;
+            if (c0 < seg.n) {
                 // lane j of the warp fetches the routing weight / output row of column c0 + j
                 float wv = 0.f;
                 int orow = 0;
@@ -340,34 +364,39 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                     if (sh) { wv = 1.0f; orow = seg.row0 + c0 + lane; }
                     else { const int ts = a.perm[seg.row0 + c0 + lane]; wv = a.route_w[ts]; orow = ts; }
                 }
-                uint32_t v0[32], v1[32];
-                tc_ld32(lane_addr + (uint32_t)c0, v0);
-                tc_ld32(lane_addr + kAcc1Col + (uint32_t)c0, v1);
-                tc_wait_ld();
-                if (GATE_UP) {
-                    __half* dst = a.mid + (int64_t)(seg.row0 + c0) * a.mid_stride + mb * 128 + r_in;
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const float wj = __shfl_sync(0xFFFFFFFFu, wv, j);
-                        if (c0 + j < seg.n) {
-                            float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
-                            if (a.clamp > 1.0e-6f) {
-                                gv = fminf(gv, a.clamp);
-                                uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
+                for (int ph = 0; ph < kAccs; ph++) {   // accumulator pair p, 16-column half hf of the chunk
+                    const int p = ph >> 1, hf = ph & 1, cb = c0 + 16 * hf;
+                    if (cb >= seg.n) continue;
+                    uint32_t v0[16], v1[16];
+                    tc_ld16(lane_addr + (uint32_t)(2 * p * kSegRows + cb), v0);
+                    tc_ld16(lane_addr + (uint32_t)((2 * p + 1) * kSegRows + cb), v1);
+                    tc_wait_ld();
+                    if (GATE_UP) {
+                        __half* dst = a.mid + (int64_t)(seg.row0 + cb) * a.mid_stride + mb * 256 + p * 128 + r_in;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const float wj = __shfl_sync(0xFFFFFFFFu, wv, 16 * hf + j);
+                            if (cb + j < seg.n) {
+                                float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
+                                if (a.clamp > 1.0e-6f) {
+                                    gv = fminf(gv, a.clamp);
+                                    uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
+                                }
+                                const float sig = __fdividef(1.0f, 1.0f + __expf(-gv));
+                                dst[(int64_t)j * a.mid_stride] = __float2half_rn(gv * sig * uv * wj);
                             }
-                            const float sig = __fdividef(1.0f, 1.0f + __expf(-gv));
-                            dst[(int64_t)j * a.mid_stride] = __float2half_rn(gv * sig * uv * wj);
                         }
-                    }
-                } else {
-                    const int h = mb * 256 + r_in;
+                    } else {
+                        const int h = mb * 512 + p * 256 + r_in;
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int rj = __shfl_sync(0xFFFFFFFFu, orow, j);
-                        if (c0 + j < seg.n) {
-                            float* dst = a.partial + (int64_t)rj * a.rows + h;
-                            dst[0] = __uint_as_float(v0[j]);
-                            dst[128] = __uint_as_float(v1[j]);
+                        for (int j = 0; j < 16; j++) {
+                            const int rj = __shfl_sync(0xFFFFFFFFu, orow, 16 * hf + j);
+                            if (cb + j < seg.n) {
+                                float* dst = a.partial + (int64_t)rj * a.rows + h;
+                                dst[0] = __uint_as_float(v0[j]);
+                                dst[128] = __uint_as_float(v1[j]);
+                            }
                         }
                     }
                 }
@@ -420,45 +449,61 @@ __device__ __forceinline__ float e2m1_value(uint32_t n) {
     return (n & 8u) ? -v : v;
 }
 
-// One warp per expert-sorted row that lies inside a segment: the row (a token's bf16 row, found through the
-// permutation, or a row of f16 mid) becomes kTerms MXFP4 rows -- codes [term][row][K/2], scales into the
-// segment's scale-factor chunks.  A lane holds 8 consecutive values; four lanes make a 32-value block.
-template <bool FROM_TOKENS>
-__global__ void __launch_bounds__(256)
-mx_quantize_rows_kernel(const void* __restrict__ src, const int32_t* __restrict__ perm, int n_used, int64_t P, int64_t rows_total, int K,
-                        const PrefillSeg* __restrict__ segs, const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq,
-                        int64_t term_stride, uint8_t* __restrict__ sfb) {
-    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= rows_total) return;
-    // the segment holding this row: the last one that starts at or before it (segments are sorted by first row)
-    const int n_segs = n_segs_p[0];
+// The segment holding expert-sorted row `row`, or -1 (a row of an expert the grouped GEMV takes): the last segment
+// that starts at or before it (segments are sorted by first row).
+__device__ __forceinline__ int find_segment(const PrefillSeg* __restrict__ segs, int n_segs, int64_t row, PrefillSeg* seg) {
+    if (n_segs == 0) return -1;
     int lo = 0, hi = n_segs;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if ((int64_t)segs[mid].row0 <= row) lo = mid; else hi = mid;
     }
-    if (n_segs == 0) return;
-    const PrefillSeg seg = segs[lo];
-    if (row < seg.row0 || row >= (int64_t)seg.row0 + seg.n) return;   // a row of an expert the grouped GEMV takes
-    const int r = (int)(row - seg.row0);
+    *seg = segs[lo];
+    if (row < seg->row0 || row >= (int64_t)seg->row0 + seg->n) return -1;
+    return lo;
+}
+
+// One warp per row: the row becomes kTerms MXFP4 rows.  A lane holds 8 consecutive values; four lanes make a
+// 32-value block.
+//   BY_TOKEN:  rows are the batch's tokens (bf16); codes to [term][token][K/2], scales row-major to
+//              [token][term][K/32] -- a token is expanded once, however many experts it visits
+//   otherwise: rows are the expert-sorted rows of mid (f16) that lie inside a segment; codes to [term][row][K/2],
+//              scales into the segment's scale-factor chunks
+template <bool BY_TOKEN>
+__global__ void __launch_bounds__(256)
+mx_quantize_rows_kernel(const void* __restrict__ src, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
+                        const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ codes_out, int64_t term_stride,
+                        uint8_t* __restrict__ scales_out) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
     const int n_kc = K / kStageK;
-    uint8_t* sf_row = sfb + (int64_t)lo * n_kc * kSfbBytes + (r >> 7) * kSfChunk + (r & 31) * 16 + ((r >> 5) & 3) * 4;
+    uint8_t* sf_row;
+    int64_t sf_stage_stride, sf_term_stride;   // bytes between 128-column stages / between terms
     const uint4* in;
-    if (FROM_TOKENS) {
-        const int64_t tok = row < P ? perm[row] / n_used : row - P;
-        in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + tok * K);
+    if (BY_TOKEN) {
+        in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + row * K);
+        sf_row = scales_out + row * (int64_t)(kTerms * (K >> 5));
+        sf_stage_stride = 4;
+        sf_term_stride = K >> 5;
     } else {
+        PrefillSeg seg;
+        const int si = find_segment(segs, n_segs_p[0], row, &seg);
+        if (si < 0) return;
+        const int r = (int)(row - seg.row0);
         in = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(src) + row * K);
+        sf_row = scales_out + (int64_t)si * n_kc * kSfbBytes + (r & 31) * 16 + ((r >> 5) & 3) * 4;   // r < 128: one chunk per term
+        sf_stage_stride = kSfbBytes;
+        sf_term_stride = kSfChunk;
     }
-    uint8_t* out_row = xq + row * (K >> 1) + lane * 4;
+    uint8_t* out_row = codes_out + row * (K >> 1) + lane * 4;
     for (int i = 0; i < (K >> 8); i++) {
         const uint4 raw = __ldg(in + i * 32 + lane);
         const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
         float v[8];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            if (FROM_TOKENS) {
+            if (BY_TOKEN) {
                 v[2 * j] = __uint_as_float(wds[j] << 16);
                 v[2 * j + 1] = __uint_as_float(wds[j] & 0xFFFF0000u);
             } else {
@@ -485,18 +530,46 @@ mx_quantize_rows_kernel(const void* __restrict__ src, const int32_t* __restrict_
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[j] = __fmaf_rn(-e2m1_value(codes >> (4 * j)), scl, v[j]);   // exact: the residual
             }
-            // the scales of 4 consecutive blocks (lanes 0,4,8,12 / 16,20,24,28) form one word of the chunk of stage 2i / 2i+1
+            // the scales of 4 consecutive blocks (lanes 0,4,8,12 / 16,20,24,28) form one word: stage 2i / 2i+1 of the row
             const int base = lane & 16;
             const uint32_t w = __shfl_sync(0xFFFFFFFFu, e, base) | (__shfl_sync(0xFFFFFFFFu, e, base + 4) << 8) |
                                (__shfl_sync(0xFFFFFFFFu, e, base + 8) << 16) | (__shfl_sync(0xFFFFFFFFu, e, base + 12) << 24);
             if ((lane & 15) == 0)
-                *reinterpret_cast<uint32_t*>(sf_row + ((int64_t)(2 * i + (lane >> 4)) * kTerms + t) * (2 * kSfChunk)) = w;
+                *reinterpret_cast<uint32_t*>(sf_row + (int64_t)(2 * i + (lane >> 4)) * sf_stage_stride + (int64_t)t * sf_term_stride) = w;
         }
     }
 }
 
+// One warp per expert-sorted row inside a segment: the terms of the row's token (found through the permutation;
+// rows P + t are the shared expert's copy of token t) are copied into the sorted term planes and the token's
+// scales into the segment's scale-factor chunks.
+__global__ void __launch_bounds__(256)
+mx_gather_rows_kernel(const uint8_t* __restrict__ tok_codes, int64_t tok_term_stride, const uint8_t* __restrict__ tok_scales,
+                      const int32_t* __restrict__ perm, int n_used, int64_t P, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
+                      const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq, int64_t term_stride, uint8_t* __restrict__ sfb) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    PrefillSeg seg;
+    const int si = find_segment(segs, n_segs_p[0], row, &seg);
+    if (si < 0) return;
+    const int r = (int)(row - seg.row0);
+    const int64_t tok = row < P ? perm[row] / n_used : row - P;
+    const int n_kc = K / kStageK, n16 = K >> 5;   // 128-column stages; 16-byte pieces of a term's code row
+    uint8_t* sf_row = sfb + (int64_t)si * n_kc * kSfbBytes + (r & 31) * 16 + ((r >> 5) & 3) * 4;
+#pragma unroll
+    for (int t = 0; t < kTerms; t++) {
+        const uint4* src = reinterpret_cast<const uint4*>(tok_codes + (int64_t)t * tok_term_stride + tok * (K >> 1));
+        uint4* dst = reinterpret_cast<uint4*>(xq + (int64_t)t * term_stride + row * (K >> 1));
+        for (int c = lane; c < n16; c += 32) dst[c] = __ldg(src + c);
+        const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(tok_scales + (tok * kTerms + t) * (int64_t)(K >> 5));
+        for (int kc = lane; kc < n_kc; kc += 32)
+            *reinterpret_cast<uint32_t*>(sf_row + (int64_t)kc * kSfbBytes + t * kSfChunk) = __ldg(ssrc + kc);
+    }
+}
+
 // (Re-)encode the weight maps when the layer points at other planes: gate/up as (bytes, row, matrix, slot)
-// with a box of 64 bytes x 128 rows x both matrices, down as (bytes, row, 1, slot) with 64 x 256.
+// with a box of 64 bytes x 256 rows x both matrices, down as (bytes, row, 1, slot) with 64 x 256.
 int map_weights(PrefillWorkspace* ws, int which, const uint8_t* km_gu, const uint8_t* km_dn, int64_t gu_stride, int64_t dn_stride,
                 int n_slots) {
     if (ws->mapped_km_gu[which] == km_gu && ws->mapped_km_dn[which] == km_dn && ws->mapped_km_slots[which] == n_slots) return DSX_OK;
@@ -504,7 +577,7 @@ int map_weights(PrefillWorkspace* ws, int which, const uint8_t* km_gu, const uin
     {
         const cuuint64_t dims[4] = {(cuuint64_t)(H / 2), (cuuint64_t)F, 2, (cuuint64_t)n_slots};
         const cuuint64_t strides[3] = {(cuuint64_t)(H / 2), (cuuint64_t)(F * (H / 2)), (cuuint64_t)gu_stride};
-        const cuuint32_t box[4] = {(cuuint32_t)kRowBytes, 128, 2, 1};
+        const cuuint32_t box[4] = {(cuuint32_t)kRowBytes, 256, 2, 1};
         if (int rc = tmap_encode(&ws->tmap_km_gu[which], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, km_gu, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
     }
@@ -525,20 +598,23 @@ int map_weights(PrefillWorkspace* ws, int which, const uint8_t* km_gu, const uin
 
 int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used) {
     ws->mx_ready = false;
-    // shapes the tiles cover: 128 gate + 128 up rows per tile, 256 down rows per tile, 128-column stages
-    if (cfg.ffn % 256 != 0 || cfg.hidden % 256 != 0 || (cfg.shared_ffn != 0 && cfg.shared_ffn != cfg.ffn)) return DSX_OK;
+    // shapes the tiles cover: 256 gate + 256 up rows per tile, 512 down rows per tile, 128-column stages
+    if (cfg.ffn % 256 != 0 || cfg.hidden % 512 != 0 || (cfg.shared_ffn != 0 && cfg.shared_ffn != cfg.ffn)) return DSX_OK;
     const int64_t Kmax = std::max(cfg.hidden, cfg.ffn);
-    ws->mx_seg_cap = cfg.router.n_expert + (int)((ws->cap_rows + kSegRows - 1) / kSegRows) + 8;
+    ws->mx_seg_cap = cfg.router.n_expert + (int)((ws->cap_rows + kSegRows - 1) / kSegRows) + 8;   // every expert's last segment may be short
     ws->mx_term_stride = ws->cap_rows * (Kmax / 2);
     DSX_CUDA(cudaMalloc((void**)&ws->xq, (size_t)kTerms * (size_t)ws->mx_term_stride));
     DSX_CUDA(cudaMalloc((void**)&ws->sfb, (size_t)ws->mx_seg_cap * (size_t)(Kmax / kStageK) * kSfbBytes));
     DSX_CUDA(cudaMalloc((void**)&ws->mx_segs, sizeof(PrefillSeg) * (size_t)ws->mx_seg_cap));
-    // activation terms as (bytes, row, term): box 64 bytes x 256 rows x 3 terms
+    ws->mx_tok_term_stride = (int64_t)cfg.max_tokens * (cfg.hidden / 2);
+    DSX_CUDA(cudaMalloc((void**)&ws->xq_tok, (size_t)kTerms * (size_t)ws->mx_tok_term_stride));
+    DSX_CUDA(cudaMalloc((void**)&ws->sf_tok, (size_t)cfg.max_tokens * kTerms * (size_t)(cfg.hidden / 32)));
+    // activation terms as (bytes, row, term): boxes of 64 bytes x 32 rows of one term
     for (int g = 0; g < 2; g++) {
         const int64_t K = g == 0 ? cfg.hidden : cfg.ffn;
         const cuuint64_t dims[3] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->cap_rows, (cuuint64_t)kTerms};
         const cuuint64_t strides[2] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->mx_term_stride};
-        const cuuint32_t box[3] = {(cuuint32_t)kRowBytes, (cuuint32_t)kBoxRows, (cuuint32_t)kTerms};
+        const cuuint32_t box[3] = {(cuuint32_t)kRowBytes, (cuuint32_t)kBoxRows, 1};
         if (int rc = tmap_encode(g == 0 ? &ws->tmap_xq : &ws->tmap_mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ws->xq, dims, strides, box,
                                  CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
@@ -553,7 +629,9 @@ void prefill_mx_workspace_free(PrefillWorkspace* ws) {
     cudaFree(ws->xq);
     cudaFree(ws->sfb);
     cudaFree(ws->mx_segs);
-    ws->xq = nullptr; ws->sfb = nullptr; ws->mx_segs = nullptr; ws->mx_ready = false;
+    cudaFree(ws->xq_tok);
+    cudaFree(ws->sf_tok);
+    ws->xq = nullptr; ws->sfb = nullptr; ws->mx_segs = nullptr; ws->xq_tok = nullptr; ws->sf_tok = nullptr; ws->mx_ready = false;
 }
 
 int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& c, cudaStream_t stream) {
@@ -583,8 +661,11 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     g.error_word = c.error_word;
 
     // first product: K = hidden, rows = ffn
-    mx_quantize_rows_kernel<true><<<qblocks, 256, 0, stream>>>(c.x, c.perm, c.n_used, P, quant_rows, (int)cfg.hidden, ws->mx_segs, ws->n_segs,
-                                                               ws->xq, ws->mx_term_stride, ws->sfb);
+    mx_quantize_rows_kernel<true><<<(unsigned)((c.T + 7) / 8), 256, 0, stream>>>(c.x, c.T, (int)cfg.hidden, nullptr, nullptr, ws->xq_tok,
+                                                                                 ws->mx_tok_term_stride, ws->sf_tok);
+    DSX_LAUNCHED();
+    mx_gather_rows_kernel<<<qblocks, 256, 0, stream>>>(ws->xq_tok, ws->mx_tok_term_stride, ws->sf_tok, c.perm, c.n_used, P, quant_rows,
+                                                       (int)cfg.hidden, ws->mx_segs, ws->n_segs, ws->xq, ws->mx_term_stride, ws->sfb);
     DSX_LAUNCHED();
     g.K = cfg.hidden; g.rows = cfg.ffn;
     g.sfa = c.sf_gu; g.sfa_slot_stride = c.sf_gu_stride; g.sfa_shared = c.sh_sf_gu;
@@ -596,8 +677,8 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
         if (int rc = launch_gemv_gate_up(v, c.sm_count, stream)) return rc;
     }
     // second product: K = ffn, rows = hidden, over the terms of mid
-    mx_quantize_rows_kernel<false><<<qblocks, 256, 0, stream>>>(c.mid, nullptr, c.n_used, P, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs,
-                                                                ws->xq, ws->mx_term_stride, ws->sfb);
+    mx_quantize_rows_kernel<false><<<qblocks, 256, 0, stream>>>(c.mid, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs, ws->xq,
+                                                                ws->mx_term_stride, ws->sfb);
     DSX_LAUNCHED();
     g.K = cfg.ffn; g.rows = cfg.hidden;
     g.sfa = c.sf_dn; g.sfa_slot_stride = c.sf_dn_stride; g.sfa_shared = c.sh_sf_dn;

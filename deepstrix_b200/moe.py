@@ -405,6 +405,16 @@ class MoeLayer:
                                                  expert_lo, 1 if with_shared else 0, _dptr(out), _stream()))
         return out
 
+    def forward_remap(self, x, selected, weights, remap, with_shared: bool = True, out=None):
+        """Owner-side forward with the reference's ownership table (het/weights.rs:1357-1381): remap int32 [n_expert],
+        negative entries -(slot + 1) are the experts this store holds."""
+        assert selected.dtype == torch.int32 and weights.dtype == torch.float32 and remap.dtype == torch.int32 and remap.is_cuda
+        if out is None:
+            out = torch.empty_like(x)
+        _check(lib().dsx_moe_layer_forward_remap(self._h, _dptr(x), C.c_int64(x.shape[0]), _dptr(selected), _dptr(weights), _dptr(remap),
+                                                 remap.numel(), 1 if with_shared else 0, _dptr(out), _stream()))
+        return out
+
     def routing(self, T: int):
         """Copies of the last forward's routing: dict of CPU numpy arrays."""
         ptrs = [C.c_void_p() for _ in range(6)]

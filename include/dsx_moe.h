@@ -96,6 +96,17 @@ DSX_API int dsx_graph_begin_capture(dsx_stream_t stream);
 DSX_API int dsx_graph_end_capture(dsx_stream_t stream, dsx_graph_t* graph_exec);
 DSX_API int dsx_graph_launch(dsx_graph_t graph_exec, dsx_stream_t stream);
 DSX_API int dsx_graph_destroy(dsx_graph_t graph_exec);
+/* Re-pointing the kernels of an instantiated graph -- sys.rs:360-382 (hipGraphGetNodes, hipGraphKernelNodeGetParams,
+ * hipGraphExecKernelNodeSetParams).  end_capture_keep also hands back the captured graph (the template; destroy it
+ * with dsx_graph_template_destroy once no more updates are needed).  kernel_nodes lists its kernel nodes in the
+ * driver's node order: call with nodes = NULL to get the count, then with room for *count handles.
+ * set_params replaces a node's arguments in the executable graph; fn / grid / block may be NULL to keep the
+ * node's kernel / grid / block and shared-memory size.  params uses the kernelParams ABI and is read during the call. */
+DSX_API int dsx_graph_end_capture_keep(dsx_stream_t stream, dsx_graph_t* graph_exec, void** graph);
+DSX_API int dsx_graph_template_destroy(void* graph);
+DSX_API int dsx_graph_kernel_nodes(void* graph, void** nodes, size_t* count);
+DSX_API int dsx_graph_exec_kernel_node_set_params(dsx_graph_t graph_exec, void* node, void* fn, const uint32_t grid[3],
+                                                  const uint32_t block[3], uint32_t shared_bytes, void** params);
 
 /* Code objects -- module.rs:28-57,141-171, launch.rs:25-40, sys.rs:317-330 (hipModuleLoadData / Unload /
  * GetFunction / LaunchKernel).  `image` is a cubin or fatbin in host memory (what `nvcc -cubin
@@ -335,6 +346,17 @@ DSX_API int dsx_moe_layer_forward_host(dsx_moe_layer* layer, const void* x_bf16_
 DSX_API int dsx_moe_layer_forward_picks(dsx_moe_layer* layer, const void* x_bf16, int64_t T,
                                         const int32_t* selected, const float* weights, int expert_lo,
                                         int with_shared, void* out_bf16, dsx_stream_t stream);
+
+/* The same with the reference's ownership table instead of a contiguous id range (encode_igpu_remap,
+ * het/weights.rs:1357-1381; kernels/moe_group_builder.hip:53-123; docs/v41/REMOTE_EXPERTS.md:204-211):
+ * remap is DEVICE int32 [n_expert]; remap[e] < 0 means this owner holds expert e in store slot -(remap[e] + 1),
+ * remap[e] >= 0 means another device does (the value is its slot there and is not used here).  Picks < 0 or
+ * >= n_expert (NO_PICK; the sentinel id n_expert that pads fixed-shape launches) belong to nobody.  Any placement
+ * can be expressed: hot / cold splits, groups interleaved over GPUs.  Owners whose tables partition the experts
+ * return partial sums that add up to the full layer. */
+DSX_API int dsx_moe_layer_forward_remap(dsx_moe_layer* layer, const void* x_bf16, int64_t T, const int32_t* selected,
+                                        const float* weights, const int32_t* remap, int n_expert, int with_shared,
+                                        void* out_bf16, dsx_stream_t stream);
 
 /* Device pointers into the layer's workspace holding the routing of the last
  * forward (valid until the next call): logits f32 [T,E], selected i32 [T,k],

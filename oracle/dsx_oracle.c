@@ -12,7 +12,7 @@
  *   - external/ds4-dump/quants_selftest_expected.inc:93-137 (MXFP4 dequant bits)
  *   - crates/v4flash-core/src/hf_v41.rs:1321-1382 (E4M3 / E8M0 / Q8_0 / nibble tests)
  *   - crates/v4flash-kernels/src/het/dispatch.rs:746-748 (work-item bound literals)
- *   - scripts/v41_oracle/kernel.py (dequant_fp4 / act_quant / fp4_gemm outputs)
+ *   - scripts/v41_oracle/kernel.py (dequant_fp4 / act_quant / fp4_act_quant / fp4_gemm outputs)
  * Parts with no counterpart in the reference (group-limited routing, Q8_0
  * routed experts, bf16 activations) are "parity unpinned": defined here under
  * the reference's conventions.  So are the router's alternatives / score range /
@@ -646,6 +646,115 @@ DSXO_API uint32_t dsxo_wi_upper_bound(uint64_t members, uint32_t groups, uint32_
     return (uint32_t)b;
 }
 
+/* ------------------------------------------------- activation quantisers */
+
+/* f32 -> nearest float8_e4m3fn value (round to nearest even, |x| <= 448 on entry), as a float.
+ * scripts/v41_oracle/kernel.py:81-82 (_fake_fp8 = torch's f32 -> float8_e4m3fn cast). */
+static float round_e4m3(float x) {
+    float a = fabsf(x);
+    if (a == 0.0f) return x;
+    int e;
+    frexpf(a, &e);                 /* a = m * 2^e, m in [0.5, 1) */
+    int ex = e - 1;                /* a in [2^ex, 2^(ex+1)) */
+    if (ex < -6) ex = -6;          /* subnormals share the smallest normal's spacing 2^-9 */
+    const float step = ldexpf(1.0f, ex - 3);
+    float q = nearbyintf(a / step) * step;   /* default rounding mode: nearest even */
+    if (q > 448.0f) q = 448.0f;
+    return copysignf(q, x);
+}
+
+/* act_quant with block 32 and ue8m0 scales (scripts/v41_oracle/kernel.py:85-106): per 32 values
+ * s = 2^ceil(log2(max(amax, 1e-4) / 448)), y = e4m3(clamp(x / s, +-448)); out = y * s. */
+DSXO_API void dsxo_act_quant_e4m3(const float* x, int64_t n, float* out) {
+    for (int64_t b = 0; b < n / 32; b++) {
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[b * 32 + i]));
+        if (amax < 1e-4f) amax = 1e-4f;
+        const float s = exp2f(ceilf(log2f(amax / 448.0f)));
+        for (int i = 0; i < 32; i++) {
+            float v = x[b * 32 + i] / s;
+            if (v > 448.0f) v = 448.0f;
+            if (v < -448.0f) v = -448.0f;
+            out[b * 32 + i] = round_e4m3(v) * s;
+        }
+    }
+}
+
+/* Nearest E2M1 magnitude code (0..7 -> 0, .5, 1, 1.5, 2, 3, 4, 6), ties to the even mantissa, saturating:
+ * scripts/v41_oracle/kernel.py:109-126 (_fake_fp4). */
+static int e2m1_code(float a) {
+    static const float grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    if (a >= 6.0f) return 7;
+    int lo = 0;
+    while (lo < 7 && grid[lo + 1] <= a) lo++;
+    const float dl = a - grid[lo], du = grid[lo + 1] - a;
+    if (dl < du) return lo;
+    if (du < dl) return lo + 1;
+    return (lo & 1) ? lo + 1 : lo;   /* even codes have an even mantissa */
+}
+
+/* The MXFP4 expansion of an activation row used by the block-scaled tensor-core kernel: term t is the
+ * reference's FP4 fake-quant (fp4_act_quant with E8M0 scales and block 32, scripts/v41_oracle/kernel.py:129-147:
+ * s = 2^ceil(log2(amax / 6)), codes = nearest E2M1 of x / s) of what terms 0..t-1 left over.  The scale is found
+ * from the bits of amax (amax = m * 2^E: s = 2^(E-2), doubled when m > 1.5), which is that formula without a
+ * logarithm, with the E8M0 byte kept inside 1..253.  Every step is exact in f32.
+ * codes: n_terms x n/2 bytes (element 2i in the low nibble), scales: n_terms x n/32 E8M0 bytes, sum: the
+ * n values the terms add up to (any output may be NULL). */
+DSXO_API void dsxo_act_terms_mxfp4(const float* x, int64_t n, int n_terms, uint8_t* codes, uint8_t* scales, float* sum) {
+    float* res = (float*)malloc(sizeof(float) * (size_t)n);
+    memcpy(res, x, sizeof(float) * (size_t)n);
+    if (sum) memset(sum, 0, sizeof(float) * (size_t)n);
+    for (int t = 0; t < n_terms; t++)
+        for (int64_t b = 0; b < n / 32; b++) {
+            float amax = 0.0f;
+            for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(res[b * 32 + i]));
+            const uint32_t bits = f32_bits(amax);
+            int e = (int)(bits >> 23) - 2 + ((bits & 0x7FFFFFu) > 0x400000u ? 1 : 0);
+            if (e < 1) e = 1;
+            if (e > 253) e = 253;
+            const float s = bits_f32((uint32_t)e << 23), inv = bits_f32((uint32_t)(254 - e) << 23);
+            if (scales) scales[(int64_t)t * (n / 32) + b] = (uint8_t)e;
+            for (int i = 0; i < 32; i++) {
+                const int64_t j = b * 32 + i;
+                const float v = res[j] * inv;
+                const int c = e2m1_code(fabsf(v)) | (v < 0.0f || (v == 0.0f && signbit(v)) ? 8 : 0);
+                const float d = (float)KVALUES_MXFP4[c] * 0.5f * s;
+                if (codes) {
+                    uint8_t* p = codes + (int64_t)t * (n / 2) + j / 2;
+                    *p = (j & 1) ? (uint8_t)((*p & 0x0F) | (c << 4)) : (uint8_t)((*p & 0xF0) | c);
+                }
+                if (sum) sum[j] += d;
+                res[j] -= d;
+            }
+        }
+    free(res);
+}
+
+/* What a row of activations becomes before a product, by act_mode:
+ *   0      unchanged (the dequantised-f32 reference, the tolerance target)
+ *   1      one E4M3 term (act_quant above: the model's own FP8 activation numerics, docs/v41/ARCH_SPEC.md:131-133)
+ *   2      two E4M3 terms (the second quantises what the first left over)
+ *   10 + k k MXFP4 terms (dsxo_act_terms_mxfp4) */
+static void apply_act_mode(int act_mode, float* row, int64_t n) {
+    if (act_mode == 0) return;
+    float* tmp = (float*)malloc(sizeof(float) * (size_t)n);
+    if (act_mode == 1 || act_mode == 2) {
+        dsxo_act_quant_e4m3(row, n, tmp);
+        if (act_mode == 2) {
+            float* res = (float*)malloc(sizeof(float) * (size_t)n);
+            float* t2 = (float*)malloc(sizeof(float) * (size_t)n);
+            for (int64_t i = 0; i < n; i++) res[i] = row[i] - tmp[i];
+            dsxo_act_quant_e4m3(res, n, t2);
+            for (int64_t i = 0; i < n; i++) tmp[i] += t2[i];
+            free(res); free(t2);
+        }
+    } else {
+        dsxo_act_terms_mxfp4(row, n, act_mode - 10, NULL, NULL, tmp);
+    }
+    memcpy(row, tmp, sizeof(float) * (size_t)n);
+    free(tmp);
+}
+
 /* ------------------------------------------------------------ expert FFN */
 
 enum { DSXO_FMT_MXFP4 = 0, DSXO_FMT_Q8_0 = 1 };
@@ -694,7 +803,7 @@ static inline int64_t sbytes(int fmt, int64_t rows, int64_t K) { return fmt == D
  * between the two products). */
 static void expert_ffn(int fmt, const uint8_t* gq, const uint8_t* gs, const uint8_t* uq, const uint8_t* us,
                        const uint8_t* dq, const uint8_t* ds, int64_t H, int64_t F, float clamp,
-                       int n, const float* const* xs, const float* ws, float* const* outs, int mid_round) {
+                       int n, const float* const* xs, const float* ws, float* const* outs, int mid_round, int act_mode) {
     float* mid = (float*)malloc(sizeof(float) * (size_t)(F * n));
 #pragma omp parallel
     {
@@ -737,6 +846,10 @@ static void expert_ffn(int fmt, const uint8_t* gq, const uint8_t* gs, const uint
                 mid[(int64_t)i * F + r] = m;
             }
         }
+        if (act_mode != 0) {   /* the rows of mid as the second product's kernel sees them */
+#pragma omp for schedule(static)
+            for (int i = 0; i < n; i++) apply_act_mode(act_mode, mid + (int64_t)i * F, F);
+        }
 #pragma omp for schedule(static)
         for (int64_t r = 0; r < H; r++) {
             dequant_row(fmt, dq, ds, F, r, row);
@@ -770,16 +883,26 @@ static void expert_ffn(int fmt, const uint8_t* gq, const uint8_t* gs, const uint
  * Expert e of a routed matrix lives at e * bytes_per_expert in each plane.
  * shared_* may be NULL (no shared expert).  partials_out (optional) receives
  * the [T*k+T, H] rows (routed in (t,s) order, then shared). */
-DSXO_API void dsxo_moe_layer_f32(
+DSXO_API void dsxo_moe_layer_act(
         int fmt, int64_t T, int64_t H, int64_t F, int n_expert, int n_used,
-        const float* x, const int32_t* selected, const float* weights,
+        const float* x_in, const int32_t* selected, const float* weights,
         const uint8_t* gate_q, const uint8_t* gate_s, const uint8_t* up_q, const uint8_t* up_s,
         const uint8_t* down_q, const uint8_t* down_s,
         int shared_fmt, int64_t Fs,
         const uint8_t* sg_q, const uint8_t* sg_s, const uint8_t* su_q, const uint8_t* su_s,
         const uint8_t* sd_q, const uint8_t* sd_s,
-        float clamp, int mid_round, float* out, float* partials_out) {
+        float clamp, int mid_round, int act_mode, float* out, float* partials_out) {
     const int64_t P = T * n_used;
+    /* act_mode != 0: both products see their activation rows (x, then mid) through apply_act_mode */
+    float* xq = NULL;
+    const float* x = x_in;
+    if (act_mode != 0) {
+        xq = (float*)malloc(sizeof(float) * (size_t)(T * H));
+        memcpy(xq, x_in, sizeof(float) * (size_t)(T * H));
+#pragma omp parallel for schedule(static)
+        for (int64_t t = 0; t < T; t++) apply_act_mode(act_mode, xq + t * H, H);
+        x = xq;
+    }
     float* partial = partials_out ? partials_out : (float*)malloc(sizeof(float) * (size_t)((P + T) * H));
     memset(partial, 0, sizeof(float) * (size_t)((P + T) * H));
     int32_t* hist = (int32_t*)malloc(sizeof(int32_t) * (size_t)n_expert);
@@ -801,7 +924,7 @@ DSXO_API void dsxo_moe_layer_f32(
             ws[i] = weights[ts];
         }
         expert_ffn(fmt, gate_q + e * gq_b, gate_s + e * gs_b, up_q + e * gq_b, up_s + e * gs_b,
-                   down_q + e * dq_b, down_s + e * ds_b, H, F, clamp, n, xs, ws, outs, mid_round);
+                   down_q + e * dq_b, down_s + e * ds_b, H, F, clamp, n, xs, ws, outs, mid_round, act_mode);
         free(xs); free(outs); free(ws);
     }
     if (sg_q) {
@@ -809,7 +932,7 @@ DSXO_API void dsxo_moe_layer_f32(
         float** outs = (float**)malloc(sizeof(float*) * (size_t)T);
         float* ws = (float*)malloc(sizeof(float) * (size_t)T);
         for (int64_t t = 0; t < T; t++) { xs[t] = x + t * H; outs[t] = partial + (P + t) * H; ws[t] = 1.0f; }
-        expert_ffn(shared_fmt, sg_q, sg_s, su_q, su_s, sd_q, sd_s, H, Fs, clamp, (int)T, xs, ws, outs, mid_round);
+        expert_ffn(shared_fmt, sg_q, sg_s, su_q, su_s, sd_q, sd_s, H, Fs, clamp, (int)T, xs, ws, outs, mid_round, act_mode);
         free(xs); free(outs); free(ws);
     }
 #pragma omp parallel for schedule(static)
@@ -821,7 +944,21 @@ DSXO_API void dsxo_moe_layer_f32(
             out[t * H + r] = acc;
         }
     free(hist); free(offs); free(perm);
+    free(xq);
     if (!partials_out) free(partial);
+}
+
+DSXO_API void dsxo_moe_layer_f32(
+        int fmt, int64_t T, int64_t H, int64_t F, int n_expert, int n_used,
+        const float* x, const int32_t* selected, const float* weights,
+        const uint8_t* gate_q, const uint8_t* gate_s, const uint8_t* up_q, const uint8_t* up_s,
+        const uint8_t* down_q, const uint8_t* down_s,
+        int shared_fmt, int64_t Fs,
+        const uint8_t* sg_q, const uint8_t* sg_s, const uint8_t* su_q, const uint8_t* su_s,
+        const uint8_t* sd_q, const uint8_t* sd_s,
+        float clamp, int mid_round, float* out, float* partials_out) {
+    dsxo_moe_layer_act(fmt, T, H, F, n_expert, n_used, x, selected, weights, gate_q, gate_s, up_q, up_s, down_q, down_s, shared_fmt, Fs,
+                       sg_q, sg_s, su_q, su_s, sd_q, sd_s, clamp, mid_round, 0, out, partials_out);
 }
 
 /* Reference-numerics variant of one routed pick for MXFP4 (the int8 path the

@@ -305,10 +305,40 @@ def wi_upper_bound(members: int, groups: int, chunk: int, cap: int = 2**62) -> i
 
 
 # -------------------------------------------------------------- MoE layer
+ACT_EXACT, ACT_E4M3, ACT_E4M3_X2 = 0, 1, 2
+
+
+def act_mxfp4(n_terms: int) -> int:
+    """act_mode of ``moe_layer_f32``: activations as a sum of n_terms MXFP4 rows."""
+    return 10 + n_terms
+
+
+def act_quant_e4m3(x: np.ndarray) -> np.ndarray:
+    """scripts/v41_oracle/kernel.py:85-106 (act_quant, block 32, ue8m0 scales): the dequantised result."""
+    x = _c(x, np.float32)
+    out = np.empty_like(x)
+    lib().dsxo_act_quant_e4m3(_p(x), C.c_int64(x.size), _p(out))
+    return out
+
+
+def act_terms_mxfp4(x: np.ndarray, n_terms: int = 3):
+    """One row -> (codes uint8 [n_terms, n/2], E8M0 scales uint8 [n_terms, n/32], sum of the terms f32 [n]);
+    term t is kernel.py's fp4_act_quant (:129-147) of what the earlier terms left over."""
+    x = _c(x, np.float32).reshape(-1)
+    n = x.size
+    codes = np.zeros((n_terms, n // 2), np.uint8)
+    scales = np.zeros((n_terms, n // 32), np.uint8)
+    total = np.empty(n, np.float32)
+    lib().dsxo_act_terms_mxfp4(_p(x), C.c_int64(n), C.c_int(n_terms), _p(codes), _p(scales), _p(total))
+    return codes, scales, total
+
+
 def moe_layer_f32(fmt, x, selected, weights, gate, up, down, shared=None, shared_fmt=None,
-                  clamp=10.0, mid_round=0, n_expert=None, return_partials=False):
+                  clamp=10.0, mid_round=0, n_expert=None, return_partials=False, act_mode=0):
     """Dequantised-f32 MoE layer.  gate/up/down are ``(q, s)`` pairs holding all
-    experts back to back; ``shared`` is ``((gq,gs),(uq,us),(dq,ds))`` or None."""
+    experts back to back; ``shared`` is ``((gq,gs),(uq,us),(dq,ds))`` or None.
+    act_mode: how the two products see their activation rows (0 exact -- the tolerance target;
+    ACT_E4M3 / ACT_E4M3_X2 / act_mxfp4(k), see apply_act_mode in the C file)."""
     x = _c(x, np.float32)
     T, H = x.shape
     selected = _c(selected, np.int32)
@@ -328,11 +358,11 @@ def moe_layer_f32(fmt, x, selected, weights, gate, up, down, shared=None, shared
         Fs = (sh[0].size * 2 // H) if sfmt == FMT_MXFP4 else (sh[0].size // H)
     out = np.empty((T, H), np.float32)
     partials = np.empty((T * k + T, H), np.float32) if return_partials else None
-    lib().dsxo_moe_layer_f32(
+    lib().dsxo_moe_layer_act(
         C.c_int(fmt), C.c_int64(T), C.c_int64(H), C.c_int64(F), C.c_int(E), C.c_int(k),
         _p(x), _p(selected), _p(weights), _p(gq), _p(gs), _p(uq), _p(us), _p(dq), _p(ds),
         C.c_int(sfmt), C.c_int64(Fs), *[_p(a) for a in sh],
-        C.c_float(clamp), C.c_int(mid_round), _p(out), _p(partials))
+        C.c_float(clamp), C.c_int(mid_round), C.c_int(act_mode), _p(out), _p(partials))
     return (out, partials) if return_partials else out
 
 

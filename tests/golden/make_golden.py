@@ -10,7 +10,7 @@ Outputs (small, committed):
       (external/ds4-dump/quants_selftest.c:45-53,82-87,102-105: LCG bytes, seed 0x3333,
       scale bytes forced to 120..127)
   kernelpy_vectors.npz inputs and outputs of the reference's CPU oracle
-      scripts/v41_oracle/kernel.py (dequant_fp4, q8_0_roundtrip, act_quant, fp4_gemm),
+      scripts/v41_oracle/kernel.py (dequant_fp4, q8_0_roundtrip, act_quant, fp4_act_quant, fp4_gemm),
       imported and executed unmodified under torch-CPU
 """
 import importlib.util
@@ -57,10 +57,18 @@ def main(ref: str):
     xq, xs = k.act_quant(torch.from_numpy(x), block_size=32, scale_fmt="ue8m0")
     gemm = k.fp4_gemm(xq, xs, torch.from_numpy(packed), s_t).float().numpy()
     xq_f = (xq.float().view(5, K // 32, 32) * xs.float().unsqueeze(-1)).view(5, K).numpy()
+    # MXFP4 activation terms: the reference's FP4 fake-quant (fp4_act_quant, block 32, E8M0 scales) applied to x,
+    # then to what it left over, three times; terms[i] is the dequantised i-th term
+    res = torch.from_numpy(x).clone()
+    terms = []
+    for _ in range(3):
+        y, _s = k.fp4_act_quant(res, block_size=32)
+        terms.append(y.float().numpy().copy())
+        res = res - y.float()
     w = rng.standard_normal((8, 64)).astype(np.float32)
     q8rt = k.q8_0_roundtrip(torch.from_numpy(w)).numpy()
     np.savez(os.path.join(here, "kernelpy_vectors.npz"), packed=packed, scales=scales, dequant=deq, x=x,
-             x_fp8_dequant=xq_f, fp4_gemm=gemm, q8_in=w, q8_roundtrip=q8rt)
+             x_fp8_dequant=xq_f, fp4_gemm=gemm, q8_in=w, q8_roundtrip=q8rt, x_fp4_terms=np.stack(terms))
     print("wrote", sorted(os.listdir(here)))
 
 

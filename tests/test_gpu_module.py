@@ -61,3 +61,48 @@ def test_stream_value_ops_order_two_streams():
     torch.cuda.synchronize()
     assert int(flag.item()) == 7
     assert bool((result == 3.0).all())
+
+
+def test_graph_kernel_node_set_params_repoints_a_captured_launch():
+    """A launch captured into a graph, instantiated once, then pointed at other buffers without re-capturing
+    (hipGraphExecKernelNodeSetParams in the reference, crates/v4flash-hip/src/sys.rs:372)."""
+    import torch
+    from deepstrix_b200 import _build, moe
+    torch.cuda.set_device(0)
+    lib = moe.lib()
+    T, k, H = 9, 4, 1024
+    rng = np.random.default_rng(3)
+    parts = [torch.from_numpy(rng.standard_normal((T * k + T, H)).astype(np.float32)).cuda() for _ in range(2)]
+    outs = [torch.zeros((T, H), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    want = [moe.reduce_partials(p, T, k, with_shared=True) for p in parts]
+    mod = moe.Module(open(_build.CUBIN_PATH, "rb").read())
+    fn = mod.get_function("dsx_combine_kernel")
+    n = T * (H // 4)
+
+    def args_for(i):
+        return [C.c_void_p(parts[i].data_ptr()), C.c_int64(T), C.c_int(k), C.c_int64(H), C.c_int(1), C.c_void_p(0), C.c_int(0), C.c_int(0),
+                C.c_void_p(outs[i].data_ptr())]
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        moe._check(lib.dsx_graph_begin_capture(C.c_void_p(stream.cuda_stream)))
+        moe.Module.launch_raw(fn, ((n + 255) // 256, 1, 1), (256, 1, 1), 0, args_for(0))
+        ge, g = C.c_void_p(), C.c_void_p()
+        moe._check(lib.dsx_graph_end_capture_keep(C.c_void_p(stream.cuda_stream), C.byref(ge), C.byref(g)))
+        count = C.c_size_t(0)
+        moe._check(lib.dsx_graph_kernel_nodes(g, None, C.byref(count)))
+        assert count.value == 1
+        nodes = (C.c_void_p * 1)()
+        moe._check(lib.dsx_graph_kernel_nodes(g, nodes, C.byref(count)))
+        moe._check(lib.dsx_graph_launch(ge, C.c_void_p(stream.cuda_stream)))
+        stream.synchronize()
+        assert torch.equal(outs[0], want[0]) and not bool(outs[1].any())
+        a1 = args_for(1)
+        ptrs = (C.c_void_p * len(a1))(*[C.cast(C.pointer(a), C.c_void_p) for a in a1])
+        moe._check(lib.dsx_graph_exec_kernel_node_set_params(ge, nodes[0], None, None, None, 0, ptrs))
+        moe._check(lib.dsx_graph_launch(ge, C.c_void_p(stream.cuda_stream)))
+        stream.synchronize()
+        assert torch.equal(outs[1], want[1])
+        lib.dsx_graph_destroy(ge)
+        lib.dsx_graph_template_destroy(g)
+    mod.close()

@@ -379,6 +379,25 @@ def test_layer_prefill_tensor_core_path_small(torch_cuda, moe, oracle, T, E, k):
     assert rel_l2(out, ref) <= REL_L2_TOL
 
 
+def test_layer_prefill_matches_oracle_with_the_same_activation_terms(torch_cuda, moe, oracle):
+    """The block-scaled path multiplies the stored FP4 weights by three MXFP4 terms per activation row.  Against
+    an oracle that sees the activations through the same three terms (and mid rounded to f16, as the kernel stores
+    it) what is left is f32 summation order and the bf16 rounding of the output: well under the distance to the
+    exact-activation oracle, which the other tests hold to 1e-2."""
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import MoeConfig, RouterConfig
+    cfg = MoeConfig(hidden=512, ffn=256, shared_ffn=256,
+                    router=RouterConfig(n_expert=32, n_used=4, n_group=1, topk_group=1, score_fn=1, route_scale=2.5))
+    out, ref, layer, w, x, routing = _layer_case(torch_cuda, moe, oracle, cfg, 2, 700)
+    xb = synth.make_tokens(cfg, 2, 700)
+    shared = tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down"))
+    same = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), routing["selected"], routing["weights"], w["gate"], w["up"], w["down"],
+                                shared=shared, clamp=cfg.clamp, mid_round=1, n_expert=32, act_mode=oracle.act_mxfp4(3))
+    exact_err, same_err = rel_l2(out, ref), rel_l2(out, same)
+    assert exact_err <= REL_L2_TOL
+    assert same_err < 2.2e-3 and same_err < exact_err, (same_err, exact_err)
+
+
 def test_layer_prefill_config0_shapes(torch_cuda, moe, oracle):
     from deepstrix_b200.config import CONFIGS
     out, ref, *_ = _layer_case(torch_cuda, moe, oracle, CONFIGS[0], 0, 192)
@@ -473,6 +492,60 @@ def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
         acc += layer.forward_picks(x, sel, wt, expert_lo=lo, with_shared=(lo == 0)).float().cpu().numpy()
         assert layer.check() == 0
     assert rel_l2(acc, out_full) < 8e-3   # three bf16 roundings instead of one
+
+
+@pytest.mark.parametrize("T", [16, 200])
+def test_forward_remap_interleaved_ownership_sums_to_full(torch_cuda, moe, oracle, T):
+    """The reference's ownership table (het/weights.rs:1357-1381): three owners hold interleaved, unequal, unordered
+    subsets of the experts (no contiguous range could describe them); each returns its weighted partial sum for the
+    picks it owns, a sentinel pick (id n_expert) and a NO_PICK belong to nobody, and the partial sums add up to the
+    full layer.  Both kernel families (16 tokens: grouped GEMV; 200: tensor cores)."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS
+    cfg = CONFIGS[0]
+    E, k = cfg.router.n_expert, cfg.router.n_used
+    w = synth.make_layer(cfg, 0)
+    full = moe.build_layer_from_host(cfg, w, max_tokens=T)
+    xb = synth.make_tokens(cfg, 0, T)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    out_full = full.forward(x).float().cpu().numpy()
+    r = full.routing(T)
+    rng = np.random.default_rng(31)
+    owner_of = rng.integers(0, 3, size=E)
+    owner_of[::7] = 0                                   # unequal shares
+    rw = torch.from_numpy(w["router_w"]).cuda()
+    shared = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
+    sel = r["selected"].copy()
+    wt = r["weights"].copy()
+    acc = np.zeros_like(out_full)
+    for owner in range(3):
+        mine = rng.permutation(np.nonzero(owner_of == owner)[0])       # slot order unrelated to expert order
+        remap = np.zeros(E, np.int32)                                   # >= 0: someone else's
+        for slot, e in enumerate(mine):
+            remap[e] = -(slot + 1)
+        store = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, tuple(a[mine] for a in w["gate"]), tuple(a[mine] for a in w["up"]),
+                                                  tuple(a[mine] for a in w["down"]))
+        layer = moe.MoeLayer(cfg, store, shared, rw, None, max_tokens=T)
+        got = layer.forward_remap(x, torch.from_numpy(sel).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(remap).cuda(),
+                                  with_shared=(owner == 0))
+        assert layer.check() == 0
+        acc += got.float().cpu().numpy()
+        layer.close()
+    assert rel_l2(acc, out_full) < 8e-3                 # bf16 rounding of three partial results instead of one
+    # a sentinel id and a NO_PICK in place of two real picks: their contribution disappears, nothing else changes
+    sel2 = sel.copy()
+    sel2[0, 0], sel2[1, 1] = E, -1
+    remap_all = -(np.arange(E, dtype=np.int32) + 1)
+    a = full.forward_remap(x, torch.from_numpy(sel2).cuda(), torch.from_numpy(wt).cuda(), torch.from_numpy(remap_all).cuda()).float().cpu().numpy()
+    shared_t = tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down"))
+    wt2 = wt.copy()
+    wt2[0, 0] = wt2[1, 1] = 0.0
+    sel_ref = np.where((sel2 < 0) | (sel2 >= E), 0, sel2)
+    ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), sel_ref, wt2, w["gate"], w["up"], w["down"], shared=shared_t,
+                               clamp=cfg.clamp, n_expert=E)
+    assert rel_l2(a, ref) <= REL_L2_TOL
+    full.close()
 
 
 @pytest.mark.parametrize("T", [3, 16, 80])

@@ -86,8 +86,10 @@ def test_layer_config2_full_size_rows_of_every_expert(torch_cuda, moe, oracle, f
     rows = [oo[e] if e % 2 == 0 else oo[e + 1] - 1 for e in range(E)]
     big = int(np.argmax(oh))
     rows += [oo[big] + oh[big] // 2 - 1, oo[big] + oh[big] // 2]      # either side of the busiest expert's split
-    tokens = _tokens_at_rows(op, k, rows)
-    assert 200 <= tokens.size <= 300
+    tokens = _tokens_at_rows(op, k, rows)          # a token sits in 8 experts' segments: fewer tokens than rows
+    assert tokens.size >= 100
+    extra = np.random.default_rng(9).choice(T, size=max(0, 256 - tokens.size), replace=False)
+    tokens = np.unique(np.concatenate([tokens, extra]))
     ref = _oracle_rows(oracle, cfg, w, xb, osel, ow, tokens)
     err = rel_l2(out[tokens], ref)
     assert err <= REL_L2_TOL, err
@@ -163,7 +165,7 @@ def test_layer_config3_full_size(torch_cuda, moe, oracle):
     rng = np.random.default_rng(5)
     extra = rng.choice(T, size=max(0, 256 - tokens.size), replace=False)
     tokens = np.unique(np.concatenate([tokens, extra]))
-    assert 200 <= tokens.size <= 400
+    assert 100 <= tokens.size <= 400
     ref = _oracle_rows(oracle, cfg, w, xb, osel, ow, tokens)
     err = rel_l2(out[tokens], ref)
     assert err <= REL_L2_TOL, err

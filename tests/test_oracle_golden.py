@@ -240,3 +240,52 @@ def test_glue_restatements_match_plain_formulas(oracle):
     got = oracle.hc_post(bo, rh, post, comb)
     ref = bo[:, None, :].astype(np.float64) * post[:, :, None] + np.einsum("tsd,tsk->tkd", rh.astype(np.float64), comb.reshape(3, 4, 4))
     assert np.abs(got - ref).max() < 1e-5
+
+
+def test_activation_quantisers_match_reference_kernel_py(oracle):
+    """The two activation quantisers the tensor-core path is judged with, against outputs of the reference's
+    scripts/v41_oracle/kernel.py: act_quant (E4M3, block 32, ue8m0 scales; :85-106) bit for bit, and the three
+    MXFP4 terms (fp4_act_quant, :129-147, applied to x and then to what each term left over) term by term."""
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kernelpy_vectors.npz"))
+    x = g["x"]
+    got = np.stack([oracle.act_quant_e4m3(r) for r in x])
+    assert np.array_equal(got.view(np.uint32), g["x_fp8_dequant"].view(np.uint32))
+    e2m1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+    for i in range(x.shape[0]):
+        codes, scales, total = oracle.act_terms_mxfp4(x[i], 3)
+        acc = np.zeros_like(x[i])
+        for t in range(3):
+            vals = np.stack([e2m1[codes[t] & 15], e2m1[codes[t] >> 4]], 1).reshape(-1)
+            term = vals * np.repeat(np.exp2(scales[t].astype(np.float32) - 127.0), 32).astype(np.float32)
+            assert np.array_equal(term, g["x_fp4_terms"][t, i])      # -0.0 == 0.0: values, not sign of zero
+            acc += term
+        assert np.array_equal(acc, total)
+    # three terms leave about 2^-9 of the row
+    left = x - g["x_fp4_terms"].sum(0)
+    assert np.linalg.norm(left) / np.linalg.norm(x) < 2.5e-3
+
+
+def test_operand_mix_error_measured_on_config0(oracle):
+    """What each tensor-core operand format costs on the layer output, measured on configuration 0 against the
+    dequantised-f32 oracle (the 1e-2 target): one E4M3 term per activation (the model's own FP8 numerics) and
+    one or two MXFP4 terms miss it; two E4M3 terms or three MXFP4 terms meet it with room to spare."""
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import CONFIGS
+    cfg = CONFIGS[0]
+    r = cfg.router
+    w = synth.make_layer(cfg, 0)
+    x = synth.bf16_bits_to_f32(synth.make_tokens(cfg, 0, 16))
+    sel, wt = oracle.router_topk(oracle.router_logits(x, w["router_w"]), w["router_bias"], r.n_used, r.n_group, r.topk_group, r.score_fn,
+                                 r.route_scale, r.weight_eps)
+    shared = tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down"))
+
+    def run(mode):
+        return oracle.moe_layer_f32(cfg.fmt, x, sel, wt, w["gate"], w["up"], w["down"], shared=shared, clamp=cfg.clamp, n_expert=r.n_expert,
+                                    act_mode=mode)
+    ref = run(oracle.ACT_EXACT).astype(np.float64)
+    err = {name: float(np.linalg.norm(run(mode) - ref) / np.linalg.norm(ref))
+           for name, mode in (("e4m3", oracle.ACT_E4M3), ("e4m3x2", oracle.ACT_E4M3_X2), ("mxfp4x1", oracle.act_mxfp4(1)),
+                              ("mxfp4x2", oracle.act_mxfp4(2)), ("mxfp4x3", oracle.act_mxfp4(3)))}
+    print("rel-L2 vs dequantised-f32 oracle:", {k: f"{v:.2e}" for k, v in err.items()})
+    assert err["e4m3"] > 1e-2 and err["mxfp4x1"] > 1e-1 and err["mxfp4x2"] > 1e-2
+    assert err["e4m3x2"] < 3e-3 and err["mxfp4x3"] < 5e-3
