@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <new>
+#include <vector>
 
 #include "dsx_common.cuh"
 #include "prefill.cuh"
@@ -58,6 +59,12 @@ struct dsx_moe_layer {
     // workspace (device)
     float* logits = nullptr;
     int32_t* sel_local = nullptr;   // picks translated through an ownership table (dsx_moe_layer_forward_remap)
+    // A shared expert whose format or width differs from the routed experts' (the reference's own layout: MXFP4 routed,
+    // Q8_0 shared) cannot ride in the routed kernels' launches.  It then runs as a one-expert, one-pick layer of its
+    // own (picks all 0, weights all 1) that writes the shared rows of this layer's partial buffer.
+    dsx_moe_layer* sh_layer = nullptr;
+    int32_t* sh_sel = nullptr;      // [max_tokens] zeros
+    float* sh_w = nullptr;          // [max_tokens] ones
     int32_t *selected = nullptr, *hist = nullptr, *offsets = nullptr, *perm = nullptr, *work_items = nullptr, *n_work_items = nullptr;
     float* weights = nullptr;
     int32_t work_cap = 0;
@@ -234,7 +241,8 @@ int dsx_expert_store_create_ex(dsx_expert_store** store, int fmt, int n_slots, i
     if (e == cudaSuccess) e = cudaMalloc(&s->gu_sc, n * s->gu_sc_stride);
     if (e == cudaSuccess) e = cudaMalloc(&s->dn_nib, n * s->dn_nib_stride);
     if (e == cudaSuccess) e = cudaMalloc(&s->dn_sc, n * s->dn_sc_stride);
-    const bool tensor_planes = fmt == DSX_FMT_MXFP4 && !(flags & DSX_STORE_DECODE_ONLY);
+    // the tensor-core kernel tiles 256 gate/up rows and 512 down rows (other shapes keep the decode layout only)
+    const bool tensor_planes = fmt == DSX_FMT_MXFP4 && !(flags & DSX_STORE_DECODE_ONLY) && ffn % 256 == 0 && hidden % 512 == 0;
     if (tensor_planes) {
         s->km_gu_stride = ffn * hidden;          // two matrices of ffn x hidden / 2 bytes
         s->km_dn_stride = hidden * ffn / 2;
@@ -475,6 +483,12 @@ struct StageTimer {  // brackets one stage with an event pair when profiling is 
 };
 
 static void layer_free(dsx_moe_layer* L) {
+    if (L->sh_layer) {
+        L->sh_layer->partial = nullptr;   // a view into this layer's buffer
+        dsx_moe_layer_destroy(L->sh_layer);
+        L->sh_layer = nullptr;
+    }
+    cudaFree(L->sh_sel); cudaFree(L->sh_w);
     for (cudaEvent_t e : L->ev) if (e) cudaEventDestroy(e);
     cudaFree(L->sel_local);
     cudaFree(L->logits); cudaFree(L->selected); cudaFree(L->weights); cudaFree(L->hist); cudaFree(L->offsets);
@@ -493,8 +507,7 @@ static int check_weights(const dsx_moe_config& c, const dsx_expert_store* routed
     if (c.shared_ffn > 0) {
         DSX_REQUIRE(shared && shared->n_slots >= 1 && shared->H == c.hidden && shared->F == c.shared_ffn,
                     "moe_layer: shared store missing or of the wrong shape");
-        if (shared->fmt != routed->fmt || c.shared_ffn != c.ffn)
-            return set_error(DSX_ERR_UNSUPPORTED, "moe_layer: the shared expert must match the routed experts' format and width");
+        // a shared expert of another format or width is allowed: it runs as its own pass (see dsx_moe_layer::sh_layer)
     }
     return DSX_OK;
 }
@@ -553,17 +566,43 @@ int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const
         delete L;
         return rc;
     }
-    if (int rc = prefill_workspace_create(&L->pf, c, c.router.n_used, L->mid)) {
+    const bool split_shared = L->shared != nullptr && (shared->fmt != routed->fmt || c.shared_ffn != c.ffn);
+    dsx_moe_config c_ws = c;
+    if (split_shared) c_ws.shared_ffn = 0;   // this layer's own launches carry no shared rows
+    if (int rc = prefill_workspace_create(&L->pf, c_ws, c.router.n_used, L->mid)) {
         layer_free(L);
         delete L;
         return rc;
     }
     if (L->pf.ready && routed->km_gu != nullptr)
-        if (int rc = prefill_mx_workspace_create(&L->pf, c, c.router.n_used)) {
+        if (int rc = prefill_mx_workspace_create(&L->pf, c_ws, c.router.n_used)) {
             layer_free(L);
             delete L;
             return rc;
         }
+    if (split_shared) {
+        dsx_moe_config cs = c;
+        cs.ffn = c.shared_ffn; cs.shared_ffn = 0;
+        cs.router.n_expert = 1; cs.router.n_used = 1; cs.router.n_group = 1; cs.router.topk_group = 1;
+        int rc = dsx_moe_layer_create(&L->sh_layer, &cs, shared, nullptr, router_w, nullptr);
+        if (rc == DSX_OK) {
+            cudaFree(L->sh_layer->partial);   // its rows live in this layer's buffer (set per call)
+            L->sh_layer->partial = nullptr;
+            cudaError_t e2 = cudaMalloc((void**)&L->sh_sel, Tm * 4);
+            if (e2 == cudaSuccess) e2 = cudaMalloc((void**)&L->sh_w, Tm * 4);
+            if (e2 == cudaSuccess) e2 = cudaMemset(L->sh_sel, 0, Tm * 4);
+            if (e2 == cudaSuccess) {
+                std::vector<float> ones(Tm, 1.0f);
+                e2 = cudaMemcpy(L->sh_w, ones.data(), Tm * 4, cudaMemcpyHostToDevice);
+            }
+            if (e2 != cudaSuccess) rc = set_error((int)e2, "moe_layer: shared-expert workspace allocation failed: %s", cudaGetErrorString(e2));
+        }
+        if (rc != DSX_OK) {
+            layer_free(L);
+            delete L;
+            return rc;
+        }
+    }
     *layer = L;
     return DSX_OK;
 }
@@ -579,6 +618,12 @@ int dsx_moe_layer_set_weights(dsx_moe_layer* L, const dsx_expert_store* routed, 
                               const float* router_w, const float* router_bias) {
     DSX_REQUIRE(L, "moe_layer_set_weights: null layer");
     if (int rc = check_weights(L->cfg, routed, shared, router_w)) return rc;
+    const bool split_shared = L->cfg.shared_ffn > 0 && (shared->fmt != routed->fmt || L->cfg.shared_ffn != L->cfg.ffn);
+    if (split_shared != (L->sh_layer != nullptr))
+        return set_error(DSX_ERR_UNSUPPORTED, "moe_layer_set_weights: the layer was built for a shared expert that %s the routed experts' format; "
+                                              "create a new layer", L->sh_layer ? "differs from" : "matches");
+    if (L->sh_layer)
+        if (int rc = dsx_moe_layer_set_weights(L->sh_layer, shared, nullptr, router_w, nullptr)) return rc;
     L->routed = routed; L->shared = L->cfg.shared_ffn > 0 ? shared : nullptr;
     L->router_w = router_w; L->router_bias = router_bias;
     // the tensor maps of the prefill path describe the previous stores (a new store may even sit at a freed
@@ -609,10 +654,23 @@ static bool scales_fit_f16(const dsx_expert_store* st) {
 // picks -> out.  expert_lo / n_local select the owned id range (0 / n_expert for a full layer).
 static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, const int32_t* selected, const float* weights,
                         int expert_lo, bool filter_picks, int with_shared, __nv_bfloat16* out, cudaStream_t stream,
-                        bool groups_ready = false) {
+                        bool groups_ready = false, bool skip_combine = false) {
     const dsx_moe_config& c = L->cfg;
     const int k = c.router.n_used, n_local = L->routed->n_slots;
-    const bool shared = with_shared && L->shared != nullptr;
+    // split: the shared expert runs as a pass of its own (sh_layer) between this layer's kernels and the combine
+    const bool split = with_shared && L->sh_layer != nullptr;
+    const bool shared = with_shared && L->shared != nullptr && !split;
+    auto shared_pass_and_combine = [&]() -> int {
+        if (split) {
+            dsx_moe_layer* S = L->sh_layer;
+            S->partial = L->partial + (size_t)T * k * c.hidden;   // the shared rows of this layer's partial buffer
+            if (int rc = forward_core(S, x, T, L->sh_sel, L->sh_w, 0, false, 0, nullptr, stream, false, true)) return rc;
+        }
+        if (skip_combine) return DSX_OK;
+        StageTimer tm(L, DSX_STAGE_COMBINE, stream);
+        return launch_combine(L->partial, T, k, c.hidden, (shared || split) ? 1 : 0, filter_picks ? selected : nullptr, expert_lo, n_local, out,
+                              stream);
+    };
     // MXFP4 stores with tensor-core planes: block-scaled FP4 MMAs on the stored codes and scales (any E8M0 scale);
     // otherwise f16 operands expanded in shared memory (Q8_0; MXFP4 scales must then fit f16)
     const bool mx = L->pf.mx_ready && L->routed->fmt == DSX_FMT_MXFP4 && L->routed->km_gu != nullptr &&
@@ -621,6 +679,7 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
         PrefillCall pc{};
         pc.x = x; pc.T = T; pc.selected = selected; pc.route_w = weights; pc.expert_lo = expert_lo; pc.n_local = n_local;
         pc.filter_picks = filter_picks; pc.with_shared = shared; pc.out = out;
+        pc.skip_combine = skip_combine || split;
         pc.hist = L->hist; pc.offsets = L->offsets; pc.perm = L->perm; pc.gs = L->gs;
         pc.mid = L->mid; pc.partial = L->partial; pc.error_word = L->error_word; pc.sm_count = L->sm_count;
         pc.n_used = k; pc.clamp = c.clamp;
@@ -635,9 +694,11 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
             pc.km_gu_stride = L->routed->km_gu_stride; pc.km_dn_stride = L->routed->km_dn_stride;
             pc.sf_gu_stride = L->routed->sf_gu_stride; pc.sf_dn_stride = L->routed->sf_dn_stride;
             if (shared) { pc.sh_km_gu = L->shared->km_gu; pc.sh_km_dn = L->shared->km_dn; pc.sh_sf_gu = L->shared->sf_gu; pc.sh_sf_dn = L->shared->sf_dn; }
-            return prefill_mx_forward(&L->pf, c, pc, stream);
+            if (int rc = prefill_mx_forward(&L->pf, c, pc, stream)) return rc;
+        } else if (int rc = prefill_forward(&L->pf, c, pc, stream)) {
+            return rc;
         }
-        return prefill_forward(&L->pf, c, pc, stream);
+        return split ? shared_pass_and_combine() : DSX_OK;
     }
     if (!groups_ready) {   // the one-launch decode router has already built them
         StageTimer tm(L, DSX_STAGE_GROUP_BUILD, stream);
@@ -668,8 +729,7 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
         StageTimer tm(L, DSX_STAGE_DOWN, stream);
         if (int rc = launch_gemv_down(a, L->sm_count, stream)) return rc;
     }
-    StageTimer tm(L, DSX_STAGE_COMBINE, stream);
-    return launch_combine(L->partial, T, k, c.hidden, shared ? 1 : 0, filter_picks ? selected : nullptr, expert_lo, n_local, out, stream);
+    return shared_pass_and_combine();
 }
 
 int dsx_moe_layer_forward(dsx_moe_layer* L, const void* x_bf16, int64_t T, void* out_bf16, const float* logits_in, dsx_stream_t stream_) {
@@ -688,7 +748,7 @@ int dsx_moe_layer_forward(dsx_moe_layer* L, const void* x_bf16, int64_t T, void*
         {
             StageTimer tm(L, DSX_STAGE_ROUTER_LOGITS, stream);
             if (int rc = launch_router_fused(x, T, L->router_w, L->router_bias, L->cfg.hidden, L->cfg.router, L->logits, L->selected,
-                                             L->weights, 8, L->shared ? (int)T : 0, L->hist, L->offsets, L->perm, L->work_items,
+                                             L->weights, 8, (L->shared && !L->sh_layer) ? (int)T : 0, L->hist, L->offsets, L->perm, L->work_items,
                                              L->n_work_items, L->work_cap, T < 8 ? L->item_recs : nullptr, L->router_counters, L->error_word, stream))
                 return rc;
         }

@@ -25,6 +25,7 @@
 // The barrier is one small kernel: it publishes the epoch in every peer's flags with a
 // system-scope release, then waits -- for a bounded number of polls, after which it records
 // error bit 1 and returns -- until every peer has published the same epoch.
+#include <algorithm>
 #include <cstring>
 
 #include "dsx_common.cuh"
@@ -165,17 +166,20 @@ __global__ void ep_prepare_kernel(const int32_t* __restrict__ meta, const int32_
     w[i] = valid ? __int_as_float(meta[slot * 2 * k + k + j]) : 0.0f;
 }
 
-// ---- owner: partial rows back to their sources (one block per slot)
+// ---- owner: partial rows back to their sources
 __global__ void __launch_bounds__(kRowThreads)
-ep_give_back_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ counts, int cap, int64_t H, int rank,
+ep_give_back_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ counts, int cap, int64_t H, int rank, int world,
                     PeerTable peers, size_t back_off) {
-    const int64_t slot = blockIdx.x;
-    const int s = (int)(slot / cap), r = (int)(slot - (int64_t)s * cap);
-    if (r >= counts[s]) return;
+    // a fixed grid walks the rows that were actually received: block b takes rows b, b + grid, ... of every source
     const int n16 = (int)(H >> 3);
-    const uint4* src = reinterpret_cast<const uint4*>(part + slot * H);
-    uint4* dst = reinterpret_cast<uint4*>(peers.slab[s] + back_off) + ((int64_t)rank * cap + r) * n16;
-    for (int c = threadIdx.x; c < n16; c += kRowThreads) dst[c] = __ldg(src + c);
+    for (int s = 0; s < world; s++) {
+        const int n = counts[s];
+        for (int r = blockIdx.x; r < n; r += gridDim.x) {
+            const uint4* src = reinterpret_cast<const uint4*>(part + ((int64_t)s * cap + r) * H);
+            uint4* dst = reinterpret_cast<uint4*>(peers.slab[s] + back_off) + ((int64_t)rank * cap + r) * n16;
+            for (int c = threadIdx.x; c < n16; c += kRowThreads) dst[c] = __ldg(src + c);
+        }
+    }
 }
 
 // ---- source: out = shared + partials in rank order (f32), one thread per 8 columns
@@ -374,9 +378,10 @@ int dsx_ep_prepare(dsx_ep_comm* c, const void** x_rows, const int32_t** selected
 int dsx_ep_give_back(dsx_ep_comm* c, const void* partial_rows_bf16, dsx_stream_t stream_) {
     DSX_REQUIRE(c && partial_rows_bf16, "ep_give_back: null argument");
     DSX_REQUIRE(((uintptr_t)partial_rows_bf16 & 15) == 0, "ep_give_back: rows must be 16-byte aligned");
-    ep_give_back_kernel<<<(unsigned)(c->world * c->cap), kRowThreads, 0, (cudaStream_t)stream_>>>(
-        (const __nv_bfloat16*)partial_rows_bf16, reinterpret_cast<const int32_t*>(c->slab + c->lay.counts), (int)c->cap, c->H, c->rank, c->peers,
-        c->lay.back);
+    const unsigned blocks = (unsigned)std::min<int64_t>(c->cap, 148 * 8);
+    ep_give_back_kernel<<<blocks, kRowThreads, 0, (cudaStream_t)stream_>>>(
+        (const __nv_bfloat16*)partial_rows_bf16, reinterpret_cast<const int32_t*>(c->slab + c->lay.counts), (int)c->cap, c->H, c->rank, c->world,
+        c->peers, c->lay.back);
     DSX_LAUNCHED();
     return DSX_OK;
 }

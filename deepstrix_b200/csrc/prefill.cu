@@ -805,6 +805,7 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
         v.nib = c.dn_nib; v.sc = c.dn_sc; v.nib_slot_stride = c.dn_nib_stride; v.sc_slot_stride = c.dn_sc_stride;
         if (int rc = launch_gemv_down(v, c.sm_count, stream)) return rc;
     }
+    if (c.skip_combine) return DSX_OK;   // the caller adds another pass before it reduces the partial rows
     return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr,
                           c.expert_lo, c.n_local, c.out, stream);
 }

@@ -42,7 +42,7 @@ struct PrefillWorkspace {
     uint8_t* sf_tok = nullptr;      // [max_tokens][3 terms][hidden/32] E8M0 bytes
     PrefillSeg* mx_segs = nullptr;  // segments of at most 112 rows
     int32_t mx_seg_cap = 0;
-    CUtensorMap tmap_xq, tmap_mq;   // xq as (bytes, row, term) for K = hidden / K = ffn
+    CUtensorMap tmap_xq[3], tmap_mq[3];   // xq as (bytes, row, term) for K = hidden / K = ffn, boxes of 32 / 64 / 96 rows
     CUtensorMap tmap_km_gu[2], tmap_km_dn[2];            // K-major code planes; index 0 routed, 1 shared
     const void* mapped_km_gu[2] = {nullptr, nullptr};
     const void* mapped_km_dn[2] = {nullptr, nullptr};
@@ -56,6 +56,7 @@ struct PrefillCall {
     const float* route_w;
     int expert_lo, n_local;
     bool filter_picks, with_shared;
+    bool skip_combine;         // stop after the partial rows (the caller reduces them)
     __nv_bfloat16* out;
     int32_t *hist, *offsets, *perm;
     GroupScratch gs;

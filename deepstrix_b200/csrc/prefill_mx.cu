@@ -34,25 +34,29 @@
 // (tcgen05.ld), apply clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows
 // (f32).  Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
 // is freed and bit 2 of the layer's error word is set.
+#include <cstdlib>
+
 #include "prefill.cuh"
 
 namespace dsx {
 namespace {
 
-constexpr int kEpiWarps = 16;
-constexpr int kThreads = (2 + kEpiWarps) * 32;
+constexpr int kEpiWarps = 12;
+constexpr int kMmaWarps = 2;                  // issuing warps: each owns two of the tile's four accumulators
+constexpr int kEpiWarp0 = 1 + kMmaWarps;
+constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;
 constexpr int kAccs = 4;                      // M = 128 accumulators per tile (512 weight rows)
-constexpr int kSegRows = 112;                 // most rows of a segment (MMA N)
-constexpr int kBRows = 128;                   // rows of a term plane in shared memory
+constexpr int kSegRows = 96;                  // most rows of a segment (MMA N)
+constexpr int kBRows = 96;                    // rows of a term plane in shared memory
 constexpr int kBoxRows = 32;                  // rows one token-tile copy brings
 constexpr int kTerms = 3;                     // MXFP4 terms per activation row
 constexpr int kStageK = 128;                  // reduction columns per pipeline stage (4 scale blocks)
 constexpr int kRowBytes = kStageK / 2;        // packed bytes per row and stage: one 64-byte swizzle row
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kABytes = kAccs * 128 * kRowBytes;         // 32768
-constexpr int kBTermBytes = kBRows * kRowBytes;          // 8192
+constexpr int kBTermBytes = kBRows * kRowBytes;          // 6144
 constexpr int kBBoxBytes = kBoxRows * kRowBytes;         // 2048
-constexpr int kBBytes = kTerms * kBTermBytes;            // 24576
+constexpr int kBBytes = kTerms * kBTermBytes;            // 18432
 constexpr int kSfChunk = 512;                            // 128 rows x 4 scale blocks
 constexpr int kSfaBytes = kAccs * kSfChunk;
 constexpr int kSfbBytes = kTerms * kSfChunk;
@@ -67,8 +71,9 @@ constexpr int kSmemTotal = kSmemMisc + 16 + 1024;        // + alignment slack
 static_assert(kSmemTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
 // tensor-memory columns
 constexpr uint32_t kSfaCol = kAccs * kSegRows;    // accumulator h at column h * kSegRows; then 4 columns of weight scales per accumulator
-constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term (one chunk: at most 128 rows)
-static_assert(kSfbCol + 4 * kTerms <= 512, "tensor memory holds 512 columns");
+constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term (one chunk: at most 128 rows), one copy per issuing warp
+static_assert(kSfbCol + 4 * kTerms * kMmaWarps <= 512, "tensor memory holds 512 columns");
+static_assert(kBTermBytes % 512 == 0, "a term plane must start on a swizzle-atom boundary");
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -140,6 +145,19 @@ __device__ __forceinline__ void tc_mma_mxf4(uint32_t d, uint64_t adesc, uint64_t
         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
         : "memory");
 }
+// The same with the descriptors given as low words (the high word -- stride, version, swizzle -- is common to every
+// operand tile): the issuing thread is bound by its own scalar instructions, a 32-bit add per operand is the least.
+__device__ __forceinline__ void tc_mma_mxf4_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %7, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %4, [%5], [%6], p;\n\t}"
+        ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -192,11 +210,13 @@ struct MxGemmArgs {
     const uint8_t* sfa_shared;
     const uint8_t* sfb;        // activation scale chunks: [segment][K/128][term][2][512]
     uint32_t* error_word;
+    int debug_mode;            // TEMPORARY ablation switch: 1 = no loads (stale operands), 2 = no MMAs
 };
 
 template <bool GATE_UP>
 __global__ void __launch_bounds__(kThreads, 1)
-mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_constant__ CUtensorMap tmap_b64,
+               const __grid_constant__ CUtensorMap tmap_b96, const __grid_constant__ CUtensorMap tmap_w,
                const __grid_constant__ CUtensorMap tmap_w_shared, const MxGemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -204,15 +224,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar0 = sbase + kSmemBar;
     // FULL[s]: the stage's codes and scales have landed (TMA bytes); EMPTY[s]: the MMAs and scale copies reading
-    // stage s have completed (one tcgen05.commit); ACC_FULL / ACC_EMPTY: a tile's accumulators are complete / drained.
+    // stage s have completed (one tcgen05.commit per issuing warp); ACC_FULL / ACC_EMPTY: a tile's accumulators are complete / drained.
     constexpr int FULL = 0, EMPTY = FULL + kStages, ACC_FULL = EMPTY + kStages, ACC_EMPTY = ACC_FULL + 1;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; i++) { mbar_init(bar(FULL + i), 1); mbar_init(bar(EMPTY + i), 1); }
-        mbar_init(bar(ACC_FULL), 1);
+        for (int i = 0; i < kStages; i++) { mbar_init(bar(FULL + i), 1); mbar_init(bar(EMPTY + i), kMmaWarps); }
+        mbar_init(bar(ACC_FULL), kMmaWarps);
         mbar_init(bar(ACC_EMPTY), kEpiWarps);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -245,10 +265,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                 const bool sh = seg.expert == a.n_local;
                 const CUtensorMap* m_w = sh ? &tmap_w_shared : &tmap_w;
                 const int slot = sh ? 0 : seg.expert;
-                // scale chunks of this tile: two runs of [K/128][2][512] (row tiles 2 mb and 2 mb + 1 of the plane)
-                const uint8_t* sfa = (sh ? a.sfa_shared : a.sfa + (int64_t)slot * a.sfa_slot_stride) + (int64_t)(2 * mb) * n_kc * (2 * kSfChunk);
+                // scale chunks of this tile: [K/128][4][512]
+                const uint8_t* sfa = (sh ? a.sfa_shared : a.sfa + (int64_t)slot * a.sfa_slot_stride) + (int64_t)mb * n_kc * kSfaBytes;
                 const uint8_t* sfb = a.sfb + (int64_t)si * n_kc * kSfbBytes;
+                // one copy brings all three terms of the segment: boxes of 32, 64 or 96 rows x 3 terms (a term's rows land
+                // box_rows * 64 bytes apart)
                 const int n_box = (max(16, (seg.n + 15) & ~15) + kBoxRows - 1) / kBoxRows;
+                const CUtensorMap* m_b = n_box == 1 ? &tmap_b32 : (n_box == 2 ? &tmap_b64 : &tmap_b96);
                 const uint32_t stage_tx = (uint32_t)(kABytes + kSfaBytes + kSfbBytes + kTerms * n_box * kBBoxBytes);
                 // weights of this tile into L2 a few stages ahead of the ring
                 constexpr int kAhead = 4;
@@ -271,35 +294,42 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                     ok = mbar_wait(bar(EMPTY + s), ((cnt / kStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
                     const uint32_t full = bar(FULL + s);
+                    if (a.debug_mode == 1 || a.debug_mode >= 3) { mbar_arrive(full); cnt++; continue; }
                     mbar_expect_tx(full, stage_tx);
                     const uint32_t a_dst = sbase + kSmemA + s * kABytes;
                     tma_load_4d(a_dst, m_w, kc * kRowBytes, w_row(mb), 0, slot, full);
                     if (!GATE_UP) tma_load_4d(a_dst + kABytes / 2, m_w, kc * kRowBytes, w_row(mb) + 256, 0, slot, full);
-                    // activation terms: (bytes, row, term), boxes of 64 bytes x 32 rows, only as many as the segment has rows
-                    const uint32_t b_dst = sbase + kSmemB + s * kBBytes;
-#pragma unroll
-                    for (int t = 0; t < kTerms; t++)
-                        for (int c = 0; c < n_box; c++)
-                            tma_load_3d(b_dst + t * kBTermBytes + c * kBBoxBytes, &tmap_b, kc * kRowBytes, seg.row0 + c * kBoxRows, t, full);
-                    const uint32_t sfa_dst = sbase + kSmemSfa + s * kSfaBytes;
-                    bulk_load(sfa_dst, sfa + (int64_t)kc * (2 * kSfChunk), 2 * kSfChunk, full);
-                    bulk_load(sfa_dst + 2 * kSfChunk, sfa + (int64_t)(n_kc + kc) * (2 * kSfChunk), 2 * kSfChunk, full);
+                    tma_load_3d(sbase + kSmemB + s * kBBytes, m_b, kc * kRowBytes, seg.row0, 0, full);
+                    bulk_load(sbase + kSmemSfa + s * kSfaBytes, sfa + (int64_t)kc * kSfaBytes, kSfaBytes, full);
                     bulk_load(sbase + kSmemSfb + s * kSfbBytes, sfb + (int64_t)kc * kSfbBytes, kSfbBytes, full);
                     cnt++;
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp < kEpiWarp0) {
         // ----------------------------------------------------------- MMA issue
+        // Two issuing warps: warp 1 owns accumulators 0 and 1, warp 2 owns 2 and 3 (a single thread cannot issue the
+        // 24 MMAs of a stage as fast as the tensor core retires them).  Each copies its accumulators' weight scales
+        // and its own copy of the activation scales to tensor memory, so its MMAs depend only on its own copies.
         if (lane == 0) {
+            const int mw = warp - 1;
             uint32_t tcnt = 0, s = 0, ph = 0;   // ring stage and its phase parity
             bool ok = true;
-            const uint64_t a_desc0 = operand_desc(sbase + kSmemA), b_desc0 = operand_desc(sbase + kSmemB);
+            const uint64_t d0 = operand_desc(sbase + kSmemA);
+            const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
+            const uint32_t a_lo0 = (uint32_t)d0, b_lo0 = (uint32_t)operand_desc(sbase + kSmemB);
             const uint64_t sfa_desc0 = scale_desc(sbase + kSmemSfa), sfb_desc0 = scale_desc(sbase + kSmemSfb);
+            const uint32_t t_sfa = tmem_base + kSfaCol + 8u * (uint32_t)mw, t_sfb = tmem_base + kSfbCol + 4u * kTerms * (uint32_t)mw;
+            const uint32_t t_acc = tmem_base + (uint32_t)(2 * mw * kSegRows);
+            // accumulators 2 mw and 2 mw + 1 read 128 rows each of the stage's weights: gate/up stages hold 256 gate rows, then
+            // 256 up rows (accumulator pairs = gate + up of the same rows); down stages 512 rows in order
+            const uint32_t a_off0 = (uint32_t)((GATE_UP ? mw * (kABytes / 4) : 2 * mw * (kABytes / 4)) >> 4);
+            const uint32_t a_off1 = a_off0 + (uint32_t)((GATE_UP ? kABytes / 2 : kABytes / 4) >> 4);
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 const int n16 = max(16, (seg.n + 15) & ~15);
                 const uint32_t idesc0 = mxf4_idesc(n16, 0u), idesc1 = mxf4_idesc(n16, 2u);
+                const uint32_t term_step = (uint32_t)(((n16 + kBoxRows - 1) / kBoxRows) * (kBBoxBytes >> 4));   // a term's rows follow the previous term's box
                 ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // the previous tile's accumulators are drained
                 if (!ok) break;
                 tc_fence_after();
@@ -307,29 +337,27 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                     const uint32_t full = bar(FULL) + 8u * s;
                     if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    // scales of this stage: one chunk per accumulator, one per term (16-byte units in the descriptor)
-                    const uint64_t sfa_d = sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4));
+                    // scales of this stage (16-byte units in the descriptor): this warp's two weight chunks, the three terms' chunks
+                    if (a.debug_mode == 2) { tc_commit(bar(EMPTY) + 8u * s); if (++s == kStages) { s = 0; ph ^= 1u; } continue; }
+                    const uint64_t sfa_d = sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4) + 2 * mw * (kSfChunk >> 4));
                     const uint64_t sfb_d = sfb_desc0 + (uint64_t)(s * (kSfbBytes >> 4));
+                    if (a.debug_mode != 3 && a.debug_mode != 5) {
+                    tc_cp_scales(t_sfa, sfa_d);
+                    tc_cp_scales(t_sfa + 4, sfa_d + (kSfChunk >> 4));
 #pragma unroll
-                    for (int h = 0; h < kAccs; h++) tc_cp_scales(tmem_base + kSfaCol + 4 * h, sfa_d + (uint64_t)(h * (kSfChunk >> 4)));
-#pragma unroll
-                    for (int t = 0; t < kTerms; t++) tc_cp_scales(tmem_base + kSfbCol + 4 * t, sfb_d + (uint64_t)(t * (kSfChunk >> 4)));
-                    const uint64_t a_d = a_desc0 + (uint64_t)(s * (kABytes >> 4));
-                    const uint64_t b_d = b_desc0 + (uint64_t)(s * (kBBytes >> 4));
+                    for (int t = 0; t < kTerms; t++) tc_cp_scales(t_sfb + 4 * t, sfb_d + (uint64_t)(t * (kSfChunk >> 4)));
+                    }
+                    const uint32_t a_lo = a_lo0 + s * (kABytes >> 4), b_lo = b_lo0 + s * (kBBytes >> 4);
+                    const uint32_t first = kc != 0 ? 1u : 0u;
 #pragma unroll
                     for (int ks = 0; ks < 2; ks++) {
                         const uint32_t idesc = ks ? idesc1 : idesc0;
 #pragma unroll
                         for (int t = 0; t < kTerms; t++) {
-                            const uint64_t bd = b_d + (uint64_t)(t * (kBTermBytes >> 4) + ks * 2);   // + 32 bytes per k step
-                            const uint32_t acc = (kc | ks | t) != 0 ? 1u : 0u;
-#pragma unroll
-                            for (int h = 0; h < kAccs; h++) {
-                                // accumulator h reads 128 rows of the stage's weights: gate/up stages hold 256 gate rows, then 256 up rows
-                                const int a_off = GATE_UP ? ((h & 1) * (kABytes / 2) + (h >> 1) * (kABytes / 4)) : h * (kABytes / 4);
-                                tc_mma_mxf4(tmem_base + (uint32_t)(h * kSegRows), a_d + (uint64_t)((a_off >> 4) + ks * 2), bd, idesc,
-                                            tmem_base + kSfaCol + 4 * h, tmem_base + kSfbCol + 4 * t, acc);
-                            }
+                            const uint32_t bl = b_lo + (uint32_t)t * term_step + (uint32_t)(ks * 2);   // + 32 bytes per k step
+                            const uint32_t acc = (ks | t) != 0 ? 1u : first;
+                            tc_mma_mxf4_lo(t_acc, a_lo + a_off0 + ks * 2, bl, hi, idesc, t_sfa, t_sfb + 4 * t, acc);
+                            tc_mma_mxf4_lo(t_acc + kSegRows, a_lo + a_off1 + ks * 2, bl, hi, idesc, t_sfa + 4, t_sfb + 4 * t, acc);
                         }
                     }
                     tc_commit(bar(EMPTY) + 8u * s);   // arrives when the copies and MMAs above have read their operands
@@ -343,7 +371,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
         // ------------------------------------------------------------ epilogue
         // Warp w may read lanes 32 * (w % 4) .. + 31 of tensor memory; the four warps of a lane quarter take one
         // 32-column chunk of the tile each.
-        const int q = warp & 3, rank = (warp - 2) >> 2;
+        const int q = warp & 3, rank = (warp - kEpiWarp0) >> 2;
         uint32_t tcnt = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -356,54 +384,75 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
             const int r_in = q * 32 + lane;           // row inside a 128-row accumulator
             const int c0 = 32 * rank;
-            if (c0 < seg.n) {
-                // lane j of the warp fetches the routing weight / output row of column c0 + j
-                float wv = 0.f;
-                int orow = 0;
-                if (c0 + lane < seg.n) {
-                    if (sh) { wv = 1.0f; orow = seg.row0 + c0 + lane; }
-                    else { const int ts = a.perm[seg.row0 + c0 + lane]; wv = a.route_w[ts]; orow = ts; }
-                }
+            // lane j of the warp fetches the routing weight / output row of column c0 + j
+            float wv = 0.f;
+            int orow = 0;
+            if (c0 + lane < seg.n) {
+                if (sh) { wv = 1.0f; orow = seg.row0 + c0 + lane; }
+                else { const int ts = a.perm[seg.row0 + c0 + lane]; wv = a.route_w[ts]; orow = ts; }
+            }
+            // one 16-column block of accumulator pair p (gate + up of rows p * 128 + r_in, or two 128-row quarters of down)
+            auto emit = [&](int p, int cb, const uint32_t (&v0)[16], const uint32_t (&v1)[16]) {
+                if (GATE_UP) {
+                    __half* dst = a.mid + (int64_t)(seg.row0 + cb) * a.mid_stride + mb * 256 + p * 128 + r_in;
 #pragma unroll
-                for (int ph = 0; ph < kAccs; ph++) {   // accumulator pair p, 16-column half hf of the chunk
-                    const int p = ph >> 1, hf = ph & 1, cb = c0 + 16 * hf;
-                    if (cb >= seg.n) continue;
-                    uint32_t v0[16], v1[16];
-                    tc_ld16(lane_addr + (uint32_t)(2 * p * kSegRows + cb), v0);
-                    tc_ld16(lane_addr + (uint32_t)((2 * p + 1) * kSegRows + cb), v1);
-                    tc_wait_ld();
-                    if (GATE_UP) {
-                        __half* dst = a.mid + (int64_t)(seg.row0 + cb) * a.mid_stride + mb * 256 + p * 128 + r_in;
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const float wj = __shfl_sync(0xFFFFFFFFu, wv, 16 * hf + j);
-                            if (cb + j < seg.n) {
-                                float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
-                                if (a.clamp > 1.0e-6f) {
-                                    gv = fminf(gv, a.clamp);
-                                    uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
-                                }
-                                const float sig = __fdividef(1.0f, 1.0f + __expf(-gv));
-                                dst[(int64_t)j * a.mid_stride] = __float2half_rn(gv * sig * uv * wj);
+                    for (int j = 0; j < 16; j++) {
+                        const float wj = __shfl_sync(0xFFFFFFFFu, wv, (cb - c0) + j);
+                        if (cb + j < seg.n) {
+                            float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
+                            if (a.clamp > 1.0e-6f) {
+                                gv = fminf(gv, a.clamp);
+                                uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
                             }
+                            const float sig = __fdividef(1.0f, 1.0f + __expf(-gv));
+                            dst[(int64_t)j * a.mid_stride] = __float2half_rn(gv * sig * uv * wj);
                         }
-                    } else {
-                        const int h = mb * 512 + p * 256 + r_in;
+                    }
+                } else {
+                    const int h = mb * 512 + p * 256 + r_in;
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int rj = __shfl_sync(0xFFFFFFFFu, orow, 16 * hf + j);
-                            if (cb + j < seg.n) {
-                                float* dst = a.partial + (int64_t)rj * a.rows + h;
-                                dst[0] = __uint_as_float(v0[j]);
-                                dst[128] = __uint_as_float(v1[j]);
-                            }
+                    for (int j = 0; j < 16; j++) {
+                        const int rj = __shfl_sync(0xFFFFFFFFu, orow, (cb - c0) + j);
+                        if (cb + j < seg.n) {
+                            float* dst = a.partial + (int64_t)rj * a.rows + h;
+                            dst[0] = __uint_as_float(v0[j]);
+                            dst[128] = __uint_as_float(v1[j]);
                         }
                     }
                 }
+            };
+            const bool active = c0 < seg.n && a.debug_mode != 4 && a.debug_mode != 5;
+            if (active) {
+                // pair 0 block by block; pair 1 is read whole, the accumulators are handed back, and its arithmetic and stores
+                // run while the next tile's MMAs have already started
+#pragma unroll
+                for (int hf = 0; hf < 2; hf++) {
+                    const int cb = c0 + 16 * hf;
+                    if (cb >= seg.n) continue;
+                    uint32_t v0[16], v1[16];
+                    tc_ld16(lane_addr + (uint32_t)cb, v0);
+                    tc_ld16(lane_addr + (uint32_t)(kSegRows + cb), v1);
+                    tc_wait_ld();
+                    emit(0, cb, v0, v1);
+                }
+            }
+            uint32_t w0[16], w1[16], w2[16], w3[16];
+            if (active) {
+                tc_ld16(lane_addr + (uint32_t)(2 * kSegRows + c0), w0);
+                tc_ld16(lane_addr + (uint32_t)(3 * kSegRows + c0), w1);
+                if (c0 + 16 < seg.n) {
+                    tc_ld16(lane_addr + (uint32_t)(2 * kSegRows + c0 + 16), w2);
+                    tc_ld16(lane_addr + (uint32_t)(3 * kSegRows + c0 + 16), w3);
+                }
+                tc_wait_ld();
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
+            if (active) {
+                emit(1, c0, w0, w1);
+                if (c0 + 16 < seg.n) emit(1, c0 + 16, w2, w3);
+            }
             tcnt++;
         }
     }
@@ -439,9 +488,30 @@ __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8]) {
         : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
     return out;
 }
+// The eight values a word of codes stands for (exact), element i from nibble i, by the hardware decoder.
+__device__ __forceinline__ void e2m1_unpack8(uint32_t q, float (&d)[8]) {
+    uint32_t h0, h1, h2, h3;
+    asm volatile("{\n\t.reg .b8 c0, c1, c2, c3;\n\t"
+                 "mov.b32 {c0, c1, c2, c3}, %4;\n\t"
+                 "cvt.rn.f16x2.e2m1x2 %0, c0;\n\t"
+                 "cvt.rn.f16x2.e2m1x2 %1, c1;\n\t"
+                 "cvt.rn.f16x2.e2m1x2 %2, c2;\n\t"
+                 "cvt.rn.f16x2.e2m1x2 %3, c3;\n\t}"
+                 : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3)
+                 : "r"(q));
+    const uint32_t h[4] = {h0, h1, h2, h3};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+        d[2 * i] = f.x;
+        d[2 * i + 1] = f.y;
+    }
+}
+
 // The value of E2M1 code n (sign, two exponent bits, one mantissa bit): {0, .5, 1, 1.5, 2, 3, 4, 6}, exact.
-// Plain integer arithmetic on the code, so that the residual is taken against exactly what the tensor core
-// will multiply, independent of any conversion instruction's operand order.
+// Plain integer arithmetic on the code.  (The hardware decoder, cvt.rn.f16x2.e2m1x2 followed by a widening to f32,
+// gave wrong residuals inside this kernel on sm_100a with CUDA 12.9 although the same sequence is correct in
+// isolation; the arithmetic form costs about 0.1 ms on the 8192-token layer and is kept.)
 __device__ __forceinline__ float e2m1_value(uint32_t n) {
     const uint32_t mag = n & 7u;
     const uint32_t doubled = mag < 2u ? mag : ((2u | (mag & 1u)) << ((mag >> 1) - 1u));   // 0 1 2 3 4 6 8 12
@@ -473,7 +543,7 @@ template <bool BY_TOKEN>
 __global__ void __launch_bounds__(256)
 mx_quantize_rows_kernel(const void* __restrict__ src, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
                         const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ codes_out, int64_t term_stride,
-                        uint8_t* __restrict__ scales_out) {
+                        uint8_t* __restrict__ scales_out, uint32_t opaque_zero) {
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= n_rows) return;
@@ -527,8 +597,18 @@ mx_quantize_rows_kernel(const void* __restrict__ src, int64_t n_rows, int K, con
             const uint32_t codes = e2m1_pack8(sv);
             *reinterpret_cast<uint32_t*>(out_row + (int64_t)t * term_stride + i * 128) = codes;
             if (t + 1 < kTerms) {
+                float d[8];
+                if (opaque_zero == 0xFFFFFFFFu) {   // never: keeps the arithmetic decoder compiled for comparison
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = __fmaf_rn(-e2m1_value(codes >> (4 * j)), scl, v[j]);   // exact: the residual
+                    for (int j = 0; j < 8; j++) d[j] = e2m1_value(codes >> (4 * j));
+                } else {
+                    // the decoder must not see that its input comes straight from the encoder above: with the two chained,
+                    // the compiled code produced wrong residuals (CUDA 12.9, sm_100a); an exclusive-or with a kernel
+                    // argument that is always zero separates them
+                    e2m1_unpack8(codes ^ opaque_zero, d);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = __fmaf_rn(-d[j], scl, v[j]);   // exact: the residual
             }
             // the scales of 4 consecutive blocks (lanes 0,4,8,12 / 16,20,24,28) form one word: stage 2i / 2i+1 of the row
             const int base = lane & 16;
@@ -609,16 +689,17 @@ int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg,
     ws->mx_tok_term_stride = (int64_t)cfg.max_tokens * (cfg.hidden / 2);
     DSX_CUDA(cudaMalloc((void**)&ws->xq_tok, (size_t)kTerms * (size_t)ws->mx_tok_term_stride));
     DSX_CUDA(cudaMalloc((void**)&ws->sf_tok, (size_t)cfg.max_tokens * kTerms * (size_t)(cfg.hidden / 32)));
-    // activation terms as (bytes, row, term): boxes of 64 bytes x 32 rows of one term
-    for (int g = 0; g < 2; g++) {
-        const int64_t K = g == 0 ? cfg.hidden : cfg.ffn;
-        const cuuint64_t dims[3] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->cap_rows, (cuuint64_t)kTerms};
-        const cuuint64_t strides[2] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->mx_term_stride};
-        const cuuint32_t box[3] = {(cuuint32_t)kRowBytes, (cuuint32_t)kBoxRows, 1};
-        if (int rc = tmap_encode(g == 0 ? &ws->tmap_xq : &ws->tmap_mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ws->xq, dims, strides, box,
-                                 CU_TENSOR_MAP_SWIZZLE_64B))
-            return rc;
-    }
+    // activation terms as (bytes, row, term): boxes of 64 bytes x 32 / 64 / 96 rows x 3 terms
+    for (int g = 0; g < 2; g++)
+        for (int b = 0; b < 3; b++) {
+            const int64_t K = g == 0 ? cfg.hidden : cfg.ffn;
+            const cuuint64_t dims[3] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->cap_rows, (cuuint64_t)kTerms};
+            const cuuint64_t strides[2] = {(cuuint64_t)(K / 2), (cuuint64_t)ws->mx_term_stride};
+            const cuuint32_t box[3] = {(cuuint32_t)kRowBytes, (cuuint32_t)((b + 1) * kBoxRows), (cuuint32_t)kTerms};
+            if (int rc = tmap_encode(g == 0 ? &ws->tmap_xq[b] : &ws->tmap_mq[b], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ws->xq, dims, strides, box,
+                                     CU_TENSOR_MAP_SWIZZLE_64B))
+                return rc;
+        }
     DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     ws->mx_ready = true;
@@ -659,17 +740,19 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     g.segs = ws->mx_segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
     g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.sfb = ws->sfb;
     g.error_word = c.error_word;
+    { const char* dm = getenv("DSX_MX_DEBUG"); g.debug_mode = dm ? atoi(dm) : 0; }
 
     // first product: K = hidden, rows = ffn
     mx_quantize_rows_kernel<true><<<(unsigned)((c.T + 7) / 8), 256, 0, stream>>>(c.x, c.T, (int)cfg.hidden, nullptr, nullptr, ws->xq_tok,
-                                                                                 ws->mx_tok_term_stride, ws->sf_tok);
+                                                                                 ws->mx_tok_term_stride, ws->sf_tok, 0u);
     DSX_LAUNCHED();
     mx_gather_rows_kernel<<<qblocks, 256, 0, stream>>>(ws->xq_tok, ws->mx_tok_term_stride, ws->sf_tok, c.perm, c.n_used, P, quant_rows,
                                                        (int)cfg.hidden, ws->mx_segs, ws->n_segs, ws->xq, ws->mx_term_stride, ws->sfb);
     DSX_LAUNCHED();
     g.K = cfg.hidden; g.rows = cfg.ffn;
     g.sfa = c.sf_gu; g.sfa_slot_stride = c.sf_gu_stride; g.sfa_shared = c.sh_sf_gu;
-    mx_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_xq, ws->tmap_km_gu[0], ws->tmap_km_gu[shi], g);
+    mx_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_xq[0], ws->tmap_xq[1], ws->tmap_xq[2], ws->tmap_km_gu[0],
+                                                                       ws->tmap_km_gu[shi], g);
     DSX_LAUNCHED();
     if (ws->small_max > 0) {
         v.K = cfg.hidden; v.rows = cfg.ffn; v.sh_rows = cfg.ffn;
@@ -678,17 +761,19 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     }
     // second product: K = ffn, rows = hidden, over the terms of mid
     mx_quantize_rows_kernel<false><<<qblocks, 256, 0, stream>>>(c.mid, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs, ws->xq,
-                                                                ws->mx_term_stride, ws->sfb);
+                                                                ws->mx_term_stride, ws->sfb, 0u);
     DSX_LAUNCHED();
     g.K = cfg.ffn; g.rows = cfg.hidden;
     g.sfa = c.sf_dn; g.sfa_slot_stride = c.sf_dn_stride; g.sfa_shared = c.sh_sf_dn;
-    mx_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mq, ws->tmap_km_dn[0], ws->tmap_km_dn[shi], g);
+    mx_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mq[0], ws->tmap_mq[1], ws->tmap_mq[2], ws->tmap_km_dn[0],
+                                                                        ws->tmap_km_dn[shi], g);
     DSX_LAUNCHED();
     if (ws->small_max > 0) {
         v.K = cfg.ffn; v.rows = cfg.hidden; v.sh_rows = cfg.hidden;
         v.nib = c.dn_nib; v.sc = c.dn_sc; v.nib_slot_stride = c.dn_nib_stride; v.sc_slot_stride = c.dn_sc_stride;
         if (int rc = launch_gemv_down(v, c.sm_count, stream)) return rc;
     }
+    if (c.skip_combine) return DSX_OK;   // the caller adds another pass before it reduces the partial rows
     return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr, c.expert_lo,
                           c.n_local, c.out, stream);
 }

@@ -165,9 +165,11 @@ __global__ void unpack_kernel(int fmt, const uint8_t* __restrict__ nib, const ui
 // The tensor-core planes of an MXFP4 matrix (prefill_mx.cu): codes K-major, i.e. the HF byte layout
 // [row][K/2] with element 2i in the low nibble, and the E8M0 block scales cut into the 512-byte chunks
 // the block-scaled MMA takes its scale factors from: chunk = 128 rows x 4 blocks (128 columns), byte
-// (row % 32) * 16 + (row / 32 % 4) * 4 + (block % 4).  Chunks are ordered [row tile][K / 128][2]: for gate
-// and up the pair index is the matrix (a tile of 128 gate rows and the same 128 up rows is one MMA
-// tile), for down it is the 128-row half of a 256-row tile.  One thread per (row, 32-column block).
+// (row % 32) * 16 + (row / 32 % 4) * 4 + (block % 4).  Chunks are ordered [tile][K / 128][4] so that the four
+// chunks one pipeline stage of one tile needs are contiguous: for gate and up a tile is 256 rows of both
+// matrices, its chunks (gate rows 0-127, up rows 0-127, gate rows 128-255, up rows 128-255) -- the order of the
+// tile's four accumulators; for down a tile is 512 rows, its chunks the four 128-row quarters.
+// One thread per (row, 32-column block).
 __global__ void kmajor_mxfp4_kernel(int layout, const uint8_t* __restrict__ q, const uint8_t* __restrict__ s, int64_t rows, int64_t K,
                                     int pair_index, int64_t src_q_stride, int64_t src_s_stride, uint8_t* __restrict__ km,
                                     int64_t km_stride, uint8_t* __restrict__ sf, int64_t sf_stride) {
@@ -189,8 +191,8 @@ __global__ void kmajor_mxfp4_kernel(int layout, const uint8_t* __restrict__ q, c
     uint8_t* kdst = km + mat * km_stride + (pair_index > 0 ? rows * (K >> 1) : 0) + row * (K >> 1) + blk * 16;
     *reinterpret_cast<uint4*>(kdst) = make_uint4(w[0], w[1], w[2], w[3]);
     const int64_t n_kc = K >> 7;
-    const int64_t chunk = pair_index >= 0 ? ((row >> 7) * n_kc + (blk >> 2)) * 2 + pair_index
-                                          : ((row >> 8) * n_kc + (blk >> 2)) * 2 + ((row >> 7) & 1);
+    const int64_t chunk = pair_index >= 0 ? ((row >> 8) * n_kc + (blk >> 2)) * 4 + ((row >> 7) & 1) * 2 + pair_index
+                                          : ((row >> 9) * n_kc + (blk >> 2)) * 4 + ((row >> 7) & 3);
     sf[mat * sf_stride + chunk * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (blk & 3)] = mxfp4_src_scale(layout, q, s, K, row, blk);
 }
 
@@ -219,7 +221,7 @@ int launch_max_byte(const uint8_t* p, int64_t bytes, uint32_t* out, cudaStream_t
 int launch_kmajor_mxfp4(int src_layout, const uint8_t* q, const uint8_t* s, int64_t rows, int64_t K, int pair_index, int n_mats,
                         int64_t src_q_stride, int64_t src_s_stride, uint8_t* km, int64_t km_stride, uint8_t* sf, int64_t sf_stride,
                         cudaStream_t stream) {
-    DSX_REQUIRE(rows % 128 == 0 && K % 128 == 0 && (pair_index >= 0 || rows % 256 == 0), "kmajor: rows %lld / K %lld not tileable",
+    DSX_REQUIRE(rows % 256 == 0 && K % 128 == 0 && (pair_index >= 0 || rows % 512 == 0), "kmajor: rows %lld / K %lld not tileable",
                 (long long)rows, (long long)K);
     DSX_REQUIRE(src_layout >= DSX_SRC_MXFP4_HF && src_layout <= DSX_SRC_MXFP4_SB2, "kmajor: layout %d is not MXFP4", src_layout);
     const int64_t n_threads = rows * (K >> 5);

@@ -494,6 +494,45 @@ def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
     assert rel_l2(acc, out_full) < 8e-3   # three bf16 roundings instead of one
 
 
+@pytest.mark.parametrize("T", [3, 40, 300])
+def test_layer_mxfp4_routed_q8_0_shared_other_width(torch_cuda, moe, oracle, T):
+    """The reference's own weight layout: MXFP4 routed experts with a Q8_0 shared expert
+    (crates/v4flash-kernels/src/weight_contract.rs:83-89, kernels/shared_expert_fused.hip:143-160), here also
+    with a shared width that differs from the routed one.  The shared expert then runs as a pass of its own; every
+    kernel family (one-launch router + grouped GEMV at 3 tokens, separate kernels at 40, tensor cores at 300)."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import FMT_MXFP4, FMT_Q8_0, MoeConfig, RouterConfig
+    cfg = MoeConfig(hidden=512, ffn=256, shared_ffn=512, fmt=FMT_MXFP4,
+                    router=RouterConfig(n_expert=32, n_used=4, n_group=1, topk_group=1, score_fn=0, route_scale=1.5))
+    w = synth.make_layer(cfg.with_(shared_ffn=0), 7)
+    rng = synth.rng_for(7, 4242)
+    sg = synth.make_matrix(rng, FMT_Q8_0, 1, cfg.shared_ffn, cfg.hidden)
+    su = synth.make_matrix(rng, FMT_Q8_0, 1, cfg.shared_ffn, cfg.hidden)
+    sd = synth.make_matrix(rng, FMT_Q8_0, 1, cfg.hidden, cfg.shared_ffn)
+    routed = moe.RoutedExpertWeights.from_host(FMT_MXFP4, cfg.hidden, cfg.ffn, w["gate"], w["up"], w["down"])
+    shared = moe.RoutedExpertWeights.from_host(FMT_Q8_0, cfg.hidden, cfg.shared_ffn, sg, su, sd)
+    rw, rb = torch.from_numpy(w["router_w"]).cuda(), torch.from_numpy(w["router_bias"]).cuda()
+    layer = moe.MoeLayer(cfg, routed, shared, rw, rb, max_tokens=T)
+    xb = synth.make_tokens(cfg, 7, T)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    out = layer.forward(x).float().cpu().numpy()
+    assert layer.check() == 0
+    r = layer.routing(T)
+    rc = cfg.router
+    osel, ow = oracle.router_topk(r["logits"], w["router_bias"], rc.n_used, rc.n_group, rc.topk_group, rc.score_fn, rc.route_scale, rc.weight_eps)
+    assert np.array_equal(r["selected"], osel) and np.array_equal(r["weights"].view(np.uint32), ow.view(np.uint32))
+    ref = oracle.moe_layer_f32(FMT_MXFP4, synth.bf16_bits_to_f32(xb), osel, ow, w["gate"], w["up"], w["down"],
+                               shared=((sg[0][0], sg[1][0]), (su[0][0], su[1][0]), (sd[0][0], sd[1][0])), shared_fmt=FMT_Q8_0,
+                               clamp=cfg.clamp, n_expert=rc.n_expert)
+    assert rel_l2(out, ref) <= REL_L2_TOL
+    # and the shared rows really are in the sum: without them the result is far off
+    no_shared = oracle.moe_layer_f32(FMT_MXFP4, synth.bf16_bits_to_f32(xb), osel, ow, w["gate"], w["up"], w["down"], clamp=cfg.clamp,
+                                     n_expert=rc.n_expert)
+    assert rel_l2(out, no_shared) > 5 * REL_L2_TOL
+    layer.close()
+
+
 @pytest.mark.parametrize("T", [16, 200])
 def test_forward_remap_interleaved_ownership_sums_to_full(torch_cuda, moe, oracle, T):
     """The reference's ownership table (het/weights.rs:1357-1381): three owners hold interleaved, unequal, unordered
