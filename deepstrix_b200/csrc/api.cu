@@ -833,14 +833,6 @@ int dsx_moe_layer_routing(const dsx_moe_layer* L, const float** logits, const in
     return DSX_OK;
 }
 
-// Development aid (not declared in the public header): device pointers into the layer's workspace.
-__attribute__((visibility("default"))) int dsx_debug_layer_buffers(dsx_moe_layer* L, void** mid, void** partial, void** xq, void** sfb,
-                                                                    void** segs, void** n_segs, int64_t* term_stride) {
-    *mid = L->mid; *partial = L->partial; *xq = L->pf.xq; *sfb = L->pf.sfb; *segs = L->pf.mx_segs; *n_segs = L->pf.n_segs;
-    *term_stride = L->pf.mx_term_stride;
-    return DSX_OK;
-}
-
 int dsx_moe_layer_profile(dsx_moe_layer* L, int enable) {
     DSX_REQUIRE(L, "moe_layer_profile: null layer");
     if (enable)

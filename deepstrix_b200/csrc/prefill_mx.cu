@@ -19,23 +19,23 @@
 // a single E4M3 term 4.6e-2), for 1.5 times the tensor-core time of one FP8 pass.
 //
 // Tiling.  Every activation row costs three operand rows, so a tile is tall on the weight side: expert-sorted
-// rows are cut into segments of at most 112 rows of one expert, and a tile = (segment, 512 weight rows) = four
+// rows are cut into segments of at most 96 rows of one expert, and a tile = (segment, 512 weight rows) = four
 // M = 128 accumulators that share the segment's rows as N (first product: gate rows f0..f0+127, up rows
 // f0..f0+127, gate f0+128.., up f0+128.., so that a tensor-memory lane holds gate and up of one output row).
-// Tensor memory: 4 x 112 accumulator columns, 16 columns of weight scales, 12 of activation scales.
-// A pipeline stage is 128 reduction columns: 32 KB of weight codes, up to 3 x 8 KB of activation terms (only the
-// 32-row boxes the segment needs are fetched), 2 KB + 1.5 KB of scale chunks, all arriving on one mbarrier; per
-// stage the issuing thread copies the seven scale chunks to tensor memory and issues 2 (k steps of 64) x 3
-// (terms) x 4 (accumulators) MMAs.  Shared-memory traffic per MMA-clock is what bounds this kernel (the L2 ->
-// shared-memory path saturates near 10 TB/s on the device): 256-row tiles with 240-row segments moved 79 bytes
-// per MMA-clock on the 8192-token workload, whose experts hold ~256 rows and so split into two half-empty
-// segments; this shape moves 38.
-// Warp roles: one producer thread, one MMA thread, 16 epilogue warps that read the accumulators
+// Tensor memory: 4 x 96 accumulator columns, 16 columns of weight scales, 2 x 12 of activation scales.
+// A pipeline stage is 128 reduction columns: 32 KB of weight codes (one TMA box), up to 3 x 6 KB of activation
+// terms (one TMA box of 32, 64 or 96 rows x 3 terms: only the rows the segment has), 2 KB + 1.5 KB of scale
+// chunks, all arriving on one mbarrier; 4 stages.  Two warps issue: each copies its two accumulators' weight
+// scales and its own copy of the activation scales to tensor memory and issues 2 (k steps of 64) x 3 (terms) x 2
+// (accumulators) MMAs per stage.  Traffic from L2 into shared memory per MMA-clock is what bounds this kernel
+// (that path saturates near 8.5 TB/s on the device): 256-row tiles with 240-row segments moved 79 bytes per
+// MMA-clock on the 8192-token workload, whose experts hold ~256 rows and so split into two half-empty segments;
+// this shape moves 44.
+// Warp roles: one producer thread, two MMA threads, 12 epilogue warps that read the accumulators
 // (tcgen05.ld), apply clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows
-// (f32).  Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
+// (f32); the second accumulator pair is read whole and tensor memory handed back before its arithmetic runs.
+// Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
 // is freed and bit 2 of the layer's error word is set.
-#include <cstdlib>
-
 #include "prefill.cuh"
 
 namespace dsx {
@@ -210,7 +210,6 @@ struct MxGemmArgs {
     const uint8_t* sfa_shared;
     const uint8_t* sfb;        // activation scale chunks: [segment][K/128][term][2][512]
     uint32_t* error_word;
-    int debug_mode;            // TEMPORARY ablation switch: 1 = no loads (stale operands), 2 = no MMAs
 };
 
 template <bool GATE_UP>
@@ -294,7 +293,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     ok = mbar_wait(bar(EMPTY + s), ((cnt / kStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
                     const uint32_t full = bar(FULL + s);
-                    if (a.debug_mode == 1 || a.debug_mode >= 3) { mbar_arrive(full); cnt++; continue; }
                     mbar_expect_tx(full, stage_tx);
                     const uint32_t a_dst = sbase + kSmemA + s * kABytes;
                     tma_load_4d(a_dst, m_w, kc * kRowBytes, w_row(mb), 0, slot, full);
@@ -338,15 +336,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     // scales of this stage (16-byte units in the descriptor): this warp's two weight chunks, the three terms' chunks
-                    if (a.debug_mode == 2) { tc_commit(bar(EMPTY) + 8u * s); if (++s == kStages) { s = 0; ph ^= 1u; } continue; }
                     const uint64_t sfa_d = sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4) + 2 * mw * (kSfChunk >> 4));
                     const uint64_t sfb_d = sfb_desc0 + (uint64_t)(s * (kSfbBytes >> 4));
-                    if (a.debug_mode != 3 && a.debug_mode != 5) {
                     tc_cp_scales(t_sfa, sfa_d);
                     tc_cp_scales(t_sfa + 4, sfa_d + (kSfChunk >> 4));
 #pragma unroll
                     for (int t = 0; t < kTerms; t++) tc_cp_scales(t_sfb + 4 * t, sfb_d + (uint64_t)(t * (kSfChunk >> 4)));
-                    }
                     const uint32_t a_lo = a_lo0 + s * (kABytes >> 4), b_lo = b_lo0 + s * (kBBytes >> 4);
                     const uint32_t first = kc != 0 ? 1u : 0u;
 #pragma unroll
@@ -421,7 +416,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     }
                 }
             };
-            const bool active = c0 < seg.n && a.debug_mode != 4 && a.debug_mode != 5;
+            const bool active = c0 < seg.n;
             if (active) {
                 // pair 0 block by block; pair 1 is read whole, the accumulators are handed back, and its arithmetic and stores
                 // run while the next tile's MMAs have already started
@@ -740,7 +735,6 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     g.segs = ws->mx_segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
     g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.sfb = ws->sfb;
     g.error_word = c.error_word;
-    { const char* dm = getenv("DSX_MX_DEBUG"); g.debug_mode = dm ? atoi(dm) : 0; }
 
     // first product: K = hidden, rows = ffn
     mx_quantize_rows_kernel<true><<<(unsigned)((c.T + 7) / 8), 256, 0, stream>>>(c.x, c.T, (int)cfg.hidden, nullptr, nullptr, ws->xq_tok,
