@@ -75,6 +75,10 @@ constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term (one chu
 static_assert(kSfbCol + 4 * kTerms * kMmaWarps <= 512, "tensor memory holds 512 columns");
 static_assert(kBTermBytes % 512 == 0, "a term plane must start on a swizzle-atom boundary");
 constexpr uint32_t kSpinLimit = 1u << 22;
+#ifndef DSX_MX_SMALL_MAX
+#define DSX_MX_SMALL_MAX 8
+#endif
+constexpr int kMxSmallMax = DSX_MX_SMALL_MAX;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -716,8 +720,13 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     if (int rc = launch_group_build(c.selected, c.T, c.n_used, c.n_local, c.expert_lo, 256, 0, c.hist, c.offsets, c.perm, nullptr, nullptr, 0,
                                     c.gs, stream))
         return rc;
+    // Experts with at most kMxSmallMax rows go to the grouped GEMV: one 8-row item streams an expert's weights once at
+    // HBM speed, which a tile pass (bound by the same bytes through L2) cannot beat; from 9 rows on the GEMV would
+    // stream them twice.  (The f16-operand kernel of Q8_0 stores hands over up to 24 rows: its tile pass is bound by
+    // weight conversion, not bytes.)
+    const int mx_small = ws->small_max > 0 ? kMxSmallMax : 0;
     if (int rc = launch_build_segments(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, kSegRows, ws->mx_segs, ws->n_segs, ws->mx_seg_cap,
-                                       ws->small_max, ws->small_items, ws->n_small, stream))
+                                       mx_small, ws->small_items, ws->n_small, stream))
         return rc;
     if (int rc = map_weights(ws, 0, c.km_gu, c.km_dn, c.km_gu_stride, c.km_dn_stride, c.n_local)) return rc;
     const int shi = c.with_shared ? 1 : 0;   // without a shared expert the shared map aliases the routed one (never used)

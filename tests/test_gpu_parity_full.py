@@ -119,7 +119,7 @@ def test_layer_mid_batch_full_size_all_tokens(torch_cuda, moe, oracle, full_mxfp
     ref_logits = oracle.router_logits(synth.bf16_bits_to_f32(xb), w["router_w"])
     assert np.abs(routing["logits"] - ref_logits).max() < 5e-5
     osel, ow, oh, oo, op = _check_routing(oracle, cfg, w["router_bias"], routing, routing["logits"])
-    assert (oh <= 24).any() and (oh > 24).any()   # both kernel families in one call
+    assert (oh <= 8).any() and (oh > 8).any()     # both kernel families in one call (experts with at most 8 rows go to the GEMV)
     ref = _oracle_rows(oracle, cfg, w, xb, osel, ow, np.arange(T))
     err = rel_l2(out, ref)
     assert err <= REL_L2_TOL, err
