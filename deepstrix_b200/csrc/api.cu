@@ -512,6 +512,11 @@ static int check_weights(const dsx_moe_config& c, const dsx_expert_store* routed
     return DSX_OK;
 }
 
+// Stores whose prefill-size batches run on block-scaled FP4 MMAs (the others take the f16-operand kernels).
+static bool takes_block_scaled(const dsx_expert_store* routed, const dsx_expert_store* shared) {
+    return routed->fmt == DSX_FMT_MXFP4 && routed->km_gu != nullptr && (!shared || (shared->fmt == DSX_FMT_MXFP4 && shared->km_gu != nullptr));
+}
+
 int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const dsx_expert_store* routed,
                          const dsx_expert_store* shared, const float* router_w, const float* router_bias) {
     DSX_REQUIRE(layer && cfg, "moe_layer_create: null argument");
@@ -569,7 +574,7 @@ int dsx_moe_layer_create(dsx_moe_layer** layer, const dsx_moe_config* cfg, const
     const bool split_shared = L->shared != nullptr && (shared->fmt != routed->fmt || c.shared_ffn != c.ffn);
     dsx_moe_config c_ws = c;
     if (split_shared) c_ws.shared_ffn = 0;   // this layer's own launches carry no shared rows
-    if (int rc = prefill_workspace_create(&L->pf, c_ws, c.router.n_used, L->mid)) {
+    if (int rc = prefill_workspace_create(&L->pf, c_ws, c.router.n_used, L->mid, !takes_block_scaled(routed, split_shared ? nullptr : L->shared))) {
         layer_free(L);
         delete L;
         return rc;
@@ -626,6 +631,8 @@ int dsx_moe_layer_set_weights(dsx_moe_layer* L, const dsx_expert_store* routed, 
         if (int rc = dsx_moe_layer_set_weights(L->sh_layer, shared, nullptr, router_w, nullptr)) return rc;
     L->routed = routed; L->shared = L->cfg.shared_ffn > 0 ? shared : nullptr;
     L->router_w = router_w; L->router_bias = router_bias;
+    if (!takes_block_scaled(routed, L->sh_layer ? nullptr : L->shared))
+        if (int rc = prefill_f16_rows_ensure(&L->pf)) return rc;
     // the tensor maps of the prefill path describe the previous stores (a new store may even sit at a freed
     // store's address with another slot count): encode them again on the next use
     for (int i = 0; i < 2; i++) L->pf.mapped_gu_nib[i] = L->pf.mapped_dn_nib[i] = L->pf.mapped_km_gu[i] = L->pf.mapped_km_dn[i] = nullptr;
@@ -673,9 +680,9 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
     };
     // MXFP4 stores with tensor-core planes: block-scaled FP4 MMAs on the stored codes and scales (any E8M0 scale);
     // otherwise f16 operands expanded in shared memory (Q8_0; MXFP4 scales must then fit f16)
-    const bool mx = L->pf.mx_ready && L->routed->fmt == DSX_FMT_MXFP4 && L->routed->km_gu != nullptr &&
-                    (!shared || (L->shared->fmt == DSX_FMT_MXFP4 && L->shared->km_gu != nullptr));
-    if (prefill_wanted(L->pf, c, L->routed->fmt, T) && (mx || (scales_fit_f16(L->routed) && (!shared || scales_fit_f16(L->shared))))) {
+    const bool mx = L->pf.mx_ready && takes_block_scaled(L->routed, shared ? L->shared : nullptr);
+    if (prefill_wanted(L->pf, c, L->routed->fmt, T) &&
+        (mx || (L->pf.xperm != nullptr && scales_fit_f16(L->routed) && (!shared || scales_fit_f16(L->shared))))) {
         PrefillCall pc{};
         pc.x = x; pc.T = T; pc.selected = selected; pc.route_w = weights; pc.expert_lo = expert_lo; pc.n_local = n_local;
         pc.filter_picks = filter_picks; pc.with_shared = shared; pc.out = out;
@@ -860,8 +867,15 @@ int dsx_moe_layer_check(dsx_moe_layer* L, dsx_stream_t stream_, uint32_t* error_
     DSX_CUDA(cudaMemcpyAsync(&w, L->error_word, 4, cudaMemcpyDeviceToHost, stream));
     DSX_CUDA(cudaStreamSynchronize(stream));
     if (w) DSX_CUDA(cudaMemsetAsync(L->error_word, 0, 4, stream));
+    if (L->sh_layer) {   // the shared expert's own pass reports into its own word
+        uint32_t ws = 0;
+        dsx_moe_layer_check(L->sh_layer, stream_, &ws);
+        w |= ws;
+    }
     if (error_word) *error_word = w;
-    if (w) return set_error(DSX_ERR_DEVICE, "a kernel reported error word 0x%x (a bounded wait ran out)", w);
+    if (w)
+        return set_error(DSX_ERR_DEVICE, "a kernel reported error word 0x%x (%s%s)", w, (w & 15u) ? "a bounded wait ran out" : "",
+                         (w & 16u) ? ((w & 15u) ? "; a value left the f16 range" : "a value left the f16 range") : "");
     return DSX_OK;
 }
 

@@ -45,6 +45,25 @@ void count_launch();
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Error-word bit of a layer: a value did not fit f16 where a kernel multiplies in f16 (an activation beyond
+// +-65504, an inf or a NaN; or an un-clamped SwiGLU product beyond it).  The result rows it feeds hold inf / NaN.
+constexpr uint32_t kErrHalfRange = 16u;
+
+// Two bf16 values (one 32-bit word) as f16x2.  `bad` collects a non-zero value when either result has all
+// exponent bits set, i.e. the source was outside the f16 range or not finite.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w, uint32_t& bad) {
+    const __half2 h = __floats2half2_rn(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    const uint32_t o = *reinterpret_cast<const uint32_t*>(&h);
+    bad |= ((o & 0x7C007C00u) + 0x04000400u) & 0x80008000u;
+    return o;
+}
+// f32 -> f16 with the same check
+__device__ __forceinline__ __half f32_to_f16_checked(float v, uint32_t& bad) {
+    const __half h = __float2half_rn(v);
+    bad |= ((uint32_t)__half_as_ushort(h) & 0x7C00u) == 0x7C00u;
+    return h;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};

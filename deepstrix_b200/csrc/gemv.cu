@@ -214,20 +214,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
         for (int s = 0; s < kStages; s++) mbar_init(my_bars + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     constexpr bool all_rows_staged = SMALL && PAIR;
+    uint32_t bad = 0;   // a value that left the f16 range (reported once, when the block ends)
     if (all_rows_staged) {
         // loads that bypass L1: this runs while the previous kernel may still be executing
         const int vec_per_row = (int)(K >> 3);
         for (int v = threadIdx.x; v < (int)a.T * vec_per_row; v += kThreads) {
             const int r = v / vec_per_row, c8 = v - r * vec_per_row;
             const uint4 in = __ldcg(reinterpret_cast<const uint4*>(a.x + (int64_t)r * K) + c8);
-            const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const __half2 h = __floats2half2_rn(__uint_as_float(wds[q] << 16), __uint_as_float(wds[q] & 0xFFFF0000u));
-                o[q] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            *reinterpret_cast<uint4*>(act + (size_t)r * act_stride + c8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(act + (size_t)r * act_stride + c8 * 8) =
+                make_uint4(bf16x2_to_f16x2(in.x, bad), bf16x2_to_f16x2(in.y, bad), bf16x2_to_f16x2(in.z, bad), bf16x2_to_f16x2(in.w, bad));
         }
     }
     __syncthreads();
@@ -331,14 +326,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
                         uint4 out;
                         if (PAIR) {
                             const uint4 in = __ldg(reinterpret_cast<const uint4*>(a.x + (int64_t)info->tok[r] * K) + c8);
-                            const uint32_t wds[4] = {in.x, in.y, in.z, in.w};
-                            uint32_t o[4];
-    #pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                const __half2 h = __floats2half2_rn(__uint_as_float(wds[q] << 16), __uint_as_float(wds[q] & 0xFFFF0000u));
-                                o[q] = *reinterpret_cast<const uint32_t*>(&h);
-                            }
-                            out = make_uint4(o[0], o[1], o[2], o[3]);
+                            out = make_uint4(bf16x2_to_f16x2(in.x, bad), bf16x2_to_f16x2(in.y, bad), bf16x2_to_f16x2(in.z, bad),
+                                             bf16x2_to_f16x2(in.w, bad));
                         } else {
                             out = *(reinterpret_cast<const uint4*>(a.mid + (int64_t)info->mid_row[r] * a.mid_stride) + c8);
                         }
@@ -422,7 +411,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
                             uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
                         }
                         const float sig = 1.0f / (1.0f + __expf(-gv));
-                        a.mid[(int64_t)info->mid_row[n] * a.mid_stride + row] = __float2half_rn(gv * sig * uv * info->w[n]);
+                        a.mid[(int64_t)info->mid_row[n] * a.mid_stride + row] = f32_to_f16_checked(gv * sig * uv * info->w[n], bad);
                     } else {
                         a.partial[(int64_t)info->out_row[n] * a.rows + row] = acc0[i];
                     }
@@ -434,6 +423,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_kernel(const GemvArgs a) {
             if (++rb == bpi) { rb = 0; item++; }
         }
     }
+    if (bad) atomicOr(a.error_word, kErrHalfRange);
 }
 
 // Shared memory of one block: 8 activation rows, the rings, barriers, the item and (two warps per row
@@ -468,7 +458,7 @@ Variant pick_variant(int fmt, bool pair, int64_t K, int64_t rows, int64_t T) {
     const bool can_wide = rows % (kTileRows * 16) == 0;
     const size_t plain = gemv_smem_bytes(K, false), split = gemv_smem_bytes(K, true);
     // gate/up of 8 or 9 tokens: ~60 items x 8 wide units leave some blocks a fourth unit while most have
-    // three; 128-row units halve that tail (measured 108 -> 104 us at 8 tokens, a loss from 12 tokens on)
+    // three; 128-row units halve that tail (a small gain at 8 tokens, a loss from 12 tokens on)
     const int64_t wide_from = ((pair || DSX_DOWN_WIDE_FROM_TOO) && n_stage % 2 == 0 && split <= kMaxSmem) ? DSX_PAIR_WIDE_FROM : 8;
     if (can_wide && T >= wide_from && plain <= kMaxSmem) return {16, 1, plain};
     if (n_stage % 2 == 0 && split <= kMaxSmem) return {16, 2, split};

@@ -284,6 +284,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         tc_fence_after();
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const int r_in = q * 32 + lane;           // row inside a 128-row half
+        uint32_t bad = 0;                         // an un-clamped SwiGLU product beyond the f16 range
         for (int c0 = 32 * rank; c0 < seg.n; c0 += 96) {
             // lane j of the warp fetches the routing weight / output row of column c0 + j
             float wv = 0.f;
@@ -308,7 +309,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                             uv = fminf(fmaxf(uv, -a.clamp), a.clamp);
                         }
                         const float sig = __fdividef(1.0f, 1.0f + __expf(-gv));
-                        dst[(int64_t)j * a.mid_stride] = __float2half_rn(gv * sig * uv * wj);
+                        dst[(int64_t)j * a.mid_stride] = f32_to_f16_checked(gv * sig * uv * wj, bad);
                     }
                 }
             } else {
@@ -324,6 +325,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 }
             }
         }
+        if (bad) atomicOr(a.error_word, kErrHalfRange);
         tc_fence_before();
         __syncwarp();
     };
@@ -537,9 +539,7 @@ __device__ __forceinline__ int seg_size(int cnt, int seg_rows) {  // even split 
 #ifndef DSX_SMALL_MAX
 #define DSX_SMALL_MAX 24
 #endif
-// Measured on the 256-expert layer: a tile pass costs an expert about as much as three GEMV items
-// of 8 rows (192 tokens 1.02 -> 0.86 ms, 512 tokens 2.10 -> 1.54 ms against a threshold of 8; no
-// change from 1024 tokens up, where no expert is this small).
+// A tile pass of the f16-operand kernels costs an expert about as much as three GEMV items of 8 rows.
 constexpr int kSmallMax = DSX_SMALL_MAX;   // at most 32 (4 work items of 8 rows per expert)
 static_assert(kSmallMax <= 32, "the work-item list holds 4 items per expert");
 
@@ -588,7 +588,8 @@ build_segments_kernel(const int32_t* __restrict__ offsets, int n_local, int64_t 
 // then every token once more for the shared expert (row P + t).
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ perm, const int32_t* __restrict__ offsets,
-                   int n_local, int n_used, int64_t P, int64_t T, int shared_rows, int64_t H, __half* __restrict__ xperm) {
+                   int n_local, int n_used, int64_t P, int64_t T, int shared_rows, int64_t H, __half* __restrict__ xperm,
+                   uint32_t* __restrict__ error_word) {
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const int64_t placed = offsets[n_local];
@@ -598,17 +599,12 @@ gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
     else return;
     const uint4* in = reinterpret_cast<const uint4*>(x + src * H);
     uint4* out = reinterpret_cast<uint4*>(xperm + dst * H);
+    uint32_t bad = 0;
     for (int64_t c = lane; c < H / 8; c += 32) {
         const uint4 v = __ldg(in + c);
-        const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
-        uint32_t o[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const __half2 h = __floats2half2_rn(__uint_as_float(wds[i] << 16), __uint_as_float(wds[i] & 0xFFFF0000u));
-            o[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        out[c] = make_uint4(o[0], o[1], o[2], o[3]);
+        out[c] = make_uint4(bf16x2_to_f16x2(v.x, bad), bf16x2_to_f16x2(v.y, bad), bf16x2_to_f16x2(v.z, bad), bf16x2_to_f16x2(v.w, bad));
     }
+    if (bad) atomicOr(error_word, kErrHalfRange);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -705,7 +701,15 @@ int map_weights(PrefillWorkspace* ws, int which, const uint8_t* gu_nib, const ui
 
 }  // namespace
 
-int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid) {
+// The f16 copy of the sorted token rows (1 KB per row and 512 hidden columns) is only read by the f16-operand
+// kernels: a layer whose stores take the block-scaled path never allocates it.
+int prefill_f16_rows_ensure(PrefillWorkspace* ws) {
+    if (!ws->ready || ws->xperm != nullptr) return DSX_OK;
+    DSX_CUDA(cudaMalloc((void**)&ws->xperm, (size_t)ws->cap_rows * (size_t)ws->H * 2));
+    return encode_rows_map(&ws->tmap_x, ws->xperm, ws->cap_rows, ws->H);
+}
+
+int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid, bool f16_rows) {
     ws->ready = false;
     // shapes the tiles cover: 128 gate + 128 up rows per tile, 256 down rows per tile, 64-column chunks
     if (cfg.ffn % 128 != 0 || cfg.hidden % 256 != 0 || (cfg.shared_ffn != 0 && cfg.shared_ffn != cfg.ffn)) return DSX_OK;
@@ -713,7 +717,6 @@ int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, in
     ws->F = cfg.ffn;
     ws->cap_rows = (int64_t)cfg.max_tokens * n_used + cfg.max_tokens;
     ws->seg_cap = cfg.router.n_expert + (int)((ws->cap_rows + kSegRows - 1) / kSegRows) + 8;
-    DSX_CUDA(cudaMalloc((void**)&ws->xperm, (size_t)ws->cap_rows * (size_t)cfg.hidden * 2));
     DSX_CUDA(cudaMalloc((void**)&ws->segs, sizeof(PrefillSeg) * (size_t)ws->seg_cap));
     DSX_CUDA(cudaMalloc((void**)&ws->n_segs, 256));
     DSX_CUDA(cudaMalloc((void**)&ws->small_items, sizeof(int32_t) * (size_t)(cfg.router.n_expert * 4 + 8)));   // up to 32 rows = 4 items per expert
@@ -721,7 +724,6 @@ int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, in
     DSX_CUDA(cudaMemset(ws->n_small, 0, 256));
     // a work item of the grouped GEMV holds at most 8 tokens; both reductions must fit its shared memory
     ws->small_max = (gemv_fits(cfg.hidden) && gemv_fits(cfg.ffn) && cfg.hidden % 128 == 0 && cfg.ffn % 128 == 0) ? kSmallMax : 0;
-    if (int rc = encode_rows_map(&ws->tmap_x, ws->xperm, ws->cap_rows, cfg.hidden)) return rc;
     if (int rc = encode_rows_map(&ws->tmap_mid, mid, ws->cap_rows, cfg.ffn)) return rc;
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
@@ -729,7 +731,7 @@ int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, in
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_Q8_0>::kSmemTotal));
     ws->min_tokens = 65;
     ws->ready = true;
-    return DSX_OK;
+    return f16_rows ? prefill_f16_rows_ensure(ws) : DSX_OK;
 }
 
 void prefill_workspace_free(PrefillWorkspace* ws) {
@@ -757,7 +759,7 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
         return rc;
     const int64_t rows = P + c.T;
     gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(c.x, c.perm, c.offsets, c.n_local, c.n_used, P, c.T,
-                                                                      c.with_shared ? 1 : 0, cfg.hidden, ws->xperm);
+                                                                      c.with_shared ? 1 : 0, cfg.hidden, ws->xperm, c.error_word);
     DSX_LAUNCHED();
     if (ws->fmt != c.fmt) { ws->fmt = c.fmt; ws->mapped_gu_nib[0] = ws->mapped_gu_nib[1] = nullptr; }
     if (int rc = map_weights(ws, 0, c.gu_nib, c.gu_sc, c.dn_nib, c.dn_sc, c.gu_nib_stride, c.gu_sc_stride, c.dn_nib_stride,

@@ -19,7 +19,7 @@ struct PrefillWorkspace {
     int64_t cap_rows = 0;      // rows of xperm / mid the tensor maps cover
     int64_t H = 0, F = 0;
     int fmt = DSX_FMT_MXFP4;   // format of the stores the weight maps describe
-    __half* xperm = nullptr;   // [cap_rows, H] f16: token rows in expert-sorted order, then all tokens (shared expert)
+    __half* xperm = nullptr;   // [cap_rows, H] f16: token rows in expert-sorted order, then all tokens (shared expert); null until a store needs it
     PrefillSeg* segs = nullptr;
     int32_t* n_segs = nullptr;
     int32_t seg_cap = 0;
@@ -40,7 +40,7 @@ struct PrefillWorkspace {
     uint8_t* xq_tok = nullptr;      // [3 terms][max_tokens][hidden/2]: every token expanded once
     int64_t mx_tok_term_stride = 0;
     uint8_t* sf_tok = nullptr;      // [max_tokens][3 terms][hidden/32] E8M0 bytes
-    PrefillSeg* mx_segs = nullptr;  // segments of at most 112 rows
+    PrefillSeg* mx_segs = nullptr;  // segments of at most 96 rows
     int32_t mx_seg_cap = 0;
     CUtensorMap tmap_xq[3], tmap_mq[3];   // xq as (bytes, row, term) for K = hidden / K = ffn, boxes of 32 / 64 / 96 rows
     CUtensorMap tmap_km_gu[2], tmap_km_dn[2];            // K-major code planes; index 0 routed, 1 shared
@@ -76,7 +76,9 @@ struct PrefillCall {
     const uint8_t *sh_km_gu, *sh_km_dn, *sh_sf_gu, *sh_sf_dn;
 };
 
-int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid);
+// f16_rows: allocate the f16 copy of the sorted rows now (stores that take the f16-operand kernels)
+int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid, bool f16_rows);
+int prefill_f16_rows_ensure(PrefillWorkspace* ws);   // allocates that copy if it is missing (not during a capture)
 void prefill_workspace_free(PrefillWorkspace* ws);
 bool prefill_wanted(const PrefillWorkspace& ws, const dsx_moe_config& cfg, int fmt, int64_t T);
 int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& call, cudaStream_t stream);

@@ -542,7 +542,7 @@ template <bool BY_TOKEN>
 __global__ void __launch_bounds__(256)
 mx_quantize_rows_kernel(const void* __restrict__ src, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
                         const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ codes_out, int64_t term_stride,
-                        uint8_t* __restrict__ scales_out, uint32_t opaque_zero) {
+                        uint8_t* __restrict__ scales_out, uint32_t opaque_zero, uint32_t* __restrict__ error_word) {
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= n_rows) return;
@@ -588,6 +588,8 @@ mx_quantize_rows_kernel(const void* __restrict__ src, int64_t n_rows, int K, con
             for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
             amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+            // an infinite value (an un-clamped SwiGLU product that left f16, or an infinite token value) has no terms
+            if (t == 0 && amax > 3.0e38f && (lane & 3) == 0) atomicOr(error_word, kErrHalfRange);
             const uint32_t e = mx_scale_byte(amax);
             const float inv = __uint_as_float((254u - e) << 23), scl = __uint_as_float(e << 23);
             float sv[8];
@@ -747,7 +749,7 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
 
     // first product: K = hidden, rows = ffn
     mx_quantize_rows_kernel<true><<<(unsigned)((c.T + 7) / 8), 256, 0, stream>>>(c.x, c.T, (int)cfg.hidden, nullptr, nullptr, ws->xq_tok,
-                                                                                 ws->mx_tok_term_stride, ws->sf_tok, 0u);
+                                                                                 ws->mx_tok_term_stride, ws->sf_tok, 0u, c.error_word);
     DSX_LAUNCHED();
     mx_gather_rows_kernel<<<qblocks, 256, 0, stream>>>(ws->xq_tok, ws->mx_tok_term_stride, ws->sf_tok, c.perm, c.n_used, P, quant_rows,
                                                        (int)cfg.hidden, ws->mx_segs, ws->n_segs, ws->xq, ws->mx_term_stride, ws->sfb);
@@ -764,7 +766,7 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     }
     // second product: K = ffn, rows = hidden, over the terms of mid
     mx_quantize_rows_kernel<false><<<qblocks, 256, 0, stream>>>(c.mid, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs, ws->xq,
-                                                                ws->mx_term_stride, ws->sfb, 0u);
+                                                                ws->mx_term_stride, ws->sfb, 0u, c.error_word);
     DSX_LAUNCHED();
     g.K = cfg.ffn; g.rows = cfg.hidden;
     g.sfa = c.sf_dn; g.sfa_slot_stride = c.sf_dn_stride; g.sfa_shared = c.sh_sf_dn;

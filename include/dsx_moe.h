@@ -366,7 +366,12 @@ DSX_API int dsx_moe_layer_routing(const dsx_moe_layer* layer, const float** logi
                                   const float** weights, const int32_t** hist, const int32_t** offsets,
                                   const int32_t** perm);
 /* Reads (and clears) the device-side error word of the layer; synchronises
- * the stream.  Non-zero means a bounded wait inside a kernel ran out. */
+ * the stream.  Bits 1, 2, 4, 8: a bounded wait inside a kernel ran out (grouped
+ * GEMV ring, tensor-core pipeline, router tile copy, wide-router grid barrier).
+ * Bit 16: a value left the f16 range where a kernel multiplies in f16 (a token
+ * value beyond +-65504 or not finite in a batch that takes the f16-operand
+ * kernels, or a SwiGLU product beyond it with clamp = 0); the output rows it
+ * feeds hold inf / NaN.  Returns DSX_ERR_DEVICE when the word is non-zero. */
 DSX_API int dsx_moe_layer_check(dsx_moe_layer* layer, dsx_stream_t stream, uint32_t* error_word);
 /* Per-stage device timing, the counterpart of EventPool::stage(name, stream)
  * (het/trace.rs:1-22): with profiling on, every forward brackets each stage with

@@ -464,6 +464,42 @@ def test_prefill_block_scales_beyond_f16(torch_cuda, moe, oracle):
         layer.close()
 
 
+def test_activation_beyond_f16_sets_the_range_bit(torch_cuda, moe, oracle):
+    """The decode kernels and the f16-operand tensor-core kernels multiply in f16: a token value beyond 65504
+    must raise bit 16 of the layer's error word (the rows it feeds are inf / NaN), a clean batch must not,
+    and the word is clear again after it was read.  The block-scaled path takes bf16 tokens as they are:
+    the same value there is no error and the result stays finite and on the oracle."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import FMT_MXFP4, FMT_Q8_0, MoeConfig, RouterConfig
+    base = MoeConfig(hidden=512, ffn=256, shared_ffn=0,
+                     router=RouterConfig(n_expert=32, n_used=2, n_group=1, topk_group=1, score_fn=1, route_scale=1.0))
+    for T, decode_only, fmt in ((6, False, FMT_MXFP4), (96, True, FMT_MXFP4), (96, False, FMT_Q8_0), (96, False, FMT_MXFP4)):
+        cfg = base.with_(fmt=fmt)
+        w = synth.make_layer(cfg, 9)
+        xb = synth.make_tokens(cfg, 9, T).copy()
+        clean = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+        big = clean.clone()
+        big[T // 2, 7] = 98304.0             # 1.5 * 2^16: a bf16 value, above the largest f16
+        layer = moe.build_layer_from_host(cfg, w, max_tokens=96, decode_only=decode_only)
+        out = layer.forward(clean).float().cpu().numpy()
+        assert layer.check() == 0 and np.isfinite(out).all()
+        out = layer.forward(big).float().cpu().numpy()
+        word = layer.check()
+        if T == 96 and not decode_only and fmt == FMT_MXFP4:   # block-scaled FP4 terms hold the full bf16 range
+            assert word == 0 and np.isfinite(out).all()
+            r = layer.routing(T)
+            xf = synth.bf16_bits_to_f32(big.view(torch.int16).cpu().numpy().view(np.uint16))
+            ref = oracle.moe_layer_f32(cfg.fmt, xf, r["selected"], r["weights"], w["gate"], w["up"], w["down"], clamp=cfg.clamp, n_expert=32)
+            assert rel_l2(out, ref) <= REL_L2_TOL
+        else:
+            assert word == 16
+            keep = np.arange(T) != T // 2    # the other tokens' rows are untouched
+            assert np.isfinite(out[keep]).all()
+        assert layer.check() == 0
+        layer.close()
+
+
 def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
     """Owner-of-a-subset form: two half stores, each returning its weighted partial
     sum, add up to the full layer (the reference's het-split property,
