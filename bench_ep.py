@@ -153,8 +153,14 @@ def run(args):
     def local_compute(xr, s, ww):
         return layer.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False)
 
+    # the shared expert's rows are written on the side stream and read on the main one: two fixed buffers taken in turn
+    # (the side stream waits for the main one before every call, so the reader of a buffer is always done with it)
+    sh_out = [torch.empty((T, H), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    sh_turn = [0]
+
     def shared_compute(xr):
-        return layer_sh.forward_picks(xr, none_sel, none_w, expert_lo=lo, with_shared=True)
+        sh_turn[0] ^= 1
+        return layer_sh.forward_picks(xr, none_sel, none_w, expert_lo=lo, with_shared=True, out=sh_out[sh_turn[0]])
 
     comm = open_peer_memory(world, rank, T, H, k) if transport != "nccl" else None
     if comm is None:
@@ -194,13 +200,16 @@ def run(args):
     moe.launch_count(reset=True)
     t_w0 = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     e0.record()
     for i in range(args.steps):
         step(xs[i % 4])
+        marks[i].record()
     e1.record()
     torch.cuda.synchronize()
     dist.barrier()
     t_w1 = time.time()
+    step_ms = [a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks)]
     launches = moe.launch_count()
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -264,7 +273,7 @@ def run(args):
                     "ms_per_step": e2e / args.steps},
             "gpu_launches": launches,
             "clocks": sampler.summary(t_w0, t_w1) if sampler else None,
-            "ep": {"phase_ms_per_step_rank0": {n: round(v, 3) for n, v in phases.items()}, "selfcheck_rel_l2_vs_unsharded_layer": check_err, "mean_received_rows_per_rank_per_layer": float(rows[0].item()) / world, "mean_fanout": float(rows[1].item()) / world},
+            "ep": {"step_ms_rank0": [round(v, 3) for v in step_ms], "phase_ms_per_step_rank0": {n: round(v, 3) for n, v in phases.items()}, "selfcheck_rel_l2_vs_unsharded_layer": check_err, "mean_received_rows_per_rank_per_layer": float(rows[0].item()) / world, "mean_fanout": float(rows[1].item()) / world},
         }
         print(json.dumps(line))
     dist.barrier()

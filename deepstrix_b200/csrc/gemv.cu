@@ -439,9 +439,6 @@ constexpr size_t kMaxSmem = 227 * 1024;
 #ifndef DSX_PAIR_WIDE_FROM
 #define DSX_PAIR_WIDE_FROM 10
 #endif
-#ifndef DSX_DOWN_WIDE_FROM_TOO
-#define DSX_DOWN_WIDE_FROM_TOO 0
-#endif
 
 struct Variant {
     int warps, ksplit;   // 0 warps: nothing fits
@@ -459,7 +456,7 @@ Variant pick_variant(int fmt, bool pair, int64_t K, int64_t rows, int64_t T) {
     const size_t plain = gemv_smem_bytes(K, false), split = gemv_smem_bytes(K, true);
     // gate/up of 8 or 9 tokens: ~60 items x 8 wide units leave some blocks a fourth unit while most have
     // three; 128-row units halve that tail (a small gain at 8 tokens, a loss from 12 tokens on)
-    const int64_t wide_from = ((pair || DSX_DOWN_WIDE_FROM_TOO) && n_stage % 2 == 0 && split <= kMaxSmem) ? DSX_PAIR_WIDE_FROM : 8;
+    const int64_t wide_from = (pair && n_stage % 2 == 0 && split <= kMaxSmem) ? DSX_PAIR_WIDE_FROM : 8;
     if (can_wide && T >= wide_from && plain <= kMaxSmem) return {16, 1, plain};
     if (n_stage % 2 == 0 && split <= kMaxSmem) return {16, 2, split};
     if (n_stage % 2 != 0 && plain <= kMaxSmem) return {8, 1, plain};

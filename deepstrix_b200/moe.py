@@ -186,6 +186,54 @@ class HcPost:
         return out
 
 
+class Q8KQuantize:
+    """``Q8KQuantize::launch`` (src/q8_k.rs:33-104): f32 rows -> 292-byte block_q8_K records."""
+
+    BLOCK, BLOCK_BYTES = 256, 292
+
+    @staticmethod
+    def launch(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        assert x.dtype == torch.float32 and x.is_contiguous() and x.numel() % Q8KQuantize.BLOCK == 0
+        nb = x.numel() // Q8KQuantize.BLOCK
+        if out is None:
+            out = torch.empty((nb * Q8KQuantize.BLOCK_BYTES,), dtype=torch.uint8, device=x.device)
+        assert out.dtype == torch.uint8 and out.is_contiguous() and out.numel() >= nb * Q8KQuantize.BLOCK_BYTES
+        _check(lib().dsx_q8_k_quantize(_dptr(x), C.c_int64(nb), _dptr(out), _stream()))
+        return out
+
+
+class SwigluClampWeighted:
+    """``SwigluClampWeighted::launch`` (src/ffn.rs:91-114): mid = silu(min(gate, c)) * clamp(up) * expert_w[e]."""
+
+    @staticmethod
+    def launch(gate: torch.Tensor, up: torch.Tensor, expert_w: torch.Tensor, clamp: float, mid: torch.Tensor | None = None) -> torch.Tensor:
+        n, ff = gate.shape
+        assert up.shape == (n, ff) and expert_w.numel() == n
+        assert all(t.dtype == torch.float32 and t.is_contiguous() for t in (gate, up, expert_w))
+        if mid is None:
+            mid = torch.empty_like(gate)
+        _check(lib().dsx_swiglu_clamp_weighted(_dptr(mid), _dptr(gate), _dptr(up), _dptr(expert_w), C.c_float(clamp), C.c_int64(ff),
+                                               C.c_int64(n), _stream()))
+        return mid
+
+
+class VecAddInplace:
+    """``VecAddInplace`` (src/ffn.rs:118-177): ``out += rhs`` and the indexed gather ``out[i] = src[idx[i]]``."""
+
+    @staticmethod
+    def launch(out: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
+        assert out.dtype == rhs.dtype == torch.float32 and out.is_contiguous() and rhs.is_contiguous() and out.numel() == rhs.numel()
+        _check(lib().dsx_vec_add_inplace(_dptr(out), _dptr(rhs), C.c_int64(out.numel()), _stream()))
+        return out
+
+    @staticmethod
+    def launch_gather(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        assert src.dtype == torch.float32 and idx.dtype == torch.int32 and src.is_contiguous() and idx.is_contiguous()
+        out = torch.empty((idx.numel(),), dtype=torch.float32, device=src.device)
+        _check(lib().dsx_gather_f32(_dptr(out), _dptr(src), _dptr(idx), C.c_int64(idx.numel()), _stream()))
+        return out
+
+
 # --------------------------------------------------------------------------
 class RoutedExpertWeights:
     """Expert store: n_slots experts (gate, up, down) resident in HBM in the

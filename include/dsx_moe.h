@@ -413,6 +413,32 @@ DSX_API int dsx_glue_check(dsx_stream_t stream, uint32_t* error_word);
 DSX_API int dsx_hc_post(const void* block_out, int block_out_is_bf16, const float* residual_hc, const float* post,
                         const float* comb, int64_t T, int64_t n_embd, int n_hc, float* out_hc, dsx_stream_t stream);
 
+/* --- Stand-alone operators of the expert path -------------------------------
+ * For callers that drive the expert FFN step by step (the reference's
+ * MoeExecutor hands Q8_K rows and runs matvec -> SwiGLU -> matvec -> add,
+ * het/remote_experts.rs:7428-7442) instead of through dsx_moe_layer_forward.
+ *
+ * Q8KQuantize::launch / launch_with_offsets (src/q8_k.rs:33-104; kernels/q8_k_quantize.hip:23-90):
+ * n_blocks blocks of 256 f32 values -> 292-byte block_q8_K records (f32 d | i8 qs[256] | i16 bsums[16]);
+ *   max = the signed value of largest |x| (ties resolved as the reference kernel's stride-128..1 tree does),
+ *   iscale = -127 / max, qs = clamp(rint(iscale * x), -128, 127), bsums[g] = sum of qs[16g .. 16g+15], d = 1 / iscale;
+ * an all-zero block gives an all-zero record.  Offsets are applied by the caller to x (16-byte aligned) and
+ * out (4-byte aligned: a record is 73 words).  Bit-exact. */
+DSX_API int dsx_q8_k_quantize(const float* x, int64_t n_blocks, void* out, dsx_stream_t stream);
+/* SwigluClampWeighted::launch (src/ffn.rs:91-114; kernels/swiglu_clamp_weighted.hip:16-37):
+ *   mid[e, r] = silu(min(gate[e, r], clamp)) * min(max(up[e, r], -clamp), clamp) * expert_w[e]
+ * (no clamping when clamp <= 1e-6), product taken left to right in f32.  The exponential inside silu is
+ * evaluated from IEEE add / multiply / fma only (the routers' deterministic form), so results are
+ * reproducible on a CPU bit for bit; they lie within 2 ulp of an expf-based evaluation.  ff_exp % 4 == 0,
+ * rows 16-byte aligned. */
+DSX_API int dsx_swiglu_clamp_weighted(float* mid, const float* gate, const float* up, const float* expert_w, float clamp,
+                                      int64_t ff_exp, int64_t n_experts, dsx_stream_t stream);
+/* VecAddInplace::launch (src/ffn.rs:135-151; kernels/vec_add.hip:6-13): out[i] += rhs[i], i < n. */
+DSX_API int dsx_vec_add_inplace(float* out, const float* rhs, int64_t n, dsx_stream_t stream);
+/* VecAddInplace::launch_gather (src/ffn.rs:155-177; kernels/vec_add.hip:18-27): out[i] = src[idx[i]] for
+ * i < n; a negative index gives -inf. */
+DSX_API int dsx_gather_f32(float* out, const float* src, const int32_t* idx, int64_t n, dsx_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * 3. Expert-parallel exchange over peer memory
  *

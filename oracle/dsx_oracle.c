@@ -382,6 +382,28 @@ static float det_log1pf(float y) { /* y >= 0 */
 }
 
 DSXO_API float dsxo_det_expf(float x) { return det_expf(x); }
+
+/* kernels/swiglu_clamp_weighted.hip:16-37: mid[e, r] = silu(min(g, c)) * clamp(u, -c, c) * w[e], left to right in
+ * f32.  use_det != 0 evaluates the exponential with det_expf (IEEE add / mul / fma only, what the CUDA operator
+ * does: bit-exact against it); 0 uses libm's expf as the reference source reads (the two differ by rounding only). */
+DSXO_API void dsxo_swiglu_clamp_weighted(float* mid, const float* gate, const float* up, const float* expert_w, float clamp,
+                                         int64_t ff_exp, int64_t n_experts, int use_det) {
+    for (int64_t e = 0; e < n_experts; e++)
+        for (int64_t r = 0; r < ff_exp; r++) {
+            float g = gate[e * ff_exp + r], u = up[e * ff_exp + r];
+            if (clamp > 1.0e-6f) {
+                if (g > clamp) g = clamp;
+                if (u > clamp) u = clamp;
+                if (u < -clamp) u = -clamp;
+            }
+            const float ex = use_det ? det_expf(-g) : expf(-g);
+            const float sig = 1.0f / (1.0f + ex);
+            float m = g * sig;
+            m = m * u;
+            m = m * expert_w[e];
+            mid[e * ff_exp + r] = m;
+        }
+}
 DSXO_API float dsxo_det_log1pf(float x) { return det_log1pf(x); }
 
 /* kernels/router_topk.hip:32-36 */

@@ -187,6 +187,16 @@ def q8_k_quantize(x: np.ndarray) -> np.ndarray:
     return out
 
 
+def swiglu_clamp_weighted(gate: np.ndarray, up: np.ndarray, expert_w: np.ndarray, clamp: float, use_det: bool = True) -> np.ndarray:
+    """[n_experts, ff_exp] f32.  use_det: the exponential from IEEE add / mul / fma only (what the CUDA operator evaluates);
+    False: libm's expf, as the reference source reads."""
+    g, u, w = _c(gate, np.float32), _c(up, np.float32), _c(expert_w, np.float32).reshape(-1)
+    n, ff = g.shape
+    out = np.empty((n, ff), np.float32)
+    lib().dsxo_swiglu_clamp_weighted(_p(out), _p(g), _p(u), _p(w), C.c_float(clamp), C.c_int64(ff), C.c_int64(n), C.c_int(1 if use_det else 0))
+    return out
+
+
 def dot_mxfp4_q8k(w_sb2: np.ndarray, y_q8k: np.ndarray) -> float:
     w = _c(w_sb2, np.uint8).reshape(-1)
     y = _c(y_q8k, np.uint8).reshape(-1)

@@ -116,6 +116,38 @@ def test_dot_mxfp4_q8k_consistency(oracle):
         assert np.array_equal(q, b[260:].view(np.int16))
 
 
+def test_q8_k_tie_takes_the_sign_the_reduction_tree_picks(oracle):
+    # kernels/q8_k_quantize.hip:50-62: stride 128..1, the upper element only when strictly larger -- of two equal
+    # |x| at indices 1 and 128, index 128 reaches slot 0 in the first round and keeps it
+    x = np.full(256, 0.25, np.float32)
+    x[1], x[128] = 2.0, -2.0
+    b = oracle.q8_k_quantize(x)
+    d = b[:4].view(np.float32)[0]
+    q = b[4:260].view(np.int8)
+    assert d == np.float32(1.0) / (np.float32(-127.0) / np.float32(-2.0)) and q[128] == -127 and q[1] == 127
+    assert np.array_equal(b[260:].view(np.int16), q.astype(np.int32).reshape(16, 16).sum(1))
+    assert not oracle.q8_k_quantize(np.zeros(256, np.float32)).any()
+
+
+def test_swiglu_clamp_weighted_oracle(oracle):
+    # kernels/swiglu_clamp_weighted.hip:16-37 -- one-sided clamp on gate, two-sided on up, times the expert's weight
+    gate = np.array([[20.0, -20.0, 1.0, 0.0], [3.0, 3.0, 3.0, 3.0]], np.float32)
+    up = np.array([[20.0, -20.0, -2.0, 5.0], [1.0, -1.0, 11.0, -11.0]], np.float32)
+    w = np.array([0.5, 2.0], np.float32)
+    for det in (True, False):
+        m = oracle.swiglu_clamp_weighted(gate, up, w, 10.0, use_det=det)
+        sil = lambda g: g / (1.0 + np.exp(-np.float64(g)))
+        want = np.array([[sil(10.0) * 10 * 0.5, sil(-20.0) * -10 * 0.5, sil(1.0) * -2 * 0.5, 0.0],
+                         [sil(3.0) * 2, -sil(3.0) * 2, sil(3.0) * 10 * 2, -sil(3.0) * 10 * 2]])
+        assert np.allclose(m, want, rtol=1e-6, atol=1e-12)
+    unclamped = oracle.swiglu_clamp_weighted(gate, up, w, 0.0)
+    assert np.isclose(unclamped[0, 0], 20.0 * 20.0 * 0.5, rtol=1e-6)
+    rng = np.random.default_rng(3)
+    g, u = (rng.standard_normal((5, 64)) * 8).astype(np.float32), (rng.standard_normal((5, 64)) * 8).astype(np.float32)
+    ww = rng.random(5).astype(np.float32)
+    assert np.allclose(oracle.swiglu_clamp_weighted(g, u, ww, 10.0), oracle.swiglu_clamp_weighted(g, u, ww, 10.0, use_det=False), rtol=1e-6, atol=1e-30)
+
+
 def test_det_math_close_to_libm(oracle):
     xs = np.linspace(-30, 30, 2001).astype(np.float32)
     for x in xs[::7]:
