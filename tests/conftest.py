@@ -27,6 +27,21 @@ def pytest_collection_modifyitems(config, items):
 
 
 @pytest.fixture(scope="session")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    return torch
+
+
+@pytest.fixture(scope="session")
+def moe():
+    from deepstrix_b200 import moe as m
+    m.lib()
+    return m
+
+
+@pytest.fixture(scope="session")
 def oracle():
     from oracle import oracle as o
     o.build()

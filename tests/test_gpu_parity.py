@@ -17,21 +17,6 @@ def rel_l2(a, b):
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
 
 
-@pytest.fixture(scope="module")
-def torch_cuda():
-    import torch
-    assert torch.cuda.is_available()
-    torch.cuda.set_device(0)
-    return torch
-
-
-@pytest.fixture(scope="module")
-def moe():
-    from deepstrix_b200 import moe as m
-    m.lib()
-    return m
-
-
 # ------------------------------------------------------------------ repack
 @pytest.mark.parametrize("layout", ["hf", "ggml", "sb2"])
 def test_repack_mxfp4_roundtrip_bitexact(torch_cuda, moe, oracle, layout):

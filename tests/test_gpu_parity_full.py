@@ -23,21 +23,6 @@ def rel_l2(a, b):
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
 
 
-@pytest.fixture(scope="module")
-def torch_cuda():
-    import torch
-    assert torch.cuda.is_available()
-    torch.cuda.set_device(0)
-    return torch
-
-
-@pytest.fixture(scope="module")
-def moe():
-    from deepstrix_b200 import moe as m
-    m.lib()
-    return m
-
-
 def _shared_of(w):
     return tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down"))
 
