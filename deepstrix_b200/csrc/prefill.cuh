@@ -40,7 +40,7 @@ struct PrefillWorkspace {
     uint8_t* xq_tok = nullptr;      // [3 terms][max_tokens][hidden/2]: every token expanded once
     int64_t mx_tok_term_stride = 0;
     uint8_t* sf_tok = nullptr;      // [max_tokens][3 terms][hidden/32] E8M0 bytes
-    PrefillSeg* mx_segs = nullptr;  // segments of at most 96 rows
+    PrefillSeg* mx_segs = nullptr;  // segments of at most 192 rows
     int32_t mx_seg_cap = 0;
     CUtensorMap tmap_xq[3], tmap_mq[3];   // xq as (bytes, row, term) for K = hidden / K = ffn, boxes of 32 / 64 / 96 rows
     CUtensorMap tmap_km_gu[2], tmap_km_dn[2];            // K-major code planes; index 0 routed, 1 shared

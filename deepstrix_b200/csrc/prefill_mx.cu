@@ -45,21 +45,22 @@ constexpr int kEpiWarps = 12;
 constexpr int kMmaWarps = 2;                  // issuing warps: each owns two of the tile's four accumulators
 constexpr int kEpiWarp0 = 1 + kMmaWarps;
 constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;
-constexpr int kAccs = 4;                      // M = 128 accumulators per tile (512 weight rows)
-constexpr int kSegRows = 96;                  // most rows of a segment (MMA N)
-constexpr int kBRows = 96;                    // rows of a term plane in shared memory
-constexpr int kBoxRows = 32;                  // rows one token-tile copy brings
+constexpr int kAccs = 2;                      // M = 128 accumulators per tile (256 weight rows), one per issuing warp
+constexpr int kSegRows = 192;                 // most rows of a segment (MMA N)
+constexpr int kBRows = 192;                   // rows of a term plane in shared memory
+constexpr int kBoxRows = 64;                  // granularity of the token-tile copy: boxes of 64, 128 or 192 rows
 constexpr int kTerms = 3;                     // MXFP4 terms per activation row
 constexpr int kStageK = 128;                  // reduction columns per pipeline stage (4 scale blocks)
 constexpr int kRowBytes = kStageK / 2;        // packed bytes per row and stage: one 64-byte swizzle row
 constexpr int kStages = 4;
-constexpr int kABytes = kAccs * 128 * kRowBytes;         // 32768
-constexpr int kBTermBytes = kBRows * kRowBytes;          // 6144
-constexpr int kBBoxBytes = kBoxRows * kRowBytes;         // 2048
-constexpr int kBBytes = kTerms * kBTermBytes;            // 18432
+constexpr int kABytes = kAccs * 128 * kRowBytes;         // 16384
+constexpr int kBTermBytes = kBRows * kRowBytes;          // 12288
+constexpr int kBBoxBytes = kBoxRows * kRowBytes;         // 4096
+constexpr int kBBytes = kTerms * kBTermBytes;            // 36864
 constexpr int kSfChunk = 512;                            // 128 rows x 4 scale blocks
+constexpr int kSfbChunks = (kSegRows + 127) / 128;       // chunks per term: rows 0..127, 128..191
 constexpr int kSfaBytes = kAccs * kSfChunk;
-constexpr int kSfbBytes = kTerms * kSfChunk;
+constexpr int kSfbBytes = kTerms * kSfbChunks * kSfChunk;
 constexpr int kSmemA = 0;
 constexpr int kSmemB = kSmemA + kStages * kABytes;
 constexpr int kSmemSfa = kSmemB + kStages * kBBytes;
@@ -71,9 +72,10 @@ constexpr int kSmemTotal = kSmemMisc + 16 + 1024;        // + alignment slack
 static_assert(kSmemTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
 // tensor-memory columns
 constexpr uint32_t kSfaCol = kAccs * kSegRows;    // accumulator h at column h * kSegRows; then 4 columns of weight scales per accumulator
-constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term (one chunk: at most 128 rows), one copy per issuing warp
-static_assert(kSfbCol + 4 * kTerms * kMmaWarps <= 512, "tensor memory holds 512 columns");
+constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term and chunk of 128 rows, one copy per issuing warp
+static_assert(kSfbCol + 4 * kSfbChunks * kTerms * kMmaWarps <= 512, "tensor memory holds 512 columns");
 static_assert(kBTermBytes % 512 == 0, "a term plane must start on a swizzle-atom boundary");
+static_assert(kMmaWarps == kAccs, "one accumulator per issuing warp");
 constexpr uint32_t kSpinLimit = 1u << 22;
 #ifndef DSX_MX_SMALL_MAX
 #define DSX_MX_SMALL_MAX 8
@@ -250,7 +252,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     const int n_segs = a.n_segs[0];
-    const int n_mb = a.rows / (GATE_UP ? 256 : 512);   // 512-row tiles (gate/up: 256 gate + 256 up)
+    const int n_mb = a.rows / (GATE_UP ? 128 : 256);   // 256-row tiles (gate/up: 128 gate + 128 up)
     const int n_tiles = n_segs * n_mb;
     const int n_kc = a.K / kStageK;
 
@@ -259,29 +261,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
         if (lane == 0) {
             uint32_t cnt = 0;
             bool ok = true;
-            // weight map: gate/up = (bytes, row, matrix, slot) with a box of 64 x 256 x 2 (lands as 256 gate rows, then 256 up
-            // rows); down = (bytes, row, 1, slot) with a box of 64 x 256 x 1, two boxes per stage
-            auto w_row = [&](int mb) { return GATE_UP ? mb * 256 : mb * 512; };
+            // weight map: gate/up = (bytes, row, matrix, slot) with a box of 64 x 128 x 2 (lands as 128 gate rows, then 128 up
+            // rows); down = (bytes, row, 1, slot) with a box of 64 x 256 x 1
+            auto w_row = [&](int mb) { return GATE_UP ? mb * 128 : mb * 256; };
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int si = tile / n_mb, mb = tile % n_mb;
                 const PrefillSeg seg = a.segs[si];
                 const bool sh = seg.expert == a.n_local;
                 const CUtensorMap* m_w = sh ? &tmap_w_shared : &tmap_w;
                 const int slot = sh ? 0 : seg.expert;
-                // scale chunks of this tile: [K/128][4][512]
-                const uint8_t* sfa = (sh ? a.sfa_shared : a.sfa + (int64_t)slot * a.sfa_slot_stride) + (int64_t)mb * n_kc * kSfaBytes;
+                // weight scale chunks are stored per 256 gate/up (512 down) rows as [K/128][4][512] = (gate, up, gate, up) of two
+                // 128-row halves (down: four 128-row quarters): this tile's two chunks are one half of such a group
+                const uint8_t* sfa = (sh ? a.sfa_shared : a.sfa + (int64_t)slot * a.sfa_slot_stride) +
+                                     ((int64_t)(mb >> 1) * n_kc * 4 + 2 * (mb & 1)) * kSfChunk;
                 const uint8_t* sfb = a.sfb + (int64_t)si * n_kc * kSfbBytes;
-                // one copy brings all three terms of the segment: boxes of 32, 64 or 96 rows x 3 terms (a term's rows land
+                // one copy brings all three terms of the segment: boxes of 64, 128 or 192 rows x 3 terms (a term's rows land
                 // box_rows * 64 bytes apart)
                 const int n_box = (max(16, (seg.n + 15) & ~15) + kBoxRows - 1) / kBoxRows;
                 const CUtensorMap* m_b = n_box == 1 ? &tmap_b32 : (n_box == 2 ? &tmap_b64 : &tmap_b96);
                 const uint32_t stage_tx = (uint32_t)(kABytes + kSfaBytes + kSfbBytes + kTerms * n_box * kBBoxBytes);
                 // weights of this tile into L2 a few stages ahead of the ring
                 constexpr int kAhead = 4;
-                auto prefetch_w = [&](const CUtensorMap* m, int kc, int mb_, int slot_) {
-                    tma_prefetch_4d(m, kc * kRowBytes, w_row(mb_), 0, slot_);
-                    if (!GATE_UP) tma_prefetch_4d(m, kc * kRowBytes, w_row(mb_) + 256, 0, slot_);
-                };
+                auto prefetch_w = [&](const CUtensorMap* m, int kc, int mb_, int slot_) { tma_prefetch_4d(m, kc * kRowBytes, w_row(mb_), 0, slot_); };
                 if (tile == (int)blockIdx.x)
                     for (int kc = 0; kc < kAhead && kc < n_kc; kc++) prefetch_w(m_w, kc, mb, slot);
                 const int ntile = tile + gridDim.x;
@@ -300,9 +301,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     mbar_expect_tx(full, stage_tx);
                     const uint32_t a_dst = sbase + kSmemA + s * kABytes;
                     tma_load_4d(a_dst, m_w, kc * kRowBytes, w_row(mb), 0, slot, full);
-                    if (!GATE_UP) tma_load_4d(a_dst + kABytes / 2, m_w, kc * kRowBytes, w_row(mb) + 256, 0, slot, full);
                     tma_load_3d(sbase + kSmemB + s * kBBytes, m_b, kc * kRowBytes, seg.row0, 0, full);
-                    bulk_load(sbase + kSmemSfa + s * kSfaBytes, sfa + (int64_t)kc * kSfaBytes, kSfaBytes, full);
+                    bulk_load(sbase + kSmemSfa + s * kSfaBytes, sfa + (int64_t)kc * 4 * kSfChunk, kSfaBytes, full);
                     bulk_load(sbase + kSmemSfb + s * kSfbBytes, sfb + (int64_t)kc * kSfbBytes, kSfbBytes, full);
                     cnt++;
                 }
@@ -310,28 +310,26 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
         }
     } else if (warp < kEpiWarp0) {
         // ----------------------------------------------------------- MMA issue
-        // Two issuing warps: warp 1 owns accumulators 0 and 1, warp 2 owns 2 and 3 (a single thread cannot issue the
-        // 24 MMAs of a stage as fast as the tensor core retires them).  Each copies its accumulators' weight scales
-        // and its own copy of the activation scales to tensor memory, so its MMAs depend only on its own copies.
+        // Two issuing warps, one accumulator each (first product: warp 1 the gate rows, warp 2 the up rows of the tile; a single
+        // thread cannot issue a stage's MMAs and scale copies as fast as the tensor core retires them).  Each copies its
+        // accumulator's weight scales and its own copy of the activation scales to tensor memory, so its MMAs depend only
+        // on its own copies.
         if (lane == 0) {
             const int mw = warp - 1;
             uint32_t tcnt = 0, s = 0, ph = 0;   // ring stage and its phase parity
             bool ok = true;
             const uint64_t d0 = operand_desc(sbase + kSmemA);
             const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
-            const uint32_t a_lo0 = (uint32_t)d0, b_lo0 = (uint32_t)operand_desc(sbase + kSmemB);
-            const uint64_t sfa_desc0 = scale_desc(sbase + kSmemSfa), sfb_desc0 = scale_desc(sbase + kSmemSfb);
-            const uint32_t t_sfa = tmem_base + kSfaCol + 8u * (uint32_t)mw, t_sfb = tmem_base + kSfbCol + 4u * kTerms * (uint32_t)mw;
-            const uint32_t t_acc = tmem_base + (uint32_t)(2 * mw * kSegRows);
-            // accumulators 2 mw and 2 mw + 1 read 128 rows each of the stage's weights: gate/up stages hold 256 gate rows, then
-            // 256 up rows (accumulator pairs = gate + up of the same rows); down stages 512 rows in order
-            const uint32_t a_off0 = (uint32_t)((GATE_UP ? mw * (kABytes / 4) : 2 * mw * (kABytes / 4)) >> 4);
-            const uint32_t a_off1 = a_off0 + (uint32_t)((GATE_UP ? kABytes / 2 : kABytes / 4) >> 4);
+            const uint32_t a_lo0 = (uint32_t)d0 + (uint32_t)((mw * 128 * kRowBytes) >> 4), b_lo0 = (uint32_t)operand_desc(sbase + kSmemB);
+            const uint64_t sfa_desc0 = scale_desc(sbase + kSmemSfa) + (uint64_t)(mw * (kSfChunk >> 4)), sfb_desc0 = scale_desc(sbase + kSmemSfb);
+            const uint32_t t_sfa = tmem_base + kSfaCol + 4u * (uint32_t)mw, t_sfb = tmem_base + kSfbCol + 4u * kSfbChunks * kTerms * (uint32_t)mw;
+            const uint32_t t_acc = tmem_base + (uint32_t)(mw * kSegRows);
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 const int n16 = max(16, (seg.n + 15) & ~15);
                 const uint32_t idesc0 = mxf4_idesc(n16, 0u), idesc1 = mxf4_idesc(n16, 2u);
                 const uint32_t term_step = (uint32_t)(((n16 + kBoxRows - 1) / kBoxRows) * (kBBoxBytes >> 4));   // a term's rows follow the previous term's box
+                const bool two_chunks = n16 > 128;   // rows 128.. have their scales in a second chunk
                 ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // the previous tile's accumulators are drained
                 if (!ok) break;
                 tc_fence_after();
@@ -339,13 +337,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     const uint32_t full = bar(FULL) + 8u * s;
                     if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    // scales of this stage (16-byte units in the descriptor): this warp's two weight chunks, the three terms' chunks
-                    const uint64_t sfa_d = sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4) + 2 * mw * (kSfChunk >> 4));
+                    // scales of this stage (16-byte units in the descriptor): this warp's weight chunk, the three terms' chunks
                     const uint64_t sfb_d = sfb_desc0 + (uint64_t)(s * (kSfbBytes >> 4));
-                    tc_cp_scales(t_sfa, sfa_d);
-                    tc_cp_scales(t_sfa + 4, sfa_d + (kSfChunk >> 4));
+                    tc_cp_scales(t_sfa, sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4)));
 #pragma unroll
-                    for (int t = 0; t < kTerms; t++) tc_cp_scales(t_sfb + 4 * t, sfb_d + (uint64_t)(t * (kSfChunk >> 4)));
+                    for (int t = 0; t < kTerms; t++) {
+                        tc_cp_scales(t_sfb + 4 * kSfbChunks * t, sfb_d + (uint64_t)(t * kSfbChunks * (kSfChunk >> 4)));
+                        if (two_chunks) tc_cp_scales(t_sfb + 4 * kSfbChunks * t + 4, sfb_d + (uint64_t)((t * kSfbChunks + 1) * (kSfChunk >> 4)));
+                    }
                     const uint32_t a_lo = a_lo0 + s * (kABytes >> 4), b_lo = b_lo0 + s * (kBBytes >> 4);
                     const uint32_t first = kc != 0 ? 1u : 0u;
 #pragma unroll
@@ -355,8 +354,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                         for (int t = 0; t < kTerms; t++) {
                             const uint32_t bl = b_lo + (uint32_t)t * term_step + (uint32_t)(ks * 2);   // + 32 bytes per k step
                             const uint32_t acc = (ks | t) != 0 ? 1u : first;
-                            tc_mma_mxf4_lo(t_acc, a_lo + a_off0 + ks * 2, bl, hi, idesc, t_sfa, t_sfb + 4 * t, acc);
-                            tc_mma_mxf4_lo(t_acc + kSegRows, a_lo + a_off1 + ks * 2, bl, hi, idesc, t_sfa + 4, t_sfb + 4 * t, acc);
+                            tc_mma_mxf4_lo(t_acc, a_lo + ks * 2, bl, hi, idesc, t_sfa, t_sfb + 4 * kSfbChunks * t, acc);
                         }
                     }
                     tc_commit(bar(EMPTY) + 8u * s);   // arrives when the copies and MMAs above have read their operands
@@ -368,8 +366,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        // Warp w may read lanes 32 * (w % 4) .. + 31 of tensor memory; the four warps of a lane quarter take one
-        // 32-column chunk of the tile each.
+        // Warp w may read lanes 32 * (w % 4) .. + 31 of tensor memory; the three warps of a lane quarter take 64 columns of
+        // the tile each, in blocks of 16.  A lane holds gate and up of one output row (first product), or rows r and r + 128.
         const int q = warp & 3, rank = (warp - kEpiWarp0) >> 2;
         uint32_t tcnt = 0;
         bool ok = true;
@@ -382,21 +380,26 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
             const int r_in = q * 32 + lane;           // row inside a 128-row accumulator
-            const int c0 = 32 * rank;
-            // lane j of the warp fetches the routing weight / output row of column c0 + j
-            float wv = 0.f;
-            int orow = 0;
-            if (c0 + lane < seg.n) {
-                if (sh) { wv = 1.0f; orow = seg.row0 + c0 + lane; }
-                else { const int ts = a.perm[seg.row0 + c0 + lane]; wv = a.route_w[ts]; orow = ts; }
+            const int c0 = 64 * rank;
+            // lane j of the warp fetches the routing weight / output row of columns c0 + j and c0 + 32 + j
+            float wv[2] = {0.f, 0.f};
+            int orow[2] = {0, 0};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int c = c0 + 32 * h + lane;
+                if (c < seg.n) {
+                    if (sh) { wv[h] = 1.0f; orow[h] = seg.row0 + c; }
+                    else { const int ts = a.perm[seg.row0 + c]; wv[h] = a.route_w[ts]; orow[h] = ts; }
+                }
             }
-            // one 16-column block of accumulator pair p (gate + up of rows p * 128 + r_in, or two 128-row quarters of down)
-            auto emit = [&](int p, int cb, const uint32_t (&v0)[16], const uint32_t (&v1)[16]) {
+            // one 16-column block: v0 = accumulator 0, v1 = accumulator 1
+            auto emit = [&](int cb, const uint32_t (&v0)[16], const uint32_t (&v1)[16]) {
+                const int h = (cb - c0) >> 5, j0 = (cb - c0) & 31;
                 if (GATE_UP) {
-                    __half* dst = a.mid + (int64_t)(seg.row0 + cb) * a.mid_stride + mb * 256 + p * 128 + r_in;
+                    __half* dst = a.mid + (int64_t)(seg.row0 + cb) * a.mid_stride + mb * 128 + r_in;
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
-                        const float wj = __shfl_sync(0xFFFFFFFFu, wv, (cb - c0) + j);
+                        const float wj = __shfl_sync(0xFFFFFFFFu, wv[h], j0 + j);
                         if (cb + j < seg.n) {
                             float gv = __uint_as_float(v0[j]), uv = __uint_as_float(v1[j]);
                             if (a.clamp > 1.0e-6f) {
@@ -408,49 +411,48 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                         }
                     }
                 } else {
-                    const int h = mb * 512 + p * 256 + r_in;
+                    const int hrow = mb * 256 + r_in;
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
-                        const int rj = __shfl_sync(0xFFFFFFFFu, orow, (cb - c0) + j);
+                        const int rj = __shfl_sync(0xFFFFFFFFu, orow[h], j0 + j);
                         if (cb + j < seg.n) {
-                            float* dst = a.partial + (int64_t)rj * a.rows + h;
+                            float* dst = a.partial + (int64_t)rj * a.rows + hrow;
                             dst[0] = __uint_as_float(v0[j]);
                             dst[128] = __uint_as_float(v1[j]);
                         }
                     }
                 }
             };
-            const bool active = c0 < seg.n;
-            if (active) {
-                // pair 0 block by block; pair 1 is read whole, the accumulators are handed back, and its arithmetic and stores
-                // run while the next tile's MMAs have already started
+            // the first 32 columns block by block; the last 32 are read whole, the accumulators are handed back, and their
+            // arithmetic and stores run while the next tile's MMAs have already started
 #pragma unroll
-                for (int hf = 0; hf < 2; hf++) {
-                    const int cb = c0 + 16 * hf;
-                    if (cb >= seg.n) continue;
+            for (int b = 0; b < 2; b++) {
+                const int cb = c0 + 16 * b;
+                if (cb < seg.n) {
                     uint32_t v0[16], v1[16];
                     tc_ld16(lane_addr + (uint32_t)cb, v0);
                     tc_ld16(lane_addr + (uint32_t)(kSegRows + cb), v1);
                     tc_wait_ld();
-                    emit(0, cb, v0, v1);
+                    emit(cb, v0, v1);
                 }
             }
             uint32_t w0[16], w1[16], w2[16], w3[16];
-            if (active) {
-                tc_ld16(lane_addr + (uint32_t)(2 * kSegRows + c0), w0);
-                tc_ld16(lane_addr + (uint32_t)(3 * kSegRows + c0), w1);
-                if (c0 + 16 < seg.n) {
-                    tc_ld16(lane_addr + (uint32_t)(2 * kSegRows + c0 + 16), w2);
-                    tc_ld16(lane_addr + (uint32_t)(3 * kSegRows + c0 + 16), w3);
+            const bool tail0 = c0 + 32 < seg.n, tail1 = c0 + 48 < seg.n;
+            if (tail0) {
+                tc_ld16(lane_addr + (uint32_t)(c0 + 32), w0);
+                tc_ld16(lane_addr + (uint32_t)(kSegRows + c0 + 32), w1);
+                if (tail1) {
+                    tc_ld16(lane_addr + (uint32_t)(c0 + 48), w2);
+                    tc_ld16(lane_addr + (uint32_t)(kSegRows + c0 + 48), w3);
                 }
                 tc_wait_ld();
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
-            if (active) {
-                emit(1, c0, w0, w1);
-                if (c0 + 16 < seg.n) emit(1, c0 + 16, w2, w3);
+            if (tail0) {
+                emit(c0 + 32, w0, w1);
+                if (tail1) emit(c0 + 48, w2, w3);
             }
             tcnt++;
         }
@@ -561,9 +563,9 @@ mx_quantize_rows_kernel(const void* __restrict__ src, int64_t n_rows, int K, con
         if (si < 0) return;
         const int r = (int)(row - seg.row0);
         in = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(src) + row * K);
-        sf_row = scales_out + (int64_t)si * n_kc * kSfbBytes + (r & 31) * 16 + ((r >> 5) & 3) * 4;   // r < 128: one chunk per term
+        sf_row = scales_out + (int64_t)si * n_kc * kSfbBytes + (r >> 7) * kSfChunk + (r & 31) * 16 + ((r >> 5) & 3) * 4;   // chunk r / 128 of its term
         sf_stage_stride = kSfbBytes;
-        sf_term_stride = kSfChunk;
+        sf_term_stride = kSfbChunks * kSfChunk;
     }
     uint8_t* out_row = codes_out + row * (K >> 1) + lane * 4;
     for (int i = 0; i < (K >> 8); i++) {
@@ -637,7 +639,7 @@ mx_gather_rows_kernel(const uint8_t* __restrict__ tok_codes, int64_t tok_term_st
     const int r = (int)(row - seg.row0);
     const int64_t tok = row < P ? perm[row] / n_used : row - P;
     const int n_kc = K / kStageK, n16 = K >> 5;   // 128-column stages; 16-byte pieces of a term's code row
-    uint8_t* sf_row = sfb + (int64_t)si * n_kc * kSfbBytes + (r & 31) * 16 + ((r >> 5) & 3) * 4;
+    uint8_t* sf_row = sfb + (int64_t)si * n_kc * kSfbBytes + (r >> 7) * kSfChunk + (r & 31) * 16 + ((r >> 5) & 3) * 4;
 #pragma unroll
     for (int t = 0; t < kTerms; t++) {
         const uint4* src = reinterpret_cast<const uint4*>(tok_codes + (int64_t)t * tok_term_stride + tok * (K >> 1));
@@ -645,12 +647,12 @@ mx_gather_rows_kernel(const uint8_t* __restrict__ tok_codes, int64_t tok_term_st
         for (int c = lane; c < n16; c += 32) dst[c] = __ldg(src + c);
         const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(tok_scales + (tok * kTerms + t) * (int64_t)(K >> 5));
         for (int kc = lane; kc < n_kc; kc += 32)
-            *reinterpret_cast<uint32_t*>(sf_row + (int64_t)kc * kSfbBytes + t * kSfChunk) = __ldg(ssrc + kc);
+            *reinterpret_cast<uint32_t*>(sf_row + (int64_t)kc * kSfbBytes + t * kSfbChunks * kSfChunk) = __ldg(ssrc + kc);
     }
 }
 
 // (Re-)encode the weight maps when the layer points at other planes: gate/up as (bytes, row, matrix, slot)
-// with a box of 64 bytes x 256 rows x both matrices, down as (bytes, row, 1, slot) with 64 x 256.
+// with a box of 64 bytes x 128 rows x both matrices, down as (bytes, row, 1, slot) with 64 x 256.
 int map_weights(PrefillWorkspace* ws, int which, const uint8_t* km_gu, const uint8_t* km_dn, int64_t gu_stride, int64_t dn_stride,
                 int n_slots) {
     if (ws->mapped_km_gu[which] == km_gu && ws->mapped_km_dn[which] == km_dn && ws->mapped_km_slots[which] == n_slots) return DSX_OK;
@@ -658,7 +660,7 @@ int map_weights(PrefillWorkspace* ws, int which, const uint8_t* km_gu, const uin
     {
         const cuuint64_t dims[4] = {(cuuint64_t)(H / 2), (cuuint64_t)F, 2, (cuuint64_t)n_slots};
         const cuuint64_t strides[3] = {(cuuint64_t)(H / 2), (cuuint64_t)(F * (H / 2)), (cuuint64_t)gu_stride};
-        const cuuint32_t box[4] = {(cuuint32_t)kRowBytes, 256, 2, 1};
+        const cuuint32_t box[4] = {(cuuint32_t)kRowBytes, 128, 2, 1};
         if (int rc = tmap_encode(&ws->tmap_km_gu[which], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, km_gu, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
     }
@@ -690,7 +692,7 @@ int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg,
     ws->mx_tok_term_stride = (int64_t)cfg.max_tokens * (cfg.hidden / 2);
     DSX_CUDA(cudaMalloc((void**)&ws->xq_tok, (size_t)kTerms * (size_t)ws->mx_tok_term_stride));
     DSX_CUDA(cudaMalloc((void**)&ws->sf_tok, (size_t)cfg.max_tokens * kTerms * (size_t)(cfg.hidden / 32)));
-    // activation terms as (bytes, row, term): boxes of 64 bytes x 32 / 64 / 96 rows x 3 terms
+    // activation terms as (bytes, row, term): boxes of 64 bytes x 64 / 128 / 192 rows x 3 terms
     for (int g = 0; g < 2; g++)
         for (int b = 0; b < 3; b++) {
             const int64_t K = g == 0 ? cfg.hidden : cfg.ffn;
