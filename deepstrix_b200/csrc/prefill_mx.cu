@@ -18,22 +18,23 @@
 // accumulator.  Three terms leave a relative error of about 3e-3 on the layer output (two terms 2.5e-2,
 // a single E4M3 term 4.6e-2), for 1.5 times the tensor-core time of one FP8 pass.
 //
-// Tiling.  Every activation row costs three operand rows, so a tile is tall on the weight side: expert-sorted
-// rows are cut into segments of at most 96 rows of one expert, and a tile = (segment, 512 weight rows) = four
-// M = 128 accumulators that share the segment's rows as N (first product: gate rows f0..f0+127, up rows
-// f0..f0+127, gate f0+128.., up f0+128.., so that a tensor-memory lane holds gate and up of one output row).
-// Tensor memory: 4 x 96 accumulator columns, 16 columns of weight scales, 2 x 12 of activation scales.
-// A pipeline stage is 128 reduction columns: 32 KB of weight codes (one TMA box), up to 3 x 6 KB of activation
-// terms (one TMA box of 32, 64 or 96 rows x 3 terms: only the rows the segment has), 2 KB + 1.5 KB of scale
-// chunks, all arriving on one mbarrier; 4 stages.  Two warps issue: each copies its two accumulators' weight
-// scales and its own copy of the activation scales to tensor memory and issues 2 (k steps of 64) x 3 (terms) x 2
-// (accumulators) MMAs per stage.  Traffic from L2 into shared memory per MMA-clock is what bounds this kernel
-// (that path saturates near 8.5 TB/s on the device): 256-row tiles with 240-row segments moved 79 bytes per
-// MMA-clock on the 8192-token workload, whose experts hold ~256 rows and so split into two half-empty segments;
-// this shape moves 44.
+// Tiling.  Expert-sorted rows are cut into segments of at most 192 rows of one expert, and a tile = (segment, 256
+// weight rows) = two M = 128 accumulators that share the segment's rows as N (first product: 128 gate rows and the
+// 128 up rows of the same outputs, so that a tensor-memory lane holds gate and up of one output row).  Tensor
+// memory: 2 x 192 accumulator columns, 8 columns of weight scales, 2 x 24 of activation scales.  A pipeline stage is
+// 128 reduction columns: 16 KB of weight codes (one TMA box), up to 3 x 12 KB of activation terms (one TMA box of
+// 64, 128 or 192 rows x 3 terms), 1 KB + 3 KB of scale chunks, all arriving on one mbarrier; 4 stages.  Two warps
+// issue, one accumulator each: each copies its accumulator's weight scales and its own copy of the activation
+// scales to tensor memory and issues 2 (k steps of 64) x 3 (terms) MMAs per stage.
+// What bounds the kernel is the shared memory's 128 bytes per clock, which the tensor core's operand reads share
+// with the TMA fills: an M = 128, K = 64 MMA over N rows reads 4 KB of weights and 32 N bytes of terms in N / 2 clocks
+// (8192 / N + 64 bytes per clock) and the fills add 45 to 55.  Tall tiles (512 weight rows x 96 rows, the first
+// shape of this kernel) minimise the fills but need 149 + 46 bytes per MMA clock: the tensor pipe could be busy 66 %
+// of the time and was measured at 60 %, with shared memory 96 % busy.  This shape needs 128 + 52 at N = 128 and
+// 107 + 45 at N = 192.
 // Warp roles: one producer thread, two MMA threads, 12 epilogue warps that read the accumulators
 // (tcgen05.ld), apply clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows
-// (f32); the second accumulator pair is read whole and tensor memory handed back before its arithmetic runs.
+// (f32); a warp's last 32 columns are read whole and tensor memory handed back before their arithmetic runs.
 // Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
 // is freed and bit 2 of the layer's error word is set.
 #include "prefill.cuh"
@@ -42,7 +43,7 @@ namespace dsx {
 namespace {
 
 constexpr int kEpiWarps = 12;
-constexpr int kMmaWarps = 2;                  // issuing warps: each owns two of the tile's four accumulators
+constexpr int kMmaWarps = 2;                  // issuing warps: each owns one of the tile's two accumulators (one warp for both: 9 % slower)
 constexpr int kEpiWarp0 = 1 + kMmaWarps;
 constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;
 constexpr int kAccs = 2;                      // M = 128 accumulators per tile (256 weight rows), one per issuing warp
@@ -75,7 +76,7 @@ constexpr uint32_t kSfaCol = kAccs * kSegRows;    // accumulator h at column h *
 constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term and chunk of 128 rows, one copy per issuing warp
 static_assert(kSfbCol + 4 * kSfbChunks * kTerms * kMmaWarps <= 512, "tensor memory holds 512 columns");
 static_assert(kBTermBytes % 512 == 0, "a term plane must start on a swizzle-atom boundary");
-static_assert(kMmaWarps == kAccs, "one accumulator per issuing warp");
+static_assert(kAccs % kMmaWarps == 0, "accumulators divide evenly over the issuing warps");
 constexpr uint32_t kSpinLimit = 1u << 22;
 #ifndef DSX_MX_SMALL_MAX
 #define DSX_MX_SMALL_MAX 8
@@ -316,14 +317,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
         // on its own copies.
         if (lane == 0) {
             const int mw = warp - 1;
+            constexpr int kAPW = kAccs / kMmaWarps;   // accumulators per issuing warp
             uint32_t tcnt = 0, s = 0, ph = 0;   // ring stage and its phase parity
             bool ok = true;
             const uint64_t d0 = operand_desc(sbase + kSmemA);
             const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
-            const uint32_t a_lo0 = (uint32_t)d0 + (uint32_t)((mw * 128 * kRowBytes) >> 4), b_lo0 = (uint32_t)operand_desc(sbase + kSmemB);
-            const uint64_t sfa_desc0 = scale_desc(sbase + kSmemSfa) + (uint64_t)(mw * (kSfChunk >> 4)), sfb_desc0 = scale_desc(sbase + kSmemSfb);
-            const uint32_t t_sfa = tmem_base + kSfaCol + 4u * (uint32_t)mw, t_sfb = tmem_base + kSfbCol + 4u * kSfbChunks * kTerms * (uint32_t)mw;
-            const uint32_t t_acc = tmem_base + (uint32_t)(mw * kSegRows);
+            const uint32_t a_lo0 = (uint32_t)d0 + (uint32_t)((mw * kAPW * 128 * kRowBytes) >> 4), b_lo0 = (uint32_t)operand_desc(sbase + kSmemB);
+            const uint64_t sfa_desc0 = scale_desc(sbase + kSmemSfa) + (uint64_t)(mw * kAPW * (kSfChunk >> 4)), sfb_desc0 = scale_desc(sbase + kSmemSfb);
+            const uint32_t t_sfa = tmem_base + kSfaCol + 4u * (uint32_t)(mw * kAPW), t_sfb = tmem_base + kSfbCol + 4u * kSfbChunks * kTerms * (uint32_t)mw;
+            const uint32_t t_acc = tmem_base + (uint32_t)(mw * kAPW * kSegRows);
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
                 const int n16 = max(16, (seg.n + 15) & ~15);
@@ -337,9 +339,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     const uint32_t full = bar(FULL) + 8u * s;
                     if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    // scales of this stage (16-byte units in the descriptor): this warp's weight chunk, the three terms' chunks
+                    // scales of this stage (16-byte units in the descriptor): this warp's weight chunks, the three terms' chunks
                     const uint64_t sfb_d = sfb_desc0 + (uint64_t)(s * (kSfbBytes >> 4));
-                    tc_cp_scales(t_sfa, sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4)));
+#pragma unroll
+                    for (int h = 0; h < kAPW; h++) tc_cp_scales(t_sfa + 4 * h, sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4) + h * (kSfChunk >> 4)));
 #pragma unroll
                     for (int t = 0; t < kTerms; t++) {
                         tc_cp_scales(t_sfb + 4 * kSfbChunks * t, sfb_d + (uint64_t)(t * kSfbChunks * (kSfChunk >> 4)));
@@ -354,7 +357,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                         for (int t = 0; t < kTerms; t++) {
                             const uint32_t bl = b_lo + (uint32_t)t * term_step + (uint32_t)(ks * 2);   // + 32 bytes per k step
                             const uint32_t acc = (ks | t) != 0 ? 1u : first;
-                            tc_mma_mxf4_lo(t_acc, a_lo + ks * 2, bl, hi, idesc, t_sfa, t_sfb + 4 * kSfbChunks * t, acc);
+#pragma unroll
+                            for (int h = 0; h < kAPW; h++)
+                                tc_mma_mxf4_lo(t_acc + h * kSegRows, a_lo + (uint32_t)((h * 128 * kRowBytes) >> 4) + ks * 2, bl, hi, idesc, t_sfa + 4 * h,
+                                               t_sfb + 4 * kSfbChunks * t, acc);
                         }
                     }
                     tc_commit(bar(EMPTY) + 8u * s);   // arrives when the copies and MMAs above have read their operands
