@@ -26,12 +26,17 @@
 // 64, 128 or 192 rows x 3 terms), 1 KB + 3 KB of scale chunks, all arriving on one mbarrier; 4 stages.  Two warps
 // issue, one accumulator each: each copies its accumulator's weight scales and its own copy of the activation
 // scales to tensor memory and issues 2 (k steps of 64) x 3 (terms) MMAs per stage.
-// What bounds the kernel is the shared memory's 128 bytes per clock, which the tensor core's operand reads share
-// with the TMA fills: an M = 128, K = 64 MMA over N rows reads 4 KB of weights and 32 N bytes of terms in N / 2 clocks
-// (8192 / N + 64 bytes per clock) and the fills add 45 to 55.  Tall tiles (512 weight rows x 96 rows, the first
-// shape of this kernel) minimise the fills but need 149 + 46 bytes per MMA clock: the tensor pipe could be busy 66 %
-// of the time and was measured at 60 %, with shared memory 96 % busy.  This shape needs 128 + 52 at N = 128 and
-// 107 + 45 at N = 192.
+// Two limits shape the tile.  (1) L2 -> shared-memory traffic: the operands of a stage arrive at no more than ~8.5 TB/s
+// over the device, which a tall tile (many weight rows per activation row) serves best.  (2) Shared memory's 128
+// bytes per clock, which the tensor core's operand reads share with those fills: an M = 128, K = 64 MMA over N rows
+// reads 4 KB of weights and 32 N bytes of terms in N / 2 clocks, i.e. 8192 / N + 64 bytes per clock, which a wide N
+// serves best.  The first shape of this kernel (512 weight rows x 96 rows, four accumulators) had the fewest fill
+// bytes but needed 149 + 46 bytes of shared-memory bandwidth per MMA clock: shared memory was 96 % busy, the tensor
+// pipe 60 %, and the fills reached only 7.1 TB/s.  This shape needs 128 + 52 at N = 128 (107 + 45 at N = 192), moves
+// 17 % more bytes and is bound by limit (1) instead: 8.1 to 8.6 TB/s measured, tensor pipe 57 to 62 % busy, 3 to 6 %
+// faster on the layers measured.  CTA pairs (cta_group::2, each CTA holding half of a segment's rows) were built
+// and measured as well: bit-identical results, 5 % slower (each tensor core fetches the other CTA's half again for
+// every accumulator that uses it).
 // Warp roles: one producer thread, two MMA threads, 12 epilogue warps that read the accumulators
 // (tcgen05.ld), apply clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows
 // (f32); a warp's last 32 columns are read whole and tensor memory handed back before their arithmetic runs.
