@@ -37,9 +37,7 @@ struct PrefillWorkspace {
     uint8_t* xq = nullptr;          // [3 terms][cap_rows][K/2]: the sorted rows (then mid) as packed E2M1 terms
     int64_t mx_term_stride = 0;     // bytes between terms
     uint8_t* sfb = nullptr;         // their block scales: [segment][K/128][term][512]
-    uint8_t* xq_tok = nullptr;      // [3 terms][max_tokens][hidden/2]: every token expanded once
-    int64_t mx_tok_term_stride = 0;
-    uint8_t* sf_tok = nullptr;      // [max_tokens][3 terms][hidden/32] E8M0 bytes
+    int32_t* mx_inv_perm = nullptr; // [max_tokens * n_used]: expert-sorted position of every pick (-1: not placed here)
     PrefillSeg* mx_segs = nullptr;  // segments of at most 192 rows
     int32_t mx_seg_cap = 0;
     CUtensorMap tmap_xq[3], tmap_mq[3];   // xq as (bytes, row, term) for K = hidden / K = ffn, boxes of 32 / 64 / 96 rows

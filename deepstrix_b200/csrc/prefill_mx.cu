@@ -13,7 +13,7 @@
 // memory by tcgen05.cp, untouched.  The other operand of kind::mxf4 is FP4 too, and one FP4 value per
 // activation is far too coarse (rel-L2 0.2 on the layer).  So an activation row x is written as a SUM of
 // three MXFP4 rows, x ~ t1 + t2 + t3: t1 = x rounded to E2M1 with a power-of-two scale per 32, t2 the
-// same rounding of the residual x - t1 with its own scales, t3 of x - t1 - t2 (mx_quantize_rows_kernel;
+// same rounding of the residual x - t1 with its own scales, t3 of x - t1 - t2 (mx_terms_of_block;
 // every step exact in f32, so the CPU can restate it bit for bit).  Each term is one more MMA into the same
 // accumulator.  Three terms leave a relative error of about 3e-3 on the layer output (two terms 2.5e-2,
 // a single E4M3 term 4.6e-2), for 1.5 times the tensor-core time of one FP8 pass.
@@ -42,6 +42,8 @@
 // (f32); a warp's last 32 columns are read whole and tensor memory handed back before their arithmetic runs.
 // Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
 // is freed and bit 2 of the layer's error word is set.
+#include <algorithm>
+
 #include "prefill.cuh"
 
 namespace dsx {
@@ -147,17 +149,8 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
-// D[128 x N] (+)= A[128 x 64] . B[N x 64]^T, E2M1 operands, one E8M0 scale per 32 columns of either operand.
-__device__ __forceinline__ void tc_mma_mxf4(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
-        : "memory");
-}
-// The same with the descriptors given as low words (the high word -- stride, version, swizzle -- is common to every
+// D[128 x N] (+)= A[128 x 64] . B[N x 64]^T, E2M1 operands, one E8M0 scale per 32 columns of either operand;
+// the descriptors are given as low words (the high word -- stride, version, swizzle -- is common to every
 // operand tile): the issuing thread is bound by its own scalar instructions, a 32-bit add per operand is the least.
 __device__ __forceinline__ void tc_mma_mxf4_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t sfa, uint32_t sfb,
                                                uint32_t accumulate) {
@@ -545,121 +538,179 @@ __device__ __forceinline__ int find_segment(const PrefillSeg* __restrict__ segs,
     return lo;
 }
 
-// One warp per row: the row becomes kTerms MXFP4 rows.  A lane holds 8 consecutive values; four lanes make a
-// 32-value block.
-//   BY_TOKEN:  rows are the batch's tokens (bf16); codes to [term][token][K/2], scales row-major to
-//              [token][term][K/32] -- a token is expanded once, however many experts it visits
-//   otherwise: rows are the expert-sorted rows of mid (f16) that lie inside a segment; codes to [term][row][K/2],
-//              scales into the segment's scale-factor chunks
-template <bool BY_TOKEN>
-__global__ void __launch_bounds__(256)
-mx_quantize_rows_kernel(const void* __restrict__ src, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
-                        const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ codes_out, int64_t term_stride,
-                        uint8_t* __restrict__ scales_out, uint32_t opaque_zero, uint32_t* __restrict__ error_word) {
-    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= n_rows) return;
-    const int n_kc = K / kStageK;
-    uint8_t* sf_row;
-    int64_t sf_stage_stride, sf_term_stride;   // bytes between 128-column stages / between terms
-    const uint4* in;
-    if (BY_TOKEN) {
-        in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) + row * K);
-        sf_row = scales_out + row * (int64_t)(kTerms * (K >> 5));
-        sf_stage_stride = 4;
-        sf_term_stride = K >> 5;
-    } else {
-        PrefillSeg seg;
-        const int si = find_segment(segs, n_segs_p[0], row, &seg);
-        if (si < 0) return;
-        const int r = (int)(row - seg.row0);
-        in = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(src) + row * K);
-        sf_row = scales_out + (int64_t)si * n_kc * kSfbBytes + (r >> 7) * kSfChunk + (r & 31) * 16 + ((r >> 5) & 3) * 4;   // chunk r / 128 of its term
-        sf_stage_stride = kSfbBytes;
-        sf_term_stride = kSfbChunks * kSfChunk;
-    }
-    uint8_t* out_row = codes_out + row * (K >> 1) + lane * 4;
-    for (int i = 0; i < (K >> 8); i++) {
-        const uint4 raw = __ldg(in + i * 32 + lane);
-        const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-        float v[8];
+// The kTerms MXFP4 terms of one 32-value block, all in one lane: codes[t] = the block's 32 E2M1 codes of term t (16
+// bytes, element 2i in the low nibble of byte i), e[t] = its E8M0 scale byte.  No lane talks to another.
+__device__ __forceinline__ void mx_terms_of_block(float (&v)[32], uint32_t opaque_zero, uint32_t* error_word, uint4 (&codes)[kTerms],
+                                                  uint32_t (&e)[kTerms]) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            if (BY_TOKEN) {
-                v[2 * j] = __uint_as_float(wds[j] << 16);
-                v[2 * j + 1] = __uint_as_float(wds[j] & 0xFFFF0000u);
-            } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wds[j]));
-                v[2 * j] = f.x;
-                v[2 * j + 1] = f.y;
-            }
-        }
+    for (int t = 0; t < kTerms; t++) {
+        float amax = 0.0f;
 #pragma unroll
-        for (int t = 0; t < kTerms; t++) {
-            float amax = 0.0f;
+        for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(v[j]));
+        // an infinite value (an un-clamped SwiGLU product that left f16, or an infinite token value) has no terms
+        if (t == 0 && amax > 3.0e38f) atomicOr(error_word, kErrHalfRange);
+        e[t] = mx_scale_byte(amax);
+        const float inv = __uint_as_float((254u - e[t]) << 23), scl = __uint_as_float(e[t] << 23);
+        uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-            // an infinite value (an un-clamped SwiGLU product that left f16, or an infinite token value) has no terms
-            if (t == 0 && amax > 3.0e38f && (lane & 3) == 0) atomicOr(error_word, kErrHalfRange);
-            const uint32_t e = mx_scale_byte(amax);
-            const float inv = __uint_as_float((254u - e) << 23), scl = __uint_as_float(e << 23);
+        for (int g = 0; g < 4; g++) {
             float sv[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) sv[j] = v[j] * inv;
-            const uint32_t codes = e2m1_pack8(sv);
-            *reinterpret_cast<uint32_t*>(out_row + (int64_t)t * term_stride + i * 128) = codes;
+            for (int j = 0; j < 8; j++) sv[j] = v[8 * g + j] * inv;
+            w[g] = e2m1_pack8(sv);
             if (t + 1 < kTerms) {
                 float d[8];
                 if (opaque_zero == 0xFFFFFFFFu) {   // never: keeps the arithmetic decoder compiled for comparison
 #pragma unroll
-                    for (int j = 0; j < 8; j++) d[j] = e2m1_value(codes >> (4 * j));
+                    for (int j = 0; j < 8; j++) d[j] = e2m1_value(w[g] >> (4 * j));
                 } else {
                     // the decoder must not see that its input comes straight from the encoder above: with the two chained,
                     // the compiled code produced wrong residuals (CUDA 12.9, sm_100a); an exclusive-or with a kernel
                     // argument that is always zero separates them
-                    e2m1_unpack8(codes ^ opaque_zero, d);
+                    e2m1_unpack8(w[g] ^ opaque_zero, d);
                 }
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = __fmaf_rn(-d[j], scl, v[j]);   // exact: the residual
+                for (int j = 0; j < 8; j++) v[8 * g + j] = __fmaf_rn(-d[j], scl, v[8 * g + j]);   // exact: the residual
             }
-            // the scales of 4 consecutive blocks (lanes 0,4,8,12 / 16,20,24,28) form one word: stage 2i / 2i+1 of the row
-            const int base = lane & 16;
-            const uint32_t w = __shfl_sync(0xFFFFFFFFu, e, base) | (__shfl_sync(0xFFFFFFFFu, e, base + 4) << 8) |
-                               (__shfl_sync(0xFFFFFFFFu, e, base + 8) << 16) | (__shfl_sync(0xFFFFFFFFu, e, base + 12) << 24);
-            if ((lane & 15) == 0)
-                *reinterpret_cast<uint32_t*>(sf_row + (int64_t)(2 * i + (lane >> 4)) * sf_stage_stride + (int64_t)t * sf_term_stride) = w;
+        }
+        codes[t] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// The scale bytes of four consecutive blocks (lanes 4j .. 4j+3, one 128-column stage) as one word, valid in lane 4j.
+__device__ __forceinline__ uint32_t mx_stage_scales(uint32_t e, int lane) {
+    const int base = lane & ~3;
+    return __shfl_sync(0xFFFFFFFFu, e, base) | (__shfl_sync(0xFFFFFFFFu, e, base + 1) << 8) | (__shfl_sync(0xFFFFFFFFu, e, base + 2) << 16) |
+           (__shfl_sync(0xFFFFFFFFu, e, base + 3) << 24);
+}
+
+// Byte offset, inside the activation scale chunks, of row r of segment si (stage 0, term 0).
+__device__ __forceinline__ int64_t mx_sf_offset(int si, int r, int n_kc) {
+    return (int64_t)si * n_kc * kSfbBytes + (r >> 7) * kSfChunk + (r & 31) * 16 + ((r >> 5) & 3) * 4;   // chunk r / 128 of its term
+}
+
+// First product's operand.  One warp per (token, 1024 columns), a lane per 32-value block: the token row (bf16) becomes
+// kTerms MXFP4 rows ONCE and is written to every expert-sorted row that holds a copy of it -- the sorted positions of its
+// picks (inv_perm, -1 for picks that are not placed here) and row P + t of the shared expert -- codes to
+// [term][row][K/2], scales into the row's segment's scale-factor chunks.  Rows outside every segment (experts handed to
+// the grouped GEMV) get nothing.
+__global__ void __launch_bounds__(256)
+mx_quantize_tokens_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, int K, const int32_t* __restrict__ inv_perm, int n_used, int64_t P,
+                          int with_shared, const PrefillSeg* __restrict__ segs, const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq,
+                          int64_t term_stride, uint8_t* __restrict__ sfb, uint32_t opaque_zero, uint32_t* __restrict__ error_word) {
+    const int parts = (K + 1023) >> 10;
+    const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t tok = w / parts;
+    const int part = (int)(w - tok * parts);
+    const int lane = threadIdx.x & 31;
+    if (tok >= T) return;
+    const int n_kc = K / kStageK;
+    // lane d < n_used: pick d of the token; lane n_used: the shared expert's copy
+    int64_t my_row = -1, my_sf = 0;
+    if (lane < n_used) my_row = inv_perm[tok * n_used + lane];
+    else if (lane == n_used && with_shared) my_row = P + tok;
+    if (my_row >= 0) {
+        PrefillSeg seg;
+        const int si = find_segment(segs, n_segs_p[0], my_row, &seg);
+        if (si < 0) my_row = -1;
+        else my_sf = mx_sf_offset(si, (int)(my_row - seg.row0), n_kc);
+    }
+    const uint32_t dests = __ballot_sync(0xFFFFFFFFu, my_row >= 0);
+    if (dests == 0u) return;
+    const int blk = part * 32 + lane;            // 32-value block of the row
+    const bool live = blk < (K >> 5);
+    float v[32];
+    if (live) {
+        const uint4* in = reinterpret_cast<const uint4*>(x + tok * K + (int64_t)blk * 32);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint4 raw = __ldg(in + q);
+            const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                v[8 * q + 2 * j] = __uint_as_float(wds[j] << 16);
+                v[8 * q + 2 * j + 1] = __uint_as_float(wds[j] & 0xFFFF0000u);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = 0.0f;
+    }
+    uint4 codes[kTerms];
+    uint32_t e[kTerms], sfw[kTerms];
+    mx_terms_of_block(v, opaque_zero, error_word, codes, e);
+#pragma unroll
+    for (int t = 0; t < kTerms; t++) sfw[t] = mx_stage_scales(e[t], lane);
+    for (uint32_t m = dests; m != 0u; m &= m - 1u) {
+        const int d = __ffs(m) - 1;
+        const int64_t row = __shfl_sync(0xFFFFFFFFu, my_row, d), sfo = __shfl_sync(0xFFFFFFFFu, my_sf, d);
+        if (live) {
+#pragma unroll
+            for (int t = 0; t < kTerms; t++) {
+                *reinterpret_cast<uint4*>(xq + (int64_t)t * term_stride + row * (K >> 1) + (int64_t)blk * 16) = codes[t];
+                if ((lane & 3) == 0)
+                    *reinterpret_cast<uint32_t*>(sfb + sfo + (int64_t)(blk >> 2) * kSfbBytes + (int64_t)t * kSfbChunks * kSfChunk) = sfw[t];
+            }
         }
     }
 }
 
-// One warp per expert-sorted row inside a segment: the terms of the row's token (found through the permutation;
-// rows P + t are the shared expert's copy of token t) are copied into the sorted term planes and the token's
-// scales into the segment's scale-factor chunks.
+// Second product's operand.  One warp per (expert-sorted row of mid inside a segment, 1024 columns), a lane per block:
+// codes to [term][row][K/2], scales into the segment's scale-factor chunks.
 __global__ void __launch_bounds__(256)
-mx_gather_rows_kernel(const uint8_t* __restrict__ tok_codes, int64_t tok_term_stride, const uint8_t* __restrict__ tok_scales,
-                      const int32_t* __restrict__ perm, int n_used, int64_t P, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
-                      const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq, int64_t term_stride, uint8_t* __restrict__ sfb) {
-    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+mx_quantize_mid_kernel(const __half* __restrict__ mid, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
+                       const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq, int64_t term_stride, uint8_t* __restrict__ sfb,
+                       uint32_t opaque_zero, uint32_t* __restrict__ error_word) {
+    const int parts = (K + 1023) >> 10;
+    const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t row = w / parts;
+    const int part = (int)(w - row * parts);
     const int lane = threadIdx.x & 31;
     if (row >= n_rows) return;
+    const int n_kc = K / kStageK;
     PrefillSeg seg;
     const int si = find_segment(segs, n_segs_p[0], row, &seg);
     if (si < 0) return;
-    const int r = (int)(row - seg.row0);
-    const int64_t tok = row < P ? perm[row] / n_used : row - P;
-    const int n_kc = K / kStageK, n16 = K >> 5;   // 128-column stages; 16-byte pieces of a term's code row
-    uint8_t* sf_row = sfb + (int64_t)si * n_kc * kSfbBytes + (r >> 7) * kSfChunk + (r & 31) * 16 + ((r >> 5) & 3) * 4;
+    const int blk = part * 32 + lane;
+    const bool live = blk < (K >> 5);
+    float v[32];
+    if (live) {
+        const uint4* in = reinterpret_cast<const uint4*>(mid + row * K + (int64_t)blk * 32);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint4 raw = __ldg(in + q);
+            const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wds[j]));
+                v[8 * q + 2 * j] = f.x;
+                v[8 * q + 2 * j + 1] = f.y;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = 0.0f;
+    }
+    uint4 codes[kTerms];
+    uint32_t e[kTerms];
+    mx_terms_of_block(v, opaque_zero, error_word, codes, e);
+    uint8_t* sf_row = sfb + mx_sf_offset(si, (int)(row - seg.row0), n_kc);
 #pragma unroll
     for (int t = 0; t < kTerms; t++) {
-        const uint4* src = reinterpret_cast<const uint4*>(tok_codes + (int64_t)t * tok_term_stride + tok * (K >> 1));
-        uint4* dst = reinterpret_cast<uint4*>(xq + (int64_t)t * term_stride + row * (K >> 1));
-        for (int c = lane; c < n16; c += 32) dst[c] = __ldg(src + c);
-        const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(tok_scales + (tok * kTerms + t) * (int64_t)(K >> 5));
-        for (int kc = lane; kc < n_kc; kc += 32)
-            *reinterpret_cast<uint32_t*>(sf_row + (int64_t)kc * kSfbBytes + t * kSfbChunks * kSfChunk) = __ldg(ssrc + kc);
+        const uint32_t sfw = mx_stage_scales(e[t], lane);
+        if (live) {
+            *reinterpret_cast<uint4*>(xq + (int64_t)t * term_stride + row * (K >> 1) + (int64_t)blk * 16) = codes[t];
+            if ((lane & 3) == 0)
+                *reinterpret_cast<uint32_t*>(sf_row + (int64_t)(blk >> 2) * kSfbBytes + (int64_t)t * kSfbChunks * kSfChunk) = sfw;
+        }
     }
+}
+
+// inv_perm[pick] = expert-sorted position of the pick (the buffer is pre-set to -1: picks that are not placed here keep it).
+__global__ void __launch_bounds__(256)
+mx_invert_perm_kernel(const int32_t* __restrict__ perm, const int32_t* __restrict__ offsets, int n_local, int32_t* __restrict__ inv_perm) {
+    const int64_t placed = offsets[n_local];
+    for (int64_t p = (int64_t)blockIdx.x * 256 + threadIdx.x; p < placed; p += (int64_t)gridDim.x * 256) inv_perm[perm[p]] = (int32_t)p;
 }
 
 // (Re-)encode the weight maps when the layer points at other planes: gate/up as (bytes, row, matrix, slot)
@@ -700,9 +751,7 @@ int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg,
     DSX_CUDA(cudaMalloc((void**)&ws->xq, (size_t)kTerms * (size_t)ws->mx_term_stride));
     DSX_CUDA(cudaMalloc((void**)&ws->sfb, (size_t)ws->mx_seg_cap * (size_t)(Kmax / kStageK) * kSfbBytes));
     DSX_CUDA(cudaMalloc((void**)&ws->mx_segs, sizeof(PrefillSeg) * (size_t)ws->mx_seg_cap));
-    ws->mx_tok_term_stride = (int64_t)cfg.max_tokens * (cfg.hidden / 2);
-    DSX_CUDA(cudaMalloc((void**)&ws->xq_tok, (size_t)kTerms * (size_t)ws->mx_tok_term_stride));
-    DSX_CUDA(cudaMalloc((void**)&ws->sf_tok, (size_t)cfg.max_tokens * kTerms * (size_t)(cfg.hidden / 32)));
+    DSX_CUDA(cudaMalloc((void**)&ws->mx_inv_perm, sizeof(int32_t) * (size_t)cfg.max_tokens * (size_t)n_used));
     // activation terms as (bytes, row, term): boxes of 64 bytes x 64 / 128 / 192 rows x 3 terms
     for (int g = 0; g < 2; g++)
         for (int b = 0; b < 3; b++) {
@@ -724,9 +773,8 @@ void prefill_mx_workspace_free(PrefillWorkspace* ws) {
     cudaFree(ws->xq);
     cudaFree(ws->sfb);
     cudaFree(ws->mx_segs);
-    cudaFree(ws->xq_tok);
-    cudaFree(ws->sf_tok);
-    ws->xq = nullptr; ws->sfb = nullptr; ws->mx_segs = nullptr; ws->xq_tok = nullptr; ws->sf_tok = nullptr; ws->mx_ready = false;
+    cudaFree(ws->mx_inv_perm);
+    ws->xq = nullptr; ws->sfb = nullptr; ws->mx_segs = nullptr; ws->mx_inv_perm = nullptr; ws->mx_ready = false;
 }
 
 int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const PrefillCall& c, cudaStream_t stream) {
@@ -748,7 +796,6 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     if (c.with_shared)
         if (int rc = map_weights(ws, 1, c.sh_km_gu, c.sh_km_dn, c.km_gu_stride, c.km_dn_stride, 1)) return rc;
     const int64_t quant_rows = c.with_shared ? rows : P;
-    const unsigned qblocks = (unsigned)((quant_rows + 7) / 8);
     // experts with a handful of rows: the decode kernels, over the same sorted rows and partial rows
     GemvArgs v{};
     v.fmt = c.fmt; v.shared_fmt = c.fmt; v.n_expert = c.n_local;
@@ -761,12 +808,16 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     g.error_word = c.error_word;
 
     // first product: K = hidden, rows = ffn
-    mx_quantize_rows_kernel<true><<<(unsigned)((c.T + 7) / 8), 256, 0, stream>>>(c.x, c.T, (int)cfg.hidden, nullptr, nullptr, ws->xq_tok,
-                                                                                 ws->mx_tok_term_stride, ws->sf_tok, 0u, c.error_word);
+    DSX_CUDA(cudaMemsetAsync(ws->mx_inv_perm, 0xFF, sizeof(int32_t) * (size_t)P, stream));
+    mx_invert_perm_kernel<<<(unsigned)std::min<int64_t>((P + 255) / 256, 4 * c.sm_count), 256, 0, stream>>>(c.perm, c.offsets, c.n_local, ws->mx_inv_perm);
     DSX_LAUNCHED();
-    mx_gather_rows_kernel<<<qblocks, 256, 0, stream>>>(ws->xq_tok, ws->mx_tok_term_stride, ws->sf_tok, c.perm, c.n_used, P, quant_rows,
-                                                       (int)cfg.hidden, ws->mx_segs, ws->n_segs, ws->xq, ws->mx_term_stride, ws->sfb);
-    DSX_LAUNCHED();
+    {
+        const int64_t warps = c.T * ((cfg.hidden + 1023) >> 10);
+        mx_quantize_tokens_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(c.x, c.T, (int)cfg.hidden, ws->mx_inv_perm, c.n_used, P,
+                                                                                 c.with_shared ? 1 : 0, ws->mx_segs, ws->n_segs, ws->xq,
+                                                                                 ws->mx_term_stride, ws->sfb, 0u, c.error_word);
+        DSX_LAUNCHED();
+    }
     g.K = cfg.hidden; g.rows = cfg.ffn;
     g.sfa = c.sf_gu; g.sfa_slot_stride = c.sf_gu_stride; g.sfa_shared = c.sh_sf_gu;
     mx_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_xq[0], ws->tmap_xq[1], ws->tmap_xq[2], ws->tmap_km_gu[0],
@@ -778,8 +829,8 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
         if (int rc = launch_gemv_gate_up(v, c.sm_count, stream)) return rc;
     }
     // second product: K = ffn, rows = hidden, over the terms of mid
-    mx_quantize_rows_kernel<false><<<qblocks, 256, 0, stream>>>(c.mid, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs, ws->xq,
-                                                                ws->mx_term_stride, ws->sfb, 0u, c.error_word);
+    mx_quantize_mid_kernel<<<(unsigned)((quant_rows * ((cfg.ffn + 1023) >> 10) + 7) / 8), 256, 0, stream>>>(
+        c.mid, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs, ws->xq, ws->mx_term_stride, ws->sfb, 0u, c.error_word);
     DSX_LAUNCHED();
     g.K = cfg.ffn; g.rows = cfg.hidden;
     g.sfa = c.sf_dn; g.sfa_slot_stride = c.sf_dn_stride; g.sfa_shared = c.sh_sf_dn;

@@ -4,7 +4,7 @@ dequantise to f32, torch matmul) on the full-size decode layer, beside the OpenM
 Test infrastructure, like everything under oracle/.  It imports the reference tree unmodified, so it runs only
 where that tree is present (the build container); bench.py cannot call it on a GPU box and reports the port.
 
-    python oracle/time_reference_kernelpy.py [--reference /path/to/deepstrix] [--tokens 4]
+    python oracle/time_reference_kernelpy.py --reference /path/to/deepstrix [--tokens 4]
 
 One step = the routed experts a batch of tokens picked plus the shared expert, each as
 mid = silu(min(gate(x), c)) * clamp(up(x)) * w; out += down(mid), with every product through fp4_gemm on
@@ -31,10 +31,12 @@ from deepstrix_b200.config import CONFIGS  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("DEEPSTRIX_REFERENCE", ""), help="root of the reference (deepstrix) source tree")
     ap.add_argument("--tokens", type=int, default=4)
     ap.add_argument("--steps", type=int, default=2)
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("give the reference tree with --reference (or DEEPSTRIX_REFERENCE)")
     path = os.path.join(args.reference, "scripts", "v41_oracle", "kernel.py")
     spec = importlib.util.spec_from_file_location("ref_kernel", path)
     K = importlib.util.module_from_spec(spec)
