@@ -40,7 +40,7 @@ struct PrefillWorkspace {
     int32_t* mx_inv_perm = nullptr; // [max_tokens * n_used]: expert-sorted position of every pick (-1: not placed here)
     PrefillSeg* mx_segs = nullptr;  // segments of at most 192 rows
     int32_t mx_seg_cap = 0;
-    CUtensorMap tmap_xq[3], tmap_mq[3];   // xq as (bytes, row, term) for K = hidden / K = ffn, boxes of 32 / 64 / 96 rows
+    CUtensorMap tmap_xq[3], tmap_mq[3];   // xq as (bytes, row, term) for K = hidden / K = ffn, boxes of 64 / 128 / 192 rows
     CUtensorMap tmap_km_gu[2], tmap_km_dn[2];            // K-major code planes; index 0 routed, 1 shared
     const void* mapped_km_gu[2] = {nullptr, nullptr};
     const void* mapped_km_dn[2] = {nullptr, nullptr};

@@ -165,10 +165,10 @@ __global__ void unpack_kernel(int fmt, const uint8_t* __restrict__ nib, const ui
 // The tensor-core planes of an MXFP4 matrix (prefill_mx.cu): codes K-major, i.e. the HF byte layout
 // [row][K/2] with element 2i in the low nibble, and the E8M0 block scales cut into the 512-byte chunks
 // the block-scaled MMA takes its scale factors from: chunk = 128 rows x 4 blocks (128 columns), byte
-// (row % 32) * 16 + (row / 32 % 4) * 4 + (block % 4).  Chunks are ordered [tile][K / 128][4] so that the four
-// chunks one pipeline stage of one tile needs are contiguous: for gate and up a tile is 256 rows of both
-// matrices, its chunks (gate rows 0-127, up rows 0-127, gate rows 128-255, up rows 128-255) -- the order of the
-// tile's four accumulators; for down a tile is 512 rows, its chunks the four 128-row quarters.
+// (row % 32) * 16 + (row / 32 % 4) * 4 + (block % 4).  Chunks are ordered [group][K / 128][4]: for gate and up a
+// group is 256 rows of both matrices, its chunks (gate rows 0-127, up rows 0-127, gate rows 128-255, up rows
+// 128-255); for down a group is 512 rows, its chunks the four 128-row quarters.  The two chunks one pipeline stage
+// of one tile of the GEMM needs (gate + up of 128 rows; two 128-row quarters) are one contiguous half of a group.
 // One thread per (row, 32-column block).
 __global__ void kmajor_mxfp4_kernel(int layout, const uint8_t* __restrict__ q, const uint8_t* __restrict__ s, int64_t rows, int64_t K,
                                     int pair_index, int64_t src_q_stride, int64_t src_s_stride, uint8_t* __restrict__ km,
