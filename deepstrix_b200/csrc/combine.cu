@@ -11,6 +11,8 @@
 // One thread per (token, 4 consecutive rows).  Unmangled name: the kernel is also shipped as a stand-alone
 // code object (deepstrix_b200/kernels/dsx_combine.cubin) for callers that load kernels through
 // dsx_module_load_data / dsx_module_get_function, the way the reference embeds its kernels.
+// A thread requests four partial rows at a time (a rolled load-add loop issues one load per round trip), and which
+// picks count is decided once per warp: a warp lies inside one token's row whenever hidden is a multiple of 128.
 extern "C" __global__ void __launch_bounds__(256)
 dsx_combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int64_t H, int with_shared,
                const int32_t* __restrict__ selected, int expert_lo, int n_local, __nv_bfloat16* __restrict__ out) {
@@ -20,17 +22,48 @@ dsx_combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int
     const int64_t per_row = H >> 2;
     if (gid >= T * per_row) return;
     const int64_t t = gid / per_row, c = gid - t * per_row;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < n_used; s++) {
-        if (selected != nullptr) {  // expert-parallel form: picks owned elsewhere were never computed
-            const int e = selected[t * n_used + s] - expert_lo;
-            if (e < 0 || e >= n_local) continue;
+    // bit s: pick s of the token counts (expert-parallel form: picks owned elsewhere were never computed)
+    uint32_t mask = n_used >= 32 ? 0xFFFFFFFFu : (1u << n_used) - 1u;
+    if (selected != nullptr) {
+        if ((per_row & 31) == 0) {   // the warp's 32 threads share the token: lane s looks at pick s
+            const int lane = threadIdx.x & 31;
+            bool own = false;
+            if (lane < n_used) {
+                const int e = selected[t * n_used + lane] - expert_lo;
+                own = e >= 0 && e < n_local;
+            }
+            mask = __ballot_sync(0xFFFFFFFFu, own);
+        } else {
+            mask = 0u;
+            for (int s = 0; s < n_used; s++) {
+                const int e = selected[t * n_used + s] - expert_lo;
+                if (e >= 0 && e < n_local) mask |= 1u << s;
+            }
         }
-        const float4 p = *(reinterpret_cast<const float4*>(partial + (t * n_used + s) * H) + c);
-        acc.x = __fadd_rn(acc.x, p.x);
-        acc.y = __fadd_rn(acc.y, p.y);
-        acc.z = __fadd_rn(acc.z, p.z);
-        acc.w = __fadd_rn(acc.w, p.w);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* base = reinterpret_cast<const float4*>(partial + t * n_used * H) + c;
+    // the counted picks in slot order, four rows requested at a time
+    for (uint32_t m = mask; m != 0u;) {
+        int s[4];
+        bool ok[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            ok[j] = m != 0u;
+            s[j] = ok[j] ? __ffs(m) - 1 : 0;
+            m &= m - 1u;   // (0 stays 0)
+        }
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = ok[j] ? base[(int64_t)s[j] * per_row] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (ok[j]) {
+                acc.x = __fadd_rn(acc.x, v[j].x);
+                acc.y = __fadd_rn(acc.y, v[j].y);
+                acc.z = __fadd_rn(acc.z, v[j].z);
+                acc.w = __fadd_rn(acc.w, v[j].w);
+            }
     }
     if (with_shared) {
         const float4 p = *(reinterpret_cast<const float4*>(partial + (T * n_used + t) * H) + c);

@@ -655,53 +655,58 @@ mx_quantize_tokens_kernel(const __nv_bfloat16* __restrict__ x, int64_t T, int K,
     }
 }
 
-// Second product's operand.  One warp per (expert-sorted row of mid inside a segment, 1024 columns), a lane per block:
-// codes to [term][row][K/2], scales into the segment's scale-factor chunks.
+// Second product's operand.  A warp per (expert-sorted row of mid, 1024 columns), a lane per block, over the rows that
+// exist: the placed picks (offsets[n_local] of them, known on the device only -- in the expert-parallel form most of the
+// P slots are empty) and the shared expert's rows P .. P + shared_rows - 1.  Rows outside every segment (experts handed
+// to the grouped GEMV) are skipped.  Codes to [term][row][K/2], scales into the segment's scale-factor chunks.
 __global__ void __launch_bounds__(256)
-mx_quantize_mid_kernel(const __half* __restrict__ mid, int64_t n_rows, int K, const PrefillSeg* __restrict__ segs,
-                       const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq, int64_t term_stride, uint8_t* __restrict__ sfb,
-                       uint32_t opaque_zero, uint32_t* __restrict__ error_word) {
+mx_quantize_mid_kernel(const __half* __restrict__ mid, const int32_t* __restrict__ offsets, int n_local, int64_t P, int64_t shared_rows, int K,
+                       const PrefillSeg* __restrict__ segs, const int32_t* __restrict__ n_segs_p, uint8_t* __restrict__ xq, int64_t term_stride,
+                       uint8_t* __restrict__ sfb, uint32_t opaque_zero, uint32_t* __restrict__ error_word) {
     const int parts = (K + 1023) >> 10;
-    const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int64_t row = w / parts;
-    const int part = (int)(w - row * parts);
     const int lane = threadIdx.x & 31;
-    if (row >= n_rows) return;
     const int n_kc = K / kStageK;
-    PrefillSeg seg;
-    const int si = find_segment(segs, n_segs_p[0], row, &seg);
-    if (si < 0) return;
-    const int blk = part * 32 + lane;
-    const bool live = blk < (K >> 5);
-    float v[32];
-    if (live) {
-        const uint4* in = reinterpret_cast<const uint4*>(mid + row * K + (int64_t)blk * 32);
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const uint4 raw = __ldg(in + q);
-            const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wds[j]));
-                v[8 * q + 2 * j] = f.x;
-                v[8 * q + 2 * j + 1] = f.y;
-            }
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; j++) v[j] = 0.0f;
-    }
-    uint4 codes[kTerms];
-    uint32_t e[kTerms];
-    mx_terms_of_block(v, opaque_zero, error_word, codes, e);
-    uint8_t* sf_row = sfb + mx_sf_offset(si, (int)(row - seg.row0), n_kc);
-#pragma unroll
-    for (int t = 0; t < kTerms; t++) {
-        const uint32_t sfw = mx_stage_scales(e[t], lane);
+    const int64_t placed = offsets[n_local], n_work = (placed + shared_rows) * parts;
+    const int n_segs = n_segs_p[0];
+    for (int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); w < n_work; w += (int64_t)gridDim.x * 8) {
+        const int64_t idx = w / parts;
+        const int part = (int)(w - idx * parts);
+        const int64_t row = idx < placed ? idx : P + (idx - placed);
+        PrefillSeg seg;
+        const int si = find_segment(segs, n_segs, row, &seg);
+        if (si < 0) continue;
+        const int blk = part * 32 + lane;
+        const bool live = blk < (K >> 5);
+        float v[32];
         if (live) {
-            *reinterpret_cast<uint4*>(xq + (int64_t)t * term_stride + row * (K >> 1) + (int64_t)blk * 16) = codes[t];
-            if ((lane & 3) == 0)
-                *reinterpret_cast<uint32_t*>(sf_row + (int64_t)(blk >> 2) * kSfbBytes + (int64_t)t * kSfbChunks * kSfChunk) = sfw;
+            const uint4* in = reinterpret_cast<const uint4*>(mid + row * K + (int64_t)blk * 32);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint4 raw = __ldg(in + q);
+                const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wds[j]));
+                    v[8 * q + 2 * j] = f.x;
+                    v[8 * q + 2 * j + 1] = f.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = 0.0f;
+        }
+        uint4 codes[kTerms];
+        uint32_t e[kTerms];
+        mx_terms_of_block(v, opaque_zero, error_word, codes, e);
+        uint8_t* sf_row = sfb + mx_sf_offset(si, (int)(row - seg.row0), n_kc);
+#pragma unroll
+        for (int t = 0; t < kTerms; t++) {
+            const uint32_t sfw = mx_stage_scales(e[t], lane);
+            if (live) {
+                *reinterpret_cast<uint4*>(xq + (int64_t)t * term_stride + row * (K >> 1) + (int64_t)blk * 16) = codes[t];
+                if ((lane & 3) == 0)
+                    *reinterpret_cast<uint32_t*>(sf_row + (int64_t)(blk >> 2) * kSfbBytes + (int64_t)t * kSfbChunks * kSfChunk) = sfw;
+            }
         }
     }
 }
@@ -829,8 +834,12 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
         if (int rc = launch_gemv_gate_up(v, c.sm_count, stream)) return rc;
     }
     // second product: K = ffn, rows = hidden, over the terms of mid
-    mx_quantize_mid_kernel<<<(unsigned)((quant_rows * ((cfg.ffn + 1023) >> 10) + 7) / 8), 256, 0, stream>>>(
-        c.mid, quant_rows, (int)cfg.ffn, ws->mx_segs, ws->n_segs, ws->xq, ws->mx_term_stride, ws->sfb, 0u, c.error_word);
+    {
+        const int64_t warps = quant_rows * ((cfg.ffn + 1023) >> 10);   // at most; the kernel walks the rows that exist
+        const unsigned blocks = (unsigned)std::min<int64_t>((warps + 7) / 8, (int64_t)c.sm_count * 64);
+        mx_quantize_mid_kernel<<<blocks, 256, 0, stream>>>(c.mid, c.offsets, c.n_local, P, c.with_shared ? c.T : 0, (int)cfg.ffn, ws->mx_segs,
+                                                           ws->n_segs, ws->xq, ws->mx_term_stride, ws->sfb, 0u, c.error_word);
+    }
     DSX_LAUNCHED();
     g.K = cfg.ffn; g.rows = cfg.hidden;
     g.sfa = c.sf_dn; g.sfa_slot_stride = c.sf_dn_stride; g.sfa_shared = c.sh_sf_dn;

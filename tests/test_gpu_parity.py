@@ -493,6 +493,43 @@ def test_activation_beyond_f16_sets_the_range_bit(torch_cuda, moe, oracle):
         layer.close()
 
 
+def test_set_weights_switches_kernel_family(torch_cuda, moe, oracle):
+    """A layer built on an MXFP4 store with tensor-core planes (block-scaled kernels, no f16 row copy allocated) is
+    re-pointed at a decode-only MXFP4 store and then at the planes again: the same batch must meet the oracle each
+    time (the f16-operand kernels' row buffer and the tensor maps follow the store), and a 96-token batch must take
+    the kernel family the bound store calls for."""
+    torch = torch_cuda
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import MoeConfig, RouterConfig
+    cfg = MoeConfig(hidden=512, ffn=256, shared_ffn=256,
+                    router=RouterConfig(n_expert=32, n_used=4, n_group=1, topk_group=1, score_fn=1, route_scale=2.5))
+    w = synth.make_layer(cfg, 4)
+    T = 300
+    planes = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, w["gate"], w["up"], w["down"])
+    planes_sh = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"])
+    plain = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.ffn, w["gate"], w["up"], w["down"], decode_only=True)
+    plain_sh = moe.RoutedExpertWeights.from_host(cfg.fmt, cfg.hidden, cfg.shared_ffn, w["shared_gate"], w["shared_up"], w["shared_down"],
+                                                 decode_only=True)
+    rw, rb = torch.from_numpy(w["router_w"]).cuda(), torch.from_numpy(w["router_bias"]).cuda()
+    layer = moe.MoeLayer(cfg, planes, planes_sh, rw, rb, max_tokens=T)
+    xb = synth.make_tokens(cfg, 4, T)
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+    shared = tuple((w[f"shared_{n}"][0][0], w[f"shared_{n}"][1][0]) for n in ("gate", "up", "down"))
+    outs = []
+    for routed, sh in ((planes, planes_sh), (plain, plain_sh), (planes, planes_sh)):
+        layer.set_weights(routed, sh, rw, rb)
+        out = layer.forward(x).float().cpu().numpy()
+        assert layer.check() == 0
+        r = layer.routing(T)
+        ref = oracle.moe_layer_f32(cfg.fmt, synth.bf16_bits_to_f32(xb), r["selected"], r["weights"], w["gate"], w["up"], w["down"],
+                                   shared=shared, clamp=cfg.clamp, n_expert=32)
+        assert rel_l2(out, ref) <= REL_L2_TOL
+        outs.append(out)
+    assert np.array_equal(outs[0], outs[2])                 # the same kernels, the same bits
+    assert not np.array_equal(outs[0], outs[1])             # f16 operands against three MXFP4 terms: close, not identical
+    layer.close()
+
+
 def test_forward_picks_split_sums_to_full(torch_cuda, moe, oracle):
     """Owner-of-a-subset form: two half stores, each returning its weighted partial
     sum, add up to the full layer (the reference's het-split property,
