@@ -465,7 +465,8 @@ int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n_used, i
 
 int dsx_reduce_partials(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared, const int32_t* selected,
                         int expert_lo, int n_local, void* out_bf16, dsx_stream_t stream) {
-    DSX_REQUIRE(T >= 0 && n_used >= 1 && hidden >= 4, "reduce_partials: %lld tokens, %d slots, %lld columns", (long long)T, n_used, (long long)hidden);
+    DSX_REQUIRE(T >= 0 && n_used >= 1 && n_used <= 32 && hidden >= 8, "reduce_partials: %lld tokens, %d slots, %lld columns", (long long)T, n_used,
+                (long long)hidden);
     if (T == 0) return DSX_OK;
     DSX_REQUIRE(partial && out_bf16, "reduce_partials: null argument");
     DSX_REQUIRE((((uintptr_t)partial | (uintptr_t)out_bf16) & 15) == 0, "reduce_partials: rows must be 16-byte aligned");

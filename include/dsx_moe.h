@@ -290,8 +290,9 @@ DSX_API int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n
  * b2_reduce_partials_zero, b2_fast_chain.hip:137-189) followed by VecAddInplace (src/ffn.rs:118-151):
  *   out[t, :] = 0 + partial[t*n_used + 0, :] + ... + partial[t*n_used + n_used-1, :]   (slot order, f32 adds)
  *             + partial[T*n_used + t, :]                                              (when with_shared != 0)
- * written as bf16 [T, hidden].  partial: f32 [T*n_used (+ T), hidden].  selected (optional, int32 [T, n_used]):
- * slots whose pick lies outside [expert_lo, expert_lo + n_local) are skipped (rows another owner computes). */
+ * written as bf16 [T, hidden].  partial: f32 [T*n_used (+ T), hidden], hidden a multiple of 8, both buffers 16-byte
+ * aligned, n_used <= 32.  selected (optional, int32 [T, n_used]): slots whose pick lies outside
+ * [expert_lo, expert_lo + n_local) are skipped (rows another owner computes). */
 DSX_API int dsx_reduce_partials(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared,
                                 const int32_t* selected, int expert_lo, int n_local, void* out_bf16, dsx_stream_t stream);
 /* moe_wi_upper_bound, het/dispatch.rs:444-454 */
