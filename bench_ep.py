@@ -95,8 +95,13 @@ def selfcheck(rank: int, world: int, use_peer: bool = True):
         if comm is not None:
             ep2 = ExpertParallelPeerMemory(E, comm, lambda xr, s, ww: part.forward_picks(xr, s, ww, expert_lo=lo, with_shared=False),
                                            lambda xr: part_sh.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True))
-            got2 = ep2.forward(x, sel.contiguous(), wt.contiguous()).float()
-            worst = max(worst, float((got2 - ref).norm() / ref.norm()))
+            raw2 = ep2.forward(x, sel.contiguous(), wt.contiguous())
+            worst = max(worst, float((raw2.float() - ref).norm() / ref.norm()))
+            # the same step with the owner's rows stored straight into the sources' slabs: the same bits
+            ep3 = ExpertParallelPeerMemory(E, comm, None, lambda xr: part_sh.forward_picks(xr, none_sel, torch.zeros_like(wt), expert_lo=lo, with_shared=True),
+                                           local_compute_to=lambda xr, s, ww, to: part.forward_picks_to(xr, s, ww, to, expert_lo=lo, with_shared=False))
+            raw3 = ep3.forward(x, sel.contiguous(), wt.contiguous())
+            assert torch.equal(raw3.view(torch.int16), raw2.view(torch.int16)), "rows stored through the table differ from the give-back pass"
     assert part.check() == 0 and part_sh.check() == 0 and full.check() == 0 and (comm is None or comm.check() == 0)
     dist.barrier()
     if comm is not None:
@@ -158,6 +163,9 @@ def run(args):
     sh_out = [torch.empty((T, H), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
     sh_turn = [0]
 
+    def local_compute_to(xr, s, ww, out_rows):
+        layer.forward_picks_to(xr, s, ww, out_rows, expert_lo=lo, with_shared=False)
+
     def shared_compute(xr):
         sh_turn[0] ^= 1
         return layer_sh.forward_picks(xr, none_sel, none_w, expert_lo=lo, with_shared=True, out=sh_out[sh_turn[0]])
@@ -166,7 +174,8 @@ def run(args):
     if comm is None:
         ep = ExpertParallelMoe(E, None, local_compute, shared_compute)
     else:
-        ep = ExpertParallelPeerMemory(E, comm, local_compute, shared_compute)
+        ep = ExpertParallelPeerMemory(E, comm, local_compute, shared_compute,
+                                      local_compute_to=None if os.environ.get("DSX_EP_GIVE_BACK_PASS") == "1" else local_compute_to)
     stats = {"received_rows": [], "fanout": []}
 
     norm_w = torch.ones((H,), device="cuda", dtype=torch.float32)
@@ -262,7 +271,8 @@ def run(args):
                                    f"({per} per GPU), shared expert replicated, {T} bf16 tokens per GPU; value counts tokens x layers",
                        "tokens_per_gpu": T, "layers": N_LAYERS, "parallelism": f"ep{world}",
                        "exchange": ("peer memory: rows, picks and weights stored straight into the owner's HBM over NVLink (CUDA IPC mapping), "
-                                    "slots by a device-side scan, two device-side barriers per layer, no host round trip"
+                                    "slots by a device-side scan, the owner's combine kernel stores its partial rows straight into the sources' HBM, "
+                                    "two device-side barriers per layer, no host round trip"
                                     if comm is not None else
                                     "per-peer NCCL send/recv batches (token rows + picks + weights once per owner rank; one partial row back)"),
                        "l2": "each layer streams the rank's expert shard (%.0f MB) and %d token rows: far above L2" % (routed.device_bytes / 1e6, T)},

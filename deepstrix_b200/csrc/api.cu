@@ -662,7 +662,7 @@ static bool scales_fit_f16(const dsx_expert_store* st) {
 // picks -> out.  expert_lo / n_local select the owned id range (0 / n_expert for a full layer).
 static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, const int32_t* selected, const float* weights,
                         int expert_lo, bool filter_picks, int with_shared, __nv_bfloat16* out, cudaStream_t stream,
-                        bool groups_ready = false, bool skip_combine = false) {
+                        bool groups_ready = false, bool skip_combine = false, __nv_bfloat16* const* out_rows = nullptr) {
     const dsx_moe_config& c = L->cfg;
     const int k = c.router.n_used, n_local = L->routed->n_slots;
     // split: the shared expert runs as a pass of its own (sh_layer) between this layer's kernels and the combine
@@ -677,7 +677,7 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
         if (skip_combine) return DSX_OK;
         StageTimer tm(L, DSX_STAGE_COMBINE, stream);
         return launch_combine(L->partial, T, k, c.hidden, (shared || split) ? 1 : 0, filter_picks ? selected : nullptr, expert_lo, n_local, out,
-                              stream);
+                              stream, out_rows);
     };
     // MXFP4 stores with tensor-core planes: block-scaled FP4 MMAs on the stored codes and scales (any E8M0 scale);
     // otherwise f16 operands expanded in shared memory (Q8_0; MXFP4 scales must then fit f16)
@@ -686,7 +686,7 @@ static int forward_core(dsx_moe_layer* L, const __nv_bfloat16* x, int64_t T, con
         (mx || (L->pf.xperm != nullptr && scales_fit_f16(L->routed) && (!shared || scales_fit_f16(L->shared))))) {
         PrefillCall pc{};
         pc.x = x; pc.T = T; pc.selected = selected; pc.route_w = weights; pc.expert_lo = expert_lo; pc.n_local = n_local;
-        pc.filter_picks = filter_picks; pc.with_shared = shared; pc.out = out;
+        pc.filter_picks = filter_picks; pc.with_shared = shared; pc.out = out; pc.out_rows = out_rows;
         pc.skip_combine = skip_combine || split;
         pc.hist = L->hist; pc.offsets = L->offsets; pc.perm = L->perm; pc.gs = L->gs;
         pc.mid = L->mid; pc.partial = L->partial; pc.error_word = L->error_word; pc.sm_count = L->sm_count;
@@ -797,6 +797,18 @@ int dsx_moe_layer_forward_picks(dsx_moe_layer* L, const void* x_bf16, int64_t T,
     L->last_logits = nullptr; L->last_selected = selected; L->last_weights = weights;
     return forward_core(L, (const __nv_bfloat16*)x_bf16, T, selected, weights, expert_lo, true, with_shared, (__nv_bfloat16*)out_bf16,
                         (cudaStream_t)stream);
+}
+
+int dsx_moe_layer_forward_picks_to(dsx_moe_layer* L, const void* x_bf16, int64_t T, const int32_t* selected, const float* weights,
+                                   int expert_lo, int with_shared, void* const* out_rows, dsx_stream_t stream) {
+    DSX_REQUIRE(L, "moe_layer_forward_picks_to: null layer");
+    DSX_REQUIRE(T >= 0 && T <= L->cfg.max_tokens, "moe_layer_forward_picks_to: %lld tokens, workspace holds %d", (long long)T, L->cfg.max_tokens);
+    if (T == 0) return DSX_OK;
+    DSX_REQUIRE(x_bf16 && selected && weights && out_rows, "moe_layer_forward_picks_to: null argument");
+    DSX_REQUIRE(L->cfg.hidden % 8 == 0, "moe_layer_forward_picks_to: hidden must be a multiple of 8");
+    L->last_logits = nullptr; L->last_selected = selected; L->last_weights = weights;
+    return forward_core(L, (const __nv_bfloat16*)x_bf16, T, selected, weights, expert_lo, true, with_shared, nullptr, (cudaStream_t)stream, false, false,
+                        (__nv_bfloat16* const*)out_rows);
 }
 
 // picks (global expert ids) -> local slots of this owner: remap[e] < 0 means slot -(remap[e] + 1) is held here,

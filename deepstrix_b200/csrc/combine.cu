@@ -13,15 +13,21 @@
 // through dsx_module_load_data / dsx_module_get_function, the way the reference embeds its kernels.
 // A thread requests four partial rows at a time (a rolled load-add loop issues one load per round trip), and which
 // picks count is decided once per warp: a warp lies inside one token's row whenever hidden is a multiple of 256.
+// out_rows (optional, [T] row pointers) replaces out: rows are stored where the table points, null entries skipped.
 extern "C" __global__ void __launch_bounds__(256)
 dsx_combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int64_t H, int with_shared,
-               const int32_t* __restrict__ selected, int expert_lo, int n_local, __nv_bfloat16* __restrict__ out) {
+               const int32_t* __restrict__ selected, int expert_lo, int n_local, __nv_bfloat16* __restrict__ out,
+               __nv_bfloat16* const* __restrict__ out_rows) {
     dsx::pdl_launch_dependents();
     dsx::pdl_wait();   // partial rows come from the down kernel
     const int64_t per_row = H >> 3, total = T * per_row;
     const bool warp_in_row = (per_row & 31) == 0;
     for (int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < total; gid += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = gid / per_row, c = gid - t * per_row;
+        // where the row goes: out[t], or (out_rows given) wherever the table says -- another GPU's memory included, which is how an
+        // expert-parallel owner hands its partial rows back without a copy pass -- and nowhere for a null entry
+        __nv_bfloat16* dst = out_rows != nullptr ? out_rows[t] : out + t * H;
+        if (dst == nullptr) continue;
         // bit s: pick s of the token counts (expert-parallel form: picks owned elsewhere were never computed)
         uint32_t mask = n_used >= 32 ? 0xFFFFFFFFu : (1u << n_used) - 1u;
         if (selected != nullptr) {
@@ -82,19 +88,19 @@ dsx_combine_kernel(const float* __restrict__ partial, int64_t T, int n_used, int
             const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
             ow[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
-        *(reinterpret_cast<uint4*>(out + t * H) + c) = o;
+        *(reinterpret_cast<uint4*>(dst) + c) = o;
     }
 }
 
 namespace dsx {
 
 int launch_combine(const float* partial, int64_t T, int n_used, int64_t H, int with_shared, const int32_t* selected,
-                   int expert_lo, int n_local, __nv_bfloat16* out, cudaStream_t stream) {
+                   int expert_lo, int n_local, __nv_bfloat16* out, cudaStream_t stream, __nv_bfloat16* const* out_rows) {
     DSX_REQUIRE(H % 8 == 0, "combine: hidden must be a multiple of 8");
     if (T == 0) return DSX_OK;
     const int64_t n = T * (H / 8);
     DSX_CUDA(launch_pdl(dsx_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, partial, T, n_used, H, with_shared,
-                        selected, expert_lo, n_local, out));
+                        selected, expert_lo, n_local, out, out_rows));
     DSX_LAUNCHED();
     return DSX_OK;
 }

@@ -280,6 +280,6 @@ bool gemv_small_batch_ok(int fmt, int64_t hidden, int64_t ffn, int64_t T);  // i
 
 // combine.cu
 int launch_combine(const float* partial, int64_t T, int n_used, int64_t H, int with_shared, const int32_t* selected,
-                   int expert_lo, int n_local, __nv_bfloat16* out, cudaStream_t stream);
+                   int expert_lo, int n_local, __nv_bfloat16* out, cudaStream_t stream, __nv_bfloat16* const* out_rows = nullptr);
 
 }  // namespace dsx

@@ -154,8 +154,11 @@ __global__ void ep_barrier_kernel(PeerTable peers, size_t flags_off, int world, 
 }
 
 // ---- owner: dense picks / weights for all world*cap slots (-1 / 0 beyond each source's count)
+// back_rows[slot]: where the owner's partial row of that slot belongs -- in the source rank's slab (null for unused slots):
+// an owner that stores its result rows through this table needs no give-back pass.
 __global__ void ep_prepare_kernel(const int32_t* __restrict__ meta, const int32_t* __restrict__ counts, int cap, int k, int64_t n_slots,
-                                  int32_t* __restrict__ sel, float* __restrict__ w) {
+                                  int32_t* __restrict__ sel, float* __restrict__ w, PeerTable peers, size_t back_off, int rank, int64_t H,
+                                  uint8_t** __restrict__ back_rows) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_slots * k) return;
     const int64_t slot = i / k;
@@ -164,6 +167,7 @@ __global__ void ep_prepare_kernel(const int32_t* __restrict__ meta, const int32_
     const bool valid = r < counts[s];
     sel[i] = valid ? meta[slot * 2 * k + j] : -1;
     w[i] = valid ? __int_as_float(meta[slot * 2 * k + k + j]) : 0.0f;
+    if (j == 0) back_rows[slot] = valid ? peers.slab[s] + back_off + ((size_t)rank * cap + r) * (size_t)H * 2 : nullptr;
 }
 
 // ---- owner: partial rows back to their sources
@@ -236,6 +240,7 @@ struct dsx_ep_comm {
     int32_t* slot_of = nullptr;        // [world][cap]
     int32_t* sel = nullptr;            // [world*cap][k]
     float* w = nullptr;                // [world*cap][k]
+    uint8_t** back_rows = nullptr;     // [world*cap]: destination of every slot's partial row in its source's slab (null: unused slot)
     uint32_t* error_word = nullptr;
     uint32_t epoch = 0;
     uint32_t barrier_polls = kBarrierPolls;   // polls (>= 100 ns each) before a barrier gives up
@@ -258,11 +263,12 @@ int dsx_ep_create(int world, int rank, int64_t cap, int64_t hidden, int n_used, 
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->slot_of, (size_t)world * cap * 4);
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->sel, (size_t)world * cap * n_used * 4);
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->w, (size_t)world * cap * n_used * 4);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&c->back_rows, (size_t)world * cap * sizeof(uint8_t*));
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->error_word, 256);
     if (e == cudaSuccess) e = cudaMemset(c->error_word, 0, 256);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
-        cudaFree(c->slab); cudaFree(c->slot_of); cudaFree(c->sel); cudaFree(c->w); cudaFree(c->error_word);
+        cudaFree(c->slab); cudaFree(c->slot_of); cudaFree(c->sel); cudaFree(c->w); cudaFree(c->back_rows); cudaFree(c->error_word);
         delete c;
         return set_error((int)e, "ep_create: allocation of %zu bytes failed: %s", slab_layout(world, cap, hidden, n_used).total, cudaGetErrorString(e));
     }
@@ -276,7 +282,7 @@ int dsx_ep_destroy(dsx_ep_comm* c) {
     cudaDeviceSynchronize();
     for (int p = 0; p < c->world; p++)
         if (c->opened[p]) cudaIpcCloseMemHandle(c->peers.slab[p]);
-    cudaFree(c->slab); cudaFree(c->slot_of); cudaFree(c->sel); cudaFree(c->w); cudaFree(c->error_word);
+    cudaFree(c->slab); cudaFree(c->slot_of); cudaFree(c->sel); cudaFree(c->w); cudaFree(c->back_rows); cudaFree(c->error_word);
     delete c;
     return DSX_OK;
 }
@@ -365,12 +371,21 @@ int dsx_ep_prepare(dsx_ep_comm* c, const void** x_rows, const int32_t** selected
     const int64_t n = slots * c->k;
     ep_prepare_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream_>>>(
         reinterpret_cast<const int32_t*>(c->slab + c->lay.recv_meta), reinterpret_cast<const int32_t*>(c->slab + c->lay.counts), (int)c->cap,
-        c->k, slots, c->sel, c->w);
+        c->k, slots, c->sel, c->w, c->peers, c->lay.back, c->rank, c->H, c->back_rows);
     DSX_LAUNCHED();
     if (x_rows) *x_rows = c->slab + c->lay.recv_x;
     if (selected) *selected = c->sel;
     if (weights) *weights = c->w;
     if (n_slots) *n_slots = slots;
+    return DSX_OK;
+}
+
+// After dsx_ep_prepare: [world*cap] row pointers, entry i = where slot i's partial row belongs in its source rank's slab (null
+// for an unused slot).  An owner that writes its result rows through this table (dsx_moe_layer_forward_picks_to) has given
+// them back already and skips dsx_ep_give_back.
+int dsx_ep_back_rows(dsx_ep_comm* c, void* const** rows) {
+    DSX_REQUIRE(c && rows, "ep_back_rows: null argument");
+    *rows = reinterpret_cast<void* const*>(c->back_rows);
     return DSX_OK;
 }
 

@@ -56,6 +56,7 @@ struct PrefillCall {
     bool filter_picks, with_shared;
     bool skip_combine;         // stop after the partial rows (the caller reduces them)
     __nv_bfloat16* out;
+    __nv_bfloat16* const* out_rows;   // optional: where each row of the result goes instead of out (null entries: nowhere)
     int32_t *hist, *offsets, *perm;
     GroupScratch gs;
     __half* mid;

@@ -853,7 +853,7 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     }
     if (c.skip_combine) return DSX_OK;   // the caller adds another pass before it reduces the partial rows
     return launch_combine(c.partial, c.T, c.n_used, cfg.hidden, c.with_shared ? 1 : 0, c.filter_picks ? c.selected : nullptr, c.expert_lo,
-                          c.n_local, c.out, stream);
+                          c.n_local, c.out, stream, c.out_rows);
 }
 
 }  // namespace dsx

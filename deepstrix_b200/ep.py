@@ -225,6 +225,13 @@ class PeerMemoryComm:
         rows = _as_tensor(px.value, (slots, self.hidden), "<i2", torch.bfloat16)
         return rows, _as_tensor(ps.value, (slots, self.k), "<i4"), _as_tensor(pw.value, (slots, self.k), "<f4")
 
+    def back_rows(self) -> torch.Tensor:
+        """After prepare(): int64 [world*cap] addresses, entry i = where slot i's partial row belongs in its source rank's slab
+        (0 for an unused slot); for ``MoeLayer.forward_picks_to``."""
+        p = self._C.c_void_p()
+        self._moe._check(self._moe.lib().dsx_ep_back_rows(self._h, self._C.byref(p)))
+        return _as_tensor(p.value, (self.world * self.cap,), "<i8")
+
     def give_back(self, part):
         assert part.dtype == torch.bfloat16 and part.is_contiguous() and part.shape == (self.world * self.cap, self.hidden)
         self._moe._check(self._moe.lib().dsx_ep_give_back(self._h, self._moe._dptr(part), self._moe._stream()))
@@ -273,9 +280,12 @@ class ExpertParallelPeerMemory:
     stream at the same time as local_compute: the two callables must not share a ``MoeLayer`` (a layer's
     workspace serves one call at a time)."""
 
-    def __init__(self, n_expert: int, comm: PeerMemoryComm, local_compute: Callable, shared_compute: Callable = None):
+    def __init__(self, n_expert: int, comm: PeerMemoryComm, local_compute: Callable, shared_compute: Callable = None,
+                 local_compute_to: Callable = None):
+        """local_compute_to(rows, selected, weights, out_rows), when given, replaces local_compute + give_back: the owner's layer
+        stores every partial row straight into its source rank's slab (``MoeLayer.forward_picks_to``)."""
         self.n_expert, self.comm = n_expert, comm
-        self.local_compute, self.shared_compute = local_compute, shared_compute
+        self.local_compute, self.shared_compute, self.local_compute_to = local_compute, shared_compute, local_compute_to
         self._side = None
         self.profile = False
         self._events = []
@@ -301,9 +311,13 @@ class ExpertParallelPeerMemory:
         c.barrier()
         self._mark("dispatch_and_barrier")
         rows, sel, w = c.prepare()
-        part = self.local_compute(rows, sel, w)
-        self._mark("owned_experts")
-        c.give_back(part)
+        if self.local_compute_to is not None:
+            self.local_compute_to(rows, sel, w, c.back_rows())   # the result rows cross NVLink as they are produced
+            self._mark("owned_experts")
+        else:
+            part = self.local_compute(rows, sel, w)
+            self._mark("owned_experts")
+            c.give_back(part)
         c.barrier()
         if sh is not None:
             torch.cuda.current_stream().wait_stream(self._side)

@@ -453,6 +453,15 @@ class MoeLayer:
                                                  expert_lo, 1 if with_shared else 0, _dptr(out), _stream()))
         return out
 
+    def forward_picks_to(self, x, selected, weights, out_rows, expert_lo: int = 0, with_shared: bool = True):
+        """forward_picks whose result rows are stored through ``out_rows`` (int64 CUDA tensor of T row addresses, 0 = the row is
+        wanted nowhere) instead of into one buffer -- an expert-parallel owner passes ``PeerMemoryComm.back_rows()`` and its
+        partial rows land in their source ranks' memory as they are produced."""
+        assert selected.dtype == torch.int32 and weights.dtype == torch.float32 and out_rows.dtype == torch.int64 and out_rows.is_cuda
+        assert out_rows.numel() >= x.shape[0]
+        _check(lib().dsx_moe_layer_forward_picks_to(self._h, _dptr(x), C.c_int64(x.shape[0]), _dptr(selected), _dptr(weights),
+                                                    expert_lo, 1 if with_shared else 0, _dptr(out_rows), _stream()))
+
     def forward_remap(self, x, selected, weights, remap, with_shared: bool = True, out=None):
         """Owner-side forward with the reference's ownership table (het/weights.rs:1357-1381): remap int32 [n_expert],
         negative entries -(slot + 1) are the experts this store holds."""

@@ -347,6 +347,12 @@ DSX_API int dsx_moe_layer_forward_host(dsx_moe_layer* layer, const void* x_bf16_
 DSX_API int dsx_moe_layer_forward_picks(dsx_moe_layer* layer, const void* x_bf16, int64_t T,
                                         const int32_t* selected, const float* weights, int expert_lo,
                                         int with_shared, void* out_bf16, dsx_stream_t stream);
+/* dsx_moe_layer_forward_picks with the result rows stored through a table instead of into one buffer: out_rows is a
+ * device array of T row pointers (bf16 [hidden] each, 16-byte aligned, possibly in another GPU's mapped memory); a
+ * NULL entry means the row is wanted nowhere and is not computed further.  hidden must be a multiple of 8. */
+DSX_API int dsx_moe_layer_forward_picks_to(dsx_moe_layer* layer, const void* x_bf16, int64_t T, const int32_t* selected,
+                                           const float* weights, int expert_lo, int with_shared, void* const* out_rows,
+                                           dsx_stream_t stream);
 
 /* The same with the reference's ownership table instead of a contiguous id range (encode_igpu_remap,
  * het/weights.rs:1357-1381; kernels/moe_group_builder.hip:53-123; docs/v41/REMOTE_EXPERTS.md:204-211):
@@ -480,6 +486,12 @@ DSX_API int dsx_ep_set_barrier_polls(dsx_ep_comm* comm, uint32_t polls);
 DSX_API int dsx_ep_prepare(dsx_ep_comm* comm, const void** x_rows, const int32_t** selected, const float** weights,
                            int64_t* n_slots, dsx_stream_t stream);
 /* partial_rows [world*cap, hidden] bf16 (row i: weighted sum of slot i's owned picks) back to their sources. */
+/* After dsx_ep_prepare: a device array of n_slots row pointers, entry i = where slot i's partial row belongs in its
+ * source rank's slab (NULL for an unused slot).  An owner that lets its layer store the result rows through this table
+ * (dsx_moe_layer_forward_picks_to) has handed them back -- the rows cross NVLink as the combine kernel produces them --
+ * and skips dsx_ep_give_back.  (The reference's executor writes its partial rows into the reply frame it sends,
+ * het/remote_experts.rs:7428-7442; there is no separate copy there either.) */
+DSX_API int dsx_ep_back_rows(dsx_ep_comm* comm, void* const** rows);
 DSX_API int dsx_ep_give_back(dsx_ep_comm* comm, const void* partial_rows_bf16, dsx_stream_t stream);
 /* out[t] = shared[t] (or 0 when NULL) + the partial rows of token t in rank order, f32 adds, bf16 result. */
 DSX_API int dsx_ep_sum(dsx_ep_comm* comm, const void* shared_bf16, int64_t T, void* out_bf16, dsx_stream_t stream);

@@ -36,15 +36,21 @@ def test_peer_memory_exchange_matches_unsharded_layer(world, T):
     for c in comms:
         c.connect_local(comms)
     outs = []
-    for rep in range(2):   # twice: the slabs are reused from step to step
+    for rep in range(3):   # several steps: the slabs are reused from step to step
         for r in range(world):
             comms[r].dispatch(xs[r], sels[r], wts[r], E)
-        given = []
         for r in range(world):
             rows, sel, wt = comms[r].prepare()
-            part = parts[r].forward_picks(rows, sel, wt, expert_lo=r * per, with_shared=False)
-            comms[r].give_back(part)
-            given.append(part)
+            if rep == 2:   # the owner's layer stores its rows straight into the sources' slabs: no give-back pass
+                table = comms[r].back_rows()
+                counts = comms[r].counts().cpu().numpy()
+                addr = table.cpu().numpy().reshape(world, T)
+                for src in range(world):   # an address for every received row, none for the unused slots
+                    assert (addr[src, :counts[src]] != 0).all() and (addr[src, counts[src]:] == 0).all()
+                parts[r].forward_picks_to(rows, sel, wt, table, expert_lo=r * per, with_shared=False)
+            else:
+                part = parts[r].forward_picks(rows, sel, wt, expert_lo=r * per, with_shared=False)
+                comms[r].give_back(part)
         none_sel = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
         res = []
         for r in range(world):
@@ -58,6 +64,7 @@ def test_peer_memory_exchange_matches_unsharded_layer(world, T):
         err = np.linalg.norm(outs[0][r] - ref) / np.linalg.norm(ref)
         assert err < 1e-2, (r, err)
         assert np.array_equal(outs[0][r], outs[1][r])
+        assert np.array_equal(outs[0][r], outs[2][r])      # rows stored through the table: the same bits
     # counts: tokens of source s with at least one pick owned by rank d
     for d in range(world):
         got = comms[d].counts().cpu().numpy()

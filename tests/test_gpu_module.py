@@ -32,7 +32,7 @@ def test_module_load_get_function_launch_matches_linked_kernel():
     out = torch.zeros((T, H), dtype=torch.bfloat16, device="cuda")
     n = T * (H // 4)
     args = [C.c_void_p(partial.data_ptr()), C.c_int64(T), C.c_int(k), C.c_int64(H), C.c_int(1), C.c_void_p(0), C.c_int(0), C.c_int(0),
-            C.c_void_p(out.data_ptr())]
+            C.c_void_p(out.data_ptr()), C.c_void_p(0)]              # ..., out, out_rows (no row table)
     before = moe.launch_count()
     moe.Module.launch_raw(fn, ((n + 255) // 256, 1, 1), (256, 1, 1), 0, args)
     torch.cuda.synchronize()
@@ -81,7 +81,7 @@ def test_graph_kernel_node_set_params_repoints_a_captured_launch():
 
     def args_for(i):
         return [C.c_void_p(parts[i].data_ptr()), C.c_int64(T), C.c_int(k), C.c_int64(H), C.c_int(1), C.c_void_p(0), C.c_int(0), C.c_int(0),
-                C.c_void_p(outs[i].data_ptr())]
+                C.c_void_p(outs[i].data_ptr()), C.c_void_p(0)]       # ..., out, out_rows (no row table)
     stream = torch.cuda.Stream()
     torch.cuda.synchronize()
     with torch.cuda.stream(stream):
