@@ -463,6 +463,17 @@ int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n_used, i
                                      (cudaStream_t)stream);
 }
 
+int dsx_reduce_partials_to(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared, const int32_t* selected,
+                           int expert_lo, int n_local, void* const* out_rows, dsx_stream_t stream) {
+    DSX_REQUIRE(T >= 0 && n_used >= 1 && n_used <= 32 && hidden >= 8, "reduce_partials_to: %lld tokens, %d slots, %lld columns", (long long)T, n_used,
+                (long long)hidden);
+    if (T == 0) return DSX_OK;
+    DSX_REQUIRE(partial && out_rows, "reduce_partials_to: null argument");
+    DSX_REQUIRE(((uintptr_t)partial & 15) == 0, "reduce_partials_to: rows must be 16-byte aligned");
+    return launch_combine(partial, T, n_used, hidden, with_shared ? 1 : 0, selected, expert_lo, n_local, nullptr, (cudaStream_t)stream,
+                          (__nv_bfloat16* const*)out_rows);
+}
+
 int dsx_reduce_partials(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared, const int32_t* selected,
                         int expert_lo, int n_local, void* out_bf16, dsx_stream_t stream) {
     DSX_REQUIRE(T >= 0 && n_used >= 1 && n_used <= 32 && hidden >= 8, "reduce_partials: %lld tokens, %d slots, %lld columns", (long long)T, n_used,

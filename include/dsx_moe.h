@@ -295,6 +295,10 @@ DSX_API int dsx_moe_group_build_static(const int32_t* selected, int64_t T, int n
  * [expert_lo, expert_lo + n_local) are skipped (rows another owner computes). */
 DSX_API int dsx_reduce_partials(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared,
                                 const int32_t* selected, int expert_lo, int n_local, void* out_bf16, dsx_stream_t stream);
+/* The same reduction with the result rows stored through a table: out_rows is a device array of T row pointers (bf16
+ * [hidden] each, 16-byte aligned, possibly in another GPU's mapped memory); rows with a NULL entry are skipped. */
+DSX_API int dsx_reduce_partials_to(const float* partial, int64_t T, int n_used, int64_t hidden, int with_shared,
+                                   const int32_t* selected, int expert_lo, int n_local, void* const* out_rows, dsx_stream_t stream);
 /* moe_wi_upper_bound, het/dispatch.rs:444-454 */
 DSX_API uint32_t dsx_wi_upper_bound(uint64_t members, uint32_t groups, uint32_t chunk, uint64_t cap);
 

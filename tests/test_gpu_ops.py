@@ -65,3 +65,42 @@ def test_vec_add_inplace_and_gather(torch_cuda, moe, n, offset):
     g = moe.VecAddInplace.launch_gather(db[offset:], torch.from_numpy(idx).cuda()).cpu().numpy()
     want = np.where(idx >= 0, b[offset:][np.maximum(idx, 0)], -np.inf).astype(np.float32)
     assert np.array_equal(g, want)
+
+
+@pytest.mark.parametrize("T,k,H", [(5, 6, 1032), (33, 8, 2048), (3, 16, 264)])
+def test_reduce_partials_owner_filter_and_row_table(torch_cuda, moe, T, k, H):
+    """The slot-order reduction with the owner filter (picks outside [lo, lo + n) were never computed: skipped), for
+    widths where a warp lies inside one token's row (multiples of 256) and where it does not; and the same through a
+    table of row pointers with some rows wanted nowhere."""
+    torch = torch_cuda
+    import ctypes as C
+    rng = np.random.default_rng(T * H)
+    partial = rng.standard_normal((T * k + T, H)).astype(np.float32)
+    sel = rng.integers(0, 32, size=(T, k)).astype(np.int32)
+    sel[0, :] = 31                                          # a token with no pick in the range
+    lo, n = 4, 12
+    want = np.zeros((T, H), np.float32)
+    for t in range(T):
+        acc = np.zeros(H, np.float32)
+        for s in range(k):
+            if lo <= sel[t, s] < lo + n:
+                acc = (acc + partial[t * k + s]).astype(np.float32)
+        want[t] = (acc + partial[T * k + t]).astype(np.float32)
+    want_bf16 = torch.from_numpy(want).to(torch.bfloat16)
+    dp, ds = torch.from_numpy(partial).cuda(), torch.from_numpy(sel).cuda()
+    got = moe.reduce_partials(dp, T, k, with_shared=True, selected=ds, expert_lo=lo, n_local=n)
+    assert torch.equal(got.cpu(), want_bf16)
+    # through a row table: even tokens into a scattered buffer, odd tokens nowhere
+    buf = torch.full((2 * T, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+    table = torch.zeros((T,), dtype=torch.int64, device="cuda")
+    for t in range(0, T, 2):
+        table[t] = buf[2 * T - 1 - t].data_ptr()
+    moe._check(moe.lib().dsx_reduce_partials_to(C.c_void_p(dp.data_ptr()), C.c_int64(T), k, C.c_int64(H), 1, C.c_void_p(ds.data_ptr()), lo, n,
+                                               C.c_void_p(table.data_ptr()), moe._stream()))
+    out = buf.cpu()
+    for t in range(T):
+        row = out[2 * T - 1 - t]
+        if t % 2 == 0:
+            assert torch.equal(row, want_bf16[t])
+        else:
+            assert torch.isnan(row.float()).all()
