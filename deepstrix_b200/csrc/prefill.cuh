@@ -40,6 +40,8 @@ struct PrefillWorkspace {
     int32_t* mx_inv_perm = nullptr; // [max_tokens * n_used]: expert-sorted position of every pick (-1: not placed here)
     PrefillSeg* mx_segs = nullptr;  // segments of at most 192 rows
     int32_t mx_seg_cap = 0;
+    int mx_pair_mode = -1;          // the block-scaled GEMMs as CTA pairs: -1 decided per call, 0 never, 1 always
+    CUtensorMap tmap_xq2[3], tmap_mq2[3]; // the same for CTA pairs: boxes of 32 / 64 / 96 rows (half a segment per CTA)
     CUtensorMap tmap_xq[3], tmap_mq[3];   // xq as (bytes, row, term) for K = hidden / K = ffn, boxes of 64 / 128 / 192 rows
     CUtensorMap tmap_km_gu[2], tmap_km_dn[2];            // K-major code planes; index 0 routed, 1 shared
     const void* mapped_km_gu[2] = {nullptr, nullptr};

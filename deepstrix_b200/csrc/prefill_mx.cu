@@ -10,7 +10,7 @@
 //
 // Operands.  The weights are E2M1 codes with one E8M0 scale per 32: exactly what kind::mxf4 multiplies,
 // so they go from HBM to shared memory by TMA (K-major rows, 64-byte swizzle) and their scales to tensor
-// memory by tcgen05.cp, untouched.  The other operand of kind::mxf4 is FP4 too, and one FP4 value per
+// memory, untouched.  The other operand of kind::mxf4 is FP4 too, and one FP4 value per
 // activation is far too coarse (rel-L2 0.2 on the layer).  So an activation row x is written as a SUM of
 // three MXFP4 rows, x ~ t1 + t2 + t3: t1 = x rounded to E2M1 with a power-of-two scale per 32, t2 the
 // same rounding of the residual x - t1 with its own scales, t3 of x - t1 - t2 (mx_terms_of_block;
@@ -21,25 +21,28 @@
 // Tiling.  Expert-sorted rows are cut into segments of at most 192 rows of one expert, and a tile = (segment, 256
 // weight rows) = two M = 128 accumulators that share the segment's rows as N (first product: 128 gate rows and the
 // 128 up rows of the same outputs, so that a tensor-memory lane holds gate and up of one output row).  Tensor
-// memory: 2 x 192 accumulator columns, 8 columns of weight scales, 2 x 24 of activation scales.  A pipeline stage is
+// memory: 2 x 192 accumulator columns and four scale slots of 32 columns, one per ring stage.  A pipeline stage is
 // 128 reduction columns: 16 KB of weight codes (one TMA box), up to 3 x 12 KB of activation terms (one TMA box of
-// 64, 128 or 192 rows x 3 terms), 1 KB + 3 KB of scale chunks, all arriving on one mbarrier; 4 stages.  Two warps
-// issue, one accumulator each: each copies its accumulator's weight scales and its own copy of the activation
-// scales to tensor memory and issues 2 (k steps of 64) x 3 (terms) MMAs per stage.
-// Two limits shape the tile.  (1) L2 -> shared-memory traffic: the operands of a stage arrive at no more than ~8.5 TB/s
-// over the device, which a tall tile (many weight rows per activation row) serves best.  (2) Shared memory's 128
-// bytes per clock, which the tensor core's operand reads share with those fills: an M = 128, K = 64 MMA over N rows
-// reads 4 KB of weights and 32 N bytes of terms in N / 2 clocks, i.e. 8192 / N + 64 bytes per clock, which a wide N
-// serves best.  The first shape of this kernel (512 weight rows x 96 rows, four accumulators) had the fewest fill
-// bytes but needed 149 + 46 bytes of shared-memory bandwidth per MMA clock: shared memory was 96 % busy, the tensor
-// pipe 60 %, and the fills reached only 7.1 TB/s.  This shape needs 128 + 52 at N = 128 (107 + 45 at N = 192), moves
-// 17 % more bytes and is bound by limit (1) instead: 8.1 to 8.6 TB/s measured, tensor pipe 57 to 62 % busy, 3 to 6 %
-// faster on the layers measured.  CTA pairs (cta_group::2, each CTA holding half of a segment's rows) were built
-// and measured as well: bit-identical results, 5 % slower (each tensor core fetches the other CTA's half again for
-// every accumulator that uses it).
-// Warp roles: one producer thread, two MMA threads, 12 epilogue warps that read the accumulators
-// (tcgen05.ld), apply clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows
-// (f32); a warp's last 32 columns are read whole and tensor memory handed back before their arithmetic runs.
+// 64, 128 or 192 rows x 3 terms), 1 KB + 3 KB of scale chunks, all arriving on one mbarrier; 4 stages.
+// Warp roles (20 warps; register counts redistributed per warp group with setmaxnreg): one producer thread; two
+// MMA threads, one accumulator each, 2 (k steps of 64) x 3 (terms) MMAs per stage; four scale warps, one per lane
+// quarter of tensor memory, that move a landed stage's scale chunks from shared memory into the stage's scale slot
+// (ld.shared + tcgen05.st -- the tensor core's own copy instruction, tcgen05.cp, runs in the MMA queue and held the
+// MMAs up for 0.4 of 3.0 ms on the 8192-token layer); 12 epilogue warps that read the accumulators (tcgen05.ld), apply
+// clamp + SwiGLU + routing weight and store mid (f16), or store the per-pick partial rows (f32): the second half of
+// a warp's columns is read whole and tensor memory handed back before their arithmetic and stores run.
+// CTA pairs.  From 96 rows per expert on (per call) the kernel runs as clusters of two CTAs with cta_group::2 MMAs:
+// a pair takes two neighbouring tiles of one segment, every MMA spans both (M = 256), and each CTA loads only half
+// of the segment's rows.  Each CTA's loads count on its own barrier; the scale warps of both report to the even CTA,
+// whose two MMA threads issue for the pair; commits arrive in both.  No load is broadcast.
+// What bounds it.  (1) L2 -> shared-memory traffic, which a tall tile (many weight rows per activation row) and the
+// pair's halved activation rows reduce.  (2) Shared memory's 128 bytes per clock, which the tensor core's operand
+// reads share with those fills: an M = 128, K = 64 MMA over N rows reads 4 KB of weights and 32 N bytes of terms in
+// N / 2 clocks, i.e. 8192 / N + 64 bytes per clock, which a wide N serves best.  The first shape of this kernel (512
+// weight rows x 96 rows, four accumulators) needed 149 + 46 bytes per MMA clock: shared memory was 96 % busy, the
+// tensor pipe 60 %.  (3) The tensor-core queue itself: MMAs, plus whatever else is put into it.  (4) The part of the
+// epilogue that runs before tensor memory is handed back (the accumulators fill it: no double buffer): with the
+// epilogue taken out the 8192-token layer is 0.46 ms shorter.
 // Every wait is bounded; on a timeout the block raises an abort flag, all roles drain, tensor memory
 // is freed and bit 2 of the layer's error word is set.
 #include <algorithm>
@@ -51,8 +54,10 @@ namespace {
 
 constexpr int kEpiWarps = 12;
 constexpr int kMmaWarps = 2;                  // issuing warps: each owns one of the tile's two accumulators (one warp for both: 9 % slower)
-constexpr int kEpiWarp0 = 1 + kMmaWarps;
+constexpr int kScWarp0 = 4;                   // four warps (one per lane quarter of tensor memory) carry the scales
+constexpr int kEpiWarp0 = 8;                  // warp 3 has no role: roles start on warp-group boundaries
 constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;
+static_assert(1 + kMmaWarps <= kScWarp0, "producer and issuing warps fit below the scale warps");
 constexpr int kAccs = 2;                      // M = 128 accumulators per tile (256 weight rows), one per issuing warp
 constexpr int kSegRows = 192;                 // most rows of a segment (MMA N)
 constexpr int kBRows = 192;                   // rows of a term plane in shared memory
@@ -63,7 +68,6 @@ constexpr int kRowBytes = kStageK / 2;        // packed bytes per row and stage:
 constexpr int kStages = 4;
 constexpr int kABytes = kAccs * 128 * kRowBytes;         // 16384
 constexpr int kBTermBytes = kBRows * kRowBytes;          // 12288
-constexpr int kBBoxBytes = kBoxRows * kRowBytes;         // 4096
 constexpr int kBBytes = kTerms * kBTermBytes;            // 36864
 constexpr int kSfChunk = 512;                            // 128 rows x 4 scale blocks
 constexpr int kSfbChunks = (kSegRows + 127) / 128;       // chunks per term: rows 0..127, 128..191
@@ -74,14 +78,17 @@ constexpr int kSmemB = kSmemA + kStages * kABytes;
 constexpr int kSmemSfa = kSmemB + kStages * kBBytes;
 constexpr int kSmemSfb = kSmemSfa + kStages * kSfaBytes;
 constexpr int kSmemBar = kSmemSfb + kStages * kSfbBytes;
-constexpr int kNumBars = 2 * kStages + 2;
+constexpr int kNumBars = 3 * kStages + 2;
 constexpr int kSmemMisc = kSmemBar + kNumBars * 8;
 constexpr int kSmemTotal = kSmemMisc + 16 + 1024;        // + alignment slack
 static_assert(kSmemTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
 // tensor-memory columns
 constexpr uint32_t kSfaCol = kAccs * kSegRows;    // accumulator h at column h * kSegRows; then 4 columns of weight scales per accumulator
-constexpr uint32_t kSfbCol = kSfaCol + 4 * kAccs; // 4 columns per term and chunk of 128 rows, one copy per issuing warp
-static_assert(kSfbCol + 4 * kSfbChunks * kTerms * kMmaWarps <= 512, "tensor memory holds 512 columns");
+// scale slot of ring stage s: kScSlot columns at kSfaCol + s * kScSlot = 4 per accumulator (weight scales), then 4 per
+// term and chunk of 128 rows (activation scales) -- the order in which a stage's chunks lie in shared memory
+constexpr uint32_t kScSlot = 4 * kAccs + 4 * kSfbChunks * kTerms;
+static_assert(kSfaCol + kStages * kScSlot <= 512, "tensor memory holds 512 columns");
+static_assert(kScSlot == 32 && kSfaBytes + kSfbBytes == 32 * 128, "a scale warp moves a stage's scales as 32 registers per lane");
 static_assert(kBTermBytes % 512 == 0, "a term plane must start on a swizzle-atom boundary");
 static_assert(kAccs % kMmaWarps == 0, "accumulators divide evenly over the issuing warps");
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -89,6 +96,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 #define DSX_MX_SMALL_MAX 8
 #endif
 constexpr int kMxSmallMax = DSX_MX_SMALL_MAX;
+constexpr int kPairFromRows = 96;             // average rows per expert from which the GEMMs run as CTA pairs
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -144,11 +152,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// 512 bytes of scale factors (32 rows of 16 bytes) from shared memory into 4 tensor-memory columns, the
-// same 16 bytes in all four lane quarters.
-__device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 // D[128 x N] (+)= A[128 x 64] . B[N x 64]^T, E2M1 operands, one E8M0 scale per 32 columns of either operand;
 // the descriptors are given as low words (the high word -- stride, version, swizzle -- is common to every
 // operand tile): the issuing thread is bound by its own scalar instructions, a 32-bit add per operand is the least.
@@ -172,6 +175,54 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr));
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// lane r of the warp writes 32 columns of its tensor-memory lane
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+          "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+          "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+// ---- CTA pairs (cta_group::2): the even CTA of a cluster of two issues the MMAs for both
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t cta) {   // the same shared-memory offset in another CTA of the cluster
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(cta));
+    return r;
+}
+// Arrival on a barrier of the other CTA of a pair.  Relaxed on purpose: what the arrival reports (tensor-memory stores
+// this warp has waited for, TMA bytes whose barrier it has seen complete) is finished before the instruction issues, and
+// the default .release form at cluster scope held the issuing thread for about a microsecond per arrival, which bounded
+// a whole pipeline stage when one thread forwarded an arrival per stage.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {   // arrives on one barrier, of either CTA of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+// D[256 x N] (+)= A[256 x 64] . B[N x 64]^T over a CTA pair: rows 0..127 of A and D belong to the even CTA, 128..255 to the
+// odd one; each CTA holds N / 2 rows of B.
+__device__ __forceinline__ void tc_mma_mxf4_lo_pair(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t sfa,
+                                                    uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %7, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %4, [%5], [%6], p;\n\t}"
+        ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
 
 // K-major operand tile with 64-byte rows and 64-byte swizzle: 8-row groups of 512 bytes.
 __device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
@@ -182,18 +233,10 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
     d |= (uint64_t)4 << 61;                         // 64-byte swizzle
     return d;
 }
-// Unswizzled 32 rows x 16 bytes (one scale-factor chunk): 8-row groups of 128 bytes.
-__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(128u >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    return d;
-}
 // kind::mxf4: E2M1 x E2M1 -> f32, E8M0 scales, both operands K-major, M = 128, K = 64; sf = byte (0 or 2) of the
 // 4-byte scale words that holds this k step's first block.
-__device__ __forceinline__ uint32_t mxf4_idesc(int n, uint32_t sf) {
-    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf << 4) | (sf << 29);
+__device__ __forceinline__ uint32_t mxf4_idesc(int n, uint32_t sf, uint32_t m) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf << 4) | (sf << 29);
 }
 
 struct MxGemmArgs {
@@ -217,7 +260,13 @@ struct MxGemmArgs {
     uint32_t* error_word;
 };
 
-template <bool GATE_UP>
+// TWO: the kernel runs as clusters of two CTAs (cta_group::2).  A pair takes two neighbouring 256-row tiles of one
+// segment, one per CTA; every MMA spans both CTAs (M = 256: 128 weight rows of each), so the segment's activation
+// terms are split between them -- each CTA loads N / 2 rows of every term instead of all N, which is what the
+// L2 -> shared-memory rate of this kernel is short of.  The even CTA issues all MMAs, scale copies and commits; each
+// CTA loads its own operands (tile loads that count on the even CTA's barrier), reads its own accumulators and
+// writes its own output rows.  The maps b32 / b64 / b96 then have boxes of 32 / 64 / 96 rows.
+template <bool GATE_UP, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_constant__ CUtensorMap tmap_b64,
                const __grid_constant__ CUtensorMap tmap_b96, const __grid_constant__ CUtensorMap tmap_w,
@@ -227,34 +276,59 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar0 = sbase + kSmemBar;
-    // FULL[s]: the stage's codes and scales have landed (TMA bytes); EMPTY[s]: the MMAs and scale copies reading
-    // stage s have completed (one tcgen05.commit per issuing warp); ACC_FULL / ACC_EMPTY: a tile's accumulators are complete / drained.
-    constexpr int FULL = 0, EMPTY = FULL + kStages, ACC_FULL = EMPTY + kStages, ACC_EMPTY = ACC_FULL + 1;
+    // FULL[s]: the stage's codes and scales have landed in this CTA (TMA bytes); SC_FULL[s]: the scale warps have moved the
+    // stage's scales into tensor memory (a pair: those of both CTAs, all counted in the even CTA, so it also says that the
+    // odd CTA's operands have landed); EMPTY[s]: the MMAs reading stage s have completed (one tcgen05.commit per issuing
+    // warp); ACC_FULL / ACC_EMPTY: a tile's accumulators are complete / drained.
+    constexpr int FULL = 0, EMPTY = FULL + kStages, ACC_FULL = EMPTY + kStages, ACC_EMPTY = ACC_FULL + 1, SC_FULL = ACC_EMPTY + 1;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const uint32_t rank = TWO ? cluster_ctarank() : 0u;   // 0: issues the MMAs
+    constexpr int kBoxRowsB = TWO ? kBoxRows / 2 : kBoxRows;         // granularity of the boxes that bring this CTA's rows of a term
+    constexpr int kBBoxBytesB = kBoxRowsB * kRowBytes;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; i++) { mbar_init(bar(FULL + i), 1); mbar_init(bar(EMPTY + i), kMmaWarps); }
+        for (int i = 0; i < kStages; i++) {
+            mbar_init(bar(FULL + i), 1);
+            mbar_init(bar(EMPTY + i), kMmaWarps);
+            mbar_init(bar(SC_FULL + i), TWO ? 8 : 4);
+        }
         mbar_init(bar(ACC_FULL), kMmaWarps);
-        mbar_init(bar(ACC_EMPTY), kEpiWarps);
+        mbar_init(bar(ACC_EMPTY), (TWO && rank == 0) ? kEpiWarps + 1 : kEpiWarps);   // + one forwarded arrival for the odd CTA's twelve
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // all 512 columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32((const void*)tmem_slot)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {  // all 512 columns of tensor memory (a pair: the same warp of both CTAs, the same columns in both)
+        if (TWO) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32((const void*)tmem_slot)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32((const void*)tmem_slot)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (TWO) cluster_sync_all();   // both CTAs' barriers exist before either signals the other
     const uint32_t tmem_base = *tmem_slot;
 
     const int n_segs = a.n_segs[0];
     const int n_mb = a.rows / (GATE_UP ? 128 : 256);   // 256-row tiles (gate/up: 128 gate + 128 up)
-    const int n_tiles = n_segs * n_mb;
     const int n_kc = a.K / kStageK;
+    // work units: tiles, or pairs of neighbouring tiles; unit u of this CTA is tile (u / per_seg, (u % per_seg) * 2 + rank)
+    const int per_seg = TWO ? n_mb / 2 : n_mb;
+    const int n_tiles = n_segs * per_seg;
+    const int unit0 = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, unit_step = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    auto unit_mb = [&](int u) { return TWO ? (u % per_seg) * 2 + (int)rank : u % per_seg; };
 
+    // The kernel starts with 96 registers per thread (640 threads = a pool of 61440 that setmaxnreg only redistributes: the
+    // three counts below add up to exactly that, and a larger request would wait for ever).  The epilogue warps need about
+    // 120 for the columns they hold while tensor memory is handed back; the other two warp groups give theirs up.
+    static_assert(128 * 64 + 128 * 56 + (kEpiWarps * 32) * 120 <= kThreads * 96, "register requests exceed the pool of the launch");
+    if (warp < kScWarp0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
@@ -263,8 +337,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             // weight map: gate/up = (bytes, row, matrix, slot) with a box of 64 x 128 x 2 (lands as 128 gate rows, then 128 up
             // rows); down = (bytes, row, 1, slot) with a box of 64 x 256 x 1
             auto w_row = [&](int mb) { return GATE_UP ? mb * 128 : mb * 256; };
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int si = tile / n_mb, mb = tile % n_mb;
+            for (int tile = unit0; tile < n_tiles && ok; tile += unit_step) {
+                const int si = tile / per_seg, mb = unit_mb(tile);
                 const PrefillSeg seg = a.segs[si];
                 const bool sh = seg.expert == a.n_local;
                 const CUtensorMap* m_w = sh ? &tmap_w_shared : &tmap_w;
@@ -276,18 +350,21 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                 const uint8_t* sfb = a.sfb + (int64_t)si * n_kc * kSfbBytes;
                 // one copy brings all three terms of the segment: boxes of 64, 128 or 192 rows x 3 terms (a term's rows land
                 // box_rows * 64 bytes apart)
-                const int n_box = (max(16, (seg.n + 15) & ~15) + kBoxRows - 1) / kBoxRows;
+                const int n16 = max(16, (seg.n + 15) & ~15);
+                const int n_mine = TWO ? n16 / 2 : n16;                     // rows of every term this CTA holds
+                const int n_box = (n_mine + kBoxRowsB - 1) / kBoxRowsB;
                 const CUtensorMap* m_b = n_box == 1 ? &tmap_b32 : (n_box == 2 ? &tmap_b64 : &tmap_b96);
-                const uint32_t stage_tx = (uint32_t)(kABytes + kSfaBytes + kSfbBytes + kTerms * n_box * kBBoxBytes);
+                const int b_row0 = seg.row0 + (TWO ? (int)rank * n_mine : 0);
+                const uint32_t tile_tx = (uint32_t)(kABytes + kTerms * n_box * kBBoxBytesB), sf_tx = (uint32_t)(kSfaBytes + kSfbBytes);
                 // weights of this tile into L2 a few stages ahead of the ring
                 constexpr int kAhead = 4;
                 auto prefetch_w = [&](const CUtensorMap* m, int kc, int mb_, int slot_) { tma_prefetch_4d(m, kc * kRowBytes, w_row(mb_), 0, slot_); };
-                if (tile == (int)blockIdx.x)
+                if (tile == unit0)
                     for (int kc = 0; kc < kAhead && kc < n_kc; kc++) prefetch_w(m_w, kc, mb, slot);
-                const int ntile = tile + gridDim.x;
+                const int ntile = tile + unit_step;
                 PrefillSeg nseg = seg;
                 int nmb = mb;
-                if (ntile < n_tiles) { nseg = a.segs[ntile / n_mb]; nmb = ntile % n_mb; }
+                if (ntile < n_tiles) { nseg = a.segs[ntile / per_seg]; nmb = unit_mb(ntile); }
                 const bool nsh = nseg.expert == a.n_local;
                 for (int kc = 0; kc < n_kc && ok; kc++) {
                     const int pk = kc + kAhead;
@@ -296,24 +373,34 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     const int s = cnt % kStages;
                     ok = mbar_wait(bar(EMPTY + s), ((cnt / kStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
-                    const uint32_t full = bar(FULL + s);
-                    mbar_expect_tx(full, stage_tx);
                     const uint32_t a_dst = sbase + kSmemA + s * kABytes;
+                    const uint32_t full = bar(FULL + s);   // every CTA's loads count on its own barrier
+                    mbar_expect_tx(full, tile_tx + sf_tx);
                     tma_load_4d(a_dst, m_w, kc * kRowBytes, w_row(mb), 0, slot, full);
-                    tma_load_3d(sbase + kSmemB + s * kBBytes, m_b, kc * kRowBytes, seg.row0, 0, full);
+                    tma_load_3d(sbase + kSmemB + s * kBBytes, m_b, kc * kRowBytes, b_row0, 0, full);
                     bulk_load(sbase + kSmemSfa + s * kSfaBytes, sfa + (int64_t)kc * 4 * kSfChunk, kSfaBytes, full);
                     bulk_load(sbase + kSmemSfb + s * kSfbBytes, sfb + (int64_t)kc * kSfbBytes, kSfbBytes, full);
                     cnt++;
                 }
             }
         }
-    } else if (warp < kEpiWarp0) {
+    } else if (warp <= kMmaWarps) {
         // ----------------------------------------------------------- MMA issue
         // Two issuing warps, one accumulator each (first product: warp 1 the gate rows, warp 2 the up rows of the tile; a single
         // thread cannot issue a stage's MMAs and scale copies as fast as the tensor core retires them).  Each copies its
         // accumulator's weight scales and its own copy of the activation scales to tensor memory, so its MMAs depend only
         // on its own copies.
-        if (lane == 0) {
+        if (TWO && rank != 0) {
+            // odd CTA of a pair: nothing to issue.  One thread forwards "all twelve epilogue warps here have read tile t's
+            // accumulators" to the even CTA.
+            if (warp == 2 && lane == 0) {
+                uint32_t t = 0;
+                for (int tile = unit0; tile < n_tiles; tile += unit_step, t++) {
+                    if (!mbar_wait(bar(ACC_EMPTY), t & 1u, abort_flag)) break;
+                    mbar_arrive_cluster(map_to_cta(bar(ACC_EMPTY), 0u));
+                }
+            }
+        } else if (lane == 0) {
             const int mw = warp - 1;
             constexpr int kAPW = kAccs / kMmaWarps;   // accumulators per issuing warp
             uint32_t tcnt = 0, s = 0, ph = 0;   // ring stage and its phase parity
@@ -321,31 +408,32 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             const uint64_t d0 = operand_desc(sbase + kSmemA);
             const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
             const uint32_t a_lo0 = (uint32_t)d0 + (uint32_t)((mw * kAPW * 128 * kRowBytes) >> 4), b_lo0 = (uint32_t)operand_desc(sbase + kSmemB);
-            const uint64_t sfa_desc0 = scale_desc(sbase + kSmemSfa) + (uint64_t)(mw * kAPW * (kSfChunk >> 4)), sfb_desc0 = scale_desc(sbase + kSmemSfb);
-            const uint32_t t_sfa = tmem_base + kSfaCol + 4u * (uint32_t)(mw * kAPW), t_sfb = tmem_base + kSfbCol + 4u * kSfbChunks * kTerms * (uint32_t)mw;
+            const uint32_t t_sfa0 = tmem_base + kSfaCol + 4u * (uint32_t)(mw * kAPW), t_sfb0 = tmem_base + kSfaCol + 4u * kAccs;
             const uint32_t t_acc = tmem_base + (uint32_t)(mw * kAPW * kSegRows);
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const PrefillSeg seg = a.segs[tile / n_mb];
+            // a pair: MMAs act in both CTAs; a commit arrives on this barrier of both, whose producers and epilogue warps each
+            // wait on their own
+            auto mma = [&](uint32_t d, uint32_t al, uint32_t bl, uint32_t h, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t acc) {
+                if (TWO) tc_mma_mxf4_lo_pair(d, al, bl, h, idesc, sfa, sfb, acc); else tc_mma_mxf4_lo(d, al, bl, h, idesc, sfa, sfb, acc);
+            };
+            auto commit = [&](uint32_t b) {
+                if (TWO) { tc_commit_pair(b); tc_commit_pair(map_to_cta(b, 1u)); } else tc_commit(b);
+            };
+            for (int tile = unit0; tile < n_tiles && ok; tile += unit_step) {
+                const PrefillSeg seg = a.segs[tile / per_seg];
                 const int n16 = max(16, (seg.n + 15) & ~15);
-                const uint32_t idesc0 = mxf4_idesc(n16, 0u), idesc1 = mxf4_idesc(n16, 2u);
-                const uint32_t term_step = (uint32_t)(((n16 + kBoxRows - 1) / kBoxRows) * (kBBoxBytes >> 4));   // a term's rows follow the previous term's box
-                const bool two_chunks = n16 > 128;   // rows 128.. have their scales in a second chunk
+                const uint32_t idesc0 = mxf4_idesc(n16, 0u, TWO ? 256u : 128u), idesc1 = mxf4_idesc(n16, 2u, TWO ? 256u : 128u);
+                const int n_mine = TWO ? n16 / 2 : n16;
+                const uint32_t term_step = (uint32_t)(((n_mine + kBoxRowsB - 1) / kBoxRowsB) * (kBBoxBytesB >> 4));   // a term's rows follow the previous term's box
                 ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // the previous tile's accumulators are drained
                 if (!ok) break;
                 tc_fence_after();
                 for (int kc = 0; kc < n_kc; kc++) {
-                    const uint32_t full = bar(FULL) + 8u * s;
+                    // the stage's operands have landed (in both CTAs of a pair) and its scales are in tensor memory
+                    const uint32_t sc_full = bar(SC_FULL) + 8u * s, full = bar(FULL) + 8u * s;
+                    if (!mbar_try(sc_full, ph) && !mbar_wait(sc_full, ph, abort_flag)) { ok = false; break; }
                     if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    // scales of this stage (16-byte units in the descriptor): this warp's weight chunks, the three terms' chunks
-                    const uint64_t sfb_d = sfb_desc0 + (uint64_t)(s * (kSfbBytes >> 4));
-#pragma unroll
-                    for (int h = 0; h < kAPW; h++) tc_cp_scales(t_sfa + 4 * h, sfa_desc0 + (uint64_t)(s * (kSfaBytes >> 4) + h * (kSfChunk >> 4)));
-#pragma unroll
-                    for (int t = 0; t < kTerms; t++) {
-                        tc_cp_scales(t_sfb + 4 * kSfbChunks * t, sfb_d + (uint64_t)(t * kSfbChunks * (kSfChunk >> 4)));
-                        if (two_chunks) tc_cp_scales(t_sfb + 4 * kSfbChunks * t + 4, sfb_d + (uint64_t)((t * kSfbChunks + 1) * (kSfChunk >> 4)));
-                    }
+                    const uint32_t t_sfa = t_sfa0 + s * kScSlot, t_sfb = t_sfb0 + s * kScSlot;
                     const uint32_t a_lo = a_lo0 + s * (kABytes >> 4), b_lo = b_lo0 + s * (kBBytes >> 4);
                     const uint32_t first = kc != 0 ? 1u : 0u;
 #pragma unroll
@@ -357,35 +445,69 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                             const uint32_t acc = (ks | t) != 0 ? 1u : first;
 #pragma unroll
                             for (int h = 0; h < kAPW; h++)
-                                tc_mma_mxf4_lo(t_acc + h * kSegRows, a_lo + (uint32_t)((h * 128 * kRowBytes) >> 4) + ks * 2, bl, hi, idesc, t_sfa + 4 * h,
-                                               t_sfb + 4 * kSfbChunks * t, acc);
+                                mma(t_acc + h * kSegRows, a_lo + (uint32_t)((h * 128 * kRowBytes) >> 4) + ks * 2, bl, hi, idesc, t_sfa + 4 * h,
+                                    t_sfb + 4 * kSfbChunks * t, acc);
                         }
                     }
-                    tc_commit(bar(EMPTY) + 8u * s);   // arrives when the copies and MMAs above have read their operands
+                    commit(bar(EMPTY) + 8u * s);   // arrives when the MMAs above have read their operands
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
-                if (ok) tc_commit(bar(ACC_FULL));
+                if (ok) commit(bar(ACC_FULL));
                 tcnt++;
+            }
+        }
+    }
+    } else if (warp < kEpiWarp0) {
+        // -------------------------------------------------------- scale warps
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
+        // A scale chunk (128 rows x 4 blocks) lies in shared memory as 32 rows of 16 bytes; the tensor core wants row r of it
+        // in lane 32 q + r of every lane quarter q, 4 columns wide.  Warp q copies the stage's 8 chunks (2 of weight scales,
+        // 3 terms x 2 of activation scales) into its quarter: lane r reads its 16 bytes of each chunk and stores them as 32
+        // columns of the stage's scale slot.  (tcgen05.cp does the same inside the tensor-core queue, where every copy holds
+        // up the MMAs behind it: 0.4 of 2.9 ms on the 8192-token layer.)
+        const int q = warp & 3;
+        uint32_t s = 0, ph = 0;
+        const uint32_t t_slot0 = tmem_base + ((uint32_t)(q * 32) << 16) + kSfaCol;
+        const uint32_t sc_bar0 = TWO ? map_to_cta(bar(SC_FULL), 0u) : bar(SC_FULL);
+        bool ok = true;
+        for (int tile = unit0; tile < n_tiles && ok; tile += unit_step) {
+            for (int kc = 0; kc < n_kc; kc++) {
+                if (!mbar_wait(bar(FULL) + 8u * s, ph, abort_flag)) { ok = false; break; }
+                uint32_t v[32];
+                const uint32_t src_a = sbase + kSmemSfa + s * kSfaBytes + (uint32_t)lane * 16u, src_b = sbase + kSmemSfb + s * kSfbBytes + (uint32_t)lane * 16u;
+#pragma unroll
+                for (int c = 0; c < kAccs; c++)
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[4 * c]), "=r"(v[4 * c + 1]), "=r"(v[4 * c + 2]), "=r"(v[4 * c + 3]) : "r"(src_a + c * kSfChunk));
+#pragma unroll
+                for (int c = 0; c < kSfbChunks * kTerms; c++)
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[4 * kAccs + 4 * c]), "=r"(v[4 * kAccs + 4 * c + 1]), "=r"(v[4 * kAccs + 4 * c + 2]), "=r"(v[4 * kAccs + 4 * c + 3]) : "r"(src_b + c * kSfChunk));
+                tc_st32(t_slot0 + s * kScSlot, v);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (TWO && rank != 0) mbar_arrive_cluster(sc_bar0 + 8u * s); else mbar_arrive(bar(SC_FULL) + 8u * s);
+                }
+                if (++s == kStages) { s = 0; ph ^= 1u; }
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 120;" ::: "memory");
         // Warp w may read lanes 32 * (w % 4) .. + 31 of tensor memory; the three warps of a lane quarter take 64 columns of
         // the tile each, in blocks of 16.  A lane holds gate and up of one output row (first product), or rows r and r + 128.
-        const int q = warp & 3, rank = (warp - kEpiWarp0) >> 2;
+        const int q = warp & 3, third = (warp - kEpiWarp0) >> 2;
         uint32_t tcnt = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const PrefillSeg seg = a.segs[tile / n_mb];
-            const int mb = tile % n_mb;
+        for (int tile = unit0; tile < n_tiles && ok; tile += unit_step) {
+            const PrefillSeg seg = a.segs[tile / per_seg];
+            const int mb = unit_mb(tile);
             const bool sh = seg.expert == a.n_local;
-            ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
             const int r_in = q * 32 + lane;           // row inside a 128-row accumulator
-            const int c0 = 64 * rank;
-            // lane j of the warp fetches the routing weight / output row of columns c0 + j and c0 + 32 + j
+            const int c0 = 64 * third;
+            // lane j of the warp fetches the routing weight / output row of columns c0 + j and c0 + 32 + j (two dependent
+            // loads: done while the tile's MMAs still run)
             float wv[2] = {0.f, 0.f};
             int orow[2] = {0, 0};
 #pragma unroll
@@ -396,6 +518,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     else { const int ts = a.perm[seg.row0 + c]; wv[h] = a.route_w[ts]; orow[h] = ts; }
                 }
             }
+            ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
             // one 16-column block: v0 = accumulator 0, v1 = accumulator 1
             auto emit = [&](int cb, const uint32_t (&v0)[16], const uint32_t (&v1)[16]) {
                 const int h = (cb - c0) >> 5, j0 = (cb - c0) & 31;
@@ -427,36 +552,33 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     }
                 }
             };
-            // the first 32 columns block by block; the last 32 are read whole, the accumulators are handed back, and their
-            // arithmetic and stores run while the next tile's MMAs have already started
-#pragma unroll
-            for (int b = 0; b < 2; b++) {
-                const int cb = c0 + 16 * b;
-                if (cb < seg.n) {
-                    uint32_t v0[16], v1[16];
-                    tc_ld16(lane_addr + (uint32_t)cb, v0);
-                    tc_ld16(lane_addr + (uint32_t)(kSegRows + cb), v1);
-                    tc_wait_ld();
-                    emit(cb, v0, v1);
-                }
-            }
-            uint32_t w0[16], w1[16], w2[16], w3[16];
-            const bool tail0 = c0 + 32 < seg.n, tail1 = c0 + 48 < seg.n;
-            if (tail0) {
-                tc_ld16(lane_addr + (uint32_t)(c0 + 32), w0);
-                tc_ld16(lane_addr + (uint32_t)(kSegRows + c0 + 32), w1);
-                if (tail1) {
-                    tc_ld16(lane_addr + (uint32_t)(c0 + 48), w2);
-                    tc_ld16(lane_addr + (uint32_t)(kSegRows + c0 + 48), w3);
-                }
+            // Four blocks of 16 columns, read two at a time (a tcgen05.ld is asynchronous: nothing but the wait may stand between
+            // it and the first use of its registers).  After the second pair has arrived the accumulators are handed back, and
+            // its arithmetic and stores run while the next tile's MMAs have already started.
+            uint32_t v0[16], v1[16], u0[16], u1[16];
+            const bool b0 = c0 < seg.n, b1 = c0 + 16 < seg.n, b2 = c0 + 32 < seg.n, b3 = c0 + 48 < seg.n;
+            auto ld_block = [&](int cb, uint32_t (&x0)[16], uint32_t (&x1)[16]) {
+                tc_ld16(lane_addr + (uint32_t)cb, x0);
+                tc_ld16(lane_addr + (uint32_t)(kSegRows + cb), x1);
+            };
+            if (b0) {
+                ld_block(c0, v0, v1);
+                if (b1) ld_block(c0 + 16, u0, u1);
                 tc_wait_ld();
+                emit(c0, v0, v1);
+                if (b1) emit(c0 + 16, u0, u1);
+                if (b2) {
+                    ld_block(c0 + 32, v0, v1);
+                    if (b3) ld_block(c0 + 48, u0, u1);
+                    tc_wait_ld();
+                }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
-            if (tail0) {
-                emit(c0 + 32, w0, w1);
-                if (tail1) emit(c0 + 48, w2, w3);
+            if (lane == 0) mbar_arrive(bar(ACC_EMPTY));   // (odd CTA of a pair: its own barrier; warp 2 forwards the completed phase)
+            if (b2) {
+                emit(c0 + 32, v0, v1);
+                if (b3) emit(c0 + 48, u0, u1);
             }
             tcnt++;
         }
@@ -465,9 +587,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error_word, 2u);
+    if (TWO) cluster_sync_all();   // neither CTA's shared or tensor memory goes away while the other may still use it
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+        if (TWO) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
     }
 }
 
@@ -744,6 +868,31 @@ int map_weights(PrefillWorkspace* ws, int which, const uint8_t* km_gu, const uin
     return DSX_OK;
 }
 
+template <bool GATE_UP>
+int launch_mx_gemm(bool pair, const CUtensorMap* b_maps, const CUtensorMap& w_map, const CUtensorMap& w_shared_map, const MxGemmArgs& g, int sm_count,
+                   cudaStream_t stream) {
+    if (!pair) {
+        mx_gemm_kernel<GATE_UP, false><<<sm_count, kThreads, kSmemTotal, stream>>>(b_maps[0], b_maps[1], b_maps[2], w_map, w_shared_map, g);
+        DSX_LAUNCHED();
+        return DSX_OK;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sm_count & ~1));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DSX_CUDA(cudaLaunchKernelEx(&cfg, mx_gemm_kernel<GATE_UP, true>, b_maps[0], b_maps[1], b_maps[2], w_map, w_shared_map, g));
+    DSX_LAUNCHED();
+    return DSX_OK;
+}
+
 }  // namespace
 
 int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used) {
@@ -767,9 +916,20 @@ int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg,
             if (int rc = tmap_encode(g == 0 ? &ws->tmap_xq[b] : &ws->tmap_mq[b], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ws->xq, dims, strides, box,
                                      CU_TENSOR_MAP_SWIZZLE_64B))
                 return rc;
+            // CTA pairs: each CTA fetches half of a segment's rows (boxes of 32 / 64 / 96 rows)
+            const cuuint32_t box2[3] = {(cuuint32_t)kRowBytes, (cuuint32_t)((b + 1) * kBoxRows / 2), (cuuint32_t)kTerms};
+            if (int rc = tmap_encode(g == 0 ? &ws->tmap_xq2[b] : &ws->tmap_mq2[b], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ws->xq, dims, strides, box2,
+                                     CU_TENSOR_MAP_SWIZZLE_64B))
+                return rc;
         }
-    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
-    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    DSX_CUDA(cudaFuncSetAttribute(mx_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    // CTA pairs need an even number of 256-row tiles per segment in both products (true of every shape this path takes)
+    // DSX_MX_PAIR=0 / 1 pins the single-CTA or the CTA-pair form (tests compare the two bit for bit); otherwise per call
+    const char* pair_env = std::getenv("DSX_MX_PAIR");
+    ws->mx_pair_mode = pair_env == nullptr ? -1 : (pair_env[0] == '1' ? 1 : (pair_env[0] == '0' ? 0 : -1));
     ws->mx_ready = true;
     return DSX_OK;
 }
@@ -793,6 +953,10 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     // stream them twice.  (The f16-operand kernel of Q8_0 stores hands over up to 24 rows: its tile pass is bound by
     // weight conversion, not bytes.)
     const int mx_small = ws->small_max > 0 ? kMxSmallMax : 0;
+    // CTA pairs halve the activation rows a CTA loads per stage, which pays once segments are long: measured on the
+    // 256-expert layer, pairs are 5 to 10 % faster from 128 rows per expert on and 2 to 9 % slower at 64 and fewer (a
+    // stage is mostly weight bytes there, and a pair adds a hop to every hand-over).
+    const bool pair = ws->mx_pair_mode >= 0 ? ws->mx_pair_mode == 1 : P >= (int64_t)kPairFromRows * c.n_local;
     if (int rc = launch_build_segments(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, kSegRows, ws->mx_segs, ws->n_segs, ws->mx_seg_cap,
                                        mx_small, ws->small_items, ws->n_small, stream))
         return rc;
@@ -825,9 +989,8 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     }
     g.K = cfg.hidden; g.rows = cfg.ffn;
     g.sfa = c.sf_gu; g.sfa_slot_stride = c.sf_gu_stride; g.sfa_shared = c.sh_sf_gu;
-    mx_gemm_kernel<true><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_xq[0], ws->tmap_xq[1], ws->tmap_xq[2], ws->tmap_km_gu[0],
-                                                                       ws->tmap_km_gu[shi], g);
-    DSX_LAUNCHED();
+    if (int rc = launch_mx_gemm<true>(pair, pair ? ws->tmap_xq2 : ws->tmap_xq, ws->tmap_km_gu[0], ws->tmap_km_gu[shi], g, c.sm_count, stream))
+        return rc;
     if (ws->small_max > 0) {
         v.K = cfg.hidden; v.rows = cfg.ffn; v.sh_rows = cfg.ffn;
         v.nib = c.gu_nib; v.sc = c.gu_sc; v.nib_slot_stride = c.gu_nib_stride; v.sc_slot_stride = c.gu_sc_stride;
@@ -843,9 +1006,8 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     DSX_LAUNCHED();
     g.K = cfg.ffn; g.rows = cfg.hidden;
     g.sfa = c.sf_dn; g.sfa_slot_stride = c.sf_dn_stride; g.sfa_shared = c.sh_sf_dn;
-    mx_gemm_kernel<false><<<c.sm_count, kThreads, kSmemTotal, stream>>>(ws->tmap_mq[0], ws->tmap_mq[1], ws->tmap_mq[2], ws->tmap_km_dn[0],
-                                                                        ws->tmap_km_dn[shi], g);
-    DSX_LAUNCHED();
+    if (int rc = launch_mx_gemm<false>(pair, pair ? ws->tmap_mq2 : ws->tmap_mq, ws->tmap_km_dn[0], ws->tmap_km_dn[shi], g, c.sm_count, stream))
+        return rc;
     if (ws->small_max > 0) {
         v.K = cfg.ffn; v.rows = cfg.hidden; v.sh_rows = cfg.hidden;
         v.nib = c.dn_nib; v.sc = c.dn_sc; v.nib_slot_stride = c.dn_nib_stride; v.sc_slot_stride = c.dn_sc_stride;

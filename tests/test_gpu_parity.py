@@ -383,6 +383,30 @@ def test_layer_prefill_matches_oracle_with_the_same_activation_terms(torch_cuda,
     assert same_err < 2.2e-3 and same_err < exact_err, (same_err, exact_err)
 
 
+def test_layer_prefill_cta_pairs_same_bits(torch_cuda, moe, monkeypatch):
+    """The block-scaled GEMMs run one tile per CTA or two neighbouring tiles per CTA pair (cta_group::2, picked per call by
+    the rows per expert).  Both forms add the same products in the same order: pinned either way by DSX_MX_PAIR, the layer
+    output is the same bits, on segments of every kind (short, 129..192 rows with their second scale chunk, split experts)."""
+    import numpy as np
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import MoeConfig, RouterConfig
+    torch = torch_cuda
+    cfg = MoeConfig(hidden=1024, ffn=512, shared_ffn=512,
+                    router=RouterConfig(n_expert=32, n_used=4, n_group=1, topk_group=1, score_fn=1, route_scale=2.5))
+    w = synth.make_layer(cfg, 2)
+    monkeypatch.setenv("DSX_MX_PAIR", "0")
+    single = moe.build_layer_from_host(cfg, w, max_tokens=2500)
+    monkeypatch.setenv("DSX_MX_PAIR", "1")
+    pair = moe.build_layer_from_host(cfg, w, max_tokens=2500)
+    for T in (70, 700, 1200, 2500):
+        x = torch.from_numpy(synth.make_tokens(cfg, 2, T).view(np.int16)).cuda().view(torch.bfloat16)
+        a = single.forward(x)
+        b = pair.forward(x)
+        torch.cuda.synchronize()
+        assert single.check() == 0 and pair.check() == 0
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), T
+
+
 def test_layer_prefill_config0_shapes(torch_cuda, moe, oracle):
     from deepstrix_b200.config import CONFIGS
     out, ref, *_ = _layer_case(torch_cuda, moe, oracle, CONFIGS[0], 0, 192)
