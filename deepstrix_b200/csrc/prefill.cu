@@ -460,22 +460,26 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                     }
                 } else {
                     // Q8_0: 32 sub-tiles of 16 rows x 32 columns, stage order [row tile][column tile 0/1][gate, up]
-                    // (down: [row tile][column tile]); four sub-tiles per warp.  A lane's 16 bytes are rows
-                    // g / g+8 x 8 consecutive columns: words {row g cols 0-3, row g+8 cols 0-3, row g cols 4-7, row g+8 cols 4-7}.
+                    // (down: [row tile][column tile]).  A warp takes two PAIRS of sub-tiles that differ in the column tile, in two
+                    // rounds each: lanes of even row g convert column tile r, lanes of odd g column tile r ^ 1, so that the
+                    // eight lanes of a quarter warp (two neighbouring g) store to eight different 16-byte bank groups of the
+                    // swizzled operand tile (one column tile per round put them on four, every store a 2-way conflict).
+                    // A lane's 16 bytes are rows g / g+8 x 8 consecutive columns: words {row g cols 0-3, row g+8 cols 0-3,
+                    // row g cols 4-7, row g+8 cols 4-7}.
                     uint4 wq[4];
                     uint32_t sw[4];
+                    constexpr int kColTileStep = GATE_UP ? 2 : 1;   // sub-tile index distance between the two column tiles
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        const int st = cw + 8 * i;
+                        const int pr = cw + 8 * (i >> 1), kt2 = (i & 1) ^ (g & 1);
+                        const int st = (GATE_UP ? (pr >> 1) * 4 + (pr & 1) : pr * 2) + kt2 * kColTileStep;
                         wq[i] = *reinterpret_cast<const uint4*>(raw + st * kSubNibBytes + lane * 16);
                         sw[i] = *reinterpret_cast<const uint32_t*>(raw + C::kRawNib + st * kSubScBytes + g * 4);
                     }
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        const int st = cw + 8 * i;
-                        int rt, kt2, gu;
-                        if (GATE_UP) { gu = st & 1; kt2 = (st >> 1) & 1; rt = st >> 2; }
-                        else { gu = 0; kt2 = st & 1; rt = st >> 1; }
+                        const int pr = cw + 8 * (i >> 1), kt2 = (i & 1) ^ (g & 1);
+                        const int gu = GATE_UP ? (pr & 1) : 0, rt = GATE_UP ? (pr >> 1) : pr;
                         const int row_base = gu * 128 + rt * 16;
                         uint8_t* arow = A + (uint32_t)((row_base + g) >> 3) * 1024u + (uint32_t)g * 128u;
                         const uint32_t m0 = (sw[i] & 0xFFFFu) * 0x00010001u, m1 = (sw[i] >> 16) * 0x00010001u;   // f16 scale of row g / g+8
