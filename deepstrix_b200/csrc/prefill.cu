@@ -45,19 +45,21 @@ template <int FMT>
 struct Shape {
     static constexpr int kSubPerChunk = FMT == DSX_FMT_MXFP4 ? 16 : 32;
     static constexpr int kKtPerChunk = FMT == DSX_FMT_MXFP4 ? 1 : 2;       // column tiles per 64 columns
-    static constexpr int kRawStages = FMT == DSX_FMT_MXFP4 ? 3 : 2;
-    static constexpr int kAStages = FMT == DSX_FMT_MXFP4 ? 3 : 2;          // also the token-tile ring (lockstep)
+    static constexpr int kRawStages = 3;
+    static constexpr int kAStages = FMT == DSX_FMT_MXFP4 ? 3 : 2;          // converted-weight ring (filled on chip: two stages cover it)
+    static constexpr int kBStages = 3;                                     // token-tile ring (filled from L2, like the raw ring)
     static constexpr int kRawNib = kSubPerChunk * kSubNibBytes;
     static constexpr int kRawSc = kSubPerChunk * kSubScBytes;
     static constexpr int kRawBytes = kRawNib + kRawSc;
     static constexpr int kSmemA = 0;
     static constexpr int kSmemB = kSmemA + kAStages * kABytes;
-    static constexpr int kSmemRaw = kSmemB + kAStages * kBBytes;
+    static constexpr int kSmemRaw = kSmemB + kBStages * kBBytes;
     static constexpr int kSmemBar = kSmemRaw + kRawStages * kRawBytes;
-    static constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2;
+    static constexpr int kNumBars = 2 * kRawStages + 2 * kAStages + 2 * kBStages + 2;
     static constexpr int kSmemMisc = kSmemBar + kNumBars * 8;              // tmem base, abort flag
     static constexpr int kSmemTotal = kSmemMisc + 16 + 1024;               // + alignment slack
 };
+static_assert(Shape<DSX_FMT_MXFP4>::kSmemTotal <= 227 * 1024 && Shape<DSX_FMT_Q8_0>::kSmemTotal <= 227 * 1024, "rings exceed the shared memory of an SM");
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -230,7 +232,9 @@ struct GemmArgs {
 
 template <int FMT, bool GATE_UP>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_nib,
+prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b64, const __grid_constant__ CUtensorMap tmap_b128,
+                    const __grid_constant__ CUtensorMap tmap_b192, const __grid_constant__ CUtensorMap tmap_b256,
+                    const __grid_constant__ CUtensorMap tmap_nib,
                     const __grid_constant__ CUtensorMap tmap_sc, const __grid_constant__ CUtensorMap tmap_sh_nib,
                     const __grid_constant__ CUtensorMap tmap_sh_sc, const GemmArgs a) {
     using C = Shape<FMT>;
@@ -241,10 +245,11 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
     const uint32_t bar0 = sbase + C::kSmemBar;
     // barrier indices
-    // AB_FULL[s]: converted weights (8 converter warps) and token tile (TMA bytes) of stage s are in
-    // shared memory; AB_EMPTY[s]: the MMAs reading stage s have completed (one tcgen05.commit).
-    constexpr int RAW_FULL = 0, RAW_EMPTY = RAW_FULL + C::kRawStages, AB_FULL = RAW_EMPTY + C::kRawStages, AB_EMPTY = AB_FULL + C::kAStages,
-                  ACC_FULL = AB_EMPTY + C::kAStages, ACC_EMPTY = ACC_FULL + 1;
+    // A_FULL[s]: the converted weights (8 converter warps) of stage s are in shared memory; B_FULL[s]: the token tile (TMA
+    // bytes) of stage s; A_EMPTY / B_EMPTY[s]: the MMAs reading the stage have completed (one tcgen05.commit each).  The two
+    // rings advance independently: the token tile comes from L2 and needs a deeper ring than the weights converted on chip.
+    constexpr int RAW_FULL = 0, RAW_EMPTY = RAW_FULL + C::kRawStages, A_FULL = RAW_EMPTY + C::kRawStages, A_EMPTY = A_FULL + C::kAStages,
+                  B_FULL = A_EMPTY + C::kAStages, B_EMPTY = B_FULL + C::kBStages, ACC_FULL = B_EMPTY + C::kBStages, ACC_EMPTY = ACC_FULL + 1;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kSmemMisc);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -252,7 +257,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::kRawStages; i++) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), kConvWarps); }
-        for (int i = 0; i < C::kAStages; i++) { mbar_init(bar(AB_FULL + i), kConvWarps + 1); mbar_init(bar(AB_EMPTY + i), 1); }
+        for (int i = 0; i < C::kAStages; i++) { mbar_init(bar(A_FULL + i), kConvWarps); mbar_init(bar(A_EMPTY + i), 1); }
+        for (int i = 0; i < C::kBStages; i++) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
         mbar_init(bar(ACC_FULL), 1);
         mbar_init(bar(ACC_EMPTY), 4 + kConvWarps);
         *abort_flag = 0u;
@@ -375,12 +381,15 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const PrefillSeg seg = a.segs[tile / n_mb];
+                // only the rows the segment has, in boxes of 64 / 128 / 192 / 256 rows
+                const int n_box = (max(16, (seg.n + 15) & ~15) + 63) >> 6;
+                const CUtensorMap* m_b = n_box == 1 ? &tmap_b64 : (n_box == 2 ? &tmap_b128 : (n_box == 3 ? &tmap_b192 : &tmap_b256));
                 for (int kc = 0; kc < n_kc && ok; kc++) {
-                    const int s = bcnt % C::kAStages;
-                    ok = mbar_wait(bar(AB_EMPTY + s), ((bcnt / C::kAStages) & 1u) ^ 1u, abort_flag);
+                    const int s = bcnt % C::kBStages;
+                    ok = mbar_wait(bar(B_EMPTY + s), ((bcnt / C::kBStages) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(bar(AB_FULL + s), kBBytes);
-                    tma_load_2d(sbase + C::kSmemB + s * kBBytes, &tmap_b, kc * kChunkK, seg.row0, bar(AB_FULL + s));
+                    mbar_expect_tx(bar(B_FULL + s), (uint32_t)(n_box * 64 * kChunkK * 2));
+                    tma_load_2d(sbase + C::kSmemB + s * kBBytes, m_b, kc * kChunkK, seg.row0, bar(B_FULL + s));
                     bcnt++;
                 }
             }
@@ -388,7 +397,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
     } else if (warp == 1) {
         // ----------------------------------------------------------- MMA issue
         if (lane == 0) {
-            uint32_t tcnt = 0, sa = 0, ph = 0;   // ring stage and its phase parity
+            uint32_t tcnt = 0, sa = 0, ph = 0, sb = 0, phb = 0;   // ring stages and their phase parities
             bool ok = true;
             const uint64_t d0 = umma_desc(sbase + C::kSmemA);
             const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
@@ -401,12 +410,15 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 if (!ok) break;
                 tc_fence_after();
                 for (int kc = 0; kc < n_kc; kc++) {
-                    const uint32_t full = bar(AB_FULL) + 8u * sa;
-                    if (!mbar_try(full, ph) && !mbar_wait(full, ph, abort_flag)) { ok = false; break; }
+                    const uint32_t a_full = bar(A_FULL) + 8u * sa, b_full = bar(B_FULL) + 8u * sb;
+                    if (!mbar_try(a_full, ph) && !mbar_wait(a_full, ph, abort_flag)) { ok = false; break; }
+                    if (!mbar_try(b_full, phb) && !mbar_wait(b_full, phb, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    tc_mma_chunk(tmem_base, a_lo0 + sa * (kABytes >> 4), b_lo0 + sa * (kBBytes >> 4), hi, idesc, kc != 0 ? 1u : 0u);
-                    tc_commit(bar(AB_EMPTY) + 8u * sa);   // arrives when the MMAs above have read their operands
+                    tc_mma_chunk(tmem_base, a_lo0 + sa * (kABytes >> 4), b_lo0 + sb * (kBBytes >> 4), hi, idesc, kc != 0 ? 1u : 0u);
+                    tc_commit(bar(A_EMPTY) + 8u * sa);   // arrive when the MMAs above have read their operands
+                    tc_commit(bar(B_EMPTY) + 8u * sb);
                     if (++sa == C::kAStages) { sa = 0; ph ^= 1u; }
+                    if (++sb == C::kBStages) { sb = 0; phb ^= 1u; }
                 }
                 if (ok) tc_commit(bar(ACC_FULL));
                 tcnt++;
@@ -421,7 +433,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             for (int kc = 0; kc < n_kc && ok; kc++) {
                 const int sr = rcnt % C::kRawStages, sa = acnt % C::kAStages;
                 ok = mbar_wait(bar(RAW_FULL + sr), (rcnt / C::kRawStages) & 1u, abort_flag);
-                ok = ok && mbar_wait(bar(AB_EMPTY + sa), ((acnt / C::kAStages) & 1u) ^ 1u, abort_flag);
+                ok = ok && mbar_wait(bar(A_EMPTY + sa), ((acnt / C::kAStages) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
                 const uint8_t* raw = smem + C::kSmemRaw + sr * C::kRawBytes;
                 uint8_t* A = smem + C::kSmemA + sa * kABytes;
@@ -495,7 +507,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(bar(AB_FULL + sa));
+                    mbar_arrive(bar(A_FULL + sa));
                     mbar_arrive(bar(RAW_EMPTY + sr));
                 }
                 rcnt++;
@@ -644,7 +656,7 @@ int launch_build_segments(const int32_t* offsets, int n_local, int64_t P, int T_
 
 namespace {
 
-int encode_rows_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
+int encode_rows_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int box_rows) {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
         void* p = nullptr;
@@ -655,7 +667,7 @@ int encode_rows_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols) {
     }
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)kSegRows};
+    const cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -710,7 +722,9 @@ int map_weights(PrefillWorkspace* ws, int which, const uint8_t* gu_nib, const ui
 int prefill_f16_rows_ensure(PrefillWorkspace* ws) {
     if (!ws->ready || ws->xperm != nullptr) return DSX_OK;
     DSX_CUDA(cudaMalloc((void**)&ws->xperm, (size_t)ws->cap_rows * (size_t)ws->H * 2));
-    return encode_rows_map(&ws->tmap_x, ws->xperm, ws->cap_rows, ws->H);
+    for (int b = 0; b < 4; b++)
+        if (int rc = encode_rows_map(&ws->tmap_x[b], ws->xperm, ws->cap_rows, ws->H, 64 * (b + 1))) return rc;
+    return DSX_OK;
 }
 
 int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, int n_used, __half* mid, bool f16_rows) {
@@ -728,7 +742,8 @@ int prefill_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg, in
     DSX_CUDA(cudaMemset(ws->n_small, 0, 256));
     // a work item of the grouped GEMV holds at most 8 tokens; both reductions must fit its shared memory
     ws->small_max = (gemv_fits(cfg.hidden) && gemv_fits(cfg.ffn) && cfg.hidden % 128 == 0 && cfg.ffn % 128 == 0) ? kSmallMax : 0;
-    if (int rc = encode_rows_map(&ws->tmap_mid, mid, ws->cap_rows, cfg.ffn)) return rc;
+    for (int b = 0; b < 4; b++)
+        if (int rc = encode_rows_map(&ws->tmap_mid[b], mid, ws->cap_rows, cfg.ffn, 64 * (b + 1))) return rc;
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_MXFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_MXFP4>::kSmemTotal));
     DSX_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel<DSX_FMT_Q8_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DSX_FMT_Q8_0>::kSmemTotal));
@@ -787,10 +802,10 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     g.K = cfg.hidden; g.rows = cfg.ffn;
     if (c.fmt == DSX_FMT_MXFP4)
         prefill_gemm_kernel<DSX_FMT_MXFP4, true><<<c.sm_count, kThreads, Shape<DSX_FMT_MXFP4>::kSmemTotal, stream>>>(
-            ws->tmap_x, ws->tmap_gu_nib[0], ws->tmap_gu_sc[0], ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
+            ws->tmap_x[0], ws->tmap_x[1], ws->tmap_x[2], ws->tmap_x[3], ws->tmap_gu_nib[0], ws->tmap_gu_sc[0], ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
     else
         prefill_gemm_kernel<DSX_FMT_Q8_0, true><<<c.sm_count, kThreads, Shape<DSX_FMT_Q8_0>::kSmemTotal, stream>>>(
-            ws->tmap_x, ws->tmap_gu_nib[0], ws->tmap_gu_sc[0], ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
+            ws->tmap_x[0], ws->tmap_x[1], ws->tmap_x[2], ws->tmap_x[3], ws->tmap_gu_nib[0], ws->tmap_gu_sc[0], ws->tmap_gu_nib[shi], ws->tmap_gu_sc[shi], g);
     DSX_LAUNCHED();
     if (ws->small_max > 0) {
         v.K = cfg.hidden; v.rows = cfg.ffn; v.sh_rows = cfg.ffn;
@@ -801,10 +816,10 @@ int prefill_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Prefi
     g.K = cfg.ffn; g.rows = cfg.hidden;
     if (c.fmt == DSX_FMT_MXFP4)
         prefill_gemm_kernel<DSX_FMT_MXFP4, false><<<c.sm_count, kThreads, Shape<DSX_FMT_MXFP4>::kSmemTotal, stream>>>(
-            ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0], ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
+            ws->tmap_mid[0], ws->tmap_mid[1], ws->tmap_mid[2], ws->tmap_mid[3], ws->tmap_dn_nib[0], ws->tmap_dn_sc[0], ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
     else
         prefill_gemm_kernel<DSX_FMT_Q8_0, false><<<c.sm_count, kThreads, Shape<DSX_FMT_Q8_0>::kSmemTotal, stream>>>(
-            ws->tmap_mid, ws->tmap_dn_nib[0], ws->tmap_dn_sc[0], ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
+            ws->tmap_mid[0], ws->tmap_mid[1], ws->tmap_mid[2], ws->tmap_mid[3], ws->tmap_dn_nib[0], ws->tmap_dn_sc[0], ws->tmap_dn_nib[shi], ws->tmap_dn_sc[shi], g);
     DSX_LAUNCHED();
     if (ws->small_max > 0) {
         v.K = cfg.ffn; v.rows = cfg.hidden; v.sh_rows = cfg.hidden;

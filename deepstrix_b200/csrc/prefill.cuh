@@ -26,8 +26,8 @@ struct PrefillWorkspace {
     int small_max = 0;         // experts with at most this many rows go to the grouped GEMV instead (0: none)
     int32_t* small_items = nullptr;   // their work items (expert << 16 | first member), one per expert
     int32_t* n_small = nullptr;
-    CUtensorMap tmap_x;        // xperm as [cap_rows, H], box 64 x 256, 128-byte swizzle
-    CUtensorMap tmap_mid;      // mid   as [cap_rows, F]
+    CUtensorMap tmap_x[4];     // xperm as [cap_rows, H], boxes of 64 columns x 64 / 128 / 192 / 256 rows, 128-byte swizzle
+    CUtensorMap tmap_mid[4];   // mid   as [cap_rows, F]
     // packed-weight planes as 4-D tensors [slot][row tile][column tile][bytes as u32]; index 0 routed, 1 shared
     CUtensorMap tmap_gu_nib[2], tmap_gu_sc[2], tmap_dn_nib[2], tmap_dn_sc[2];
     const void* mapped_gu_nib[2] = {nullptr, nullptr};   // planes the maps above were encoded for
