@@ -553,9 +553,10 @@ __device__ __forceinline__ int seg_size(int cnt, int seg_rows) {  // even split 
 // segment: a tile would spend a full pass of weight conversion on a handful of tokens, while the
 // grouped GEMV streams the same weights at HBM speed, so they become GEMV work items instead.
 #ifndef DSX_SMALL_MAX
-#define DSX_SMALL_MAX 24
+#define DSX_SMALL_MAX 8
 #endif
-// A tile pass of the f16-operand kernels costs an expert about as much as three GEMV items of 8 rows.
+// One GEMV item (8 rows) streams an expert's weights once; from 9 rows on it would stream them again per item.  (With
+// token-tile and converted-weight rings in lockstep a tile pass used to cost about three items, and the threshold was 24.)
 constexpr int kSmallMax = DSX_SMALL_MAX;   // at most 32 (4 work items of 8 rows per expert)
 static_assert(kSmallMax <= 32, "the work-item list holds 4 items per expert");
 

@@ -950,8 +950,7 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
         return rc;
     // Experts with at most kMxSmallMax rows go to the grouped GEMV: one 8-row item streams an expert's weights once at
     // HBM speed, which a tile pass (bound by the same bytes through L2) cannot beat; from 9 rows on the GEMV would
-    // stream them twice.  (The f16-operand kernel of Q8_0 stores hands over up to 24 rows: its tile pass is bound by
-    // weight conversion, not bytes.)
+    // stream them twice.
     const int mx_small = ws->small_max > 0 ? kMxSmallMax : 0;
     // CTA pairs halve the activation rows a CTA loads per stage, which pays once segments are long: measured on the
     // 256-expert layer, pairs are 5 to 10 % faster from 128 rows per expert on and 2 to 9 % slower at 64 and fewer (a

@@ -117,8 +117,8 @@ def test_layer_config3_full_size(torch_cuda, moe, oracle):
     """Configuration 3 as the benchmark builds it: Q8_0 experts, 256 experts, 2048 tokens, router bias
     skewed to a Zipf(1.1) popularity profile.  Routing, histogram, offsets and permutation bit-exact on all
     2048 tokens; outputs of 256+ tokens against the oracle, chosen to cover the busiest expert (several
-    segments, first / middle / last rows), experts with 25..60 rows (one tensor tile) and experts with at
-    most 24 rows (handed to the grouped GEMV)."""
+    segments, first / middle / last rows), experts with 9..60 rows (one tensor tile) and experts with at
+    most 8 rows (handed to the grouped GEMV)."""
     torch = torch_cuda
     from deepstrix_b200 import synth
     from deepstrix_b200.config import CONFIGS
@@ -137,8 +137,8 @@ def test_layer_config3_full_size(torch_cuda, moe, oracle):
     osel, ow, oh, oo, op = _check_routing(oracle, cfg, w["router_bias"], routing, routing["logits"])
     big = int(np.argmax(oh))
     assert oh[big] > 512                                   # several segments
-    mids = [e for e in range(E) if 25 <= oh[e] <= 60]
-    smalls = [e for e in range(E) if 1 <= oh[e] <= 24]
+    mids = [e for e in range(E) if 9 <= oh[e] <= 60]
+    smalls = [e for e in range(E) if 1 <= oh[e] <= 8]
     assert mids and smalls
     rows = list(range(oo[big], oo[big] + 24)) + list(range(oo[big] + oh[big] // 2 - 12, oo[big] + oh[big] // 2 + 12)) + \
         list(range(oo[big + 1] - 24, oo[big + 1]))
