@@ -78,7 +78,7 @@ constexpr int kSmemB = kSmemA + kStages * kABytes;
 constexpr int kSmemSfa = kSmemB + kStages * kBBytes;
 constexpr int kSmemSfb = kSmemSfa + kStages * kSfaBytes;
 constexpr int kSmemBar = kSmemSfb + kStages * kSfbBytes;
-constexpr int kNumBars = 3 * kStages + 2;
+constexpr int kNumBars = 3 * kStages + 4;
 constexpr int kSmemMisc = kSmemBar + kNumBars * 8;
 constexpr int kSmemTotal = kSmemMisc + 16 + 1024;        // + alignment slack
 static_assert(kSmemTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
@@ -96,6 +96,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 #define DSX_MX_SMALL_MAX 8
 #endif
 constexpr int kMxSmallMax = DSX_MX_SMALL_MAX;
+constexpr int kShortRows = 96;                // segment cap of the double-buffered form: 2 buffers x 2 accumulators x 96 columns
 constexpr int kPairFromRows = 96;             // average rows per expert from which the GEMMs run as CTA pairs
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -258,6 +259,7 @@ struct MxGemmArgs {
     const uint8_t* sfa_shared;
     const uint8_t* sfb;        // activation scale chunks: [segment][K/128][term][2][512]
     uint32_t* error_word;
+    int short_segments;        // every segment has at most kShortRows rows: two accumulator buffers, alternating per tile
 };
 
 // TWO: the kernel runs as clusters of two CTAs (cta_group::2).  A pair takes two neighbouring 256-row tiles of one
@@ -279,8 +281,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
     // FULL[s]: the stage's codes and scales have landed in this CTA (TMA bytes); SC_FULL[s]: the scale warps have moved the
     // stage's scales into tensor memory (a pair: those of both CTAs, all counted in the even CTA, so it also says that the
     // odd CTA's operands have landed); EMPTY[s]: the MMAs reading stage s have completed (one tcgen05.commit per issuing
-    // warp); ACC_FULL / ACC_EMPTY: a tile's accumulators are complete / drained.
-    constexpr int FULL = 0, EMPTY = FULL + kStages, ACC_FULL = EMPTY + kStages, ACC_EMPTY = ACC_FULL + 1, SC_FULL = ACC_EMPTY + 1;
+    // warp); ACC_FULL[b] / ACC_EMPTY[b]: the accumulators of buffer b are complete / drained.  Buffer 1 exists only when every
+    // segment is short (at most kShortRows rows; single CTAs): a tile's two accumulators then take 2 x 96 of the 384
+    // accumulator columns, tiles alternate between the two halves, and a tile's read-out runs under the next tile's MMAs.
+    constexpr int FULL = 0, EMPTY = FULL + kStages, ACC_FULL = EMPTY + kStages, ACC_EMPTY = ACC_FULL + 2, SC_FULL = ACC_EMPTY + 2;
+    const bool dbl = !TWO && a.short_segments != 0;
+    const uint32_t acc1_col = dbl ? (uint32_t)kShortRows : (uint32_t)kSegRows;   // column of the second accumulator inside a buffer
+    auto acc_buf = [&](uint32_t t) { return dbl ? (t & 1u) : 0u; };             // buffer of this CTA's t-th tile
+    auto acc_use = [&](uint32_t t) { return dbl ? (t >> 1) : t; };              // how often that buffer was used before
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     const uint32_t rank = TWO ? cluster_ctarank() : 0u;   // 0: issues the MMAs
     constexpr int kBoxRowsB = TWO ? kBoxRows / 2 : kBoxRows;         // granularity of the boxes that bring this CTA's rows of a term
@@ -294,8 +302,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             mbar_init(bar(EMPTY + i), kMmaWarps);
             mbar_init(bar(SC_FULL + i), TWO ? 8 : 4);
         }
-        mbar_init(bar(ACC_FULL), kMmaWarps);
-        mbar_init(bar(ACC_EMPTY), (TWO && rank == 0) ? kEpiWarps + 1 : kEpiWarps);   // + one forwarded arrival for the odd CTA's twelve
+        for (int b = 0; b < 2; b++) {
+            mbar_init(bar(ACC_FULL + b), kMmaWarps);
+            mbar_init(bar(ACC_EMPTY + b), (TWO && rank == 0) ? kEpiWarps + 1 : kEpiWarps);   // + one forwarded arrival for the odd CTA's twelve
+        }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -409,7 +419,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             const uint32_t hi = (uint32_t)(d0 >> 32);                       // same for every operand tile
             const uint32_t a_lo0 = (uint32_t)d0 + (uint32_t)((mw * kAPW * 128 * kRowBytes) >> 4), b_lo0 = (uint32_t)operand_desc(sbase + kSmemB);
             const uint32_t t_sfa0 = tmem_base + kSfaCol + 4u * (uint32_t)(mw * kAPW), t_sfb0 = tmem_base + kSfaCol + 4u * kAccs;
-            const uint32_t t_acc = tmem_base + (uint32_t)(mw * kAPW * kSegRows);
+            const uint32_t t_acc0 = tmem_base + (uint32_t)(mw * kAPW) * acc1_col;
             // a pair: MMAs act in both CTAs; a commit arrives on this barrier of both, whose producers and epilogue warps each
             // wait on their own
             auto mma = [&](uint32_t d, uint32_t al, uint32_t bl, uint32_t h, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t acc) {
@@ -424,7 +434,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                 const uint32_t idesc0 = mxf4_idesc(n16, 0u, TWO ? 256u : 128u), idesc1 = mxf4_idesc(n16, 2u, TWO ? 256u : 128u);
                 const int n_mine = TWO ? n16 / 2 : n16;
                 const uint32_t term_step = (uint32_t)(((n_mine + kBoxRowsB - 1) / kBoxRowsB) * (kBBoxBytesB >> 4));   // a term's rows follow the previous term's box
-                ok = mbar_wait(bar(ACC_EMPTY), (tcnt & 1u) ^ 1u, abort_flag);   // the previous tile's accumulators are drained
+                const uint32_t buf = acc_buf(tcnt), t_acc = t_acc0 + buf * (2u * kShortRows);
+                ok = mbar_wait(bar(ACC_EMPTY) + 8u * buf, (acc_use(tcnt) & 1u) ^ 1u, abort_flag);   // the buffer's previous tile is read out
                 if (!ok) break;
                 tc_fence_after();
                 for (int kc = 0; kc < n_kc; kc++) {
@@ -445,14 +456,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                             const uint32_t acc = (ks | t) != 0 ? 1u : first;
 #pragma unroll
                             for (int h = 0; h < kAPW; h++)
-                                mma(t_acc + h * kSegRows, a_lo + (uint32_t)((h * 128 * kRowBytes) >> 4) + ks * 2, bl, hi, idesc, t_sfa + 4 * h,
+                                mma(t_acc + h * acc1_col, a_lo + (uint32_t)((h * 128 * kRowBytes) >> 4) + ks * 2, bl, hi, idesc, t_sfa + 4 * h,
                                     t_sfb + 4 * kSfbChunks * t, acc);
                         }
                     }
                     commit(bar(EMPTY) + 8u * s);   // arrives when the MMAs above have read their operands
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
-                if (ok) commit(bar(ACC_FULL));
+                if (ok) commit(bar(ACC_FULL) + 8u * buf);
                 tcnt++;
             }
         }
@@ -503,9 +514,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             const PrefillSeg seg = a.segs[tile / per_seg];
             const int mb = unit_mb(tile);
             const bool sh = seg.expert == a.n_local;
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const uint32_t buf = acc_buf(tcnt);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (2u * kShortRows);
             const int r_in = q * 32 + lane;           // row inside a 128-row accumulator
-            const int c0 = 64 * third;
+            const int c0 = (dbl ? 32 : 64) * third;   // short segments: 32 columns per warp cover the 96
             // lane j of the warp fetches the routing weight / output row of columns c0 + j and c0 + 32 + j (two dependent
             // loads: done while the tile's MMAs still run)
             float wv[2] = {0.f, 0.f};
@@ -518,7 +530,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
                     else { const int ts = a.perm[seg.row0 + c]; wv[h] = a.route_w[ts]; orow[h] = ts; }
                 }
             }
-            ok = mbar_wait(bar(ACC_FULL), tcnt & 1u, abort_flag);
+            ok = mbar_wait(bar(ACC_FULL) + 8u * buf, acc_use(tcnt) & 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
             // one 16-column block: v0 = accumulator 0, v1 = accumulator 1
@@ -556,10 +568,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             // it and the first use of its registers).  After the second pair has arrived the accumulators are handed back, and
             // its arithmetic and stores run while the next tile's MMAs have already started.
             uint32_t v0[16], v1[16], u0[16], u1[16];
-            const bool b0 = c0 < seg.n, b1 = c0 + 16 < seg.n, b2 = c0 + 32 < seg.n, b3 = c0 + 48 < seg.n;
+            const bool b0 = c0 < seg.n, b1 = c0 + 16 < seg.n, b2 = !dbl && c0 + 32 < seg.n, b3 = !dbl && c0 + 48 < seg.n;
             auto ld_block = [&](int cb, uint32_t (&x0)[16], uint32_t (&x1)[16]) {
                 tc_ld16(lane_addr + (uint32_t)cb, x0);
-                tc_ld16(lane_addr + (uint32_t)(kSegRows + cb), x1);
+                tc_ld16(lane_addr + acc1_col + (uint32_t)cb, x1);
             };
             if (b0) {
                 ld_block(c0, v0, v1);
@@ -575,7 +587,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_b32, const __grid_consta
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(ACC_EMPTY));   // (odd CTA of a pair: its own barrier; warp 2 forwards the completed phase)
+            if (lane == 0) mbar_arrive(bar(ACC_EMPTY) + 8u * buf);   // (odd CTA of a pair: its own barrier; warp 2 forwards the completed phase)
             if (b2) {
                 emit(c0 + 32, v0, v1);
                 if (b3) emit(c0 + 48, u0, u1);
@@ -900,7 +912,7 @@ int prefill_mx_workspace_create(PrefillWorkspace* ws, const dsx_moe_config& cfg,
     // shapes the tiles cover: 256 gate + 256 up rows per tile, 512 down rows per tile, 128-column stages
     if (cfg.ffn % 256 != 0 || cfg.hidden % 512 != 0 || (cfg.shared_ffn != 0 && cfg.shared_ffn != cfg.ffn)) return DSX_OK;
     const int64_t Kmax = std::max(cfg.hidden, cfg.ffn);
-    ws->mx_seg_cap = cfg.router.n_expert + (int)((ws->cap_rows + kSegRows - 1) / kSegRows) + 8;   // every expert's last segment may be short
+    ws->mx_seg_cap = cfg.router.n_expert + (int)((ws->cap_rows + kShortRows - 1) / kShortRows) + 8;   // every expert's last segment may be short
     ws->mx_term_stride = ws->cap_rows * (Kmax / 2);
     DSX_CUDA(cudaMalloc((void**)&ws->xq, (size_t)kTerms * (size_t)ws->mx_term_stride));
     DSX_CUDA(cudaMalloc((void**)&ws->sfb, (size_t)ws->mx_seg_cap * (size_t)(Kmax / kStageK) * kSfbBytes));
@@ -974,8 +986,12 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     // 256-expert layer, pairs are 5 to 10 % faster from 128 rows per expert on and 2 to 9 % slower at 64 and fewer (a
     // stage is mostly weight bytes there, and a pair adds a hop to every hand-over).
     const bool pair = ws->mx_pair_mode >= 0 ? ws->mx_pair_mode == 1 : P >= (int64_t)kPairFromRows * c.n_local;
-    if (int rc = launch_build_segments(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, kSegRows, ws->mx_segs, ws->n_segs, ws->mx_seg_cap,
-                                       mx_small, ws->small_items, ws->n_small, stream))
+    // Below that, segments are capped at kShortRows rows, which leaves tensor memory for two accumulator buffers: a tile's
+    // read-out then runs under the next tile's MMAs (tiles are short there, and the hand-over between them was a quarter
+    // of their time).
+    const bool short_segments = !pair;
+    if (int rc = launch_build_segments(c.offsets, c.n_local, P, c.with_shared ? (int)c.T : 0, short_segments ? kShortRows : kSegRows, ws->mx_segs,
+                                       ws->n_segs, ws->mx_seg_cap, mx_small, ws->small_items, ws->n_small, stream))
         return rc;
     if (int rc = map_weights(ws, 0, c.km_gu, c.km_dn, c.km_gu_stride, c.km_dn_stride, c.n_local)) return rc;
     const int shi = c.with_shared ? 1 : 0;   // without a shared expert the shared map aliases the routed one (never used)
@@ -992,6 +1008,7 @@ int prefill_mx_forward(PrefillWorkspace* ws, const dsx_moe_config& cfg, const Pr
     g.segs = ws->mx_segs; g.n_segs = ws->n_segs; g.n_local = c.n_local; g.n_used = c.n_used; g.P = P; g.perm = c.perm;
     g.route_w = c.route_w; g.clamp = cfg.clamp; g.mid = c.mid; g.mid_stride = cfg.ffn; g.partial = c.partial; g.sfb = ws->sfb;
     g.error_word = c.error_word;
+    g.short_segments = short_segments ? 1 : 0;
 
     // first product: K = hidden, rows = ffn
     DSX_CUDA(cudaMemsetAsync(ws->mx_inv_perm, 0xFF, sizeof(int32_t) * (size_t)P, stream));
