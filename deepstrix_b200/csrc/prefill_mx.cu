@@ -35,6 +35,8 @@
 // a pair takes two neighbouring tiles of one segment, every MMA spans both (M = 256), and each CTA loads only half
 // of the segment's rows.  Each CTA's loads count on its own barrier; the scale warps of both report to the even CTA,
 // whose two MMA threads issue for the pair; commits arrive in both.  No load is broadcast.
+// Single CTAs (fewer rows per expert) cap their segments at 96 rows, which leaves tensor memory for two accumulator
+// buffers that alternate per tile: a tile's read-out then runs under the next tile's MMAs.
 // What bounds it.  (1) L2 -> shared-memory traffic, which a tall tile (many weight rows per activation row) and the
 // pair's halved activation rows reduce.  (2) Shared memory's 128 bytes per clock, which the tensor core's operand
 // reads share with those fills: an M = 128, K = 64 MMA over N rows reads 4 KB of weights and 32 N bytes of terms in
