@@ -407,6 +407,40 @@ def test_layer_prefill_cta_pairs_same_bits(torch_cuda, moe, monkeypatch):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16)), T
 
 
+@pytest.mark.parametrize("T", [300, 2500])
+def test_layer_prefill_forward_replays_from_a_cuda_graph(torch_cuda, moe, T):
+    """A large-batch forward allocates nothing and synchronises nothing, so a serving loop can capture it once and replay
+    it: both forms of the block-scaled GEMM (300 tokens: single CTAs with two accumulator buffers; 2500 tokens: CTA pairs
+    launched as clusters), the quantisers, the GEMV hand-off and the combine.  The replays write the bits of the eager call."""
+    import ctypes as C
+    from deepstrix_b200 import synth
+    from deepstrix_b200.config import MoeConfig, RouterConfig
+    torch = torch_cuda
+    lib = moe.lib()
+    cfg = MoeConfig(hidden=1024, ffn=512, shared_ffn=512,
+                    router=RouterConfig(n_expert=32, n_used=4, n_group=1, topk_group=1, score_fn=1, route_scale=2.5))
+    layer = moe.build_layer_from_host(cfg, synth.make_layer(cfg, 4), max_tokens=T)
+    x = torch.from_numpy(synth.make_tokens(cfg, 4, T).view(np.int16)).cuda().view(torch.bfloat16)
+    want = layer.forward(x)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    out = torch.zeros_like(x)
+    with torch.cuda.stream(stream):
+        layer.forward(x, out=out)   # first-use work on this stream outside the capture
+        stream.synchronize()
+        moe._check(lib.dsx_graph_begin_capture(C.c_void_p(stream.cuda_stream)))
+        layer.forward(x, out=out)
+        g = C.c_void_p()
+        moe._check(lib.dsx_graph_end_capture(C.c_void_p(stream.cuda_stream), C.byref(g)))
+        for _ in range(2):
+            out.zero_()
+            moe._check(lib.dsx_graph_launch(g, C.c_void_p(stream.cuda_stream)))
+            stream.synchronize()
+            assert layer.check() == 0
+            assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+        lib.dsx_graph_destroy(g)
+
+
 def test_layer_prefill_config0_shapes(torch_cuda, moe, oracle):
     from deepstrix_b200.config import CONFIGS
     out, ref, *_ = _layer_case(torch_cuda, moe, oracle, CONFIGS[0], 0, 192)
